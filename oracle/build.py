@@ -1,0 +1,54 @@
+"""Compile the CPU oracle (oracle.cpp) and, when the reference tree is mounted, the reference's
+own CPU test functions (ref_wrap.cpp, which includes src/TwoStage/kernel_test.cpp where it
+lies) into oracle/_ref/.  Test infrastructure only; building the checker is not using it.
+
+    python oracle/build.py [--reference /path/to/CXX-GPT]
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+DEFAULT_REFERENCE = os.environ.get("CXXGPT_REFERENCE", "/root/reference")
+
+
+def _stale(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.exists(s) and os.path.getmtime(s) > t for s in sources)
+
+
+def build_oracle(force=False):
+    src = os.path.join(HERE, "oracle.cpp")
+    out = os.path.join(HERE, "liboracle.so")
+    if force or _stale(out, [src]):
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fopenmp",
+                               "-o", out, src])
+    return out
+
+
+def build_reference(reference=DEFAULT_REFERENCE, force=False):
+    """Returns the path of libref_kernel_test.so, or None when neither the reference tree nor a
+    previously built copy is available."""
+    out_dir = os.path.join(HERE, "_ref")
+    out = os.path.join(out_dir, "libref_kernel_test.so")
+    ref_src = os.path.join(reference, "src", "TwoStage", "kernel_test.cpp")
+    if not os.path.exists(ref_src):
+        return out if os.path.exists(out) else None
+    wrap = os.path.join(HERE, "ref_wrap.cpp")
+    stub = os.path.join(HERE, "ref_stub")
+    if force or _stale(out, [wrap, ref_src, os.path.join(stub, "TwoStage", "two_stage_gpt.hpp")]):
+        os.makedirs(out_dir, exist_ok=True)
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared",
+                               "-I", stub, "-I", os.path.join(reference, "src"),
+                               "-o", out, wrap])
+    return out
+
+
+if __name__ == "__main__":
+    ref = DEFAULT_REFERENCE
+    if "--reference" in sys.argv:
+        ref = sys.argv[sys.argv.index("--reference") + 1]
+    print(build_oracle(force="--force" in sys.argv))
+    print(build_reference(ref, force="--force" in sys.argv))
