@@ -1,0 +1,276 @@
+"""Python front end of libcxxattn.so, used by the tests and the benchmark.
+
+The product is the shared library and its C-ABI (include/cxxattn.h); this module only binds
+it with ctypes and mirrors the reference's kernel entry points by name and argument order
+(`two_stage_cuda.*` = src/TwoStage/two_stage_cuda_kernels.cuh:18-85, `linear_cuda.*` =
+src/LinearAttention/linear_cuda_kernels.cuh:11-46) on torch CUDA tensors, which stand in for
+TensorN::CudaTensor<float>.  torch supplies device memory and streams, nothing else: there is no
+fallback, and loading fails loudly when the library has not been built.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcxxattn.so")
+
+F32, BF16 = 0, 1
+MAP_NONE, MAP_ELU1 = 0, 1
+
+SYMBOLS = [
+    "cxxattn_strerror", "cxxattn_version",
+    "cxxattn_mha_fwd", "cxxattn_mha_bwd_workspace_bytes", "cxxattn_mha_bwd",
+    "cxxattn_linattn_workspace_bytes", "cxxattn_linattn_fwd", "cxxattn_linattn_bwd_step1",
+    "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
+    "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
+]
+
+
+class MhaDesc(C.Structure):
+    _fields_ = [("B", C.c_int64), ("S", C.c_int64), ("H", C.c_int64), ("Dh", C.c_int64),
+                ("stride_b", C.c_int64), ("stride_s", C.c_int64), ("stride_h", C.c_int64),
+                ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
+class LinDesc(C.Structure):
+    _fields_ = [("B", C.c_int64), ("S", C.c_int64), ("D", C.c_int64), ("E", C.c_int64),
+                ("dtype", C.c_int32), ("feature_map", C.c_int32), ("eps_in_den", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+class CxxAttnError(RuntimeError):
+    def __init__(self, code, what):
+        super().__init__(f"{what}: {strerror(code)} ({code})")
+        self.code = code
+
+
+_lib = None
+
+
+def lib():
+    """The loaded C-ABI library.  Raises if it has not been built (python cxx-gpt_b200/build.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(f"{LIB_PATH} is missing: build it with `python cxx-gpt_b200/build.py`; "
+                                    "there is no fallback path")
+        L = C.CDLL(LIB_PATH)
+        vp, sz, i32, f32p = C.c_void_p, C.c_size_t, C.c_int, C.c_void_p
+        L.cxxattn_strerror.restype = C.c_char_p
+        L.cxxattn_strerror.argtypes = [i32]
+        L.cxxattn_version.restype = C.c_char_p
+        L.cxxattn_mha_fwd.argtypes = [C.POINTER(MhaDesc), vp, vp, vp, vp, f32p, vp]
+        L.cxxattn_mha_bwd_workspace_bytes.restype = sz
+        L.cxxattn_mha_bwd_workspace_bytes.argtypes = [C.POINTER(MhaDesc), i32]
+        L.cxxattn_mha_bwd.argtypes = [C.POINTER(MhaDesc)] + [vp] * 9 + [vp, sz, vp]
+        L.cxxattn_linattn_workspace_bytes.restype = sz
+        L.cxxattn_linattn_workspace_bytes.argtypes = [C.POINTER(LinDesc)]
+        L.cxxattn_linattn_fwd.argtypes = [C.POINTER(LinDesc)] + [vp] * 6 + [vp, sz, vp]
+        L.cxxattn_linattn_bwd_step1.argtypes = [vp] * 5 + [sz, sz, vp]
+        L.cxxattn_linattn_bwd_dq.argtypes = [C.POINTER(LinDesc)] + [vp] * 7 + [vp, sz, vp]
+        L.cxxattn_linattn_bwd_dkdv.argtypes = [C.POINTER(LinDesc)] + [vp] * 7 + [vp, sz, vp]
+        L.cxxattn_linattn_bwd.argtypes = [C.POINTER(LinDesc)] + [vp] * 9 + [vp, sz, vp]
+        L.cxxattn_phi_elu_fwd.argtypes = [vp, vp, sz, sz, sz, vp]
+        L.cxxattn_phi_elu_bwd.argtypes = [vp, vp, vp, sz, sz, sz, vp]
+        L.cxxattn_rope.argtypes = [vp, vp, sz, sz, sz, sz, C.c_float, vp]
+        L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
+        _lib = L
+    return _lib
+
+
+def strerror(code):
+    return lib().cxxattn_strerror(int(code)).decode()
+
+
+def check(code, what):
+    if code != 0:
+        raise CxxAttnError(code, what)
+
+
+# ---------------------------------------------------------------------------------------------
+# torch plumbing: device pointers, the current stream, cached workspaces
+# ---------------------------------------------------------------------------------------------
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("cxxattn kernels take CUDA tensors; there is no CPU path")
+    if not t.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    return t.data_ptr()
+
+
+def _stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+_ws_cache = {}
+
+
+def workspace(nbytes, device):
+    """A cached device byte buffer of at least nbytes (grown on demand, one per device)."""
+    import torch
+    key = str(device)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
+def _dtype_code(t):
+    import torch
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise ValueError(f"unsupported dtype {t.dtype}")
+
+
+def mha_desc(B, S, H, Dh, dtype=F32, strides=None):
+    sb, ss, sh = strides if strides else (0, 0, 0)
+    return MhaDesc(B, S, H, Dh, sb, ss, sh, dtype, 0)
+
+
+def lin_desc(B, S, D, E, dtype=F32, feature_map=MAP_ELU1, eps_in_den=0):
+    return LinDesc(B, S, D, E, dtype, feature_map, eps_in_den, 0)
+
+
+# ---------------------------------------------------------------------------------------------
+# thin C-ABI callers
+# ---------------------------------------------------------------------------------------------
+
+def mha_fwd(Q, K, V, O, B, S, H, Dh, lse=None, strides=None):
+    d = mha_desc(B, S, H, Dh, _dtype_code(Q), strides)
+    check(lib().cxxattn_mha_fwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(lse), _stream()),
+          "cxxattn_mha_fwd")
+
+
+def mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, Dh, lse=None, strides=None):
+    d = mha_desc(B, S, H, Dh, _dtype_code(Q), strides)
+    n = lib().cxxattn_mha_bwd_workspace_bytes(C.byref(d), int(lse is not None))
+    ws = workspace(n, Q.device)
+    check(lib().cxxattn_mha_bwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(lse),
+                                _ptr(dQ), _ptr(dK), _ptr(dV), ws.data_ptr(), ws.numel(), _stream()),
+          "cxxattn_mha_bwd")
+
+
+def _lin_ws(d, device):
+    n = lib().cxxattn_linattn_workspace_bytes(C.byref(d))
+    return workspace(n, device)
+
+
+def linattn_fwd(Q, K, V, O, den, z_cache, B, S, D, E, feature_map, eps_in_den):
+    d = lin_desc(B, S, D, E, _dtype_code(Q), feature_map, eps_in_den)
+    ws = _lin_ws(d, Q.device)
+    check(lib().cxxattn_linattn_fwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(den),
+                                    _ptr(z_cache), ws.data_ptr(), ws.numel(), _stream()),
+          "cxxattn_linattn_fwd")
+
+
+def linattn_bwd_step1(O, dO, den, dnum, dden, N, E):
+    check(lib().cxxattn_linattn_bwd_step1(_ptr(O), _ptr(dO), _ptr(den), _ptr(dnum), _ptr(dden), N, E,
+                                          _stream()), "cxxattn_linattn_bwd_step1")
+
+
+def linattn_bwd_dq(K, V, dnum, dden, z_cache, Q, dQ, B, S, D, E, feature_map, eps_in_den):
+    d = lin_desc(B, S, D, E, F32, feature_map, eps_in_den)
+    ws = _lin_ws(d, K.device)
+    check(lib().cxxattn_linattn_bwd_dq(C.byref(d), _ptr(K), _ptr(V), _ptr(dnum), _ptr(dden),
+                                       _ptr(z_cache), _ptr(Q), _ptr(dQ), ws.data_ptr(), ws.numel(),
+                                       _stream()), "cxxattn_linattn_bwd_dq")
+
+
+def linattn_bwd_dkdv(Q, K, V, dnum, dden, dK, dV, B, S, D, E, feature_map, eps_in_den):
+    d = lin_desc(B, S, D, E, F32, feature_map, eps_in_den)
+    ws = _lin_ws(d, K.device)
+    check(lib().cxxattn_linattn_bwd_dkdv(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(dnum), _ptr(dden),
+                                         _ptr(dK), _ptr(dV), ws.data_ptr(), ws.numel(), _stream()),
+          "cxxattn_linattn_bwd_dkdv")
+
+
+def linattn_bwd(Q, K, V, O, dO, den, dQ, dK, dV, B, S, D, E, feature_map, eps_in_den):
+    d = lin_desc(B, S, D, E, _dtype_code(Q), feature_map, eps_in_den)
+    ws = _lin_ws(d, Q.device)
+    check(lib().cxxattn_linattn_bwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(den),
+                                    _ptr(dQ), _ptr(dK), _ptr(dV), ws.data_ptr(), ws.numel(), _stream()),
+          "cxxattn_linattn_bwd")
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's operator interface, by name
+# ---------------------------------------------------------------------------------------------
+
+class two_stage_cuda:
+    """namespace two_stage_cuda (src/TwoStage/two_stage_cuda_kernels.cuh:18-85)."""
+
+    @staticmethod
+    def fused_mha_fwd(Q, K, V, O, B, S, H, Dh):
+        mha_fwd(Q, K, V, O, B, S, H, Dh)
+
+    @staticmethod
+    def fused_mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, Dh):
+        mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, Dh)
+
+    @staticmethod
+    def kernel_attn_fwd(Q, K, V, O, den_cache, z_cache, S_buf, z_buf, B, S, D, E):
+        # S_buf / z_buf are the reference's serial-scan scratch; the chunked scan does not use them.
+        linattn_fwd(Q, K, V, O, den_cache, z_cache, B, S, D, E, MAP_ELU1, 0)
+
+    @staticmethod
+    def kernel_attn_bwd_step1(O, dO, den_cache, dnum, dden, N, E):
+        linattn_bwd_step1(O, dO, den_cache, dnum, dden, N, E)
+
+    @staticmethod
+    def kernel_attn_bwd_dQ(K, V, dnum, dden, z_cache, Q, dQ, S_buf, B, S, D, E):
+        linattn_bwd_dq(K, V, dnum, dden, z_cache, Q, dQ, B, S, D, E, MAP_ELU1, 0)
+
+    @staticmethod
+    def kernel_attn_bwd_dKdV(Q, K, V, dnum, dden, dK, dV, B, S, D, E):
+        linattn_bwd_dkdv(Q, K, V, dnum, dden, dK, dV, B, S, D, E, MAP_ELU1, 0)
+
+    @staticmethod
+    def rope_fwd(Q, K, B, S, D, head_dim):
+        check(lib().cxxattn_rope(_ptr(Q), _ptr(K), B, S, D, head_dim, 1.0, _stream()), "cxxattn_rope")
+
+    @staticmethod
+    def rope_bwd(dQ, dK, B, S, D, head_dim):
+        check(lib().cxxattn_rope(_ptr(dQ), _ptr(dK), B, S, D, head_dim, -1.0, _stream()), "cxxattn_rope")
+
+    @staticmethod
+    def gelu_exact(A, Cout):
+        check(lib().cxxattn_gelu_exact(_ptr(A), _ptr(Cout), A.numel(), 0, _stream()), "cxxattn_gelu_exact")
+
+    @staticmethod
+    def gelu_exact_deriv(A, Cout):
+        check(lib().cxxattn_gelu_exact(_ptr(A), _ptr(Cout), A.numel(), 1, _stream()), "cxxattn_gelu_exact")
+
+
+class linear_cuda:
+    """namespace linear_cuda (src/LinearAttention/linear_cuda_kernels.cuh:11-46)."""
+
+    @staticmethod
+    def causal_linear_attention_fwd(Q_phi, K_phi, V, O, den_cache, z_cache, S_buf, z_buf, B, S, D, E):
+        linattn_fwd(Q_phi, K_phi, V, O, den_cache, z_cache, B, S, D, E, MAP_NONE, 1)
+
+    @staticmethod
+    def causal_linear_attention_bwd_step1(O, dO, den_cache, dnum, dden, N, E):
+        linattn_bwd_step1(O, dO, den_cache, dnum, dden, N, E)
+
+    @staticmethod
+    def causal_linear_attention_bwd_dQ(K_phi, V, dnum, dden, z_cache, dQ_phi, S_buf, B, S, D, E):
+        linattn_bwd_dq(K_phi, V, dnum, dden, z_cache, None, dQ_phi, B, S, D, E, MAP_NONE, 1)
+
+    @staticmethod
+    def causal_linear_attention_bwd_dKdV(Q_phi, K_phi, V, dnum, dden, dK_phi, dV, B, S, D, E):
+        linattn_bwd_dkdv(Q_phi, K_phi, V, dnum, dden, dK_phi, dV, B, S, D, E, MAP_NONE, 1)
+
+    @staticmethod
+    def phi_elu_forward(x, phi, D, E):
+        check(lib().cxxattn_phi_elu_fwd(_ptr(x), _ptr(phi), x.shape[0], D, E, _stream()), "cxxattn_phi_elu_fwd")
+
+    @staticmethod
+    def phi_elu_backward(dphi, x, dx, D, E):
+        check(lib().cxxattn_phi_elu_bwd(_ptr(dphi), _ptr(x), _ptr(dx), dphi.shape[0], D, E, _stream()),
+              "cxxattn_phi_elu_bwd")

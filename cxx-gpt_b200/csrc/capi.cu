@@ -1,0 +1,158 @@
+// extern "C" surface of libcxxattn.so: argument validation and dispatch to the kernel families.
+// No device memory is allocated here and nothing is synchronised; a request that no kernel of
+// this build covers is an error, never a silent detour.
+#include "internal.cuh"
+#include <cmath>
+
+using namespace cxxattn;
+
+namespace {
+
+bool resolve(const cxxattn_mha_desc* d, MhaShape* p) {
+    if (d == nullptr || d->B <= 0 || d->S <= 0 || d->H <= 0 || d->Dh <= 0 || d->reserved != 0) return false;
+    if (d->B > INT32_MAX || d->S > INT32_MAX || d->H > INT32_MAX || d->Dh > INT32_MAX) return false;
+    p->B = (int)d->B; p->S = (int)d->S; p->H = (int)d->H; p->Dh = (int)d->Dh;
+    if (d->stride_b == 0 && d->stride_s == 0 && d->stride_h == 0) {
+        p->sh = d->Dh; p->ss = d->H * d->Dh; p->sb = d->S * p->ss;
+    } else {
+        if (d->stride_b <= 0 || d->stride_s <= 0 || d->stride_h <= 0) return false;
+        p->sb = d->stride_b; p->ss = d->stride_s; p->sh = d->stride_h;
+    }
+    p->scale = 1.0f / sqrtf((float)d->Dh);
+    return true;
+}
+
+bool lin_ok(const cxxattn_lin_desc* d) {
+    return d != nullptr && d->B > 0 && d->S > 0 && d->D > 0 && d->E > 0 && d->reserved == 0 &&
+           d->B <= INT32_MAX && d->S <= INT32_MAX && d->D <= INT32_MAX && d->E <= INT32_MAX &&
+           (d->feature_map == CXXATTN_MAP_NONE || d->feature_map == CXXATTN_MAP_ELU1) &&
+           (d->eps_in_den == 0 || d->eps_in_den == 1);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* cxxattn_strerror(int code) {
+    switch (code) {
+        case CXXATTN_OK: return "ok";
+        case CXXATTN_ERR_INVALID: return "invalid argument";
+        case CXXATTN_ERR_UNSUPPORTED: return "unsupported shape or type for this build";
+        case CXXATTN_ERR_WORKSPACE: return "workspace missing or too small";
+        case CXXATTN_ERR_CUDA: return "CUDA runtime error";
+        case CXXATTN_ERR_TIMEOUT: return "device-side wait timed out";
+        case CXXATTN_ERR_ALIGNMENT: return "pointer or stride misaligned";
+        case CXXATTN_ERR_TOO_LARGE: return "size beyond a fixed maximum";
+        default: return "unknown error";
+    }
+}
+
+const char* cxxattn_version(void) { return "0.1 sm_100a"; }
+
+int cxxattn_mha_fwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, const void* V,
+                    void* O, float* lse, cxxattn_stream_t stream) {
+    MhaShape p;
+    if (!resolve(desc, &p) || !Q || !K || !V || !O) return CXXATTN_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == CXXATTN_F32)
+        return mha_f32_fwd(p, (const float*)Q, (const float*)K, (const float*)V, (float*)O, lse, st);
+    return CXXATTN_ERR_UNSUPPORTED;
+}
+
+size_t cxxattn_mha_bwd_workspace_bytes(const cxxattn_mha_desc* desc, int have_lse) {
+    MhaShape p;
+    if (!resolve(desc, &p)) return 0;
+    if (desc->dtype == CXXATTN_F32) return mha_f32_bwd_workspace(p, have_lse != 0);
+    return 0;
+}
+
+int cxxattn_mha_bwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, const void* V,
+                    const void* O, const void* dO, const float* lse, void* dQ, void* dK, void* dV,
+                    void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
+    MhaShape p;
+    if (!resolve(desc, &p) || !Q || !K || !V || !O || !dO || !dQ || !dK || !dV) return CXXATTN_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == CXXATTN_F32)
+        return mha_f32_bwd(p, (const float*)Q, (const float*)K, (const float*)V, (const float*)O,
+                           (const float*)dO, lse, (float*)dQ, (float*)dK, (float*)dV,
+                           workspace, workspace_bytes, st);
+    return CXXATTN_ERR_UNSUPPORTED;
+}
+
+size_t cxxattn_linattn_workspace_bytes(const cxxattn_lin_desc* desc) {
+    if (!lin_ok(desc)) return 0;
+    if (desc->dtype == CXXATTN_F32) return linattn_f32_workspace(*desc);
+    return 0;
+}
+
+int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void* K, const void* V,
+                        void* O, float* den, float* z_cache, void* workspace, size_t workspace_bytes,
+                        cxxattn_stream_t stream) {
+    if (!lin_ok(desc) || !Q || !K || !V || !O || !den) return CXXATTN_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == CXXATTN_F32)
+        return linattn_f32_fwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (float*)O, den,
+                               z_cache, workspace, workspace_bytes, st);
+    return CXXATTN_ERR_UNSUPPORTED;
+}
+
+int cxxattn_linattn_bwd_step1(const float* O, const float* dO, const float* den, float* dnum,
+                              float* dden, size_t N, size_t E, cxxattn_stream_t stream) {
+    if (!O || !dO || !den || !dnum || !dden || N == 0 || E == 0) return CXXATTN_ERR_INVALID;
+    return step1_f32(O, dO, den, dnum, dden, N, E, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_linattn_bwd_dq(const cxxattn_lin_desc* desc, const float* K, const float* V,
+                           const float* dnum, const float* dden, const float* z_cache, const float* Q,
+                           float* dQ, void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
+    if (!lin_ok(desc) || !K || !V || !dnum || !dden || !dQ) return CXXATTN_ERR_INVALID;
+    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
+    return linattn_f32_bwd_dq(*desc, K, V, dnum, dden, z_cache, Q, dQ, workspace, workspace_bytes,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_linattn_bwd_dkdv(const cxxattn_lin_desc* desc, const float* Q, const float* K,
+                             const float* V, const float* dnum, const float* dden, float* dK, float* dV,
+                             void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
+    if (!lin_ok(desc) || !Q || !K || !V || !dnum || !dden || !dK || !dV) return CXXATTN_ERR_INVALID;
+    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
+    return linattn_f32_bwd_dkdv(*desc, Q, K, V, dnum, dden, dK, dV, workspace, workspace_bytes,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void* K, const void* V,
+                        const void* O, const void* dO, const float* den, void* dQ, void* dK, void* dV,
+                        void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
+    if (!lin_ok(desc) || !Q || !K || !V || !O || !dO || !den || !dQ || !dK || !dV) return CXXATTN_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == CXXATTN_F32)
+        return linattn_f32_bwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (const float*)O,
+                               (const float*)dO, den, (float*)dQ, (float*)dK, (float*)dV,
+                               workspace, workspace_bytes, st);
+    return CXXATTN_ERR_UNSUPPORTED;
+}
+
+int cxxattn_phi_elu_fwd(const float* x, float* phi, size_t N, size_t D, size_t E, cxxattn_stream_t stream) {
+    if (!x || !phi || N == 0 || D == 0 || E == 0 || E > D) return CXXATTN_ERR_INVALID;
+    return phi_elu_fwd(x, phi, N, D, E, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, size_t D, size_t E,
+                        cxxattn_stream_t stream) {
+    if (!dphi || !x || !dx || N == 0 || D == 0 || E == 0 || E > D) return CXXATTN_ERR_INVALID;
+    return phi_elu_bwd(dphi, x, dx, N, D, E, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_dim, float sign,
+                 cxxattn_stream_t stream) {
+    if ((!Q && !K) || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 2 || D % head_dim)
+        return CXXATTN_ERR_INVALID;
+    return rope(Q, K, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {
+    if (!A || !C || n == 0) return CXXATTN_ERR_INVALID;
+    return gelu_exact(A, C, n, deriv != 0, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

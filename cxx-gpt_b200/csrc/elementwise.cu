@@ -1,0 +1,123 @@
+// Elementwise neighbours of the attention kernels that share the reference's kernel headers:
+// step 1 of the linear-attention backward, the ELU+1 feature map of LinearGPT, rotary embedding
+// and erf-GELU.  All are HBM-bound single-pass kernels: one warp per row for the row-wise ones,
+// grid-stride for the flat ones.
+#include "internal.cuh"
+
+namespace cxxattn {
+namespace {
+
+// dnum = dO / den, dden = -(dO . O) / den  (ts.cu:1190-1219, lin.cu:101-134).  One warp per row.
+__global__ void step1_kernel(const float* __restrict__ O, const float* __restrict__ dO,
+                             const float* __restrict__ den, float* __restrict__ dnum,
+                             float* __restrict__ dden, size_t N, size_t E) {
+    const size_t row = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    if (row >= N) return;
+    const float inv = 1.0f / den[row];
+    float sum = 0.f;
+    for (size_t e = lane; e < E; e += 32) {
+        const float g = dO[row * E + e];
+        dnum[row * E + e] = g * inv;
+        sum = fmaf(g, O[row * E + e], sum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) dden[row] = -sum * inv;
+}
+
+// phi[n,d] = ELU(x[n,d]) + 1 for d < E, 0 for E <= d < D  (lin.cu:305-325).
+__global__ void phi_fwd_kernel(const float* __restrict__ x, float* __restrict__ phi, size_t total,
+                               size_t D, size_t E) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / D, d = i % D;
+        float v = 0.f;
+        if (d < E) {
+            const float xv = x[n * E + d];
+            v = (xv > 0.f ? xv : expf(xv) - 1.0f) + 1.0f;
+        }
+        phi[i] = v;
+    }
+}
+
+// dx[n,e] = dphi[n,e] * (x > 0 ? 1 : exp(x))  (lin.cu:347-364); dphi has D columns, x and dx have E.
+__global__ void phi_bwd_kernel(const float* __restrict__ dphi, const float* __restrict__ x,
+                               float* __restrict__ dx, size_t total, size_t D, size_t E) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / E, e = i % E;
+        const float xv = x[i];
+        dx[i] = dphi[n * D + e] * (xv > 0.f ? 1.0f : expf(xv));
+    }
+}
+
+// Rotary embedding, in place, one thread per (row, pair)  (ts.cu:1820-1857).  The frequency is
+// 10000^(-2i/head_dim) and the position is row % S.  Q and K are rotated one after the other by
+// the same thread, so passing the same pointer twice rotates twice, as in the reference.
+__global__ void rope_kernel(float* Q, float* K, size_t total, size_t S, size_t D, size_t hd, float sign) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t npairs = D / 2, pph = hd / 2;
+    const size_t row = idx / npairs, pair = idx % npairs, i = pair % pph;
+    const size_t off = row * D + (pair / pph) * hd + 2 * i;
+    const float ang = sign * (float)(row % S) * expf(-2.0f * (float)i / (float)hd * 9.210340371976184f);
+    float s, c;
+    sincosf(ang, &s, &c);
+    if (Q) {
+        const float x0 = Q[off], x1 = Q[off + 1];
+        Q[off] = x0 * c - x1 * s;
+        Q[off + 1] = x0 * s + x1 * c;
+    }
+    if (K) {
+        const float x0 = K[off], x1 = K[off + 1];
+        K[off] = x0 * c - x1 * s;
+        K[off + 1] = x0 * s + x1 * c;
+    }
+}
+
+// erf-GELU and its derivative  (ts.cu:1888-1915).
+__global__ void gelu_kernel(const float* __restrict__ A, float* __restrict__ C, size_t n, int deriv) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const float x = A[i];
+        const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+        C[i] = deriv ? cdf + x * expf(-0.5f * x * x) * 0.3989422804014327f : x * cdf;
+    }
+}
+
+inline unsigned flat_grid(size_t n) {
+    const size_t blocks = (n + 255) / 256;
+    return (unsigned)(blocks < 148 * 16 ? (blocks ? blocks : 1) : 148 * 16);  // 148 SMs x 16 resident CTAs
+}
+
+}  // namespace
+
+int step1_f32(const float* O, const float* dO, const float* den, float* dnum, float* dden,
+              size_t N, size_t E, cudaStream_t st) {
+    step1_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(O, dO, den, dnum, dden, N, E);
+    return check_launch();
+}
+
+int phi_elu_fwd(const float* x, float* phi, size_t N, size_t D, size_t E, cudaStream_t st) {
+    phi_fwd_kernel<<<flat_grid(N * D), 256, 0, st>>>(x, phi, N * D, D, E);
+    return check_launch();
+}
+
+int phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, size_t D, size_t E, cudaStream_t st) {
+    phi_bwd_kernel<<<flat_grid(N * E), 256, 0, st>>>(dphi, x, dx, N * E, D, E);
+    return check_launch();
+}
+
+int rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t hd, float sign, cudaStream_t st) {
+    const size_t total = B * S * (D / 2);
+    rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(Q, K, total, S, D, hd, sign);
+    return check_launch();
+}
+
+int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st) {
+    gelu_kernel<<<flat_grid(n), 256, 0, st>>>(A, C, n, deriv);
+    return check_launch();
+}
+
+}  // namespace cxxattn

@@ -1,0 +1,54 @@
+// Internal declarations shared by the translation units of libcxxattn.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstddef>
+#include <cstdint>
+#include "cxxattn.h"
+
+namespace cxxattn {
+
+// Softmax MHA problem as the kernels see it (strides resolved, in elements).
+struct MhaShape {
+    int B, S, H, Dh;
+    int64_t sb, ss, sh;
+    float scale;  // 1/sqrt(Dh)
+};
+
+inline int check_launch() {
+    return cudaGetLastError() == cudaSuccess ? CXXATTN_OK : CXXATTN_ERR_CUDA;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- exact fp32 SIMT softmax MHA (mha_f32.cu) ----
+int mha_f32_fwd(const MhaShape& p, const float* Q, const float* K, const float* V, float* O,
+                float* lse, cudaStream_t st);
+size_t mha_f32_bwd_workspace(const MhaShape& p, bool have_lse);
+int mha_f32_bwd(const MhaShape& p, const float* Q, const float* K, const float* V, const float* O,
+                const float* dO, const float* lse, float* dQ, float* dK, float* dV,
+                void* ws, size_t ws_bytes, cudaStream_t st);
+
+// ---- exact fp32 chunk-parallel linear attention (linattn_f32.cu) ----
+size_t linattn_f32_workspace(const cxxattn_lin_desc& d);
+int linattn_f32_fwd(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
+                    float* O, float* den, float* z_cache, void* ws, size_t ws_bytes, cudaStream_t st);
+int linattn_f32_bwd_dq(const cxxattn_lin_desc& d, const float* K, const float* V, const float* dnum,
+                       const float* dden, const float* z_cache, const float* Q, float* dQ,
+                       void* ws, size_t ws_bytes, cudaStream_t st);
+int linattn_f32_bwd_dkdv(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
+                         const float* dnum, const float* dden, float* dK, float* dV,
+                         void* ws, size_t ws_bytes, cudaStream_t st);
+int linattn_f32_bwd(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
+                    const float* O, const float* dO, const float* den, float* dQ, float* dK, float* dV,
+                    void* ws, size_t ws_bytes, cudaStream_t st);
+
+// ---- elementwise (elementwise.cu) ----
+int step1_f32(const float* O, const float* dO, const float* den, float* dnum, float* dden,
+              size_t N, size_t E, cudaStream_t st);
+int phi_elu_fwd(const float* x, float* phi, size_t N, size_t D, size_t E, cudaStream_t st);
+int phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, size_t D, size_t E, cudaStream_t st);
+int rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t hd, float sign, cudaStream_t st);
+int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st);
+
+}  // namespace cxxattn

@@ -1,0 +1,162 @@
+/* cxxattn — B200 (sm_100a) attention kernels behind CXX-GPT's kernel entry points.
+ *
+ * C-ABI of libcxxattn.so.  Every function takes plain device (or, for the *_host functions,
+ * host) pointers and sizes, launches on the given CUDA stream without synchronising (the
+ * *_host functions synchronise before returning), never allocates device memory unless stated,
+ * never aborts, and returns CXXATTN_OK or a negative error code (cxxattn_strerror()).
+ *
+ * Citations name the reference interface each entry point replaces, as
+ * file:line inside the CXX-GPT source tree ("ts.cuh" = src/TwoStage/two_stage_cuda_kernels.cuh,
+ * "ts.cu" the matching .cu, "lin.cuh"/"lin.cu" = src/LinearAttention/linear_cuda_kernels.cuh/.cu).
+ *
+ * Layouts (all row-major):
+ *   softmax MHA   Q,K,V,O,dO,dQ,dK,dV : (B*S, H*Dh); element (b,s,h,c) at ((b*S+s)*H+h)*Dh+c
+ *                 (ts.cuh:13-15), or any layout given by the element strides in the descriptor.
+ *                 lse : (B, H, S) float, natural-log-sum-exp of the scaled causal scores.
+ *   linear attn   Q,K,dQ,dK,z_cache : (B*S, D);  V,O,dO,dV,dnum : (B*S, E);  den,dden : (B*S).
+ *                 Multi-head tensors are passed with heads folded into B (layout [B,H,S,Dh]).
+ */
+#ifndef CXXATTN_H_
+#define CXXATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque CUDA stream handle (cudaStream_t); NULL is the legacy default stream, which is the
+ * stream the reference launches on (ts.cu:44, lin.cu:93). */
+typedef void* cxxattn_stream_t;
+
+enum {
+    CXXATTN_OK = 0,
+    CXXATTN_ERR_INVALID = -1,     /* null pointer, zero/negative size, bad enum               */
+    CXXATTN_ERR_UNSUPPORTED = -2, /* valid request that no kernel of this build covers        */
+    CXXATTN_ERR_WORKSPACE = -3,   /* workspace pointer null or smaller than *_workspace_bytes */
+    CXXATTN_ERR_CUDA = -4,        /* a CUDA runtime call failed (launch, copy, attribute)     */
+    CXXATTN_ERR_TIMEOUT = -5,     /* a bounded device-side wait gave up (status word set)     */
+    CXXATTN_ERR_ALIGNMENT = -6,   /* pointer or stride not aligned as the chosen kernel needs */
+    CXXATTN_ERR_TOO_LARGE = -7    /* size beyond a stated fixed maximum                       */
+};
+
+enum { CXXATTN_F32 = 0, CXXATTN_BF16 = 1 };
+
+/* feature map applied to Q and K inside the linear-attention kernels */
+enum {
+    CXXATTN_MAP_NONE = 0, /* inputs are already mapped (linear_cuda::*, lin.cuh:11-37)        */
+    CXXATTN_MAP_ELU1 = 1  /* phi(x) = x > 0 ? x + 1 : exp(x) fused (two_stage_cuda, ts.cu:928) */
+};
+
+/* Softmax MHA problem.  dtype F32 selects the exact fp32 SIMT kernels; dtype BF16 selects the
+ * tcgen05 tensor-core kernels (bf16 operands, fp32 accumulation and softmax). */
+typedef struct cxxattn_mha_desc {
+    int64_t B, S, H, Dh;
+    int64_t stride_b, stride_s, stride_h; /* element strides shared by all 8 tensors; all three 0
+                                             = reference layout (S*H*Dh, H*Dh, Dh)              */
+    int32_t dtype;                        /* CXXATTN_F32 | CXXATTN_BF16                          */
+    int32_t reserved;                     /* must be 0                                           */
+} cxxattn_mha_desc;
+
+/* Causal linear attention problem. */
+typedef struct cxxattn_lin_desc {
+    int64_t B, S, D, E;
+    int32_t dtype;       /* type of Q,K,V,O,dO,dQ,dK,dV; den, dden, dnum, z_cache are always float */
+    int32_t feature_map; /* CXXATTN_MAP_*                                                        */
+    int32_t eps_in_den;  /* 0: den = phi(q).z stored, O = num/(den+1e-8)   (ts.cu:971-972)
+                            1: den = q.z + 1e-8 stored, O = num/den        (lin.cu:66-75)        */
+    int32_t reserved;    /* must be 0                                                            */
+} cxxattn_lin_desc;
+
+const char* cxxattn_strerror(int code);
+/* "major.minor sm_100a" build string. */
+const char* cxxattn_version(void);
+
+/* ---- softmax MHA ------------------------------------------------------------------------- */
+
+/* O = softmax_causal(QK^T / sqrt(Dh)) V.  Replaces two_stage_cuda::fused_mha_fwd (ts.cuh:18-20,
+ * ts.cu:285-326).  lse may be NULL; when given it receives the row log-sum-exp that
+ * cxxattn_mha_bwd can reuse (the reference forward emits none and its backward recomputes). */
+int cxxattn_mha_fwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, const void* V,
+                    void* O, float* lse, cxxattn_stream_t stream);
+
+/* Bytes of device workspace cxxattn_mha_bwd needs (0 on a bad descriptor). */
+size_t cxxattn_mha_bwd_workspace_bytes(const cxxattn_mha_desc* desc, int have_lse);
+
+/* dQ, dK, dV of the above given dO and the stored O; outputs are overwritten.  Replaces
+ * two_stage_cuda::fused_mha_bwd (ts.cuh:22-27, ts.cu:830-882).  lse may be NULL: the row
+ * statistics are then recomputed from Q,K in a pre-pass, as the reference's backward does. */
+int cxxattn_mha_bwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, const void* V,
+                    const void* O, const void* dO, const float* lse,
+                    void* dQ, void* dK, void* dV,
+                    void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
+
+/* ---- causal linear attention ------------------------------------------------------------- */
+
+/* Workspace shared by all linear-attention entry points of one descriptor. */
+size_t cxxattn_linattn_workspace_bytes(const cxxattn_lin_desc* desc);
+
+/* Forward.  Replaces two_stage_cuda::kernel_attn_fwd (ts.cuh:39-44, ts.cu:1133-1185) with
+ * feature_map=ELU1, eps_in_den=0 and linear_cuda::causal_linear_attention_fwd (lin.cuh:11-17,
+ * lin.cu:81-99) with feature_map=NONE, eps_in_den=1.  z_cache may be NULL (then not written).
+ * The reference's S_buf / z_buf scratch arguments have no counterpart: the sequence is cut into
+ * chunks whose states live in `workspace`. */
+int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void* K, const void* V,
+                        void* O, float* den, float* z_cache,
+                        void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
+
+/* dnum = dO/den, dden = -(dO.O)/den per row.  Replaces two_stage_cuda::kernel_attn_bwd_step1
+ * (ts.cuh:46-49, ts.cu:1235-1248) and linear_cuda::causal_linear_attention_bwd_step1
+ * (lin.cuh:19-23, lin.cu:136-150).  O and dO are float. */
+int cxxattn_linattn_bwd_step1(const float* O, const float* dO, const float* den,
+                              float* dnum, float* dden, size_t N, size_t E,
+                              cxxattn_stream_t stream);
+
+/* dQ from (dnum, dden).  Replaces two_stage_cuda::kernel_attn_bwd_dQ (ts.cuh:51-55,
+ * ts.cu:1408-1453; Q needed for phi') and linear_cuda::causal_linear_attention_bwd_dQ
+ * (lin.cuh:25-30, lin.cu:199-215; Q may be NULL).  z_cache may be NULL: the z term is then
+ * rebuilt from K.  float tensors only. */
+int cxxattn_linattn_bwd_dq(const cxxattn_lin_desc* desc, const float* K, const float* V,
+                           const float* dnum, const float* dden, const float* z_cache,
+                           const float* Q, float* dQ,
+                           void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
+
+/* dK, dV from (dnum, dden).  Replaces two_stage_cuda::kernel_attn_bwd_dKdV (ts.cuh:57-61,
+ * ts.cu:1743-1809) and linear_cuda::causal_linear_attention_bwd_dKdV (lin.cuh:32-37,
+ * lin.cu:275-298).  float tensors only. */
+int cxxattn_linattn_bwd_dkdv(const cxxattn_lin_desc* desc, const float* Q, const float* K,
+                             const float* V, const float* dnum, const float* dden,
+                             float* dK, float* dV,
+                             void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
+
+/* Whole backward in one call (step1 + dQ + dK/dV without the dnum/dden/z_cache round trips).
+ * Same results as the three calls above; the grouping has no reference counterpart. */
+int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void* K, const void* V,
+                        const void* O, const void* dO, const float* den,
+                        void* dQ, void* dK, void* dV,
+                        void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
+
+/* ---- elementwise neighbours that share the reference headers ------------------------------ */
+
+/* phi[n,d] = ELU(x[n,d])+1 for d<E, 0 for E<=d<D.  linear_cuda::phi_elu_forward (lin.cuh:39-42,
+ * lin.cu:327-340). */
+int cxxattn_phi_elu_fwd(const float* x, float* phi, size_t N, size_t D, size_t E,
+                        cxxattn_stream_t stream);
+/* dx[n,e] = dphi[n,e] * (x>0 ? 1 : exp(x)).  linear_cuda::phi_elu_backward (lin.cuh:44-46,
+ * lin.cu:366-378). */
+int cxxattn_phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, size_t D, size_t E,
+                        cxxattn_stream_t stream);
+/* In-place rotary embedding of Q and/or K (either may be NULL, they may alias: the rotation is
+ * then applied twice, as the reference kernel does).  sign=+1: two_stage_cuda::rope_fwd,
+ * sign=-1: rope_bwd (ts.cuh:72-76, ts.cu:1820-1880). */
+int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_dim, float sign,
+                 cxxattn_stream_t stream);
+/* erf-GELU (deriv=0) and its derivative (deriv=1).  two_stage_cuda::gelu_exact /
+ * gelu_exact_deriv (ts.cuh:84-85, ts.cu:1888-1924). */
+int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CXXATTN_H_ */

@@ -1,0 +1,67 @@
+"""CPU checks of the drop-in boundary: the shared library loads, exports every symbol that
+include/cxxattn.h declares, and rejects bad arguments with error codes before touching a device."""
+import ctypes as C
+import os
+import re
+
+from conftest import ROOT
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "cxxattn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(cxxattn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = pkg.lib()
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/cxxattn.h but not exported"
+    assert set(pkg.SYMBOLS) <= set(names)
+
+
+def test_version_and_strerror(pkg):
+    assert b"sm_100a" in pkg.lib().cxxattn_version()
+    assert pkg.strerror(0) == "ok"
+    for code in range(-7, 0):
+        assert pkg.strerror(code) not in ("ok", "unknown error")
+    assert pkg.strerror(-99) == "unknown error"
+
+
+def test_bad_arguments_are_rejected_without_a_device(pkg):
+    lib = pkg.lib()
+    d = pkg.mha_desc(2, 8, 2, 16)
+    one = C.c_void_p(16)
+    assert lib.cxxattn_mha_fwd(None, one, one, one, one, None, None) == -1
+    assert lib.cxxattn_mha_fwd(C.byref(d), None, one, one, one, None, None) == -1
+    bad = pkg.mha_desc(0, 8, 2, 16)
+    assert lib.cxxattn_mha_fwd(C.byref(bad), one, one, one, one, None, None) == -1
+    assert lib.cxxattn_mha_bwd_workspace_bytes(C.byref(bad), 0) == 0
+    assert lib.cxxattn_mha_bwd_workspace_bytes(C.byref(d), 0) >= 2 * 2 * 2 * 8 * 4
+    # backward without a workspace
+    assert lib.cxxattn_mha_bwd(C.byref(d), one, one, one, one, one, None, one, one, one, None, 0, None) == -3
+    # head dimension beyond 256 is unsupported, as in the reference (which aborts instead)
+    big = pkg.mha_desc(1, 8, 1, 512)
+    assert lib.cxxattn_mha_bwd(C.byref(big), one, one, one, one, one, None, one, one, one, one, 1 << 20, None) == -2
+    ld = pkg.lin_desc(2, 8, 4, 4)
+    assert lib.cxxattn_linattn_workspace_bytes(C.byref(ld)) > 0
+    assert lib.cxxattn_linattn_fwd(C.byref(ld), one, one, one, one, one, None, None, 0, None) == -3
+    badmap = pkg.lin_desc(2, 8, 4, 4, feature_map=7)
+    assert lib.cxxattn_linattn_fwd(C.byref(badmap), one, one, one, one, one, None, one, 1 << 20, None) == -1
+    assert lib.cxxattn_rope(None, None, 1, 1, 8, 8, 1.0, None) == -1
+    assert lib.cxxattn_rope(one, one, 1, 1, 8, 3, 1.0, None) == -1
+    assert lib.cxxattn_phi_elu_fwd(one, one, 4, 2, 4, None) == -1   # E > D
+    assert lib.cxxattn_gelu_exact(one, one, 0, 0, None) == -1
+
+
+def test_python_front_end_mirrors_reference_names(pkg):
+    for n in ("fused_mha_fwd", "fused_mha_bwd", "kernel_attn_fwd", "kernel_attn_bwd_step1",
+              "kernel_attn_bwd_dQ", "kernel_attn_bwd_dKdV", "rope_fwd", "rope_bwd", "gelu_exact",
+              "gelu_exact_deriv"):
+        assert callable(getattr(pkg.two_stage_cuda, n))
+    for n in ("causal_linear_attention_fwd", "causal_linear_attention_bwd_step1",
+              "causal_linear_attention_bwd_dQ", "causal_linear_attention_bwd_dKdV",
+              "phi_elu_forward", "phi_elu_backward"):
+        assert callable(getattr(pkg.linear_cuda, n))

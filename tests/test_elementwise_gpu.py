@@ -1,0 +1,63 @@
+"""GPU parity of the elementwise neighbours (RoPE, erf-GELU, phi) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err, seeded_normal
+
+pytestmark = pytest.mark.gpu
+
+
+def test_rope_block_of_reference_kernel_test(pkg, dev, orc):
+    """B=2, S=6, D=16, head_dim=8, forward, backward and the aliased round trip
+    (kernel_test.cpp:445-498)."""
+    B, S, D, hd = 2, 6, 16, 8
+    skip = sum(4 * d["B"] * d["S"] * d["H"] * d["Dh"] if k == "mha"
+               else d["B"] * d["S"] * (2 * d["D"] + 2 * d["E"])
+               for k, d in __import__("conftest").KT_BLOCKS)
+    x = orc.frand(4 * B * S * D, skip)
+    Q, K, dQ, dK = (x[i * B * S * D:(i + 1) * B * S * D].reshape(B * S, D) for i in range(4))
+    ts = pkg.two_stage_cuda
+    tq, tk = torch.from_numpy(Q.copy()).to(dev), torch.from_numpy(K.copy()).to(dev)
+    ts.rope_fwd(tq, tk, B, S, D, hd)
+    assert np.abs(tq.cpu().numpy() - orc.rope(Q, S, hd, 1.0)).max() < 2e-6
+    assert np.abs(tk.cpu().numpy() - orc.rope(K, S, hd, 1.0)).max() < 2e-6
+    tdq, tdk = torch.from_numpy(dQ.copy()).to(dev), torch.from_numpy(dK.copy()).to(dev)
+    ts.rope_bwd(tdq, tdk, B, S, D, hd)
+    assert np.abs(tdq.cpu().numpy() - orc.rope(dQ, S, hd, -1.0)).max() < 2e-6
+    assert np.abs(tdk.cpu().numpy() - orc.rope(dK, S, hd, -1.0)).max() < 2e-6
+    t2 = torch.from_numpy(Q.copy()).to(dev)
+    ts.rope_fwd(t2, t2, B, S, D, hd)   # same tensor twice: rotated twice
+    ts.rope_bwd(t2, t2, B, S, D, hd)
+    assert np.abs(t2.cpu().numpy() - Q).max() < 2e-6
+
+
+def test_rope_whole_vector_and_long_positions(pkg, dev, orc):
+    B, S, D = 2, 256, 64
+    X, = seeded_normal(61, [(B * S, D)])
+    t = torch.from_numpy(X.copy()).to(dev)
+    pkg.two_stage_cuda.rope_fwd(t, None, B, S, D, D)
+    assert rel_err(t.cpu().numpy(), orc.rope(X, S, D, 1.0)) < 1e-4   # fp32 angle at p ~ 255
+
+
+def test_gelu_exact_and_derivative(pkg, dev, orc):
+    X, = seeded_normal(62, [(1000, 37)])
+    X *= 3
+    t = torch.from_numpy(X).to(dev)
+    out = torch.empty_like(t)
+    pkg.two_stage_cuda.gelu_exact(t, out)
+    assert np.abs(out.cpu().numpy() - orc.gelu_exact(X)).max() < 1e-6
+    pkg.two_stage_cuda.gelu_exact_deriv(t, out)
+    assert np.abs(out.cpu().numpy() - orc.gelu_exact(X, deriv=True)).max() < 1e-6
+
+
+def test_phi_elu_padding(pkg, dev, orc):
+    N, D, E = 77, 128, 100
+    X, G = seeded_normal(63, [(N, E), (N, D)])
+    tx, tg = torch.from_numpy(X).to(dev), torch.from_numpy(G).to(dev)
+    phi = torch.full((N, D), float("nan"), device=dev)
+    pkg.linear_cuda.phi_elu_forward(tx, phi, D, E)
+    assert rel_err(phi.cpu().numpy(), orc.phi_elu_fwd(X, D)) < 1e-6
+    dx = torch.empty(N, E, device=dev)
+    pkg.linear_cuda.phi_elu_backward(tg, tx, dx, D, E)
+    assert rel_err(dx.cpu().numpy(), orc.phi_elu_bwd(G, X)) < 1e-6

@@ -1,0 +1,190 @@
+"""GPU parity of the chunk-parallel linear attention kernels against the CPU oracle, through the
+C-ABI, for both reference flavours: two_stage_cuda (ELU+1 fused, den without eps) and linear_cuda
+(pre-mapped inputs, den with eps).  fp32 tolerance 1e-5 as max|a-b| / max|b| per tensor."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import KT_BLOCKS, kt_block_inputs, rel_err, seeded_normal
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def to_dev(dev, *xs):
+    return [torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in xs]
+
+
+def run_two_stage(pkg, dev, Q, K, V, dO, B, S, D, E):
+    """The reference call sequence (two_stage_gpt.hpp:121, 149-156)."""
+    ts = pkg.two_stage_cuda
+    N = B * S
+    tq, tk, tv, tg = to_dev(dev, Q, K, V, dO)
+    O = torch.full((N, E), float("nan"), device=dev)
+    den = torch.empty(N, device=dev)
+    zc = torch.empty(N, D, device=dev)
+    Sb, zb = torch.empty(B * E, D, device=dev), torch.empty(B, D, device=dev)
+    ts.kernel_attn_fwd(tq, tk, tv, O, den, zc, Sb, zb, B, S, D, E)
+    dnum, dden = torch.empty(N, E, device=dev), torch.empty(N, device=dev)
+    ts.kernel_attn_bwd_step1(O, tg, den, dnum, dden, N, E)
+    dQ, dK, dV = (torch.full(s, float("nan"), device=dev) for s in ((N, D), (N, D), (N, E)))
+    ts.kernel_attn_bwd_dQ(tk, tv, dnum, dden, zc, tq, dQ, Sb, B, S, D, E)
+    ts.kernel_attn_bwd_dKdV(tq, tk, tv, dnum, dden, dK, dV, B, S, D, E)
+    fQ, fK, fV = (torch.full(s, float("nan"), device=dev) for s in ((N, D), (N, D), (N, E)))
+    pkg.linattn_bwd(tq, tk, tv, O, tg, den, fQ, fK, fV, B, S, D, E, pkg.MAP_ELU1, 0)
+    torch.cuda.synchronize()
+    names = "O den zc dnum dden dQ dK dV fQ fK fV".split()
+    return dict(zip(names, (t.cpu().numpy() for t in (O, den, zc, dnum, dden, dQ, dK, dV, fQ, fK, fV))))
+
+
+def check_two_stage(pkg, dev, orc, Q, K, V, dO, B, S, D, E, tol=TOL):
+    g = run_two_stage(pkg, dev, Q, K, V, dO, B, S, D, E)
+    rO, rden, rzc = orc.linattn_fwd(Q, K, V, B, S, D, E, elu=True)
+    rdnum, rdden = orc.linattn_step1(g["O"], dO, g["den"])
+    rdQ, rdK, rdV = orc.linattn_bwd(Q, K, V, rdnum, rdden, B, S, D, E, elu=True)
+    want = dict(O=rO, den=rden, zc=rzc, dnum=rdnum, dden=rdden, dQ=rdQ, dK=rdK, dV=rdV,
+                fQ=rdQ, fK=rdK, fV=rdV)
+    for k, w in want.items():
+        assert np.all(np.isfinite(g[k])), k
+        assert rel_err(g[k], w) < tol, (k, rel_err(g[k], w))
+    return g
+
+
+@pytest.mark.parametrize("index", [1, 3, 5])
+def test_reference_kernel_test_blocks(pkg, dev, orc, index):
+    """Stage-2 blocks of the reference kernel test: D=E=8; D=7,E=6 (odd); D=E=256
+    (kernel_test.cpp:254, 337, 412), same input stream, same checked tensors."""
+    kind, d, (Q, K, V, dO) = kt_block_inputs(orc.frand, index)
+    assert kind == "lin"
+    g = check_two_stage(pkg, dev, orc, Q, K, V, dO, **d)
+    gold = np.load(os.path.join(GOLD, "kernel_test_blocks.npz"))
+    for name, key in (("O", "O"), ("den", "den"), ("dQ", "dQ"), ("dK", "dK"), ("dV", "dV")):
+        k = f"b{index}_{key}"
+        want = gold[k] if k in gold else gold[k + "__sub"]
+        got = g[name].ravel() if k in gold else g[name].ravel()[::61]
+        assert rel_err(got, want) < TOL, (name, rel_err(got, want))
+
+
+@pytest.mark.parametrize("S", [64, 1024])
+def test_baseline_config_2(pkg, dev, orc, S):
+    """ELU+1, B=8 x 4 heads folded (B'=32), head_dim 32, N(0,1) seed 1."""
+    B, D, E = 32, 32, 32
+    Q, K, V, dO = seeded_normal(1, [(B * S, D), (B * S, D), (B * S, E), (B * S, E)])
+    g = check_two_stage(pkg, dev, orc, Q, K, V, dO, B, S, D, E)
+    if S == 64:
+        gold = np.load(os.path.join(GOLD, "seeded_cases.npz"))
+        for name in ("O", "den", "dQ", "dK", "dV"):
+            assert rel_err(g[name].ravel()[::61], gold[f"cfg2_{name}__sub"]) < TOL
+
+
+def test_baseline_config_2_unfolded_model_shape(pkg, dev, orc):
+    """The shape TwoStageGPT really calls with: one state per batch item, D=E=n_embd=128."""
+    B, S, D, E = 8, 64, 128, 128
+    Q, K, V, dO = seeded_normal(2, [(B * S, D), (B * S, D), (B * S, E), (B * S, E)])
+    check_two_stage(pkg, dev, orc, Q, K, V, dO, B, S, D, E)
+
+
+@pytest.mark.parametrize("B,S,D,E", [(1, 1, 1, 1), (2, 63, 5, 9), (2, 65, 33, 31), (1, 200, 70, 130),
+                                     (3, 128, 64, 64), (1, 129, 64, 16)])
+def test_ragged_shapes(pkg, dev, orc, B, S, D, E):
+    Q, K, V, dO = seeded_normal(50 + S + D, [(B * S, D), (B * S, D), (B * S, E), (B * S, E)])
+    check_two_stage(pkg, dev, orc, Q, K, V, dO, B, S, D, E)
+
+
+def run_linear_gpt(pkg, dev, xq, xk, V, dO, B, S, D, E):
+    """LinearBlock::forward / backward call sequence (linear_gpt.hpp:100-112, 154-172): phi outside,
+    scan on the mapped features, phi backward outside."""
+    lc = pkg.linear_cuda
+    N = B * S
+    tq, tk, tv, tg = to_dev(dev, xq, xk, V, dO)
+    Qp, Kp = torch.empty(N, D, device=dev), torch.empty(N, D, device=dev)
+    lc.phi_elu_forward(tq, Qp, D, E)
+    lc.phi_elu_forward(tk, Kp, D, E)
+    O, den, zc = torch.empty(N, E, device=dev), torch.empty(N, device=dev), torch.empty(N, D, device=dev)
+    Sb, zb = torch.empty(B * D, E, device=dev), torch.empty(B, D, device=dev)
+    lc.causal_linear_attention_fwd(Qp, Kp, tv, O, den, zc, Sb, zb, B, S, D, E)
+    dnum, dden = torch.empty(N, E, device=dev), torch.empty(N, device=dev)
+    lc.causal_linear_attention_bwd_step1(O, tg, den, dnum, dden, N, E)
+    dQp, dKp, dV = torch.empty(N, D, device=dev), torch.empty(N, D, device=dev), torch.empty(N, E, device=dev)
+    lc.causal_linear_attention_bwd_dQ(Kp, tv, dnum, dden, zc, dQp, Sb, B, S, D, E)
+    lc.causal_linear_attention_bwd_dKdV(Qp, Kp, tv, dnum, dden, dKp, dV, B, S, D, E)
+    dxq, dxk = torch.empty(N, E, device=dev), torch.empty(N, E, device=dev)
+    lc.phi_elu_backward(dQp, tq, dxq, D, E)
+    lc.phi_elu_backward(dKp, tk, dxk, D, E)
+    torch.cuda.synchronize()
+    names = "Qp Kp O den zc dnum dden dQp dKp dV dxq dxk".split()
+    return dict(zip(names, (t.cpu().numpy() for t in (Qp, Kp, O, den, zc, dnum, dden, dQp, dKp, dV, dxq, dxk))))
+
+
+def check_linear_gpt(pkg, dev, orc, xq, xk, V, dO, B, S, D, E):
+    g = run_linear_gpt(pkg, dev, xq, xk, V, dO, B, S, D, E)
+    rQp, rKp = orc.phi_elu_fwd(xq, D), orc.phi_elu_fwd(xk, D)
+    rO, rden, rzc = orc.linattn_fwd(rQp, rKp, V, B, S, D, E, elu=False)
+    rdnum, rdden = orc.linattn_step1(g["O"], dO, g["den"])
+    rdQp, rdKp, rdV = orc.linattn_bwd(rQp, rKp, V, rdnum, rdden, B, S, D, E, elu=False)
+    want = dict(Qp=rQp, Kp=rKp, O=rO, den=rden, zc=rzc, dnum=rdnum, dden=rdden, dQp=rdQp, dKp=rdKp,
+                dV=rdV, dxq=orc.phi_elu_bwd(rdQp, xq), dxk=orc.phi_elu_bwd(rdKp, xk))
+    for k, w in want.items():
+        assert rel_err(g[k], w) < TOL, (k, rel_err(g[k], w))
+    assert np.all(g["Qp"][:, E:] == 0)
+    return g
+
+
+def test_baseline_config_3_folded(pkg, dev, orc):
+    """LinearGPT scan, 12 heads x 64 folded into the batch (B'=96), S=256; Q,K,V ~ N(0,0.02^2)."""
+    B, S, D, E = 96, 256, 64, 64
+    xq, xk, V = seeded_normal(2, [(B * S, E)] * 3, std=0.02)
+    dO, = seeded_normal(3, [(B * S, E)])
+    check_linear_gpt(pkg, dev, orc, xq, xk, V, dO, B, S, D, E)
+
+
+def test_baseline_config_3_model_shape(pkg, dev, orc):
+    """The shape LinearGPT really calls with: E=n_embd=768 zero-padded to D=1024 (linear_gpt.hpp:232),
+    one state per batch item.  B reduced to 2 to keep the oracle within seconds."""
+    B, S, D, E = 2, 256, 1024, 768
+    xq, xk, V = seeded_normal(4, [(B * S, E)] * 3, std=0.02)
+    dO, = seeded_normal(5, [(B * S, E)])
+    check_linear_gpt(pkg, dev, orc, xq, xk, V, dO, B, S, D, E)
+
+
+def test_dq_without_z_cache_matches(pkg, dev, orc):
+    B, S, D, E = 2, 150, 32, 48
+    Q, K, V, dO = seeded_normal(31, [(B * S, D), (B * S, D), (B * S, E), (B * S, E)])
+    tq, tk, tv, tg = to_dev(dev, Q, K, V, dO)
+    N = B * S
+    O, den, zc = torch.empty(N, E, device=dev), torch.empty(N, device=dev), torch.empty(N, D, device=dev)
+    pkg.linattn_fwd(tq, tk, tv, O, den, zc, B, S, D, E, pkg.MAP_ELU1, 0)
+    O2, den2 = torch.empty_like(O), torch.empty_like(den)
+    pkg.linattn_fwd(tq, tk, tv, O2, den2, None, B, S, D, E, pkg.MAP_ELU1, 0)
+    assert torch.equal(O, O2) and torch.equal(den, den2)
+    dnum, dden = torch.empty(N, E, device=dev), torch.empty(N, device=dev)
+    pkg.linattn_bwd_step1(O, tg, den, dnum, dden, N, E)
+    a, b = torch.empty(N, D, device=dev), torch.empty(N, D, device=dev)
+    pkg.linattn_bwd_dq(tk, tv, dnum, dden, zc, tq, a, B, S, D, E, pkg.MAP_ELU1, 0)
+    pkg.linattn_bwd_dq(tk, tv, dnum, dden, None, tq, b, B, S, D, E, pkg.MAP_ELU1, 0)
+    assert rel_err(a.cpu().numpy(), b.cpu().numpy()) < TOL
+
+
+def test_long_sequence_properties(pkg, dev, orc):
+    """S=4096, D=E=64 (the long-sequence shape): causality (a change at position t leaves earlier
+    outputs bit-identical) and agreement with the oracle on a 2-unit subset."""
+    B, S, D, E = 6, 4096, 64, 64
+    Q, K, V, dO = seeded_normal(41, [(B * S, D), (B * S, D), (B * S, E), (B * S, E)])
+    tq, tk, tv = to_dev(dev, Q, K, V)
+    N = B * S
+    O, den = torch.empty(N, E, device=dev), torch.empty(N, device=dev)
+    pkg.linattn_fwd(tq, tk, tv, O, den, None, B, S, D, E, pkg.MAP_ELU1, 0)
+    cut = 3000
+    tk2, tv2 = tk.clone(), tv.clone()
+    tk2.view(B, S, D)[:, cut:] *= -1
+    tv2.view(B, S, E)[:, cut:] += 3
+    O2, den2 = torch.empty_like(O), torch.empty_like(den)
+    pkg.linattn_fwd(tq, tk2, tv2, O2, den2, None, B, S, D, E, pkg.MAP_ELU1, 0)
+    assert torch.equal(O.view(B, S, E)[:, :cut], O2.view(B, S, E)[:, :cut])
+    sub = 2
+    rO, rden, _ = orc.linattn_fwd(Q[:sub * S], K[:sub * S], V[:sub * S], sub, S, D, E, elu=True, f64=True)
+    assert rel_err(O[:sub * S].cpu().numpy(), rO) < TOL
+    assert rel_err(den[:sub * S].cpu().numpy(), rden) < TOL

@@ -1,0 +1,125 @@
+"""GPU parity of the softmax MHA kernels against the CPU oracle, through the C-ABI.
+Tolerance for the fp32 path: 1e-5 as max|a-b| / max|b| per tensor."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import KT_BLOCKS, kt_block_inputs, rel_err, seeded_normal
+
+pytestmark = pytest.mark.gpu
+TOL_F32 = 1e-5
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def run_mha(pkg, dev, Q, K, V, dO, B, S, H, Dh, use_lse):
+    tq, tk, tv, tg = (torch.from_numpy(np.ascontiguousarray(x)).to(dev) for x in (Q, K, V, dO))
+    to, tdq, tdk, tdv = (torch.full_like(tq, float("nan")) for _ in range(4))
+    lse = torch.empty(B * H * S, device=dev) if use_lse else None
+    pkg.mha_fwd(tq, tk, tv, to, B, S, H, Dh, lse=lse)
+    pkg.mha_bwd(tq, tk, tv, to, tg, tdq, tdk, tdv, B, S, H, Dh, lse=lse)
+    torch.cuda.synchronize()
+    return [t.cpu().numpy() for t in (to, tdq, tdk, tdv)] + [lse.cpu().numpy() if use_lse else None]
+
+
+def check_mha(pkg, dev, orc, Q, K, V, dO, B, S, H, Dh, use_lse=False, tol=TOL_F32):
+    O, dQ, dK, dV, lse = run_mha(pkg, dev, Q, K, V, dO, B, S, H, Dh, use_lse)
+    rO = orc.mha_fwd(Q, K, V, B, S, H, Dh)
+    # the reference backward consumes the stored O of the forward under test (kernel_test.cpp:246)
+    rdQ, rdK, rdV = orc.mha_bwd(Q, K, V, O, dO, B, S, H, Dh)
+    for name, a, b in (("O", O, rO), ("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert np.all(np.isfinite(a)), name
+        assert rel_err(a, b) < tol, (name, rel_err(a, b))
+    if use_lse:
+        _, rl = orc.mha_fwd(Q, K, V, B, S, H, Dh, f64=True, want_lse=True)
+        assert np.abs(lse - rl).max() < 1e-4
+    return O, dQ, dK, dV
+
+
+@pytest.mark.parametrize("index", [0, 2, 4])
+def test_reference_kernel_test_blocks(pkg, dev, orc, index):
+    """The three softmax blocks of the reference kernel test: B=2,S=6,H=2,Dh=8; S=300,Dh=128;
+    S=256,H=2,Dh=64 (kernel_test.cpp:217, 303, 378), same input stream."""
+    kind, d, (Q, K, V, dO) = kt_block_inputs(orc.frand, index)
+    assert kind == "mha"
+    O, dQ, dK, dV = check_mha(pkg, dev, orc, Q, K, V, dO, **d)
+    gold = np.load(os.path.join(GOLD, "kernel_test_blocks.npz"))
+    for name, a in (("O", O), ("dQ", dQ), ("dK", dK), ("dV", dV)):
+        key = f"b{index}_{name}"
+        want = gold[key] if key in gold else gold[key + "__sub"]
+        got = a.ravel() if key in gold else a.ravel()[::61]
+        # dQ/dK/dV in the golden file were computed from the reference's own O; 1e-5 still holds
+        assert rel_err(got, want) < TOL_F32, (name, rel_err(got, want))
+
+
+def test_baseline_config_1(pkg, dev, orc):
+    """B=8, S=64, n_embd=128, 4 heads x 32, N(0,1) seed 0."""
+    B, S, H, Dh = 8, 64, 4, 32
+    Q, K, V, dO = seeded_normal(0, [(B * S, H * Dh)] * 4)
+    O, dQ, dK, dV = check_mha(pkg, dev, orc, Q, K, V, dO, B, S, H, Dh)
+    gold = np.load(os.path.join(GOLD, "seeded_cases.npz"))
+    for name, a in (("O", O), ("dQ", dQ), ("dK", dK), ("dV", dV)):
+        assert rel_err(a.ravel()[::61], gold[f"cfg1_{name}__sub"]) < TOL_F32
+
+
+@pytest.mark.parametrize("B,S,H,Dh", [(1, 1, 1, 1), (2, 7, 3, 5), (1, 65, 2, 33), (2, 129, 1, 200),
+                                      (1, 64, 1, 256), (3, 100, 2, 64), (1, 513, 1, 16)])
+def test_odd_and_edge_shapes(pkg, dev, orc, B, S, H, Dh):
+    Q, K, V, dO = seeded_normal(100 + S + Dh, [(B * S, H * Dh)] * 4)
+    check_mha(pkg, dev, orc, Q, K, V, dO, B, S, H, Dh)
+
+
+def test_lse_reuse_matches_recompute(pkg, dev, orc):
+    B, S, H, Dh = 2, 200, 2, 64
+    Q, K, V, dO = seeded_normal(21, [(B * S, H * Dh)] * 4)
+    a = check_mha(pkg, dev, orc, Q, K, V, dO, B, S, H, Dh, use_lse=True)
+    b = run_mha(pkg, dev, Q, K, V, dO, B, S, H, Dh, use_lse=False)
+    for x, y in zip(a, b[:4]):
+        assert rel_err(x, y) < 1e-6  # same statistics either way
+
+
+def test_large_inputs_do_not_overflow(pkg, dev, orc):
+    """Scores of magnitude ~1e3: the running-max form must stay finite."""
+    B, S, H, Dh = 1, 96, 1, 32
+    Q, K, V, dO = seeded_normal(22, [(B * S, H * Dh)] * 4)
+    check_mha(pkg, dev, orc, Q * 30, K * 30, V, dO, B, S, H, Dh, tol=5e-5)
+
+
+def test_strided_heads_in_place(pkg, dev, orc):
+    """[B,H,S,Dh] storage addressed through the descriptor's strides gives the same numbers as the
+    reference layout."""
+    B, S, H, Dh = 2, 70, 3, 32
+    Q, K, V, dO = seeded_normal(23, [(B * S, H * Dh)] * 4)
+    want = run_mha(pkg, dev, Q, K, V, dO, B, S, H, Dh, False)[:4]
+
+    def bhsd(x):
+        return torch.from_numpy(x).view(B, S, H, Dh).permute(0, 2, 1, 3).contiguous().to(dev)
+    tq, tk, tv, tg = map(bhsd, (Q, K, V, dO))
+    to, tdq, tdk, tdv = (torch.empty_like(tq) for _ in range(4))
+    strides = (H * S * Dh, Dh, S * Dh)  # batch, sequence, head
+    pkg.mha_fwd(tq, tk, tv, to, B, S, H, Dh, strides=strides)
+    pkg.mha_bwd(tq, tk, tv, to, tg, tdq, tdk, tdv, B, S, H, Dh, strides=strides)
+    for t, w in zip((to, tdq, tdk, tdv), want):
+        got = t.permute(0, 2, 1, 3).reshape(B * S, H * Dh).cpu().numpy()
+        np.testing.assert_array_equal(got, w)
+
+
+def test_causality_and_batch_independence(pkg, dev):
+    """Changing keys/values after position t must not change outputs up to t, and each (batch,
+    head) is independent: size-independent properties checked at a size the oracle cannot reach."""
+    B, S, H, Dh = 2, 2048, 2, 64
+    g = torch.Generator(device="cpu").manual_seed(5)
+    Q, K, V = (torch.randn(B * S, H * Dh, generator=g).to(dev) for _ in range(3))
+    O1 = torch.empty_like(Q)
+    pkg.mha_fwd(Q, K, V, O1, B, S, H, Dh)
+    K2, V2 = K.clone(), V.clone()
+    cut = 1500
+    K2.view(B, S, H * Dh)[:, cut:] += 1.0
+    V2.view(B, S, H * Dh)[:, cut:] -= 2.0
+    O2 = torch.empty_like(Q)
+    pkg.mha_fwd(Q, K2, V2, O2, B, S, H, Dh)
+    a, b = O1.view(B, S, -1), O2.view(B, S, -1)
+    assert torch.equal(a[:, :cut], b[:, :cut]) and not torch.equal(a[:, cut:], b[:, cut:])
+    # row 0 attends to itself only
+    assert torch.allclose(a[:, 0], V.view(B, S, -1)[:, 0], atol=1e-6)
