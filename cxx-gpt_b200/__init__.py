@@ -22,6 +22,7 @@ SYMBOLS = [
     "cxxattn_linattn_workspace_bytes", "cxxattn_linattn_fwd", "cxxattn_linattn_bwd_step1",
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
+    "cxxattn_sync_status", "cxxattn_selftest_umma",
 ]
 
 
@@ -73,6 +74,8 @@ def lib():
         L.cxxattn_phi_elu_bwd.argtypes = [vp, vp, vp, sz, sz, sz, vp]
         L.cxxattn_rope.argtypes = [vp, vp, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
+        L.cxxattn_sync_status.argtypes = [vp]
+        L.cxxattn_selftest_umma.argtypes = [i32, vp, vp, vp, vp]
         _lib = L
     return _lib
 
@@ -196,6 +199,15 @@ def linattn_bwd(Q, K, V, O, dO, den, dQ, dK, dV, B, S, D, E, feature_map, eps_in
     check(lib().cxxattn_linattn_bwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(den),
                                     _ptr(dQ), _ptr(dK), _ptr(dV), ws.data_ptr(), ws.numel(), _stream()),
           "cxxattn_linattn_bwd")
+
+
+def sync_status():
+    """Synchronises the current stream and raises if a tensor-core kernel gave up a bounded wait."""
+    check(lib().cxxattn_sync_status(_stream()), "cxxattn_sync_status")
+
+
+def selftest_umma(mode, A, B, D):
+    check(lib().cxxattn_selftest_umma(mode, _ptr(A), _ptr(B), _ptr(D), _stream()), "cxxattn_selftest_umma")
 
 
 # ---------------------------------------------------------------------------------------------

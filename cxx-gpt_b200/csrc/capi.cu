@@ -56,7 +56,8 @@ int cxxattn_mha_fwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (desc->dtype == CXXATTN_F32)
         return mha_f32_fwd(p, (const float*)Q, (const float*)K, (const float*)V, (float*)O, lse, st);
-    return CXXATTN_ERR_UNSUPPORTED;
+    if (desc->dtype == CXXATTN_BF16) return mha_tc_fwd(p, Q, K, V, O, lse, st);
+    return CXXATTN_ERR_INVALID;
 }
 
 size_t cxxattn_mha_bwd_workspace_bytes(const cxxattn_mha_desc* desc, int have_lse) {
@@ -148,6 +149,13 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
     if ((!Q && !K) || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 2 || D % head_dim)
         return CXXATTN_ERR_INVALID;
     return rope(Q, K, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_sync_status(cxxattn_stream_t stream) { return sync_status(static_cast<cudaStream_t>(stream)); }
+
+int cxxattn_selftest_umma(int mode, const void* A, const void* B, float* D, cxxattn_stream_t stream) {
+    if (!A || !B || !D) return CXXATTN_ERR_INVALID;
+    return umma_selftest(mode, A, B, D, static_cast<cudaStream_t>(stream));
 }
 
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {

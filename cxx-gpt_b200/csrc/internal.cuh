@@ -29,6 +29,15 @@ int mha_f32_bwd(const MhaShape& p, const float* Q, const float* K, const float* 
                 const float* dO, const float* lse, float* dQ, float* dK, float* dV,
                 void* ws, size_t ws_bytes, cudaStream_t st);
 
+// ---- tcgen05 bf16 softmax MHA, head dimension 64 (mha_tc_fwd.cu, mha_tc_bwd.cu) ----
+bool mha_tc_supported(const MhaShape& p);
+int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, void* O, float* lse,
+               cudaStream_t st);
+
+// ---- diagnostics (umma_selftest.cu) ----
+int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);
+int sync_status(cudaStream_t st);
+
 // ---- exact fp32 chunk-parallel linear attention (linattn_f32.cu) ----
 size_t linattn_f32_workspace(const cxxattn_lin_desc& d);
 int linattn_f32_fwd(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,

@@ -1,0 +1,321 @@
+// Causal softmax MHA forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), bf16
+// operands, fp32 accumulation and softmax, head dimension 64.
+//
+// Replaces two_stage_cuda::fused_mha_fwd (src/TwoStage/two_stage_cuda_kernels.cu:54-326) for
+// dtype BF16.  Where the reference gives one warp one query row and walks the keys one at a
+// time with shuffle reductions, this kernel is a FlashAttention pipeline:
+//
+//   CTA  = 2 query tiles of 128 rows (rows q0 .. q0+255 of one (batch, head)), 10 warps:
+//          warps 0-3  softmax group of tile 0  (thread i <-> query row i <-> TMEM lane i)
+//          warps 4-7  softmax group of tile 1
+//          warp  8    TMA producer: Q once, then K/V tiles of 128 keys through a 3-stage ring
+//          warp  9    MMA issuer (one elected thread) and TMEM owner
+//   TMEM = S0 | S1 (128 fp32 columns each) | O0 | O1 (64 columns each); P (bf16) overwrites the
+//          first 64 columns of its S and feeds the PV product directly from TMEM.
+//
+//   per KV tile j:   S_t = Q_t K_j^T   (SS MMA, 128x128x64)      -> softmax group t
+//                    P_t = exp2(c*S_t - m_t), l_t += rowsum      -> TMEM (bf16)
+//                    O_t += P_t V_j    (TS MMA, 128x64x128)
+//
+// The MMA warp interleaves the two tiles (PV0(j), S0(j+1), PV1(j), S1(j+1), ...) so one group's
+// exponentials overlap the other group's matrix products.  KV tiles above the causal diagonal
+// are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
+// when it grows by more than 8 (in log2 units), so the rescaling of O in TMEM is rare.
+#include "internal.cuh"
+#include "tc_common.cuh"
+
+namespace cxxattn {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;       // rows per query tile
+constexpr int BN = 128;       // keys per KV tile
+constexpr int DH = 64;        // head dimension
+constexpr int STAGES = 3;
+constexpr int TILE_BYTES = BM * DH * 2;  // 16 KB: one 128 x 64 bf16 tile
+constexpr int NTHREADS = 320;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_S = 0, COL_O = 256;
+constexpr size_t SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + 1024;  // + alignment slack
+
+struct FwdParams {
+    __nv_bfloat16* O;
+    float* lse;  // may be null
+    int* status;
+    int B, S, H;
+    int64_t sb, ss, sh;
+    float scale_log2;  // 1/sqrt(Dh) * log2(e)
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], o_done[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;                                // 2 tiles
+    uint8_t* sK = smem + 2 * TILE_BYTES;               // STAGES tiles
+    uint8_t* sV = smem + (2 + STAGES) * TILE_BYTES;    // STAGES tiles
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
+    const int nbh = p.B * p.H;
+    const int pair = npairs - 1 - (int)(blockIdx.x / nbh);  // longest CTAs first
+    const int bh = blockIdx.x % nbh;
+    const int b = bh / p.H, h = bh % p.H;
+    const int q0 = pair * 2 * BM;
+    const bool has_t1 = q0 + BM < p.S;
+    const int n0 = q0 / BN;                  // diagonal KV tile of query tile 0
+    const int nkv = has_t1 ? n0 + 2 : n0 + 1;
+    const Guard guard{&abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(&s_full[t], 1);
+            mbar_init(&p_full[t], BM);
+            mbar_init(&o_done[t], 1);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 9) tmem_alloc(&tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 8) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            prefetch_tmap(&tmQ);
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+            mbar_expect_tx(&q_full, 2 * TILE_BYTES);
+            tma_load_4d(sQ, &tmQ, &q_full, 0, h, q0, b);
+            tma_load_4d(sQ + TILE_BYTES, &tmQ, &q_full, 0, h, q0 + BM, b);
+            for (int j = 0; j < nkv; j++) {
+                const int s = j % STAGES;
+                if (j >= STAGES) mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, guard, 101);
+                mbar_expect_tx(&k_full[s], TILE_BYTES);
+                tma_load_4d(sK + s * TILE_BYTES, &tmK, &k_full[s], 0, h, j * BN, b);
+                mbar_expect_tx(&v_full[s], TILE_BYTES);
+                tma_load_4d(sV + s * TILE_BYTES, &tmV, &v_full[s], 0, h, j * BN, b);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = idesc_bf16(BM, BN, 0, 0);  // Q, K both K-major
+            constexpr uint32_t IDESC_O = idesc_bf16(BM, DH, 0, 1);  // P from TMEM, V MN-major
+            auto issue_s = [&](int t, int s) {
+                const uint32_t qa = smem_u32(sQ + t * TILE_BYTES), ka = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < DH / 16; k++)
+                    umma_ss(tmem + COL_S + t * BN, smem_desc_sw128(qa + 32 * k, 16), smem_desc_sw128(ka + 32 * k, 16),
+                            IDESC_S, k > 0);
+                umma_commit(&s_full[t]);
+            };
+            auto issue_pv = [&](int t, int s, bool acc) {
+                const uint32_t va = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BN / 16; k++)
+                    umma_ts(tmem + COL_O + t * DH, tmem + COL_S + t * BN + 8 * k, smem_desc_sw128(va + 2048 * k, 0),
+                            IDESC_O, acc || k > 0);
+            };
+            const int last0 = n0, last1 = n0 + 1;  // last KV tile of each query tile
+            mbar_wait(&q_full, 0, guard, 201);
+            mbar_wait(&k_full[0], 0, guard, 202);
+            tc_fence_after();
+            issue_s(0, 0);
+            if (has_t1) issue_s(1, 0);
+            for (int j = 0; j < nkv; j++) {
+                const int s = j % STAGES, sn = (j + 1) % STAGES;
+                mbar_wait(&v_full[s], (j / STAGES) & 1, guard, 203);
+                if (j <= last0) {
+                    mbar_wait(&p_full[0], j & 1, guard, 204);
+                    tc_fence_after();
+                    issue_pv(0, s, j > 0);
+                    if (j == last0) umma_commit(&o_done[0]);
+                }
+                if (j + 1 < nkv) {
+                    mbar_wait(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
+                    tc_fence_after();
+                    if (j + 1 <= last0) issue_s(0, sn);
+                }
+                if (has_t1) {
+                    mbar_wait(&p_full[1], j & 1, guard, 206);
+                    tc_fence_after();
+                    issue_pv(1, s, j > 0);
+                    if (j == last1) umma_commit(&o_done[1]);
+                }
+                umma_commit(&kv_empty[s]);
+                if (j + 1 < nkv && has_t1) issue_s(1, sn);
+            }
+        }
+    } else {
+        // ---------------- softmax groups ----------------
+        const int t = warp / 4;
+        const int r = (warp % 4) * 32 + lane;  // row inside the tile == TMEM lane
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
+        const uint32_t tS = lane_base + COL_S + t * BN;
+        const uint32_t tO = lane_base + COL_O + t * DH;
+        const int jlast = n0 + t;
+        const bool active = t == 0 || has_t1;
+        float m = -INFINITY, l = 0.f;
+        if (active) {
+            for (int j = 0; j <= jlast; j++) {
+                mbar_wait(&s_full[t], j & 1, guard, 301 + t);
+                tc_fence_after();
+                // pass 1: row maximum (the diagonal tile is masked: key column c is visible iff c <= r)
+                float mx = -INFINITY;
+                const bool diag = j == jlast;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(tS + 64 * c, v0);
+                    tmem_ld32(tS + 64 * c + 32, v1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const float a = (!diag || 64 * c + i <= r) ? __uint_as_float(v0[i]) : -INFINITY;
+                        const float bb = (!diag || 64 * c + 32 + i <= r) ? __uint_as_float(v1[i]) : -INFINITY;
+                        mx = fmaxf(mx, fmaxf(a, bb));
+                    }
+                }
+                const float m_new = fmaxf(m, mx * p.scale_log2);
+                const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
+                const float m_use = raise ? m_new : m;
+                const float alpha = raise ? ex2(m - m_new) : 1.0f;
+                if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                    // S_t(j) completing implies PV_t(j-1) has completed: O_t is stable here.
+                    uint32_t o0[32], o1[32];
+                    tmem_ld32(tO, o0);
+                    tmem_ld32(tO + 32, o1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+                        o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+                    }
+                    tmem_st32(tO, o0);
+                    tmem_st32(tO + 32, o1);
+                    tmem_st_wait();
+                }
+                m = m_use;
+                // pass 2: P = exp2(c*S - m) as bf16 pairs; chunk c of P (64 values, 32 columns) only
+                // overwrites S columns that have already been consumed.
+                float rs = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    uint32_t v0[32], v1[32], pk[32];
+                    tmem_ld32(tS + 64 * c, v0);
+                    tmem_ld32(tS + 64 * c + 32, v1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float a0 = ex2(fmaf(__uint_as_float(v0[i]), p.scale_log2, -m_use));
+                        float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), p.scale_log2, -m_use));
+                        float b0 = ex2(fmaf(__uint_as_float(v1[i]), p.scale_log2, -m_use));
+                        float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), p.scale_log2, -m_use));
+                        if (diag) {
+                            a0 = 64 * c + i <= r ? a0 : 0.f;
+                            a1 = 64 * c + i + 1 <= r ? a1 : 0.f;
+                            b0 = 64 * c + 32 + i <= r ? b0 : 0.f;
+                            b1 = 64 * c + 32 + i + 1 <= r ? b1 : 0.f;
+                        }
+                        rs += (a0 + a1) + (b0 + b1);
+                        pk[i / 2] = pack_bf16(a0, a1);
+                        pk[16 + i / 2] = pack_bf16(b0, b1);
+                    }
+                    tmem_st32(tS + 32 * c, pk);
+                }
+                l = l * alpha + rs;
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&p_full[t]);
+            }
+            // epilogue: O_t / l -> bf16 -> global; lse
+            mbar_wait(&o_done[t], 0, guard, 311 + t);
+            tc_fence_after();
+            const int qr = q0 + t * BM + r;
+            const float inv = 1.0f / l;
+            uint32_t o[2][32];
+            tmem_ld32(tO, o[0]);
+            tmem_ld32(tO + 32, o[1]);
+            tmem_ld_wait();
+            if (qr < p.S) {
+                uint4* dst = reinterpret_cast<uint4*>(p.O + (int64_t)b * p.sb + (int64_t)qr * p.ss + (int64_t)h * p.sh);
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(__uint_as_float(o[c][i + 0]) * inv, __uint_as_float(o[c][i + 1]) * inv);
+                        v.y = pack_bf16(__uint_as_float(o[c][i + 2]) * inv, __uint_as_float(o[c][i + 3]) * inv);
+                        v.z = pack_bf16(__uint_as_float(o[c][i + 4]) * inv, __uint_as_float(o[c][i + 5]) * inv);
+                        v.w = pack_bf16(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
+                        dst[(c * 32 + i) / 8] = v;
+                    }
+                if (p.lse != nullptr) p.lse[(int64_t)bh * p.S + qr] = (m + log2f(l)) * 0.6931471805599453f;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+bool mha_tc_supported(const MhaShape& p) {
+    return p.Dh == DH && p.sh % 8 == 0 && p.ss % 8 == 0 && p.sb % 8 == 0;
+}
+
+int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, void* O, float* lse,
+               cudaStream_t st) {
+    if (!mha_tc_supported(p)) return CXXATTN_ERR_UNSUPPORTED;
+    for (const void* q : {Q, K, V, (const void*)O})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    CUtensorMap tmQ, tmK, tmV;
+    if (!make_tmap_bhsd(&tmQ, Q, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BM) ||
+        !make_tmap_bhsd(&tmK, K, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BN) ||
+        !make_tmap_bhsd(&tmV, V, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BN))
+        return CXXATTN_ERR_CUDA;
+    FwdParams fp;
+    fp.O = static_cast<__nv_bfloat16*>(O);
+    fp.lse = lse;
+    fp.status = status_word();
+    if (fp.status == nullptr) return CXXATTN_ERR_CUDA;
+    fp.B = p.B; fp.S = p.S; fp.H = p.H;
+    fp.sb = p.sb; fp.ss = p.ss; fp.sh = p.sh;
+    fp.scale_log2 = p.scale * 1.4426950408889634f;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(mha_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
+            cudaSuccess)
+            return CXXATTN_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
+    const int64_t grid = (int64_t)npairs * p.B * p.H;
+    mha_tc_fwd_kernel<<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
+    return check_launch();
+}
+
+}  // namespace cxxattn

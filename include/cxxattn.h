@@ -156,6 +156,18 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
  * gelu_exact_deriv (ts.cuh:84-85, ts.cu:1888-1924). */
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream);
 
+/* ---- status and diagnostics (no reference counterpart) ------------------------------------- */
+
+/* Synchronises `stream`, then reports whether any tensor-core kernel launched so far on the
+ * current device gave up a bounded device-side wait (CXXATTN_ERR_TIMEOUT, and the flag is
+ * cleared) or not (CXXATTN_OK).  Results of a launch that timed out are undefined. */
+int cxxattn_sync_status(cxxattn_stream_t stream);
+
+/* One-tile check of the tcgen05 operand conventions (bf16 device buffers, float result):
+ *   mode 0: D[128x128] = A[128x64] B[128x64]^T;  mode 1: D[128x64] = A[128x128] B[128x64];
+ *   mode 2: D[128x64]  = A[128x128]^T B[128x64]. */
+int cxxattn_selftest_umma(int mode, const void* A, const void* B, float* D, cxxattn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import KT_BLOCKS, kt_block_inputs, rel_err, seeded_normal
+from conftest import KT_BLOCKS, assert_parity, kt_block_inputs, rel_err, seeded_normal
 
 pytestmark = pytest.mark.gpu
 TOL_F32 = 1e-5
@@ -28,9 +28,16 @@ def check_mha(pkg, dev, orc, Q, K, V, dO, B, S, H, Dh, use_lse=False, tol=TOL_F3
     rO = orc.mha_fwd(Q, K, V, B, S, H, Dh)
     # the reference backward consumes the stored O of the forward under test (kernel_test.cpp:246)
     rdQ, rdK, rdV = orc.mha_bwd(Q, K, V, O, dO, B, S, H, Dh)
+    cache = {}
+
+    def f64(k):
+        if not cache:
+            cache["O"] = orc.mha_fwd(Q, K, V, B, S, H, Dh, f64=True)
+            cache["dQ"], cache["dK"], cache["dV"] = orc.mha_bwd(Q, K, V, O, dO, B, S, H, Dh, f64=True)
+        return cache[k]
     for name, a, b in (("O", O, rO), ("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
         assert np.all(np.isfinite(a)), name
-        assert rel_err(a, b) < tol, (name, rel_err(a, b))
+        assert_parity(name, a, b, lambda name=name: f64(name), tol=tol, floor=1e-3)
     if use_lse:
         _, rl = orc.mha_fwd(Q, K, V, B, S, H, Dh, f64=True, want_lse=True)
         assert np.abs(lse - rl).max() < 1e-4
@@ -80,10 +87,12 @@ def test_lse_reuse_matches_recompute(pkg, dev, orc):
 
 
 def test_large_inputs_do_not_overflow(pkg, dev, orc):
-    """Scores of magnitude ~1e3: the running-max form must stay finite."""
+    """Scores of magnitude ~1e3: the running-max form must stay finite.  An fp32 score of that size
+    carries ~1e-4 absolute rounding, so the fp32 oracle is itself ~1e-4 from the exact softmax; the
+    fp64 oracle adjudicates (see assert_parity)."""
     B, S, H, Dh = 1, 96, 1, 32
     Q, K, V, dO = seeded_normal(22, [(B * S, H * Dh)] * 4)
-    check_mha(pkg, dev, orc, Q * 30, K * 30, V, dO, B, S, H, Dh, tol=5e-5)
+    check_mha(pkg, dev, orc, Q * 30, K * 30, V, dO, B, S, H, Dh)
 
 
 def test_strided_heads_in_place(pkg, dev, orc):

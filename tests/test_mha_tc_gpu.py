@@ -1,0 +1,75 @@
+"""GPU parity of the tcgen05 (bf16) softmax MHA kernels against the CPU oracle, through the C-ABI.
+Inputs are generated in fp32, rounded to bf16, and the SAME rounded values are given to the oracle
+(double accumulation).  Tolerance for the bf16 tensor-core path: 2e-2 as max|a-b| / max|b|."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL_BF16 = 2e-2
+
+
+def test_umma_operand_conventions(pkg, dev):
+    """Single-tile products that pin the shared-memory / tensor-memory operand layouts the attention
+    kernels assume (K-major x K-major, TMEM x MN-major, MN-major x MN-major)."""
+    g = torch.Generator().manual_seed(1)
+    A64 = torch.randn(128, 64, generator=g).bfloat16()
+    A128 = torch.randn(128, 128, generator=g).bfloat16()
+    B = torch.randn(128, 64, generator=g).bfloat16()
+    cases = [(0, A64, (128, 128), A64.float() @ B.float().T),
+             (1, A128, (128, 64), A128.float() @ B.float()),
+             (2, A128, (128, 64), A128.float().T @ B.float())]
+    for mode, A, shape, want in cases:
+        D = torch.full(shape, float("nan"), device=dev)
+        pkg.selftest_umma(mode, A.to(dev), B.to(dev), D)
+        pkg.sync_status()
+        err = rel_err(D.cpu().numpy(), want.numpy())
+        assert err < 1e-5, (mode, err)
+
+
+def bf16_inputs(seed, B, S, H, Dh, n=4, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(B * S, H * Dh, generator=g) * scale).bfloat16() for _ in range(n)]
+
+
+def run_fwd(pkg, dev, Q, K, V, B, S, H, Dh):
+    tq, tk, tv = (x.to(dev) for x in (Q, K, V))
+    O = torch.full_like(tq, float("nan"))
+    lse = torch.full((B * H * S,), float("nan"), device=dev)
+    pkg.mha_fwd(tq, tk, tv, O, B, S, H, Dh, lse=lse)
+    pkg.sync_status()
+    return O, lse
+
+
+@pytest.mark.parametrize("B,S,H,Dh", [(1, 128, 1, 64), (1, 256, 1, 64), (2, 512, 3, 64), (1, 384, 2, 64),
+                                      (2, 1024, 2, 64), (1, 200, 2, 64), (1, 77, 1, 64), (1, 2048, 1, 64)])
+def test_forward_matches_oracle(pkg, dev, orc, B, S, H, Dh):
+    Q, K, V = bf16_inputs(7 + S, B, S, H, Dh, n=3)
+    O, lse = run_fwd(pkg, dev, Q, K, V, B, S, H, Dh)
+    rO, rl = orc.mha_fwd(Q.float().numpy(), K.float().numpy(), V.float().numpy(), B, S, H, Dh,
+                         f64=True, want_lse=True)
+    got = O.float().cpu().numpy()
+    assert np.all(np.isfinite(got))
+    assert rel_err(got, rO) < TOL_BF16, rel_err(got, rO)
+    assert np.abs(lse.cpu().numpy() - rl).max() < 2e-2
+
+
+def test_forward_long_sequence_properties(pkg, dev, orc):
+    """S=4096 with 12 heads of 64 (the long-sequence shape): causality (bit-identical prefix when
+    later keys/values change) and parity on one (batch, head) slice."""
+    B, S, H, Dh = 1, 4096, 12, 64
+    Q, K, V = bf16_inputs(3, B, S, H, Dh, n=3)
+    O1, _ = run_fwd(pkg, dev, Q, K, V, B, S, H, Dh)
+    cut = 3000
+    K2, V2 = K.clone(), V.clone()
+    K2[cut:] = -K2[cut:]
+    V2[cut:] = V2[cut:] + 1
+    O2, _ = run_fwd(pkg, dev, Q, K2, V2, B, S, H, Dh)
+    assert torch.equal(O1[:cut], O2[:cut]) and not torch.equal(O1[cut:], O2[cut:])
+    h = 5
+    sl = slice(h * Dh, (h + 1) * Dh)
+    rO = orc.mha_fwd(Q[:, sl].float().numpy(), K[:, sl].float().numpy(), V[:, sl].float().numpy(),
+                     1, S, 1, Dh, f64=True)
+    assert rel_err(O1[:, sl].float().cpu().numpy(), rO) < TOL_BF16
