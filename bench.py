@@ -1,0 +1,268 @@
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one forward + backward pass of causal softmax attention over one batch of synthetic
+bf16 inputs (the long-sequence configuration: 12 heads x 64, B*S = 65536 tokens, S = 4096 by
+default).  With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the
+same per-GPU workload on its own shard of (batch, head) units; nothing is exchanged between
+ranks (weak scaling), the timed region is bracketed by barriers and the slowest rank counts.
+
+One JSON line is printed by rank 0.  `value` is device-resident throughput (CUDA events),
+`e2e` the same metric through the host-buffer entry point with the copies inside the timed
+region, `roofline` the tensor-pipe roofline of the dominant kernel (the backward main kernel),
+`cpu_baseline` the CPU oracle timed on a bounded sample of the same workload.
+
+--impl reference times the reference's CPU implementation of the path (the oracle port) on the
+host cores, on a bounded sample of the same workload, and prints the same line shape.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, DH = 12, 64
+WORKLOADS = {  # name -> (B, S): B*S = 65536 tokens
+    "softmax_s1024": (64, 1024),
+    "softmax_s4096": (16, 4096),
+    "softmax_s16384": (4, 16384),
+}
+METRIC = "causal_softmax_attn_fwd_bwd_tflops_per_job"
+UNIT = "TFLOP/s"
+
+
+def flops_fwd_bwd(B, S):
+    """FlashAttention convention, causal = half: forward 2*B*H*S^2*Dh, backward 2.5x."""
+    return 7.0 * B * H * S * S * DH
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.samples, self.reasons, self.max_mhz = index, False, [], set(), None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+            while not self.stop_flag:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.02)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add("nvml_unavailable:" + type(e).__name__)
+
+    def result(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def cpu_sample(B, S, threads=None, units=None):
+    """Times the CPU oracle (fp32, the reference's operation order) on `units` (batch, head) units
+    of the workload, one per host thread by default.  Returns (TFLOP/s, cores, description)."""
+    import numpy as np
+    import oracle
+    orc = oracle.Oracle()
+    cores = threads or orc.num_threads()
+    orc.set_threads(cores)
+    units = units or cores
+    rng = np.random.default_rng(3)
+    Q, K, V, dO = (rng.standard_normal((units * S, DH)).astype(np.float32) for _ in range(4))
+    t0 = time.perf_counter()
+    O = orc.mha_fwd(Q, K, V, units, S, 1, DH)
+    orc.mha_bwd(Q, K, V, O, dO, units, S, 1, DH)
+    dt = time.perf_counter() - t0
+    tf = 7.0 * units * S * S * DH / dt / 1e12
+    return tf, cores, dt, f"{units} of {B * H} (batch, head) units of S={S}, Dh={DH}, fp32 oracle, fwd+bwd"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, S = WORKLOADS[args.workload]
+    # bounded sample: one unit per core and step; S=16384 units are cut to keep a step in seconds
+    s_eff = min(S, 4096)
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(B, min(S, 512))
+    vals, times = [], []
+    desc, cores = "", 1
+    for _ in range(args.steps):
+        tf, cores, dt, desc = cpu_sample(B, s_eff)
+        vals.append(tf)
+        times.append(dt)
+    value = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "gpu_launches": 0,
+            "config": {"workload": args.workload, "B": B, "S": S, "H": H, "Dh": DH,
+                       "note": "CPU oracle port of the reference math on host cores; each step is a bounded sample"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    pkg = g.load_package()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path in the product")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, S = WORKLOADS[args.workload]
+    N = B * S
+    gen = torch.Generator(device="cpu").manual_seed(3 + rank)
+    hQ, hK, hV, hdO = (torch.randn(N, H * DH, generator=gen).bfloat16().pin_memory() for _ in range(4))
+    hO, hdQ, hdK, hdV = (torch.empty(N, H * DH, dtype=torch.bfloat16).pin_memory() for _ in range(4))
+    Q, K, V, dO = (t.to(dev) for t in (hQ, hK, hV, hdO))
+    O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
+    lse = torch.empty(B * H * S, device=dev)
+
+    def step():
+        pkg.mha_fwd(Q, K, V, O, B, S, H, DH, lse=lse)
+        pkg.mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, DH, lse=lse)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    pkg.sync_status()
+
+    # ---- device-resident timing: K steps between two events on the launching stream ----
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    sampler.stop_flag = True
+    ms = e0.elapsed_time(e1) / args.steps
+    pkg.sync_status()
+
+    # ---- per-kernel split (forward call, backward call) for the roofline ----
+    ef = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    fwd_ms = bwd_ms = 0.0
+    reps = max(3, min(args.steps, 10))
+    for _ in range(reps):
+        ef[0].record()
+        pkg.mha_fwd(Q, K, V, O, B, S, H, DH, lse=lse)
+        ef[1].record()
+        pkg.mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, DH, lse=lse)
+        ef[2].record()
+        torch.cuda.synchronize()
+        fwd_ms += ef[0].elapsed_time(ef[1]) / reps
+        bwd_ms += ef[1].elapsed_time(ef[2]) / reps
+
+    # ---- end to end: host buffers in, host buffers out, through the C-ABI host entry point ----
+    plan = pkg.HostPlan(B, S, H, DH, pkg.BF16, max(1, B // 8))
+    for _ in range(2):
+        plan.fwd_bwd(hQ, hK, hV, hdO, hO, hdQ, hdK, hdV)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(e2e_steps):
+        plan.fwd_bwd(hQ, hK, hV, hdO, hO, hdQ, hdK, hdV)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    plan.close()
+    pkg.sync_status()
+    # the end-to-end results must be the same numbers as the device-resident path
+    assert torch.equal(hO, O.cpu()), "host entry point and device path disagree"
+
+    t = torch.tensor([ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, fwd_ms, bwd_ms = t.tolist()
+
+    if rank == 0:
+        fl = flops_fwd_bwd(B, S)
+        peak, peak_sustained, how = measured_peaks()
+        bwd_tf = fl * (2.5 / 3.5) / (bwd_ms * 1e-3) / 1e12
+        nbytes = 4 * N * H * DH * 2
+        line = {"metric": METRIC, "value": world * fl / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, "B_per_gpu": B, "S": S, "H": H, "Dh": DH,
+                           "tokens_per_gpu": N, "sharding": "(batch, head) units per rank, no collective",
+                           "l2": "inputs+outputs 8 x %.0f MB per step exceed the 126 MB L2" % (N * H * DH * 2 / 1e6)},
+                "tokens_per_s": world * N / (ms * 1e-3),
+                "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                "fwd_tflops": fl / 3.5 / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": bwd_tf,
+                "frac_of_peak_fwd_bwd": fl / (ms * 1e-3) / 1e12 / peak,
+                "gpu_launches": args.steps * 4,
+                "clocks": sampler.result(),
+                "e2e": {"value": world * fl / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+                "roofline": {"bound": "tensor", "kernel": "mha_tc_bwd (pre + main + post launches)",
+                             "achieved": bwd_tf, "peak": peak, "peak_sustained": peak_sustained,
+                             "peak_source": how, "unit": UNIT, "frac": bwd_tf / peak, "traffic": None}}
+        if world == 1 and not args.no_cpu_baseline:
+            tf, cores, dt, desc = cpu_sample(B, min(S, 4096))
+            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": desc + " (%.1f s)" % dt}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = min(args.steps, 3)
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

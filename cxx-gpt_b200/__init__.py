@@ -23,6 +23,7 @@ SYMBOLS = [
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
     "cxxattn_sync_status", "cxxattn_selftest_umma",
+    "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
 ]
 
 
@@ -75,6 +76,10 @@ def lib():
         L.cxxattn_rope.argtypes = [vp, vp, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
         L.cxxattn_sync_status.argtypes = [vp]
+        L.cxxattn_host_plan_create.argtypes = [C.POINTER(vp), C.POINTER(MhaDesc), i32]
+        L.cxxattn_host_plan_destroy.argtypes = [vp]
+        L.cxxattn_host_plan_destroy.restype = None
+        L.cxxattn_mha_fwd_bwd_host.argtypes = [vp] * 9
         L.cxxattn_selftest_umma.argtypes = [i32, vp, vp, vp, vp]
         _lib = L
     return _lib
@@ -199,6 +204,32 @@ def linattn_bwd(Q, K, V, O, dO, den, dQ, dK, dV, B, S, D, E, feature_map, eps_in
     check(lib().cxxattn_linattn_bwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(den),
                                     _ptr(dQ), _ptr(dK), _ptr(dV), ws.data_ptr(), ws.numel(), _stream()),
           "cxxattn_linattn_bwd")
+
+
+class HostPlan:
+    """Owner of the device staging buffers behind cxxattn_mha_fwd_bwd_host (host tensors in,
+    host tensors out; torch CPU tensors, ideally pinned)."""
+
+    def __init__(self, B, S, H, Dh, dtype, batch_per_chunk):
+        self.handle = C.c_void_p()
+        d = mha_desc(B, S, H, Dh, dtype)
+        check(lib().cxxattn_host_plan_create(C.byref(self.handle), C.byref(d), batch_per_chunk),
+              "cxxattn_host_plan_create")
+
+    def fwd_bwd(self, Q, K, V, dO, O, dQ, dK, dV):
+        ptrs = [t.data_ptr() for t in (Q, K, V, dO, O, dQ, dK, dV)]
+        check(lib().cxxattn_mha_fwd_bwd_host(self.handle, *ptrs), "cxxattn_mha_fwd_bwd_host")
+
+    def close(self):
+        if self.handle:
+            lib().cxxattn_host_plan_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def sync_status():

@@ -1,0 +1,151 @@
+// Adapter: CXX-GPT's C++ kernel entry points on top of the C-ABI of libcxxattn.so.
+//
+// Semantics kept from the reference wrappers (two_stage_cuda_kernels.cu:285-326, 830-882, 1133-1185,
+// 1235-1248, 1408-1453, 1743-1809, 1859-1924; linear_cuda_kernels.cu:81-99, 136-150, 199-215,
+// 275-298, 327-378): launches go to the legacy default stream without synchronising, outputs are
+// overwritten, temporary scratch is owned by the callee, and a failure throws std::runtime_error
+// (what CHECK_CUDA_ERROR does there).  Unlike the reference, Dh > 256 throws instead of aborting.
+// The S_buf / z_buf arguments are accepted and left untouched: the chunked scan keeps its states
+// in the adapter's scratch.
+#include "cxxgpt_kernels.hpp"
+#include "cxxattn.h"
+
+namespace {
+
+void ok(int rc, const char* what) {
+    if (rc != CXXATTN_OK) throw std::runtime_error(std::string(what) + ": " + cxxattn_strerror(rc));
+}
+
+// Per-device scratch that only grows; freed at process exit by the driver.
+void* scratch(size_t bytes) {
+    static void* buf[64] = {};
+    static size_t cap[64] = {};
+    int dev = 0;
+    CHECK_CUDA_ERROR(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) throw std::runtime_error("device index out of range");
+    if (cap[dev] < bytes) {
+        if (buf[dev]) {
+            CHECK_CUDA_ERROR(cudaDeviceSynchronize());
+            CHECK_CUDA_ERROR(cudaFree(buf[dev]));
+        }
+        CHECK_CUDA_ERROR(cudaMalloc(&buf[dev], bytes));
+        cap[dev] = bytes;
+    }
+    return buf[dev];
+}
+
+cxxattn_mha_desc mha(size_t B, size_t S, size_t H, size_t Dh) {
+    cxxattn_mha_desc d = {};
+    d.B = (int64_t)B; d.S = (int64_t)S; d.H = (int64_t)H; d.Dh = (int64_t)Dh;
+    d.dtype = CXXATTN_F32;
+    return d;
+}
+
+cxxattn_lin_desc lin(size_t B, size_t S, size_t D, size_t E, int map, int eps_in_den) {
+    cxxattn_lin_desc d = {};
+    d.B = (int64_t)B; d.S = (int64_t)S; d.D = (int64_t)D; d.E = (int64_t)E;
+    d.dtype = CXXATTN_F32;
+    d.feature_map = map;
+    d.eps_in_den = eps_in_den;
+    return d;
+}
+
+void lin_fwd(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V, float* O, float* den,
+             float* zc) {
+    const size_t n = cxxattn_linattn_workspace_bytes(&d);
+    ok(cxxattn_linattn_fwd(&d, Q, K, V, O, den, zc, scratch(n), n, nullptr), "cxxattn_linattn_fwd");
+}
+void lin_dq(const cxxattn_lin_desc& d, const float* K, const float* V, const float* dnum, const float* dden,
+            const float* zc, const float* Q, float* dQ) {
+    const size_t n = cxxattn_linattn_workspace_bytes(&d);
+    ok(cxxattn_linattn_bwd_dq(&d, K, V, dnum, dden, zc, Q, dQ, scratch(n), n, nullptr), "cxxattn_linattn_bwd_dq");
+}
+void lin_dkdv(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V, const float* dnum,
+              const float* dden, float* dK, float* dV) {
+    const size_t n = cxxattn_linattn_workspace_bytes(&d);
+    ok(cxxattn_linattn_bwd_dkdv(&d, Q, K, V, dnum, dden, dK, dV, scratch(n), n, nullptr), "cxxattn_linattn_bwd_dkdv");
+}
+
+}  // namespace
+
+namespace two_stage_cuda {
+
+void fused_mha_fwd(In Q, In K, In V, Out O, size_t B, size_t S, size_t H, size_t Dh) {
+    const cxxattn_mha_desc d = mha(B, S, H, Dh);
+    ok(cxxattn_mha_fwd(&d, Q.device_ptr(), K.device_ptr(), V.device_ptr(), O.device_ptr(), nullptr, nullptr),
+       "cxxattn_mha_fwd");
+}
+
+void fused_mha_bwd(In Q, In K, In V, In O, In dO, Out dQ, Out dK, Out dV, size_t B, size_t S, size_t H, size_t Dh) {
+    const cxxattn_mha_desc d = mha(B, S, H, Dh);
+    const size_t n = cxxattn_mha_bwd_workspace_bytes(&d, 0);
+    ok(cxxattn_mha_bwd(&d, Q.device_ptr(), K.device_ptr(), V.device_ptr(), O.device_ptr(), dO.device_ptr(), nullptr,
+                       dQ.device_ptr(), dK.device_ptr(), dV.device_ptr(), scratch(n), n, nullptr),
+       "cxxattn_mha_bwd");
+}
+
+void kernel_attn_fwd(In Q, In K, In V, Out O, Out den_cache, Out z_cache, Out, Out, size_t B, size_t S, size_t D,
+                     size_t E) {
+    lin_fwd(lin(B, S, D, E, CXXATTN_MAP_ELU1, 0), Q.device_ptr(), K.device_ptr(), V.device_ptr(), O.device_ptr(),
+            den_cache.device_ptr(), z_cache.device_ptr());
+}
+
+void kernel_attn_bwd_step1(In O, In dO, In den_cache, Out dnum, Out dden, size_t N, size_t E) {
+    ok(cxxattn_linattn_bwd_step1(O.device_ptr(), dO.device_ptr(), den_cache.device_ptr(), dnum.device_ptr(),
+                                 dden.device_ptr(), N, E, nullptr),
+       "cxxattn_linattn_bwd_step1");
+}
+
+void kernel_attn_bwd_dQ(In K, In V, In dnum, In dden, In z_cache, In Q, Out dQ, Out, size_t B, size_t S, size_t D,
+                        size_t E) {
+    lin_dq(lin(B, S, D, E, CXXATTN_MAP_ELU1, 0), K.device_ptr(), V.device_ptr(), dnum.device_ptr(), dden.device_ptr(),
+           z_cache.device_ptr(), Q.device_ptr(), dQ.device_ptr());
+}
+
+void kernel_attn_bwd_dKdV(In Q, In K, In V, In dnum, In dden, Out dK, Out dV, size_t B, size_t S, size_t D, size_t E) {
+    lin_dkdv(lin(B, S, D, E, CXXATTN_MAP_ELU1, 0), Q.device_ptr(), K.device_ptr(), V.device_ptr(), dnum.device_ptr(),
+             dden.device_ptr(), dK.device_ptr(), dV.device_ptr());
+}
+
+void rope_fwd(Out Q, Out K, size_t B, size_t S, size_t D, size_t head_dim) {
+    ok(cxxattn_rope(Q.device_ptr(), K.device_ptr(), B, S, D, head_dim, 1.0f, nullptr), "cxxattn_rope");
+}
+void rope_bwd(Out dQ, Out dK, size_t B, size_t S, size_t D, size_t head_dim) {
+    ok(cxxattn_rope(dQ.device_ptr(), dK.device_ptr(), B, S, D, head_dim, -1.0f, nullptr), "cxxattn_rope");
+}
+void gelu_exact(In A, Out C) { ok(cxxattn_gelu_exact(A.device_ptr(), C.device_ptr(), A.size(), 0, nullptr), "cxxattn_gelu_exact"); }
+void gelu_exact_deriv(In A, Out C) { ok(cxxattn_gelu_exact(A.device_ptr(), C.device_ptr(), A.size(), 1, nullptr), "cxxattn_gelu_exact"); }
+
+}  // namespace two_stage_cuda
+
+namespace linear_cuda {
+
+void causal_linear_attention_fwd(In Q_phi, In K_phi, In V, Out O, Out den_cache, Out z_cache, Out, Out, size_t B,
+                                 size_t S, size_t D, size_t E) {
+    lin_fwd(lin(B, S, D, E, CXXATTN_MAP_NONE, 1), Q_phi.device_ptr(), K_phi.device_ptr(), V.device_ptr(),
+            O.device_ptr(), den_cache.device_ptr(), z_cache.device_ptr());
+}
+void causal_linear_attention_bwd_step1(In O, In dO, In den_cache, Out dnum, Out dden, size_t N, size_t E) {
+    ok(cxxattn_linattn_bwd_step1(O.device_ptr(), dO.device_ptr(), den_cache.device_ptr(), dnum.device_ptr(),
+                                 dden.device_ptr(), N, E, nullptr),
+       "cxxattn_linattn_bwd_step1");
+}
+void causal_linear_attention_bwd_dQ(In K_phi, In V, In dnum, In dden, In z_cache, Out dQ_phi, Out, size_t B, size_t S,
+                                    size_t D, size_t E) {
+    lin_dq(lin(B, S, D, E, CXXATTN_MAP_NONE, 1), K_phi.device_ptr(), V.device_ptr(), dnum.device_ptr(),
+           dden.device_ptr(), z_cache.device_ptr(), nullptr, dQ_phi.device_ptr());
+}
+void causal_linear_attention_bwd_dKdV(In Q_phi, In K_phi, In V, In dnum, In dden, Out dK_phi, Out dV, size_t B,
+                                      size_t S, size_t D, size_t E) {
+    lin_dkdv(lin(B, S, D, E, CXXATTN_MAP_NONE, 1), Q_phi.device_ptr(), K_phi.device_ptr(), V.device_ptr(),
+             dnum.device_ptr(), dden.device_ptr(), dK_phi.device_ptr(), dV.device_ptr());
+}
+void phi_elu_forward(In x, Out phi, size_t D, size_t E) {
+    ok(cxxattn_phi_elu_fwd(x.device_ptr(), phi.device_ptr(), x.shape()[0], D, E, nullptr), "cxxattn_phi_elu_fwd");
+}
+void phi_elu_backward(In dphi, In x, Out dx, size_t D, size_t E) {
+    ok(cxxattn_phi_elu_bwd(dphi.device_ptr(), x.device_ptr(), dx.device_ptr(), dphi.shape()[0], D, E, nullptr),
+       "cxxattn_phi_elu_bwd");
+}
+
+}  // namespace linear_cuda

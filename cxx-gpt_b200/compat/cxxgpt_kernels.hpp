@@ -1,0 +1,40 @@
+// The C++ kernel entry points that CXX-GPT's models call, declared with the signatures of
+// src/TwoStage/two_stage_cuda_kernels.cuh:18-85 and src/LinearAttention/linear_cuda_kernels.cuh:11-46
+// and implemented in cxxgpt_kernels.cpp on top of the C-ABI of libcxxattn.so.  A CXX-GPT build keeps
+// its own two headers and links cxxgpt_kernels.cpp + libcxxattn.so instead of its two .cu files;
+// this header exists so that the adapter also compiles without the CXX-GPT tree.
+#pragma once
+#include "TensorN.hpp"
+
+namespace two_stage_cuda {
+using TensorN::CudaTensor;
+typedef const CudaTensor<float>& In;
+typedef CudaTensor<float>& Out;
+void fused_mha_fwd(In Q, In K, In V, Out O, size_t B, size_t S, size_t H, size_t Dh);
+void fused_mha_bwd(In Q, In K, In V, In O, In dO, Out dQ, Out dK, Out dV, size_t B, size_t S, size_t H, size_t Dh);
+void kernel_attn_fwd(In Q, In K, In V, Out O, Out den_cache, Out z_cache, Out S_buf, Out z_buf,
+                     size_t B, size_t S, size_t D, size_t E);
+void kernel_attn_bwd_step1(In O, In dO, In den_cache, Out dnum, Out dden, size_t N, size_t E);
+void kernel_attn_bwd_dQ(In K, In V, In dnum, In dden, In z_cache, In Q, Out dQ, Out S_buf,
+                        size_t B, size_t S, size_t D, size_t E);
+void kernel_attn_bwd_dKdV(In Q, In K, In V, In dnum, In dden, Out dK, Out dV, size_t B, size_t S, size_t D, size_t E);
+void rope_fwd(Out Q, Out K, size_t B, size_t S, size_t D, size_t head_dim);
+void rope_bwd(Out dQ, Out dK, size_t B, size_t S, size_t D, size_t head_dim);
+void gelu_exact(In A, Out C);
+void gelu_exact_deriv(In A, Out C);
+}  // namespace two_stage_cuda
+
+namespace linear_cuda {
+using TensorN::CudaTensor;
+typedef const CudaTensor<float>& In;
+typedef CudaTensor<float>& Out;
+void causal_linear_attention_fwd(In Q_phi, In K_phi, In V, Out O, Out den_cache, Out z_cache, Out S_buf, Out z_buf,
+                                 size_t B, size_t S, size_t D, size_t E);
+void causal_linear_attention_bwd_step1(In O, In dO, In den_cache, Out dnum, Out dden, size_t N, size_t E);
+void causal_linear_attention_bwd_dQ(In K_phi, In V, In dnum, In dden, In z_cache, Out dQ_phi, Out S_buf,
+                                    size_t B, size_t S, size_t D, size_t E);
+void causal_linear_attention_bwd_dKdV(In Q_phi, In K_phi, In V, In dnum, In dden, Out dK_phi, Out dV,
+                                      size_t B, size_t S, size_t D, size_t E);
+void phi_elu_forward(In x, Out phi, size_t D, size_t E);
+void phi_elu_backward(In dphi, In x, Out dx, size_t D, size_t E);
+}  // namespace linear_cuda

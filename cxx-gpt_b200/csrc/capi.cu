@@ -64,6 +64,7 @@ size_t cxxattn_mha_bwd_workspace_bytes(const cxxattn_mha_desc* desc, int have_ls
     MhaShape p;
     if (!resolve(desc, &p)) return 0;
     if (desc->dtype == CXXATTN_F32) return mha_f32_bwd_workspace(p, have_lse != 0);
+    if (desc->dtype == CXXATTN_BF16 && mha_tc_supported(p)) return mha_tc_bwd_workspace(p, have_lse != 0);
     return 0;
 }
 
@@ -77,7 +78,9 @@ int cxxattn_mha_bwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, 
         return mha_f32_bwd(p, (const float*)Q, (const float*)K, (const float*)V, (const float*)O,
                            (const float*)dO, lse, (float*)dQ, (float*)dK, (float*)dV,
                            workspace, workspace_bytes, st);
-    return CXXATTN_ERR_UNSUPPORTED;
+    if (desc->dtype == CXXATTN_BF16)
+        return mha_tc_bwd(p, Q, K, V, O, dO, lse, dQ, dK, dV, workspace, workspace_bytes, st);
+    return CXXATTN_ERR_INVALID;
 }
 
 size_t cxxattn_linattn_workspace_bytes(const cxxattn_lin_desc* desc) {

@@ -33,6 +33,9 @@ int mha_f32_bwd(const MhaShape& p, const float* Q, const float* K, const float* 
 bool mha_tc_supported(const MhaShape& p);
 int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, void* O, float* lse,
                cudaStream_t st);
+size_t mha_tc_bwd_workspace(const MhaShape& p, bool have_lse);
+int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, const void* O, const void* dO,
+               const float* lse, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes, cudaStream_t st);
 
 // ---- diagnostics (umma_selftest.cu) ----
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);

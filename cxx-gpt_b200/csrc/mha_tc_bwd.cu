@@ -1,0 +1,443 @@
+// Causal softmax MHA backward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), bf16
+// operands, fp32 accumulation, head dimension 64.
+//
+// Replaces two_stage_cuda::fused_mha_bwd (src/TwoStage/two_stage_cuda_kernels.cu:334-882) for dtype
+// BF16.  The reference keeps the S x S matrices P and dP of one (batch, head) in shared memory or
+// in freshly allocated global scratch; here nothing of size S x S exists.  A CTA owns one tile of
+// 128 keys, keeps dK and dV for it in tensor memory, walks the query tiles at or below the causal
+// diagonal and recomputes the probabilities from the row log-sum-exp:
+//
+//   S^T  = K Q_i^T                 (SS MMA, keys on the 128 TMEM lanes, queries on 128 columns)
+//   dP^T = V dO_i^T                (SS MMA)
+//   P^T  = exp2(c S^T - lse2_q)    dS^T = P^T o (dP^T - delta_q)        (8 warps, lane = key row)
+//   dV  += P^T dO_i                (TS MMA: P^T bf16 in TMEM, dO_i as an MN-major operand)
+//   dK  += dS^T Q_i                (TS MMA: dS^T bf16 in TMEM)
+//   dQ_i = dS K                    (SS MMA: dS written to shared memory as an MN-major operand),
+//                                  drained from TMEM with vector red.add into an fp32 accumulator
+//
+// Three launches per call: a row pre-pass (delta = dO.O, lse in log2 units padded to whole tiles,
+// accumulator cleared), the main kernel, and a pass turning the accumulator into bf16 dQ.
+// dQ is summed with atomics, so its low bits depend on the order in which CTAs arrive.
+#include "internal.cuh"
+#include "tc_common.cuh"
+
+namespace cxxattn {
+namespace {
+
+using namespace tc;
+
+constexpr int BT = 128;  // rows per tile (queries and keys)
+constexpr int DH = 64;
+constexpr int TILE_BYTES = BT * DH * 2;  // 16 KB
+constexpr int NTHREADS = 320;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_ST = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_P = 448;
+// K | V | Q x2 | dO x2 | dS (2 blocks) | (lse2, delta) x2
+constexpr size_t SMEM_BYTES = 8 * TILE_BYTES + 2 * 1024 + 1024;
+
+struct BwdParams {
+    const float* lse2;   // [BH][Spad]  lse * log2(e), +inf on padding rows
+    const float* delta;  // [BH][Spad]
+    float* dq_acc;       // [BH][Spad][64]
+    __nv_bfloat16* dK;
+    __nv_bfloat16* dV;
+    int* status;
+    int B, S, H, Spad;
+    int64_t sb, ss, sh;
+    float scale, scale_log2;
+};
+
+// One warp per (batch*head, row < Spad): delta, lse2, and a cleared accumulator row.
+__global__ void mha_tc_bwd_pre_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                      const float* __restrict__ lse, float* __restrict__ lse2,
+                                      float* __restrict__ delta, float* __restrict__ dq_acc, int B, int S, int H,
+                                      int Spad, int64_t sb, int64_t ss, int64_t sh) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    if (row >= (int64_t)B * H * Spad) return;
+    const int s = row % Spad;
+    const int bh = row / Spad;
+    reinterpret_cast<float2*>(dq_acc + row * DH)[lane] = make_float2(0.f, 0.f);
+    float acc = 0.f;
+    if (s < S) {
+        const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
+        const float2 o = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(O + off)[lane]);
+        const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dO + off)[lane]);
+        acc = o.x * g.x + o.y * g.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        delta[row] = acc;
+        lse2[row] = s < S ? lse[(int64_t)bh * S + s] * 1.4426950408889634f : INFINITY;
+    }
+}
+
+// dQ[b,s,h,:] = bf16(scale * acc[bh][s][:]); one warp per row.
+__global__ void mha_tc_bwd_post_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dQ, int B,
+                                       int S, int H, int Spad, int64_t sb, int64_t ss, int64_t sh, float scale) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    if (row >= (int64_t)B * H * S) return;
+    const int s = row % S;
+    const int bh = row / S;
+    const float2 a = reinterpret_cast<const float2*>(dq_acc + ((int64_t)bh * Spad + s) * DH)[lane];
+    const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
+    reinterpret_cast<__nv_bfloat162*>(dQ + off)[lane] = __floats2bfloat162_rn(a.x * scale, a.y * scale);
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t kv_full, q_full[2], do_full[2], qdo_free[2], s_full, s_free, dp_full, p_ready, ds_ready,
+        dq_full, dq_free, all_done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sK = smem;
+    uint8_t* sV = smem + TILE_BYTES;
+    uint8_t* sQ = smem + 2 * TILE_BYTES;   // 2 stages
+    uint8_t* sdO = smem + 4 * TILE_BYTES;  // 2 stages
+    uint8_t* sDS = smem + 6 * TILE_BYTES;  // 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
+    float* sStat = reinterpret_cast<float*>(smem + 8 * TILE_BYTES);  // [stage][lse2 | delta][128]
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int ntile = p.Spad / BT;
+    const int nbh = p.B * p.H;
+    const int n = blockIdx.x / nbh;  // key tile; tile 0 meets every query tile, so it is scheduled first
+    const int bh = blockIdx.x % nbh;
+    const int b = bh / p.H, h = bh % p.H;
+    const int niter = ntile - n;
+    const int k0 = n * BT;
+    const Guard guard{&abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&kv_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&q_full[s], 1);
+            mbar_init(&do_full[s], 1);
+            mbar_init(&qdo_free[s], 1);
+        }
+        mbar_init(&s_full, 1);
+        mbar_init(&s_free, 256);
+        mbar_init(&dp_full, 1);
+        mbar_init(&p_ready, 256);
+        mbar_init(&ds_ready, 256);
+        mbar_init(&dq_full, 1);
+        mbar_init(&dq_free, 256);
+        mbar_init(&all_done, 1);
+        fence_barrier_init();
+    }
+    if (warp == 9) tmem_alloc(&tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 8) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            prefetch_tmap(&tmQ);
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+            prefetch_tmap(&tmdO);
+            mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
+            tma_load_4d(sK, &tmK, &kv_full, 0, h, k0, b);
+            tma_load_4d(sV, &tmV, &kv_full, 0, h, k0, b);
+            for (int it = 0; it < niter; it++) {
+                const int s = it & 1, q0 = (n + it) * BT;
+                if (it >= 2) mbar_wait(&qdo_free[s], ((it / 2) - 1) & 1, guard, 401);
+                mbar_expect_tx(&q_full[s], TILE_BYTES + 1024);
+                tma_load_4d(sQ + s * TILE_BYTES, &tmQ, &q_full[s], 0, h, q0, b);
+                bulk_load_1d(sStat + s * 256, p.lse2 + (int64_t)bh * p.Spad + q0, 512, &q_full[s]);
+                bulk_load_1d(sStat + s * 256 + 128, p.delta + (int64_t)bh * p.Spad + q0, 512, &q_full[s]);
+                mbar_expect_tx(&do_full[s], TILE_BYTES);
+                tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &do_full[s], 0, h, q0, b);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC_SS = idesc_bf16(BT, BT, 0, 0);  // S^T, dP^T: both operands K-major
+            constexpr uint32_t IDESC_TS = idesc_bf16(BT, DH, 0, 1);  // dV, dK: A in TMEM, B MN-major
+            constexpr uint32_t IDESC_DQ = idesc_bf16(BT, DH, 1, 1);  // dQ: dS and K both MN-major
+            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+            auto issue_st = [&](int s) {
+                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < DH / 16; k++)
+                    umma_ss(tmem + COL_ST, smem_desc_sw128(aK + 32 * k, 16), smem_desc_sw128(aQ + 32 * k, 16), IDESC_SS,
+                            k > 0);
+                umma_commit(&s_full);
+            };
+            auto issue_dp = [&](int s) {
+                const uint32_t aG = smem_u32(sdO + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < DH / 16; k++)
+                    umma_ss(tmem + COL_DP, smem_desc_sw128(aV + 32 * k, 16), smem_desc_sw128(aG + 32 * k, 16), IDESC_SS,
+                            k > 0);
+                umma_commit(&dp_full);
+            };
+            mbar_wait(&kv_full, 0, guard, 501);
+            mbar_wait(&q_full[0], 0, guard, 502);
+            tc_fence_after();
+            issue_st(0);
+            mbar_wait(&do_full[0], 0, guard, 503);
+            tc_fence_after();
+            issue_dp(0);
+            for (int it = 0; it < niter; it++) {
+                const int s = it & 1, sn = s ^ 1;
+                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), aG = smem_u32(sdO + s * TILE_BYTES);
+                mbar_wait(&s_free, it & 1, guard, 504);
+                mbar_wait(&p_ready, it & 1, guard, 505);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i
+                    umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, smem_desc_sw128(aG + 2048 * k, 0), IDESC_TS,
+                            it > 0 || k > 0);
+                if (it + 1 < niter) {
+                    mbar_wait(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
+                    tc_fence_after();
+                    issue_st(sn);  // its commit also covers the dV product above: P may then be rewritten
+                }
+                mbar_wait(&ds_ready, it & 1, guard, 507);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i
+                    umma_ts(tmem + COL_DK, tmem + COL_DP + 8 * k, smem_desc_sw128(aQ + 2048 * k, 0), IDESC_TS,
+                            it > 0 || k > 0);
+                umma_commit(&qdo_free[s]);
+                if (it > 0) {
+                    mbar_wait(&dq_free, (it - 1) & 1, guard, 508);
+                    tc_fence_after();
+                }
+#pragma unroll
+                for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K
+                    umma_ss(tmem + COL_DQ, smem_desc_sw128(aDS + 2048 * k, TILE_BYTES), smem_desc_sw128(aK + 2048 * k, 0),
+                            IDESC_DQ, k > 0);
+                umma_commit(&dq_full);
+                if (it + 1 < niter) {
+                    mbar_wait(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
+                    tc_fence_after();
+                    issue_dp(sn);  // its commit also covers dK and dQ above: dS may then be rewritten
+                }
+            }
+            umma_commit(&all_done);
+        }
+    } else {
+        // ---------------- compute warps: lane = key row, group w owns query columns 64w .. 64w+63 ----------------
+        const int w = warp / 4;
+        const int r = (warp % 4) * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
+        float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + r) * DH + 32 * w;
+        auto drain_dq = [&](int q0) {
+            uint32_t dq[32];
+            tmem_ld32(lane_base + COL_DQ + 32 * w, dq);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&dq_free);
+            float* dst = acc_base + (int64_t)q0 * DH;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                red_add_v4(dst + i, __uint_as_float(dq[i]), __uint_as_float(dq[i + 1]), __uint_as_float(dq[i + 2]),
+                           __uint_as_float(dq[i + 3]));
+        };
+        for (int it = 0; it < niter; it++) {
+            const int s = it & 1;
+            const bool diag = it == 0;
+            mbar_wait(&q_full[s], (it / 2) & 1, guard, 601);
+            const float* l2 = sStat + s * 256 + 64 * w;
+            const float* dl = l2 + 128;
+            mbar_wait(&s_full, it & 1, guard, 602);
+            tc_fence_after();
+            uint32_t v0[32], v1[32], pk[32];
+            tmem_ld32(lane_base + COL_ST + 64 * w, v0);
+            tmem_ld32(lane_base + COL_ST + 64 * w + 32, v1);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&s_free);
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float a0 = ex2(fmaf(__uint_as_float(v0[i]), p.scale_log2, -l2[i]));
+                float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), p.scale_log2, -l2[i + 1]));
+                float b0 = ex2(fmaf(__uint_as_float(v1[i]), p.scale_log2, -l2[32 + i]));
+                float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), p.scale_log2, -l2[32 + i + 1]));
+                if (diag) {  // key k0+r is visible to query q0 + 64w + c iff r <= 64w + c
+                    a0 = r <= 64 * w + i ? a0 : 0.f;
+                    a1 = r <= 64 * w + i + 1 ? a1 : 0.f;
+                    b0 = r <= 64 * w + 32 + i ? b0 : 0.f;
+                    b1 = r <= 64 * w + 32 + i + 1 ? b1 : 0.f;
+                }
+                pk[i / 2] = pack_bf16(a0, a1);
+                pk[16 + i / 2] = pack_bf16(b0, b1);
+            }
+            tmem_st32(lane_base + COL_P + 32 * w, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_ready);
+
+            if (it > 0) {
+                mbar_wait(&dq_full, (it - 1) & 1, guard, 603);
+                tc_fence_after();
+                drain_dq((n + it - 1) * BT);
+            }
+
+            mbar_wait(&dp_full, it & 1, guard, 604);
+            tc_fence_after();
+            tmem_ld32(lane_base + COL_DP + 64 * w, v0);
+            tmem_ld32(lane_base + COL_DP + 64 * w + 32, v1);
+            tmem_ld_wait();
+            compute_bar_sync();  // both groups hold their dP^T before anyone overwrites it with dS^T
+            uint32_t dsk[32];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float a0 = bf_lo(pk[i / 2]) * (__uint_as_float(v0[i]) - dl[i]);
+                const float a1 = bf_hi(pk[i / 2]) * (__uint_as_float(v0[i + 1]) - dl[i + 1]);
+                const float b0 = bf_lo(pk[16 + i / 2]) * (__uint_as_float(v1[i]) - dl[32 + i]);
+                const float b1 = bf_hi(pk[16 + i / 2]) * (__uint_as_float(v1[i + 1]) - dl[32 + i + 1]);
+                dsk[i / 2] = pack_bf16(a0, a1);
+                dsk[16 + i / 2] = pack_bf16(b0, b1);
+            }
+            tmem_st32(lane_base + COL_DP + 32 * w, dsk);
+            // the same 64 values as one 128-byte row of block w of the MN-major dS operand
+            uint8_t* row = sDS + w * TILE_BYTES + r * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+                *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) =
+                    make_uint4(dsk[4 * ch], dsk[4 * ch + 1], dsk[4 * ch + 2], dsk[4 * ch + 3]);
+            tmem_st_wait();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(&ds_ready);
+        }
+        mbar_wait(&dq_full, (niter - 1) & 1, guard, 605);
+        tc_fence_after();
+        drain_dq((n + niter - 1) * BT);
+
+        // epilogue: group 0 stores dV, group 1 stores scale * dK
+        mbar_wait(&all_done, 0, guard, 606);
+        tc_fence_after();
+        uint32_t o0[32], o1[32];
+        const uint32_t col = w == 0 ? COL_DV : COL_DK;
+        tmem_ld32(lane_base + col, o0);
+        tmem_ld32(lane_base + col + 32, o1);
+        tmem_ld_wait();
+        const int key = k0 + r;
+        if (key < p.S) {
+            const float f = w == 0 ? 1.0f : p.scale;
+            __nv_bfloat16* out = (w == 0 ? p.dV : p.dK) + (int64_t)b * p.sb + (int64_t)key * p.ss + (int64_t)h * p.sh;
+            uint4* dst = reinterpret_cast<uint4*>(out);
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * f, __uint_as_float(o0[i + 1]) * f),
+                                        pack_bf16(__uint_as_float(o0[i + 2]) * f, __uint_as_float(o0[i + 3]) * f),
+                                        pack_bf16(__uint_as_float(o0[i + 4]) * f, __uint_as_float(o0[i + 5]) * f),
+                                        pack_bf16(__uint_as_float(o0[i + 6]) * f, __uint_as_float(o0[i + 7]) * f));
+                dst[4 + i / 8] = make_uint4(pack_bf16(__uint_as_float(o1[i]) * f, __uint_as_float(o1[i + 1]) * f),
+                                            pack_bf16(__uint_as_float(o1[i + 2]) * f, __uint_as_float(o1[i + 3]) * f),
+                                            pack_bf16(__uint_as_float(o1[i + 4]) * f, __uint_as_float(o1[i + 5]) * f),
+                                            pack_bf16(__uint_as_float(o1[i + 6]) * f, __uint_as_float(o1[i + 7]) * f));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+static size_t rows_bytes(const MhaShape& p) {
+    const size_t spad = ((size_t)p.S + BT - 1) / BT * BT;
+    return align_up((size_t)p.B * p.H * spad * sizeof(float), 256);
+}
+
+size_t mha_tc_bwd_workspace(const MhaShape& p, bool have_lse) {
+    const size_t rows = rows_bytes(p);
+    return 2 * rows + rows * DH + (have_lse ? 0 : align_up((size_t)p.B * p.H * p.S * sizeof(float), 256));
+}
+
+int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, const void* O, const void* dO,
+               const float* lse, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (!mha_tc_supported(p)) return CXXATTN_ERR_UNSUPPORTED;
+    for (const void* q : {Q, K, V, O, dO, (const void*)dQ, (const void*)dK, (const void*)dV})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    if (ws == nullptr || ws_bytes < mha_tc_bwd_workspace(p, lse != nullptr)) return CXXATTN_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(ws) % 256) return CXXATTN_ERR_ALIGNMENT;
+    const int Spad = (p.S + BT - 1) / BT * BT;
+    const size_t rows = rows_bytes(p);
+    char* base = static_cast<char*>(ws);
+    float* lse2 = reinterpret_cast<float*>(base);
+    float* delta = reinterpret_cast<float*>(base + rows);
+    float* dq_acc = reinterpret_cast<float*>(base + 2 * rows);
+    if (lse == nullptr) {
+        // The reference backward recomputes the row statistics from Q and K; so does this pre-pass
+        // (the forward kernel with its output store switched off).
+        float* tmp = reinterpret_cast<float*>(base + 2 * rows + rows * DH);
+        const int rc = mha_tc_fwd(p, Q, K, V, nullptr, tmp, st);
+        if (rc != CXXATTN_OK) return rc;
+        lse = tmp;
+    }
+    const int64_t nrows = (int64_t)p.B * p.H * Spad;
+    mha_tc_bwd_pre_kernel<<<(unsigned)((nrows + 7) / 8), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(O), static_cast<const __nv_bfloat16*>(dO), lse, lse2, delta, dq_acc, p.B,
+        p.S, p.H, Spad, p.sb, p.ss, p.sh);
+    if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+
+    CUtensorMap tmQ, tmK, tmV, tmG;
+    if (!make_tmap_bhsd(&tmQ, Q, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BT) ||
+        !make_tmap_bhsd(&tmK, K, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BT) ||
+        !make_tmap_bhsd(&tmV, V, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BT) ||
+        !make_tmap_bhsd(&tmG, dO, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BT))
+        return CXXATTN_ERR_CUDA;
+    BwdParams bp;
+    bp.lse2 = lse2; bp.delta = delta; bp.dq_acc = dq_acc;
+    bp.dK = static_cast<__nv_bfloat16*>(dK);
+    bp.dV = static_cast<__nv_bfloat16*>(dV);
+    bp.status = status_word();
+    if (bp.status == nullptr) return CXXATTN_ERR_CUDA;
+    bp.B = p.B; bp.S = p.S; bp.H = p.H; bp.Spad = Spad;
+    bp.sb = p.sb; bp.ss = p.ss; bp.sh = p.sh;
+    bp.scale = p.scale;
+    bp.scale_log2 = p.scale * 1.4426950408889634f;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(mha_tc_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
+            cudaSuccess)
+            return CXXATTN_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    const int64_t grid = (int64_t)(Spad / BT) * p.B * p.H;
+    mha_tc_bwd_kernel<<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);
+    if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+
+    const int64_t orows = (int64_t)p.B * p.H * p.S;
+    mha_tc_bwd_post_kernel<<<(unsigned)((orows + 7) / 8), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dQ), p.B,
+                                                                      p.S, p.H, Spad, p.sb, p.ss, p.sh, p.scale);
+    return check_launch();
+}
+
+}  // namespace cxxattn

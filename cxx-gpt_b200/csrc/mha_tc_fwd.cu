@@ -253,7 +253,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_ld32(tO, o[0]);
             tmem_ld32(tO + 32, o[1]);
             tmem_ld_wait();
-            if (qr < p.S) {
+            if (qr < p.S && p.O != nullptr) {
                 uint4* dst = reinterpret_cast<uint4*>(p.O + (int64_t)b * p.sb + (int64_t)qr * p.ss + (int64_t)h * p.sh);
 #pragma unroll
                 for (int c = 0; c < 2; c++)
@@ -266,6 +266,8 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         v.w = pack_bf16(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
                         dst[(c * 32 + i) / 8] = v;
                     }
+                }
+            if (qr < p.S) {
                 if (p.lse != nullptr) p.lse[(int64_t)bh * p.S + qr] = (m + log2f(l)) * 0.6931471805599453f;
             }
         }
@@ -288,7 +290,7 @@ bool mha_tc_supported(const MhaShape& p) {
 int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, void* O, float* lse,
                cudaStream_t st) {
     if (!mha_tc_supported(p)) return CXXATTN_ERR_UNSUPPORTED;
-    for (const void* q : {Q, K, V, (const void*)O})
+    for (const void* q : {Q, K, V, (const void*)O})  // O may be null: statistics-only pass
         if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
     CUtensorMap tmQ, tmK, tmV;
     if (!make_tmap_bhsd(&tmQ, Q, p.B, p.S, p.H, p.Dh, p.sb, p.ss, p.sh, BM) ||

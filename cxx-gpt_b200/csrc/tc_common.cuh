@@ -23,7 +23,7 @@ struct Guard {
     int* status;
 };
 
-constexpr uint32_t kSpinLimit = 1u << 20;  // try_wait attempts before a wait gives up
+constexpr uint64_t kWaitNs = 2000000000ull;  // a wait gives up after 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -54,16 +54,27 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait; `code` identifies the wait site in the status word.
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait; `code` identifies the wait site in the status word.  Gives up after kWaitNs of
+// wall time, or at once when this CTA has aborted or any CTA of the device has recorded a
+// failure (so a fault costs one timeout for the whole grid, not one per CTA).
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const Guard& g, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; i++) {
+    if (mbar_try(bar, parity)) return;
+    const uint64_t t0 = global_ns();
+    for (uint32_t i = 1;; i++) {
         if (mbar_try(bar, parity)) return;
-        if ((i & 255u) == 255u && *g.abort_flag) return;
+        if ((i & 63u) == 0u) {
+            if (*g.abort_flag) return;
+            if (*reinterpret_cast<volatile int*>(g.status) != 0) break;
+            if (global_ns() - t0 > kWaitNs) break;
+        }
     }
-    if (!*g.abort_flag) {
-        *g.abort_flag = 1;
-        atomicCAS(g.status, 0, code);
-    }
+    *g.abort_flag = 1;
+    atomicCAS(g.status, 0, code);
 }
 
 // ---- TMA -----------------------------------------------------------------------------------

@@ -156,6 +156,19 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
  * gelu_exact_deriv (ts.cuh:84-85, ts.cu:1888-1924). */
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream);
 
+/* ---- host-buffer entry points ------------------------------------------------------------- */
+
+/* Softmax MHA forward + backward on HOST tensors in the reference layout (what kernel_test.cpp
+ * does around fused_mha_fwd / fused_mha_bwd with fromTensor / toTensor, kernel_test.cpp:225-249):
+ * the plan owns device buffers for up to three chunks of `batch_per_chunk` batch items
+ * (allocated by _create, freed by _destroy) and pipelines copy-in, kernels and copy-out across
+ * chunks.  cxxattn_mha_fwd_bwd_host returns after all results are in the host buffers. */
+typedef struct cxxattn_host_plan cxxattn_host_plan;
+int cxxattn_host_plan_create(cxxattn_host_plan** out, const cxxattn_mha_desc* desc, int batch_per_chunk);
+void cxxattn_host_plan_destroy(cxxattn_host_plan* plan);
+int cxxattn_mha_fwd_bwd_host(cxxattn_host_plan* plan, const void* hQ, const void* hK, const void* hV,
+                             const void* hdO, void* hO, void* hdQ, void* hdK, void* hdV);
+
 /* ---- status and diagnostics (no reference counterpart) ------------------------------------- */
 
 /* Synchronises `stream`, then reports whether any tensor-core kernel launched so far on the

@@ -46,9 +46,35 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
     return out
 
 
+def build_dropin_kernel_test(reference=DEFAULT_REFERENCE, force=False):
+    """Compiles the reference's UNMODIFIED src/TwoStage/kernel_test.cpp against this repository's
+    kernels (compat adapter + libcxxattn.so) into oracle/_ref/kernel_test_dropin.  Returns its path,
+    or None when neither the reference tree nor a previously built binary is available."""
+    root = os.path.dirname(HERE)
+    pkg = os.path.join(root, "cxx-gpt_b200")
+    out_dir = os.path.join(HERE, "_ref")
+    out = os.path.join(out_dir, "kernel_test_dropin")
+    ref_src = os.path.join(reference, "src", "TwoStage", "kernel_test.cpp")
+    if not os.path.exists(ref_src):
+        return out if os.path.exists(out) else None
+    adapter = os.path.join(pkg, "compat", "cxxgpt_kernels.cpp")
+    lib = os.path.join(pkg, "libcxxattn.so")
+    deps = [ref_src, adapter, lib, os.path.join(pkg, "compat", "cxxgpt_kernels.hpp"),
+            os.path.join(pkg, "compat", "TensorN.hpp"), os.path.join(root, "include", "cxxattn.h")]
+    if force or _stale(out, deps):
+        os.makedirs(out_dir, exist_ok=True)
+        subprocess.check_call(["nvcc", "-std=c++17", "-O2", "-Wno-deprecated-gpu-targets",
+                               "-I", os.path.join(pkg, "compat"), "-I", os.path.join(root, "include"),
+                               "-I", os.path.join(reference, "src"), "-o", out, ref_src, adapter,
+                               "-L", pkg, "-lcxxattn", "-Xlinker", "-rpath", "-Xlinker",
+                               "$ORIGIN/../../cxx-gpt_b200"])
+    return out
+
+
 if __name__ == "__main__":
     ref = DEFAULT_REFERENCE
     if "--reference" in sys.argv:
         ref = sys.argv[sys.argv.index("--reference") + 1]
     print(build_oracle(force="--force" in sys.argv))
     print(build_reference(ref, force="--force" in sys.argv))
+    print(build_dropin_kernel_test(ref, force="--force" in sys.argv))

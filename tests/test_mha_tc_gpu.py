@@ -73,3 +73,56 @@ def test_forward_long_sequence_properties(pkg, dev, orc):
     rO = orc.mha_fwd(Q[:, sl].float().numpy(), K[:, sl].float().numpy(), V[:, sl].float().numpy(),
                      1, S, 1, Dh, f64=True)
     assert rel_err(O1[:, sl].float().cpu().numpy(), rO) < TOL_BF16
+
+
+def run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh, use_lse=True):
+    tq, tk, tv, tg = (x.to(dev) for x in (Q, K, V, dO))
+    O = torch.full_like(tq, float("nan"))
+    lse = torch.full((B * H * S,), float("nan"), device=dev)
+    pkg.mha_fwd(tq, tk, tv, O, B, S, H, Dh, lse=lse)
+    dQ, dK, dV = (torch.full_like(tq, float("nan")) for _ in range(3))
+    pkg.mha_bwd(tq, tk, tv, O, tg, dQ, dK, dV, B, S, H, Dh, lse=lse if use_lse else None)
+    pkg.sync_status()
+    return O, dQ, dK, dV
+
+
+@pytest.mark.parametrize("B,S,H,Dh", [(1, 128, 1, 64), (1, 256, 1, 64), (2, 512, 3, 64), (1, 384, 2, 64),
+                                      (2, 1024, 2, 64), (1, 200, 2, 64), (1, 77, 1, 64)])
+def test_backward_matches_oracle(pkg, dev, orc, B, S, H, Dh):
+    Q, K, V, dO = bf16_inputs(17 + S, B, S, H, Dh)
+    O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    # the reference backward consumes the stored (here bf16-rounded) O of the forward under test
+    rdQ, rdK, rdV = orc.mha_bwd(f[0], f[1], f[2], O.float().cpu().numpy(), f[3], B, S, H, Dh, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        got = a.float().cpu().numpy()
+        assert np.all(np.isfinite(got)), name
+        assert rel_err(got, b) < TOL_BF16, (name, rel_err(got, b))
+
+
+def test_backward_without_lse_recomputes_statistics(pkg, dev):
+    """The kept reference signature carries no row statistics: passing lse=NULL must give the same
+    gradients as reusing the forward's (dK and dV bit-identical; dQ is summed with atomics)."""
+    B, S, H, Dh = 2, 640, 2, 64
+    Q, K, V, dO = bf16_inputs(5, B, S, H, Dh)
+    a = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh, use_lse=True)
+    b = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh, use_lse=False)
+    assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+    assert rel_err(a[1].float().cpu().numpy(), b[1].float().cpu().numpy()) < 1e-2
+
+
+def test_backward_long_sequence_properties(pkg, dev, orc):
+    """S=4096, 12 heads x 64: gradients of one (batch, head) slice against the oracle, and
+    linearity in dO (dX(a*dO) == a*dX(dO) for a power of two, exact in bf16/fp32)."""
+    B, S, H, Dh = 1, 4096, 12, 64
+    Q, K, V, dO = bf16_inputs(9, B, S, H, Dh)
+    O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+    _, dQ2, dK2, dV2 = run_fwd_bwd(pkg, dev, Q, K, V, dO * 4, B, S, H, Dh)
+    assert torch.equal(dK2.float(), dK.float() * 4) and torch.equal(dV2.float(), dV.float() * 4)
+    assert rel_err(dQ2.float().cpu().numpy(), 4 * dQ.float().cpu().numpy()) < 1e-2
+    h = 7
+    sl = slice(h * Dh, (h + 1) * Dh)
+    f = [x[:, sl].float().numpy() for x in (Q, K, V, dO)]
+    rdQ, rdK, rdV = orc.mha_bwd(f[0], f[1], f[2], O[:, sl].float().cpu().numpy(), f[3], 1, S, 1, Dh, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert rel_err(a[:, sl].float().cpu().numpy(), b) < TOL_BF16, name
