@@ -25,7 +25,14 @@ def test_reference_kernel_test_program_passes_on_this_library():
     # 4 + 7 + 4 + 5 + 4 + 5 attention lines and 5 RoPE lines (kernel_test.cpp:239-498)
     assert len(lines) == 34, out.stdout
     assert out.stdout.strip().endswith("done")
+    bad = []
     for name, val in lines:
         v = float(val)
-        # the reference README expects ~1e-7; the S=300, Dh=128 block sums 300 terms per element
-        assert v == v and v < 2e-5, (name, val)
+        # The program prints ABSOLUTE differences.  The reference README expects ~1e-7 for values of
+        # order one; the S=300, Dh=128 block sums 300 terms per element, and the denominators of the
+        # D=E=256 block are of order 1e4 (sum over 256 features and up to 32 keys), so for the "den"
+        # lines 1e-2 absolute is 1e-6 relative.
+        limit = 1e-2 if name.split()[-1] == "den" else 2e-5
+        if not (v == v and v < limit):
+            bad.append((name, val))
+    assert not bad, (bad, out.stdout)
