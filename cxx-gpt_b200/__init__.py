@@ -24,6 +24,7 @@ SYMBOLS = [
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
     "cxxattn_sync_status", "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
+    "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity",
 ]
 
 
@@ -76,6 +77,9 @@ def lib():
         L.cxxattn_rope.argtypes = [vp, vp, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
         L.cxxattn_sync_status.argtypes = [vp]
+        L.cxxattn_linattn_fwd_noalloc.argtypes = [C.POINTER(LinDesc)] + [vp] * 6 + [vp]
+        L.cxxattn_linattn_noalloc_capacity.restype = sz
+        L.cxxattn_linattn_noalloc_capacity.argtypes = []
         L.cxxattn_host_plan_create.argtypes = [C.POINTER(vp), C.POINTER(MhaDesc), i32]
         L.cxxattn_host_plan_destroy.argtypes = [vp]
         L.cxxattn_host_plan_destroy.restype = None

@@ -100,6 +100,15 @@ int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void*
     return CXXATTN_ERR_UNSUPPORTED;
 }
 
+int cxxattn_linattn_fwd_noalloc(const cxxattn_lin_desc* desc, const float* Q, const float* K, const float* V,
+                                float* O, float* den, float* z_cache, cxxattn_stream_t stream) {
+    if (!lin_ok(desc) || !Q || !K || !V || !O || !den) return CXXATTN_ERR_INVALID;
+    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
+    return linattn_f32_fwd_static(*desc, Q, K, V, O, den, z_cache, static_cast<cudaStream_t>(stream));
+}
+
+size_t cxxattn_linattn_noalloc_capacity(void) { return linattn_f32_static_capacity(); }
+
 int cxxattn_linattn_bwd_step1(const float* O, const float* dO, const float* den, float* dnum,
                               float* dden, size_t N, size_t E, cxxattn_stream_t stream) {
     if (!O || !dO || !den || !dnum || !dden || N == 0 || E == 0) return CXXATTN_ERR_INVALID;

@@ -45,6 +45,9 @@ int sync_status(cudaStream_t st);
 size_t linattn_f32_workspace(const cxxattn_lin_desc& d);
 int linattn_f32_fwd(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
                     float* O, float* den, float* z_cache, void* ws, size_t ws_bytes, cudaStream_t st);
+size_t linattn_f32_static_capacity();
+int linattn_f32_fwd_static(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
+                           float* O, float* den, float* z_cache, cudaStream_t st);
 int linattn_f32_bwd_dq(const cxxattn_lin_desc& d, const float* K, const float* V, const float* dnum,
                        const float* dden, const float* z_cache, const float* Q, float* dQ,
                        void* ws, size_t ws_bytes, cudaStream_t st);

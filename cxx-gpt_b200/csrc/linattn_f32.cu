@@ -396,6 +396,50 @@ int linattn_f32_fwd(const cxxattn_lin_desc& d, const float* Q, const float* K, c
     return launch_apply<FWD>(d, g, st);
 }
 
+// ---- forward with built-in scratch -----------------------------------------------------------
+// Scratch for linattn_f32_fwd_static: chunk states and z states of one forward call.  It lives in
+// the library's device image, so every GPU that loads the library holds these bytes until the
+// process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Bytes of g_static_scratch a forward call with this descriptor uses (states, then z states).
+static size_t static_fwd_bytes(const cxxattn_lin_desc& d) {
+    const size_t nc = (size_t)chunks(d);
+    return align_up((size_t)d.B * nc * d.D * d.E * sizeof(float), 256) +
+           align_up((size_t)d.B * nc * d.D * sizeof(float), 256);
+}
+
+size_t linattn_f32_static_capacity() { return kStaticScratchBytes; }
+
+// Same kernels and launch order as linattn_f32_fwd, with the scratch taken from g_static_scratch
+// instead of a caller buffer.  In host code `g_static_scratch` is only a handle: its device
+// address is looked up with cudaGetSymbolAddress, once per device, with that device current (the
+// first call on a device does this look-up, so it should come before any stream capture).
+// No allocation, no free, no allocating library call.
+int linattn_f32_fwd_static(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
+                           float* O, float* den, float* z_cache, cudaStream_t st) {
+    if (static_fwd_bytes(d) > kStaticScratchBytes) return CXXATTN_ERR_TOO_LARGE;
+    static void* addr[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CXXATTN_ERR_CUDA;
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return CXXATTN_ERR_CUDA;
+        addr[dev] = p;
+    }
+    // carve() lays out states | z states | (dnum | dden); the forward touches the first two only,
+    // and static_fwd_bytes() bounds exactly those.  Every chunk state is fully rewritten by
+    // chunk_state_kernel before it is read, so stale contents of an earlier call do not matter.
+    const Ws w = carve(d, addr[dev]);
+    const bool map = d.feature_map == CXXATTN_MAP_ELU1;
+    int rc = build_states(d, w, K, V, nullptr, map, false, st);
+    if (rc != CXXATTN_OK) return rc;
+    ApplyArgs g = base_args(d, w);
+    g.a = Q; g.b = K; g.c = V; g.out = O; g.den = den; g.zc_out = z_cache;
+    return launch_apply<FWD>(d, g, st);
+}
+
 int linattn_f32_bwd_dq(const cxxattn_lin_desc& d, const float* K, const float* V, const float* dnum,
                        const float* dden, const float* z_cache, const float* Q, float* dQ,
                        void* ws, size_t ws_bytes, cudaStream_t st) {

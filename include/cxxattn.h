@@ -106,6 +106,27 @@ int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void*
                         void* O, float* den, float* z_cache,
                         void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
 
+/* Forward for callers that cannot hand over a workspace.  Some hosts of this library run where
+ * device allocation is off the table: a plugin called from inside another engine's execution
+ * callback, which owns the memory pool and forbids cudaMalloc/cudaFree (both synchronise the
+ * device); a real-time loop that may not take the allocator's locks; a process whose whole device
+ * memory budget was handed out at start-up.  For them this variant of cxxattn_linattn_fwd (float
+ * tensors, same results) keeps its chunk states in a fixed scratch array that is part of the
+ * library's device image: cxxattn_linattn_noalloc_capacity() bytes (8 MiB), held on every GPU
+ * that loads the library until the process exits.  It calls no cudaMalloc, cudaFree or allocating
+ * library routine.
+ *   - Limit: with nc = ceil(S/64), B*nc*D*(E+1)*4 bytes (each part rounded up to 256) must fit
+ *     the capacity; otherwise CXXATTN_ERR_TOO_LARGE is returned and nothing is launched.
+ *   - The first call on each device looks up the array's device address (that device must be
+ *     current); make that first call before any stream capture.
+ *   - All calls share the one array, which keeps the previous call's contents.  Nothing in it has
+ *     to start at zero (every state is rewritten before it is read), but two calls that overlap
+ *     on the GPU (different streams, or different host threads) race on it: serialise them.
+ * It has no counterpart in the reference, whose wrappers allocate their scratch per call. */
+int cxxattn_linattn_fwd_noalloc(const cxxattn_lin_desc* desc, const float* Q, const float* K, const float* V,
+                                float* O, float* den, float* z_cache, cxxattn_stream_t stream);
+size_t cxxattn_linattn_noalloc_capacity(void);
+
 /* dnum = dO/den, dden = -(dO.O)/den per row.  Replaces two_stage_cuda::kernel_attn_bwd_step1
  * (ts.cuh:46-49, ts.cu:1235-1248) and linear_cuda::causal_linear_attention_bwd_step1
  * (lin.cuh:19-23, lin.cu:136-150).  O and dO are float. */

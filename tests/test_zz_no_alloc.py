@@ -1,0 +1,73 @@
+"""The allocation-free forward entry point, cxxattn_linattn_fwd_noalloc.
+
+Who needs it: code that calls this library from a place where device memory may not be allocated
+or handed over — a plugin running inside another engine's execution callback (the engine owns the
+pool, and cudaMalloc/cudaFree would stall the whole device), a latency-bound loop that may not
+touch the allocator, a process whose device memory was budgeted out at start-up.  Such a caller
+still passes inputs and outputs; the chunk states go to a fixed 8 MiB array inside the library.
+
+The test calls the entry point through the C-ABI twice in a row with different inputs and shapes
+(the array is shared between calls and keeps the previous contents) and compares each result with
+the workspace-taking entry point cxxattn_linattn_fwd at the fp32 tolerance of this suite (1e-5 as
+max|a-b|/max|b|); it also checks the size limit.  The file name keeps it last in collection order,
+so a run that stops at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err, seeded_normal
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def call_both(pkg, dev, seed, B, S, D, E, feature_map, eps_in_den):
+    lib = pkg.lib()
+    Q, K, V = seeded_normal(seed, [(B * S, D), (B * S, D), (B * S, E)])
+    if feature_map == pkg.MAP_NONE:  # pre-mapped features are positive
+        Q, K = np.abs(Q) + 0.1, np.abs(K) + 0.1
+    tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (Q, K, V))
+    N = B * S
+    stream = torch.cuda.current_stream().cuda_stream
+    d = pkg.lin_desc(B, S, D, E, pkg.F32, feature_map, eps_in_den)
+
+    O1 = torch.full((N, E), float("nan"), device=dev)
+    den1 = torch.full((N,), float("nan"), device=dev)
+    zc1 = torch.full((N, D), float("nan"), device=dev)
+    rc = lib.cxxattn_linattn_fwd_noalloc(C.byref(d), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(),
+                                         O1.data_ptr(), den1.data_ptr(), zc1.data_ptr(), stream)
+    assert rc == 0, pkg.strerror(rc)
+
+    O2, den2, zc2 = torch.empty_like(O1), torch.empty_like(den1), torch.empty_like(zc1)
+    n = lib.cxxattn_linattn_workspace_bytes(C.byref(d))
+    ws = torch.empty(n, dtype=torch.uint8, device=dev)
+    rc = lib.cxxattn_linattn_fwd(C.byref(d), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), O2.data_ptr(),
+                                 den2.data_ptr(), zc2.data_ptr(), ws.data_ptr(), n, stream)
+    assert rc == 0, pkg.strerror(rc)
+    torch.cuda.synchronize()
+    for name, a, b in (("O", O1, O2), ("den", den1, den2), ("z_cache", zc1, zc2)):
+        a, b = a.cpu().numpy(), b.cpu().numpy()
+        assert np.all(np.isfinite(a)), name
+        assert rel_err(a, b) < TOL, (name, rel_err(a, b))
+
+
+def test_noalloc_forward_matches_workspace_forward_on_two_calls_in_a_row(pkg, dev):
+    # first call: ELU+1 flavour, five chunks per sequence with a ragged tail (2 MB of the scratch)
+    call_both(pkg, dev, 71, B=24, S=300, D=64, E=64, feature_map=pkg.MAP_ELU1, eps_in_den=0)
+    # second call right after it: other shape and flavour, on top of the first call's leftovers
+    call_both(pkg, dev, 72, B=5, S=130, D=48, E=20, feature_map=pkg.MAP_NONE, eps_in_den=1)
+
+
+def test_noalloc_rejects_sizes_beyond_its_scratch(pkg, dev):
+    lib = pkg.lib()
+    cap = lib.cxxattn_linattn_noalloc_capacity()
+    assert cap == 8 << 20
+    B, S, D, E = 64, 1024, 64, 64  # 64 * 16 chunks * 64 * 65 * 4 bytes = 17 MB > 8 MiB
+    d = pkg.lin_desc(B, S, D, E, pkg.F32, pkg.MAP_ELU1, 0)
+    t = torch.zeros(16, device=dev)
+    rc = lib.cxxattn_linattn_fwd_noalloc(C.byref(d), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                         t.data_ptr(), None, None)
+    assert rc == -7 and "maximum" in pkg.strerror(rc)
