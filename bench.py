@@ -31,6 +31,7 @@ WORKLOADS = {  # name -> (B, S): B*S = 65536 tokens
     "softmax_s1024": (64, 1024),
     "softmax_s4096": (16, 4096),
     "softmax_s16384": (4, 16384),
+    "softmax_s4096_b4": (4, 4096),  # a quarter of the S=4096 point: the case profiler captures use
 }
 METRIC = "causal_softmax_attn_fwd_bwd_tflops_per_job"
 UNIT = "TFLOP/s"
