@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libcxxattn.so")
+# CXXATTN_LIBRARY points the binding at another build of the same C-ABI (an experimental variant).
+LIB_PATH = os.environ.get("CXXATTN_LIBRARY") or os.path.join(_HERE, "libcxxattn.so")
 
 F32, BF16 = 0, 1
 MAP_NONE, MAP_ELU1 = 0, 1

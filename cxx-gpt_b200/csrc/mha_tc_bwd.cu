@@ -32,13 +32,14 @@ constexpr int TILE_BYTES = BT * DH * 2;  // 16 KB
 constexpr int NTHREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_ST = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_P = 448;
-// K | V | Q x2 | dO x2 | dS (2 blocks) | (lse2, delta) x2
-constexpr size_t SMEM_BYTES = 8 * TILE_BYTES + 2 * 1024 + 1024;
+// K | V | Q x2 | dO x2 | dS (2 blocks) | (lse2, delta) x2 | dQ staging
+constexpr int STAGE_BYTES = 8 * 4096;  // dQ staging: one 32-row x 32-column fp32 block per compute warp
+constexpr size_t SMEM_BYTES = 8 * TILE_BYTES + 2 * 1024 + STAGE_BYTES + 1024;
 
 struct BwdParams {
     const float* lse2;   // [BH][Spad]  lse * log2(e), +inf on padding rows
     const float* delta;  // [BH][Spad]
-    float* dq_acc;       // [BH][Spad][64]
+    float* dq_acc;       // [BH][Spad/128][2 column halves][128 rows][32], 16-byte chunks XOR (row & 7)
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
     int* status;
@@ -81,7 +82,12 @@ __global__ void mha_tc_bwd_post_kernel(const float* __restrict__ dq_acc, __nv_bf
     if (row >= (int64_t)B * H * S) return;
     const int s = row % S;
     const int bh = row / S;
-    const float2 a = reinterpret_cast<const float2*>(dq_acc + ((int64_t)bh * Spad + s) * DH)[lane];
+    // accumulator layout of the main kernel: [bh][tile][column half][row][32], chunk ch of a row
+    // stored at chunk position ch ^ (row & 7)
+    const int tile = s / BT, r = s % BT, w = lane / 16, cc = (2 * lane) % 32;
+    const int pos = (((cc / 4) ^ (r & 7)) * 4) + (cc % 4);
+    const float2 a = *reinterpret_cast<const float2*>(
+        dq_acc + ((((int64_t)bh * (Spad / BT) + tile) * 2 + w) * BT + r) * 32 + pos);
     const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
     reinterpret_cast<__nv_bfloat162*>(dQ + off)[lane] = __floats2bfloat162_rn(a.x * scale, a.y * scale);
 }
@@ -92,9 +98,58 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                  "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+// Adds `bytes` of fp32 from shared memory into global memory (one bulk reduction in the L2).
+__device__ __forceinline__ void bulk_reduce_add_f32(float* gdst, const void* ssrc, uint32_t bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst),
+                 "r"(smem_u32(ssrc)), "r"(bytes)
                  : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// One arrival per warp, after every lane of the warp has done its part.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+// P^T for 64 query columns of one key row: exp2(c*S - lse2_q), masked on the diagonal tile (key
+// row r is visible to query column qc iff r <= qc), packed as bf16 pairs.
+template <bool DIAG>
+__device__ __forceinline__ void make_p(const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* l2, float c,
+                                       int r, int qc0, uint32_t (&pk)[32]) {
+    const float4* l4 = reinterpret_cast<const float4*>(l2);
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float4 la = l4[i / 4], lb = l4[8 + i / 4];
+        float a0 = ex2(fmaf(__uint_as_float(v0[i]), c, -la.x));
+        float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), c, -la.y));
+        float a2 = ex2(fmaf(__uint_as_float(v0[i + 2]), c, -la.z));
+        float a3 = ex2(fmaf(__uint_as_float(v0[i + 3]), c, -la.w));
+        float b0 = ex2(fmaf(__uint_as_float(v1[i]), c, -lb.x));
+        float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), c, -lb.y));
+        float b2 = ex2(fmaf(__uint_as_float(v1[i + 2]), c, -lb.z));
+        float b3 = ex2(fmaf(__uint_as_float(v1[i + 3]), c, -lb.w));
+        if (DIAG) {
+            a0 = r <= qc0 + i ? a0 : 0.f;
+            a1 = r <= qc0 + i + 1 ? a1 : 0.f;
+            a2 = r <= qc0 + i + 2 ? a2 : 0.f;
+            a3 = r <= qc0 + i + 3 ? a3 : 0.f;
+            b0 = r <= qc0 + 32 + i ? b0 : 0.f;
+            b1 = r <= qc0 + 32 + i + 1 ? b1 : 0.f;
+            b2 = r <= qc0 + 32 + i + 2 ? b2 : 0.f;
+            b3 = r <= qc0 + 32 + i + 3 ? b3 : 0.f;
+        }
+        pk[i / 2] = pack_bf16(a0, a1);
+        pk[i / 2 + 1] = pack_bf16(a2, a3);
+        pk[16 + i / 2] = pack_bf16(b0, b1);
+        pk[16 + i / 2 + 1] = pack_bf16(b2, b3);
+    }
+}
+// dS^T = P^T o (dP^T - delta_q) in packed bf16 arithmetic (the result is a bf16 MMA operand anyway).
+__device__ __forceinline__ uint32_t ds_pair(uint32_t p2, float dp0, float dp1, float d0, float d1) {
+    const __nv_bfloat162 t = __floats2bfloat162_rn(dp0 - d0, dp1 - d1);
+    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p2), t);
+    return *reinterpret_cast<const uint32_t*>(&r);
 }
 __device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
@@ -116,6 +171,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* sdO = smem + 4 * TILE_BYTES;  // 2 stages
     uint8_t* sDS = smem + 6 * TILE_BYTES;  // 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
     float* sStat = reinterpret_cast<float*>(smem + 8 * TILE_BYTES);  // [stage][lse2 | delta][128]
+    uint8_t* sStage = smem + 8 * TILE_BYTES + 2048;                  // [compute warp][32 rows][128 B]
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int ntile = p.Spad / BT;
@@ -136,12 +192,12 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(&qdo_free[s], 1);
         }
         mbar_init(&s_full, 1);
-        mbar_init(&s_free, 256);
+        mbar_init(&s_free, 8);  // one arrival per compute warp
         mbar_init(&dp_full, 1);
-        mbar_init(&p_ready, 256);
-        mbar_init(&ds_ready, 256);
+        mbar_init(&p_ready, 8);  // one arrival per compute warp
+        mbar_init(&ds_ready, 8);  // one arrival per compute warp
         mbar_init(&dq_full, 1);
-        mbar_init(&dq_free, 256);
+        mbar_init(&dq_free, 8);  // one arrival per compute warp
         mbar_init(&all_done, 1);
         fence_barrier_init();
     }
@@ -178,63 +234,61 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             constexpr uint32_t IDESC_SS = idesc_bf16(BT, BT, 0, 0);  // S^T, dP^T: both operands K-major
             constexpr uint32_t IDESC_TS = idesc_bf16(BT, DH, 0, 1);  // dV, dK: A in TMEM, B MN-major
             constexpr uint32_t IDESC_DQ = idesc_bf16(BT, DH, 1, 1);  // dQ: dS and K both MN-major
-            const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+            // Descriptors are built once; K steps and ring stages add constants to the start-address
+            // field (units of 16 bytes).
+            constexpr uint64_t TILE16 = TILE_BYTES >> 4;
+            const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16), dV = smem_desc_sw128(smem_u32(sV), 16);
+            const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16), dG0 = smem_desc_sw128(smem_u32(sdO), 16);
+            const uint64_t dDS = smem_desc_sw128(smem_u32(sDS), TILE_BYTES);
             auto issue_st = [&](int s) {
-                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES);
+                const uint64_t q = dQ0 + s * TILE16;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++)
-                    umma_ss(tmem + COL_ST, smem_desc_sw128(aK + 32 * k, 16), smem_desc_sw128(aQ + 32 * k, 16), IDESC_SS,
-                            k > 0);
+                for (int k = 0; k < DH / 16; k++) umma_ss(tmem + COL_ST, dK + 2 * k, q + 2 * k, IDESC_SS, k > 0);
                 umma_commit(&s_full);
             };
             auto issue_dp = [&](int s) {
-                const uint32_t aG = smem_u32(sdO + s * TILE_BYTES);
+                const uint64_t g = dG0 + s * TILE16;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++)
-                    umma_ss(tmem + COL_DP, smem_desc_sw128(aV + 32 * k, 16), smem_desc_sw128(aG + 32 * k, 16), IDESC_SS,
-                            k > 0);
+                for (int k = 0; k < DH / 16; k++) umma_ss(tmem + COL_DP, dV + 2 * k, g + 2 * k, IDESC_SS, k > 0);
                 umma_commit(&dp_full);
             };
-            mbar_wait(&kv_full, 0, guard, 501);
-            mbar_wait(&q_full[0], 0, guard, 502);
+            mbar_wait_poll(&kv_full, 0, guard, 501);
+            mbar_wait_poll(&q_full[0], 0, guard, 502);
             tc_fence_after();
             issue_st(0);
-            mbar_wait(&do_full[0], 0, guard, 503);
+            mbar_wait_poll(&do_full[0], 0, guard, 503);
             tc_fence_after();
             issue_dp(0);
             for (int it = 0; it < niter; it++) {
                 const int s = it & 1, sn = s ^ 1;
-                const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), aG = smem_u32(sdO + s * TILE_BYTES);
-                mbar_wait(&s_free, it & 1, guard, 504);
-                mbar_wait(&p_ready, it & 1, guard, 505);
+                const uint64_t q = dQ0 + s * TILE16, g = dG0 + s * TILE16;
+                mbar_wait_poll(&s_free, it & 1, guard, 504);
+                mbar_wait_poll(&p_ready, it & 1, guard, 505);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i
-                    umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, smem_desc_sw128(aG + 2048 * k, 0), IDESC_TS,
-                            it > 0 || k > 0);
+                    umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_TS, it > 0 || k > 0);
                 if (it + 1 < niter) {
-                    mbar_wait(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
+                    mbar_wait_poll(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
                     tc_fence_after();
                     issue_st(sn);  // its commit also covers the dV product above: P may then be rewritten
                 }
-                mbar_wait(&ds_ready, it & 1, guard, 507);
+                mbar_wait_poll(&ds_ready, it & 1, guard, 507);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i
-                    umma_ts(tmem + COL_DK, tmem + COL_DP + 8 * k, smem_desc_sw128(aQ + 2048 * k, 0), IDESC_TS,
-                            it > 0 || k > 0);
+                    umma_ts(tmem + COL_DK, tmem + COL_DP + 8 * k, q + 128 * k, IDESC_TS, it > 0 || k > 0);
                 umma_commit(&qdo_free[s]);
                 if (it > 0) {
-                    mbar_wait(&dq_free, (it - 1) & 1, guard, 508);
+                    mbar_wait_poll(&dq_free, (it - 1) & 1, guard, 508);
                     tc_fence_after();
                 }
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K
-                    umma_ss(tmem + COL_DQ, smem_desc_sw128(aDS + 2048 * k, TILE_BYTES), smem_desc_sw128(aK + 2048 * k, 0),
-                            IDESC_DQ, k > 0);
+                    umma_ss(tmem + COL_DQ, dDS + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
                 umma_commit(&dq_full);
                 if (it + 1 < niter) {
-                    mbar_wait(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
+                    mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
                     tc_fence_after();
                     issue_dp(sn);  // its commit also covers dK and dQ above: dS may then be rewritten
                 }
@@ -246,18 +300,25 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int w = warp / 4;
         const int r = (warp % 4) * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
-        float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + r) * DH + 32 * w;
-        auto drain_dq = [&](int q0) {
+        // dQ tile -> this warp's staging block (its 32 query rows x its 32 columns) -> one bulk
+        // reduction into the matching 4 KB block of the accumulator.
+        uint8_t* stage = sStage + warp * 4096;
+        float* acc_base = p.dq_acc + (((int64_t)bh * ntile * 2 + w) * BT + (warp % 4) * 32) * 32;
+        auto drain_dq = [&](int tile) {
             uint32_t dq[32];
             tmem_ld32(lane_base + COL_DQ + 32 * w, dq);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&dq_free);
-            float* dst = acc_base + (int64_t)q0 * DH;
+            warp_arrive(&dq_free, lane);
+            if (lane == 0) bulk_wait_read();  // the previous reduction has finished reading the block
+            __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-                red_add_v4(dst + i, __uint_as_float(dq[i]), __uint_as_float(dq[i + 1]), __uint_as_float(dq[i + 2]),
-                           __uint_as_float(dq[i + 3]));
+            for (int ch = 0; ch < 8; ch++)
+                *reinterpret_cast<uint4*>(stage + lane * 128 + ((ch ^ (lane & 7)) * 16)) =
+                    make_uint4(dq[4 * ch], dq[4 * ch + 1], dq[4 * ch + 2], dq[4 * ch + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)tile * 2 * BT * 32, stage, 4096);
         };
         for (int it = 0; it < niter; it++) {
             const int s = it & 1;
@@ -272,31 +333,18 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_ld32(lane_base + COL_ST + 64 * w + 32, v1);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&s_free);
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float a0 = ex2(fmaf(__uint_as_float(v0[i]), p.scale_log2, -l2[i]));
-                float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), p.scale_log2, -l2[i + 1]));
-                float b0 = ex2(fmaf(__uint_as_float(v1[i]), p.scale_log2, -l2[32 + i]));
-                float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), p.scale_log2, -l2[32 + i + 1]));
-                if (diag) {  // key k0+r is visible to query q0 + 64w + c iff r <= 64w + c
-                    a0 = r <= 64 * w + i ? a0 : 0.f;
-                    a1 = r <= 64 * w + i + 1 ? a1 : 0.f;
-                    b0 = r <= 64 * w + 32 + i ? b0 : 0.f;
-                    b1 = r <= 64 * w + 32 + i + 1 ? b1 : 0.f;
-                }
-                pk[i / 2] = pack_bf16(a0, a1);
-                pk[16 + i / 2] = pack_bf16(b0, b1);
-            }
+            warp_arrive(&s_free, lane);
+            if (diag) make_p<true>(v0, v1, l2, p.scale_log2, r, 64 * w, pk);
+            else make_p<false>(v0, v1, l2, p.scale_log2, r, 64 * w, pk);
             tmem_st32(lane_base + COL_P + 32 * w, pk);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_ready);
+            warp_arrive(&p_ready, lane);
 
             if (it > 0) {
                 mbar_wait(&dq_full, (it - 1) & 1, guard, 603);
                 tc_fence_after();
-                drain_dq((n + it - 1) * BT);
+                drain_dq(n + it - 1);
             }
 
             mbar_wait(&dp_full, it & 1, guard, 604);
@@ -306,14 +354,15 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_ld_wait();
             compute_bar_sync();  // both groups hold their dP^T before anyone overwrites it with dS^T
             uint32_t dsk[32];
+            const float4* d4 = reinterpret_cast<const float4*>(dl);
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                const float a0 = bf_lo(pk[i / 2]) * (__uint_as_float(v0[i]) - dl[i]);
-                const float a1 = bf_hi(pk[i / 2]) * (__uint_as_float(v0[i + 1]) - dl[i + 1]);
-                const float b0 = bf_lo(pk[16 + i / 2]) * (__uint_as_float(v1[i]) - dl[32 + i]);
-                const float b1 = bf_hi(pk[16 + i / 2]) * (__uint_as_float(v1[i + 1]) - dl[32 + i + 1]);
-                dsk[i / 2] = pack_bf16(a0, a1);
-                dsk[16 + i / 2] = pack_bf16(b0, b1);
+            for (int i = 0; i < 32; i += 4) {
+                const float4 da = d4[i / 4], db = d4[8 + i / 4];
+                dsk[i / 2] = ds_pair(pk[i / 2], __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]), da.x, da.y);
+                dsk[i / 2 + 1] = ds_pair(pk[i / 2 + 1], __uint_as_float(v0[i + 2]), __uint_as_float(v0[i + 3]), da.z, da.w);
+                dsk[16 + i / 2] = ds_pair(pk[16 + i / 2], __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]), db.x, db.y);
+                dsk[16 + i / 2 + 1] =
+                    ds_pair(pk[16 + i / 2 + 1], __uint_as_float(v1[i + 2]), __uint_as_float(v1[i + 3]), db.z, db.w);
             }
             tmem_st32(lane_base + COL_DP + 32 * w, dsk);
             // the same 64 values as one 128-byte row of block w of the MN-major dS operand
@@ -325,11 +374,12 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_st_wait();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(&ds_ready);
+            warp_arrive(&ds_ready, lane);
         }
         mbar_wait(&dq_full, (niter - 1) & 1, guard, 605);
         tc_fence_after();
-        drain_dq((n + niter - 1) * BT);
+        drain_dq(n + niter - 1);
+        if (lane == 0) bulk_wait_all();
 
         // epilogue: group 0 stores dV, group 1 stores scale * dK
         mbar_wait(&all_done, 0, guard, 606);

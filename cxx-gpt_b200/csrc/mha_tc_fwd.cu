@@ -83,7 +83,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&p_full[t], BM);
+            mbar_init(&p_full[t], 4);  // one arrival per softmax warp
             mbar_init(&o_done[t], 1);
         }
         fence_barrier_init();
@@ -117,43 +117,48 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t IDESC_S = idesc_bf16(BM, BN, 0, 0);  // Q, K both K-major
             constexpr uint32_t IDESC_O = idesc_bf16(BM, DH, 0, 1);  // P from TMEM, V MN-major
+            // Descriptors are built once; a K step or a ring stage only adds a constant to the
+            // 14-bit start-address field (units of 16 bytes), which cannot carry out of it.
+            const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16);
+            const uint64_t dK0 = smem_desc_sw128(smem_u32(sK), 16);
+            const uint64_t dV0 = smem_desc_sw128(smem_u32(sV), 0);
+            constexpr uint64_t TILE16 = TILE_BYTES >> 4;
             auto issue_s = [&](int t, int s) {
-                const uint32_t qa = smem_u32(sQ + t * TILE_BYTES), ka = smem_u32(sK + s * TILE_BYTES);
+                const uint64_t qd = dQ0 + t * TILE16, kd = dK0 + s * TILE16;
+                const uint32_t d = tmem + COL_S + t * BN;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++)
-                    umma_ss(tmem + COL_S + t * BN, smem_desc_sw128(qa + 32 * k, 16), smem_desc_sw128(ka + 32 * k, 16),
-                            IDESC_S, k > 0);
+                for (int k = 0; k < DH / 16; k++) umma_ss(d, qd + 2 * k, kd + 2 * k, IDESC_S, k > 0);
                 umma_commit(&s_full[t]);
             };
             auto issue_pv = [&](int t, int s, bool acc) {
-                const uint32_t va = smem_u32(sV + s * TILE_BYTES);
+                const uint64_t vd = dV0 + s * TILE16;
+                const uint32_t d = tmem + COL_O + t * DH, a = tmem + COL_S + t * BN;
+                umma_ts(d, a, vd, IDESC_O, acc);
 #pragma unroll
-                for (int k = 0; k < BN / 16; k++)
-                    umma_ts(tmem + COL_O + t * DH, tmem + COL_S + t * BN + 8 * k, smem_desc_sw128(va + 2048 * k, 0),
-                            IDESC_O, acc || k > 0);
+                for (int k = 1; k < BN / 16; k++) umma_ts(d, a + 8 * k, vd + 128 * k, IDESC_O, true);
             };
             const int last0 = n0, last1 = n0 + 1;  // last KV tile of each query tile
-            mbar_wait(&q_full, 0, guard, 201);
-            mbar_wait(&k_full[0], 0, guard, 202);
+            mbar_wait_poll(&q_full, 0, guard, 201);
+            mbar_wait_poll(&k_full[0], 0, guard, 202);
             tc_fence_after();
             issue_s(0, 0);
             if (has_t1) issue_s(1, 0);
             for (int j = 0; j < nkv; j++) {
                 const int s = j % STAGES, sn = (j + 1) % STAGES;
-                mbar_wait(&v_full[s], (j / STAGES) & 1, guard, 203);
+                mbar_wait_poll(&v_full[s], (j / STAGES) & 1, guard, 203);
                 if (j <= last0) {
-                    mbar_wait(&p_full[0], j & 1, guard, 204);
+                    mbar_wait_poll(&p_full[0], j & 1, guard, 204);
                     tc_fence_after();
                     issue_pv(0, s, j > 0);
                     if (j == last0) umma_commit(&o_done[0]);
                 }
                 if (j + 1 < nkv) {
-                    mbar_wait(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
+                    mbar_wait_poll(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
                     tc_fence_after();
                     if (j + 1 <= last0) issue_s(0, sn);
                 }
                 if (has_t1) {
-                    mbar_wait(&p_full[1], j & 1, guard, 206);
+                    mbar_wait_poll(&p_full[1], j & 1, guard, 206);
                     tc_fence_after();
                     issue_pv(1, s, j > 0);
                     if (j == last1) umma_commit(&o_done[1]);
@@ -176,73 +181,112 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int j = 0; j <= jlast; j++) {
                 mbar_wait(&s_full[t], j & 1, guard, 301 + t);
                 tc_fence_after();
-                // pass 1: row maximum (the diagonal tile is masked: key column c is visible iff c <= r)
-                float mx = -INFINITY;
                 const bool diag = j == jlast;
+                bool slow = j == 0 || diag;
+                if (!slow) {
+                    // Fast path (interior tiles): one pass against the current maximum m.  The 128
+                    // scores are read in four chunks, the next chunk's TMEM load in flight while
+                    // this one is exponentiated; P stays in registers until the whole row is known
+                    // to fit (max P <= 2^8), so S is still intact if the slow path has to take over.
+                    uint32_t pk[64], va[32], vb[32];
+                    float rs = 0.f;
+                    __nv_bfloat162 pmax = __floats2bfloat162_rn(0.f, 0.f);
+                    tmem_ld32(tS, va);
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t v0[32], v1[32];
-                    tmem_ld32(tS + 64 * c, v0);
-                    tmem_ld32(tS + 64 * c + 32, v1);
-                    tmem_ld_wait();
+                    for (int c = 0; c < 4; c++) {
+                        tmem_ld_wait();
+                        if (c == 0 || c == 2) tmem_ld32(tS + 32 * (c + 1), vb);
+                        if (c == 1) tmem_ld32(tS + 64, va);
+                        const uint32_t(&cur)[32] = (c & 1) ? vb : va;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const float a = (!diag || 64 * c + i <= r) ? __uint_as_float(v0[i]) : -INFINITY;
-                        const float bb = (!diag || 64 * c + 32 + i <= r) ? __uint_as_float(v1[i]) : -INFINITY;
-                        mx = fmaxf(mx, fmaxf(a, bb));
-                    }
-                }
-                const float m_new = fmaxf(m, mx * p.scale_log2);
-                const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
-                const float m_use = raise ? m_new : m;
-                const float alpha = raise ? ex2(m - m_new) : 1.0f;
-                if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                    // S_t(j) completing implies PV_t(j-1) has completed: O_t is stable here.
-                    uint32_t o0[32], o1[32];
-                    tmem_ld32(tO, o0);
-                    tmem_ld32(tO + 32, o1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-                        o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
-                    }
-                    tmem_st32(tO, o0);
-                    tmem_st32(tO + 32, o1);
-                    tmem_st_wait();
-                }
-                m = m_use;
-                // pass 2: P = exp2(c*S - m) as bf16 pairs; chunk c of P (64 values, 32 columns) only
-                // overwrites S columns that have already been consumed.
-                float rs = 0.f;
-#pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t v0[32], v1[32], pk[32];
-                    tmem_ld32(tS + 64 * c, v0);
-                    tmem_ld32(tS + 64 * c + 32, v1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float a0 = ex2(fmaf(__uint_as_float(v0[i]), p.scale_log2, -m_use));
-                        float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), p.scale_log2, -m_use));
-                        float b0 = ex2(fmaf(__uint_as_float(v1[i]), p.scale_log2, -m_use));
-                        float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), p.scale_log2, -m_use));
-                        if (diag) {
-                            a0 = 64 * c + i <= r ? a0 : 0.f;
-                            a1 = 64 * c + i + 1 <= r ? a1 : 0.f;
-                            b0 = 64 * c + 32 + i <= r ? b0 : 0.f;
-                            b1 = 64 * c + 32 + i + 1 <= r ? b1 : 0.f;
+                        for (int i = 0; i < 32; i += 2) {
+                            const float a0 = ex2(fmaf(__uint_as_float(cur[i]), p.scale_log2, -m));
+                            const float a1 = ex2(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2, -m));
+                            rs += a0 + a1;
+                            const __nv_bfloat162 pp = __floats2bfloat162_rn(a0, a1);
+                            pmax = __hmax2(pmax, pp);
+                            pk[16 * c + i / 2] = *reinterpret_cast<const uint32_t*>(&pp);
                         }
-                        rs += (a0 + a1) + (b0 + b1);
-                        pk[i / 2] = pack_bf16(a0, a1);
-                        pk[16 + i / 2] = pack_bf16(b0, b1);
                     }
-                    tmem_st32(tS + 32 * c, pk);
+                    const float pm = fmaxf(__low2float(pmax), __high2float(pmax));
+                    slow = __any_sync(0xffffffffu, !(pm <= 256.0f));
+                    if (!slow) {
+                        tmem_st32(tS, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+                        tmem_st32(tS + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+                        l += rs;
+                    }
                 }
-                l = l * alpha + rs;
+                if (slow) {
+                    // Slow path (first tile, diagonal tile, or a row whose maximum grows by more than
+                    // 2^8): pass 1 finds the masked row maximum, O is rescaled if needed, pass 2
+                    // exponentiates.  On the diagonal tile key column c is visible iff c <= r.
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        uint32_t v0[32], v1[32];
+                        tmem_ld32(tS + 64 * c, v0);
+                        tmem_ld32(tS + 64 * c + 32, v1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const float a = (!diag || 64 * c + i <= r) ? __uint_as_float(v0[i]) : -INFINITY;
+                            const float bb = (!diag || 64 * c + 32 + i <= r) ? __uint_as_float(v1[i]) : -INFINITY;
+                            mx = fmaxf(mx, fmaxf(a, bb));
+                        }
+                    }
+                    const float m_new = fmaxf(m, mx * p.scale_log2);
+                    const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
+                    const float m_use = raise ? m_new : m;
+                    const float alpha = raise ? ex2(m - m_new) : 1.0f;
+                    if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                        // S_t(j) completing implies PV_t(j-1) has completed: O_t is stable here.
+                        uint32_t o0[32], o1[32];
+                        tmem_ld32(tO, o0);
+                        tmem_ld32(tO + 32, o1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+                            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+                        }
+                        tmem_st32(tO, o0);
+                        tmem_st32(tO + 32, o1);
+                        tmem_st_wait();
+                    }
+                    m = m_use;
+                    // pass 2: chunk c of P (64 values, 32 columns) only overwrites S columns that
+                    // have already been consumed.
+                    float rs = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        uint32_t v0[32], v1[32], pk[32];
+                        tmem_ld32(tS + 64 * c, v0);
+                        tmem_ld32(tS + 64 * c + 32, v1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float a0 = ex2(fmaf(__uint_as_float(v0[i]), p.scale_log2, -m_use));
+                            float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), p.scale_log2, -m_use));
+                            float b0 = ex2(fmaf(__uint_as_float(v1[i]), p.scale_log2, -m_use));
+                            float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), p.scale_log2, -m_use));
+                            if (diag) {
+                                a0 = 64 * c + i <= r ? a0 : 0.f;
+                                a1 = 64 * c + i + 1 <= r ? a1 : 0.f;
+                                b0 = 64 * c + 32 + i <= r ? b0 : 0.f;
+                                b1 = 64 * c + 32 + i + 1 <= r ? b1 : 0.f;
+                            }
+                            rs += (a0 + a1) + (b0 + b1);
+                            pk[i / 2] = pack_bf16(a0, a1);
+                            pk[16 + i / 2] = pack_bf16(b0, b1);
+                        }
+                        tmem_st32(tS + 32 * c, pk);
+                    }
+                    l = l * alpha + rs;
+                }
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(&p_full[t]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[t]);
             }
             // epilogue: O_t / l -> bf16 -> global; lse
             mbar_wait(&o_done[t], 0, guard, 311 + t);

@@ -24,6 +24,7 @@ struct Guard {
 };
 
 constexpr uint64_t kWaitNs = 2000000000ull;  // a wait gives up after 2 s
+constexpr uint32_t kSuspendHintNs = 20000;   // how long one try_wait may keep the thread suspended
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -47,10 +48,10 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
@@ -71,6 +72,33 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
             if (*g.abort_flag) return;
             if (*reinterpret_cast<volatile int*>(g.status) != 0) break;
             if (global_ns() - t0 > kWaitNs) break;
+        }
+    }
+    *g.abort_flag = 1;
+    atomicCAS(g.status, 0, code);
+}
+
+// The same bounded wait for a role that is a single thread (the MMA issuer): it polls without the
+// suspend hint, so it reacts within a few cycles of the arrival; one polling thread costs nothing.
+__device__ __forceinline__ void mbar_wait_poll(uint64_t* bar, uint32_t parity, const Guard& g, int code) {
+    const uint32_t addr = smem_u32(bar);
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return;
+        if ((i & 1023u) == 1023u) {
+            if (*g.abort_flag) return;
+            if (*reinterpret_cast<volatile int*>(g.status) != 0) break;
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitNs) break;
         }
     }
     *g.abort_flag = 1;
