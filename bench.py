@@ -32,7 +32,12 @@ WORKLOADS = {  # name -> (B, S): B*S = 65536 tokens
     "softmax_s4096": (16, 4096),
     "softmax_s16384": (4, 16384),
     "softmax_s4096_b4": (4, 4096),  # a quarter of the S=4096 point: the case profiler captures use
+    # ELU+1 linear attention on the same tokens (heads folded into the batch: B' = B*12, D = E = 64, fp32)
+    "linattn_s1024": (64, 1024),
+    "linattn_s4096": (16, 4096),
+    "linattn_s16384": (4, 16384),
 }
+LIN_METRIC = "causal_linear_attn_fwd_bwd_algorithmic_gbps_per_job"
 METRIC = "causal_softmax_attn_fwd_bwd_tflops_per_job"
 UNIT = "TFLOP/s"
 
@@ -110,15 +115,33 @@ def run_reference(args):
     B, S = WORKLOADS[args.workload]
     # bounded sample: one unit per core and step; S=16384 units are cut to keep a step in seconds
     s_eff = min(S, 4096)
+    lin = args.workload.startswith("linattn")
+
+    def sample(s_len):
+        if not lin:
+            return cpu_sample(B, s_len)
+        import numpy as np
+        import oracle
+        orc = oracle.Oracle()
+        units = orc.num_threads()
+        rng = np.random.default_rng(3)
+        q, k, v, g_ = (rng.standard_normal((units * s_len, DH)).astype(np.float32) for _ in range(4))
+        t0 = time.perf_counter()
+        o, dn, _ = orc.linattn_fwd(q, k, v, units, s_len, DH, DH)
+        orc.kernel_attn_bwd(q, k, v, o, g_, dn, units, s_len, DH, DH)
+        dt = time.perf_counter() - t0
+        return (lin_bytes_fwd_bwd(units, s_len, DH, DH) / dt / 1e9, units, dt,
+                f"{units} of {B * H} units of S={s_len}, D=E={DH}, fp32 oracle, fwd+bwd")
     for _ in range(min(args.warmup, 1)):
-        cpu_sample(B, min(S, 512))
+        sample(min(S, 512))
     vals, times = [], []
     desc, cores = "", 1
     for _ in range(args.steps):
-        tf, cores, dt, desc = cpu_sample(B, s_eff)
+        tf, cores, dt, desc = sample(s_eff)
         vals.append(tf)
         times.append(dt)
     value = sum(vals) / len(vals)
+    METRIC, UNIT = (LIN_METRIC, "GB/s") if lin else (globals()["METRIC"], globals()["UNIT"])
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -249,6 +272,150 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def lin_bytes_fwd_bwd(units, S, D, E, w=4):
+    """Algorithmic HBM bytes of forward + backward per the roofline definition: forward reads Q,K,V
+    and writes O, den; backward reads Q,K,V,O,dO,den and writes dQ,dK,dV; caches, dnum/dden and chunk
+    states do not count."""
+    fwd = (2 * D + 2 * E) * w + 4
+    bwd = (2 * D + 3 * E) * w + 4 + (2 * D + E) * w
+    return float(units) * S * (fwd + bwd)
+
+
+def run_ours_linattn(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path in the product")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B0, S = WORKLOADS[args.workload]
+    B, D, E = B0 * H, DH, DH
+    N = B * S
+    gen = torch.Generator(device="cpu").manual_seed(3 + rank)
+    hQ, hK, hV, hdO = (torch.randn(N, D, generator=gen).pin_memory() for _ in range(4))
+    Q, K, V, dO = (t.to(dev) for t in (hQ, hK, hV, hdO))
+    O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
+    den = torch.empty(N, device=dev)
+
+    def step():
+        pkg.linattn_fwd(Q, K, V, O, den, None, B, S, D, E, pkg.MAP_ELU1, 0)
+        pkg.linattn_bwd(Q, K, V, O, dO, den, dQ, dK, dV, B, S, D, E, pkg.MAP_ELU1, 0)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    sampler.stop_flag = True
+    ms = e0.elapsed_time(e1) / args.steps
+
+    # end to end: pinned host tensors in, host tensors out (plain copies around the same two calls)
+    hO, hdQ, hdK, hdV = (torch.empty(N, D).pin_memory() for _ in range(4))
+    hden = torch.empty(N).pin_memory()
+
+    def e2e_step():
+        for d_, h_ in ((Q, hQ), (K, hK), (V, hV), (dO, hdO)):
+            d_.copy_(h_, non_blocking=True)
+        step()
+        for h_, d_ in ((hO, O), (hden, den), (hdQ, dQ), (hdK, dK), (hdV, dV)):
+            h_.copy_(d_, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(3, min(args.steps, 10))
+    for _ in range(n_e2e):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
+
+    # the reference's own serial-scan CUDA kernels on the same tensors (when they were built)
+    ref_ms = None
+    try:
+        import oracle
+        if rank == 0 and oracle.ReferenceCuda.available():
+            rc = oracle.ReferenceCuda()
+            buf = rc.scan_buffers(B, S, D, E, dev)
+            rc.kernel_attn(Q, K, V, dO, buf, B, S, D, E)
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
+            for _ in range(2):
+                rc.kernel_attn(Q, K, V, dO, buf, B, S, D, E)
+            r1.record()
+            torch.cuda.synchronize()
+            ref_ms = r0.elapsed_time(r1) / 2
+            ref_err = float((buf["O"] - O).abs().max() / buf["O"].abs().max())
+    except Exception as e:  # the baseline is optional; say why it is missing
+        ref_ms, ref_err = None, repr(e)
+
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    if rank == 0:
+        nbytes = lin_bytes_fwd_bwd(B, S, D, E)
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                hbm, how = float(json.load(f)["hbm_gbs"]), "measured"
+        except Exception:
+            hbm, how = 6650.0, "fallback"
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        line = {"metric": LIN_METRIC, "value": world * gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.workload, "units_per_gpu": B, "S": S, "D": D, "E": E,
+                           "tokens_per_gpu": B0 * S, "feature_map": "elu+1",
+                           "l2": "9 tensors x %.0f MB per step exceed the 126 MB L2" % (N * D * 4 / 1e6)},
+                "tokens_per_s": world * B0 * S / (ms * 1e-3), "gpu_launches": args.steps * 12,
+                "clocks": sampler.result(),
+                "e2e": {"value": world * nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": 4 * N * D * 4, "d2h_bytes_per_step": 4 * N * D * 4 + N * 4},
+                "roofline": {"bound": "hbm", "kernel": "chunk_state + chunk_scan + chunk_apply (fwd + bwd call)",
+                             "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s", "frac": gbs / hbm,
+                             "traffic": None},
+                "reference_cuda": {"ms_per_step": ref_ms, "speedup": (ref_ms / ms) if ref_ms else None,
+                                   "max_rel_diff_O": ref_err if ref_ms else None,
+                                   "what": "reference two_stage_cuda kernel_attn fwd+step1+dQ+dKdV, unmodified, sm_100"}}
+        if world == 1 and not args.no_cpu_baseline:
+            import numpy as np
+            import oracle
+            orc = oracle.Oracle()
+            units = orc.num_threads()
+            s_eff = min(S, 4096)
+            rng = np.random.default_rng(3)
+            q, k, v, g_ = (rng.standard_normal((units * s_eff, D)).astype(np.float32) for _ in range(4))
+            t0 = time.perf_counter()
+            o, dn, _ = orc.linattn_fwd(q, k, v, units, s_eff, D, E)
+            orc.kernel_attn_bwd(q, k, v, o, g_, dn, units, s_eff, D, E)
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": lin_bytes_fwd_bwd(units, s_eff, D, E) / dt / 1e9, "unit": "GB/s",
+                                    "cores": units, "kind": "port",
+                                    "sample": f"{units} of {B} units of S={s_eff}, fp32 oracle, fwd+bwd ({dt:.1f} s)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -261,6 +428,8 @@ def main():
     if args.impl == "reference":
         args.steps = min(args.steps, 3)
         run_reference(args)
+    elif args.workload.startswith("linattn"):
+        run_ours_linattn(args)
     else:
         run_ours(args)
 

@@ -58,7 +58,7 @@ public:
     CudaTensor(const CudaTensor& o) : CudaTensor(o.shape_) {
         if (n_) CHECK_CUDA_ERROR(cudaMemcpy(ptr_, o.ptr_, n_ * sizeof(T), cudaMemcpyDeviceToDevice));
     }
-    CudaTensor(CudaTensor&& o) noexcept : shape_(std::move(o.shape_)), n_(o.n_), ptr_(o.ptr_) {
+    CudaTensor(CudaTensor&& o) noexcept : shape_(std::move(o.shape_)), n_(o.n_), ptr_(o.ptr_), owns_(o.owns_) {
         o.ptr_ = nullptr;
         o.n_ = 0;
     }
@@ -66,10 +66,21 @@ public:
         std::swap(shape_, o.shape_);
         std::swap(n_, o.n_);
         std::swap(ptr_, o.ptr_);
+        std::swap(owns_, o.owns_);
         return *this;
     }
     ~CudaTensor() {
-        if (ptr_) cudaFree(ptr_);
+        if (ptr_ && owns_) cudaFree(ptr_);
+    }
+    // Not part of TensorN: wraps device memory owned by someone else (used by test harnesses that
+    // hand raw pointers to functions taking CudaTensor references).
+    static CudaTensor view(T* ptr, std::vector<size_t> shape) {
+        CudaTensor c;
+        c.shape_ = std::move(shape);
+        c.n_ = shape_size(c.shape_);
+        c.ptr_ = ptr;
+        c.owns_ = false;
+        return c;
     }
     T* device_ptr() { return ptr_; }
     const T* device_ptr() const { return ptr_; }
@@ -96,6 +107,7 @@ private:
     std::vector<size_t> shape_;
     size_t n_ = 0;
     T* ptr_ = nullptr;
+    bool owns_ = true;
 };
 
 }  // namespace TensorN

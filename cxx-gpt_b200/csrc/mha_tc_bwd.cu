@@ -9,11 +9,17 @@
 //
 //   S^T  = K Q_i^T                 (SS MMA, keys on the 128 TMEM lanes, queries on 128 columns)
 //   dP^T = V dO_i^T                (SS MMA)
-//   P^T  = exp2(c S^T - lse2_q)    dS^T = P^T o (dP^T - delta_q)        (8 warps, lane = key row)
-//   dV  += P^T dO_i                (TS MMA: P^T bf16 in TMEM, dO_i as an MN-major operand)
-//   dK  += dS^T Q_i                (TS MMA: dS^T bf16 in TMEM)
-//   dQ_i = dS K                    (SS MMA: dS written to shared memory as an MN-major operand),
-//                                  drained from TMEM with vector red.add into an fp32 accumulator
+//   P^T  = exp2(c S^T - lse2_q)    (warps 0-3, lane = key row)  -> bf16 in TMEM
+//   dS^T = P^T o (dP^T - delta_q)  (warps 4-7, lane = key row)  -> bf16 in shared memory, one tile that
+//                                  is both a K-major operand [keys][queries] and an MN-major one
+//   dV  += P^T dO_i                (TS MMA: P^T from TMEM, dO_i as an MN-major operand)
+//   dK  += dS^T Q_i                (SS MMA: dS read K-major, Q_i MN-major)
+//   dQ_i = dS K                    (SS MMA: dS read MN-major), drained from TMEM through shared memory
+//                                  with one bulk reduce-add per warp into an fp32 accumulator
+//
+// The two warp groups work on different phases of the pipeline (the P group is already on tile i+1
+// while the dS group finishes tile i), and the MMA warp issues S^T(i+1) and dP^T(i+1) as soon as
+// tile i's have been read out of TMEM, so the tensor pipe does not wait for the exponentials.
 //
 // Three launches per call: a row pre-pass (delta = dO.O, lse in log2 units padded to whole tiles,
 // accumulator cleared), the main kernel, and a pass turning the accumulator into bf16 dQ.
@@ -33,13 +39,13 @@ constexpr int NTHREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_ST = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_P = 448;
 // K | V | Q x2 | dO x2 | dS (2 blocks) | (lse2, delta) x2 | dQ staging
-constexpr int STAGE_BYTES = 8 * 4096;  // dQ staging: one 32-row x 32-column fp32 block per compute warp
+constexpr int STAGE_BYTES = 4 * 8192;  // dQ staging: 32 rows x 64 fp32 per warp of the dS group
 constexpr size_t SMEM_BYTES = 8 * TILE_BYTES + 2 * 1024 + STAGE_BYTES + 1024;
 
 struct BwdParams {
     const float* lse2;   // [BH][Spad]  lse * log2(e), +inf on padding rows
     const float* delta;  // [BH][Spad]
-    float* dq_acc;       // [BH][Spad/128][2 column halves][128 rows][32], 16-byte chunks XOR (row & 7)
+    float* dq_acc;       // [BH][Spad][64]; the 16-byte chunk ch of a row is stored at chunk ch ^ (row & 7)
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
     int* status;
@@ -82,12 +88,10 @@ __global__ void mha_tc_bwd_post_kernel(const float* __restrict__ dq_acc, __nv_bf
     if (row >= (int64_t)B * H * S) return;
     const int s = row % S;
     const int bh = row / S;
-    // accumulator layout of the main kernel: [bh][tile][column half][row][32], chunk ch of a row
-    // stored at chunk position ch ^ (row & 7)
-    const int tile = s / BT, r = s % BT, w = lane / 16, cc = (2 * lane) % 32;
-    const int pos = (((cc / 4) ^ (r & 7)) * 4) + (cc % 4);
-    const float2 a = *reinterpret_cast<const float2*>(
-        dq_acc + ((((int64_t)bh * (Spad / BT) + tile) * 2 + w) * BT + r) * 32 + pos);
+    // accumulator layout of the main kernel: row-major [bh][Spad][64] with the 16-byte chunk ch of a
+    // row stored at chunk position ch ^ (row & 7)
+    const int pos = (((lane / 2) ^ (s & 7)) * 4) + (2 * lane) % 4;
+    const float2 a = *reinterpret_cast<const float2*>(dq_acc + ((int64_t)bh * Spad + s) * DH + pos);
     const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
     reinterpret_cast<__nv_bfloat162*>(dQ + off)[lane] = __floats2bfloat162_rn(a.x * scale, a.y * scale);
 }
@@ -112,55 +116,72 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
     __syncwarp();
     if (lane == 0) mbar_arrive(bar);
 }
-// P^T for 64 query columns of one key row: exp2(c*S - lse2_q), masked on the diagonal tile (key
-// row r is visible to query column qc iff r <= qc), packed as bf16 pairs.
+// P^T for 32 query columns of one key row: exp2(c*S - lse2_q) as 16 bf16 pairs; on the diagonal
+// tile key row r is visible to query column qc iff r <= qc.
 template <bool DIAG>
-__device__ __forceinline__ void make_p(const uint32_t (&v0)[32], const uint32_t (&v1)[32], const float* l2, float c,
-                                       int r, int qc0, uint32_t (&pk)[32]) {
+__device__ __forceinline__ void p_chunk(const uint32_t (&v)[32], const float* l2, float c, int r, int qc0,
+                                        uint32_t* pk) {
     const float4* l4 = reinterpret_cast<const float4*>(l2);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-        const float4 la = l4[i / 4], lb = l4[8 + i / 4];
-        float a0 = ex2(fmaf(__uint_as_float(v0[i]), c, -la.x));
-        float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), c, -la.y));
-        float a2 = ex2(fmaf(__uint_as_float(v0[i + 2]), c, -la.z));
-        float a3 = ex2(fmaf(__uint_as_float(v0[i + 3]), c, -la.w));
-        float b0 = ex2(fmaf(__uint_as_float(v1[i]), c, -lb.x));
-        float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), c, -lb.y));
-        float b2 = ex2(fmaf(__uint_as_float(v1[i + 2]), c, -lb.z));
-        float b3 = ex2(fmaf(__uint_as_float(v1[i + 3]), c, -lb.w));
+        const float4 la = l4[i / 4];
+        float a0 = ex2(fmaf(__uint_as_float(v[i]), c, -la.x));
+        float a1 = ex2(fmaf(__uint_as_float(v[i + 1]), c, -la.y));
+        float a2 = ex2(fmaf(__uint_as_float(v[i + 2]), c, -la.z));
+        float a3 = ex2(fmaf(__uint_as_float(v[i + 3]), c, -la.w));
         if (DIAG) {
             a0 = r <= qc0 + i ? a0 : 0.f;
             a1 = r <= qc0 + i + 1 ? a1 : 0.f;
             a2 = r <= qc0 + i + 2 ? a2 : 0.f;
             a3 = r <= qc0 + i + 3 ? a3 : 0.f;
-            b0 = r <= qc0 + 32 + i ? b0 : 0.f;
-            b1 = r <= qc0 + 32 + i + 1 ? b1 : 0.f;
-            b2 = r <= qc0 + 32 + i + 2 ? b2 : 0.f;
-            b3 = r <= qc0 + 32 + i + 3 ? b3 : 0.f;
         }
         pk[i / 2] = pack_bf16(a0, a1);
         pk[i / 2 + 1] = pack_bf16(a2, a3);
-        pk[16 + i / 2] = pack_bf16(b0, b1);
-        pk[16 + i / 2 + 1] = pack_bf16(b2, b3);
     }
 }
-// dS^T = P^T o (dP^T - delta_q) in packed bf16 arithmetic (the result is a bf16 MMA operand anyway).
-__device__ __forceinline__ uint32_t ds_pair(uint32_t p2, float dp0, float dp1, float d0, float d1) {
-    const __nv_bfloat162 t = __floats2bfloat162_rn(dp0 - d0, dp1 - d1);
-    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p2), t);
-    return *reinterpret_cast<const uint32_t*>(&r);
+// dS^T = P^T o (dP^T - delta_q) for 32 query columns, in packed bf16 arithmetic (the result is a
+// bf16 MMA operand anyway).
+__device__ __forceinline__ void ds_chunk(const uint32_t* p16, const uint32_t (&v)[32], const float* dl, uint32_t* ds) {
+    const float4* d4 = reinterpret_cast<const float4*>(dl);
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float4 d = d4[i / 4];
+        const __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[i]) - d.x, __uint_as_float(v[i + 1]) - d.y);
+        const __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[i + 2]) - d.z, __uint_as_float(v[i + 3]) - d.w);
+        const __nv_bfloat162 r0 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p16[i / 2]), t0);
+        const __nv_bfloat162 r1 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p16[i / 2 + 1]), t1);
+        ds[i / 2] = *reinterpret_cast<const uint32_t*>(&r0);
+        ds[i / 2 + 1] = *reinterpret_cast<const uint32_t*>(&r1);
+    }
 }
-__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+// One key row (64 fp32 TMEM columns of this lane) -> scaled bf16 -> global.
+__device__ __forceinline__ void store_rows(uint32_t taddr, __nv_bfloat16* base, float f, int key, int b, int h,
+                                           const BwdParams& p) {
+    uint32_t o0[32], o1[32];
+    tmem_ld32(taddr, o0);
+    tmem_ld32(taddr + 32, o1);
+    tmem_ld_wait();
+    if (key >= p.S) return;
+    uint4* dst = reinterpret_cast<uint4*>(base + (int64_t)b * p.sb + (int64_t)key * p.ss + (int64_t)h * p.sh);
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * f, __uint_as_float(o0[i + 1]) * f),
+                                pack_bf16(__uint_as_float(o0[i + 2]) * f, __uint_as_float(o0[i + 3]) * f),
+                                pack_bf16(__uint_as_float(o0[i + 4]) * f, __uint_as_float(o0[i + 5]) * f),
+                                pack_bf16(__uint_as_float(o0[i + 6]) * f, __uint_as_float(o0[i + 7]) * f));
+        dst[4 + i / 8] = make_uint4(pack_bf16(__uint_as_float(o1[i]) * f, __uint_as_float(o1[i + 1]) * f),
+                                    pack_bf16(__uint_as_float(o1[i + 2]) * f, __uint_as_float(o1[i + 3]) * f),
+                                    pack_bf16(__uint_as_float(o1[i + 4]) * f, __uint_as_float(o1[i + 5]) * f),
+                                    pack_bf16(__uint_as_float(o1[i + 6]) * f, __uint_as_float(o1[i + 7]) * f));
+    }
+}
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t kv_full, q_full[2], do_full[2], qdo_free[2], s_full, s_free, dp_full, p_ready, ds_ready,
-        dq_full, dq_free, all_done;
+    __shared__ uint64_t kv_full, q_full[2], do_full[2], qdo_free[2], s_full, s_free, dp_full, dp_free, p_ready, p_read,
+        dv_done, ds_ready, dq_full, dq_free, all_done;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -171,7 +192,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* sdO = smem + 4 * TILE_BYTES;  // 2 stages
     uint8_t* sDS = smem + 6 * TILE_BYTES;  // 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
     float* sStat = reinterpret_cast<float*>(smem + 8 * TILE_BYTES);  // [stage][lse2 | delta][128]
-    uint8_t* sStage = smem + 8 * TILE_BYTES + 2048;                  // [compute warp][32 rows][128 B]
+    uint8_t* sStage = smem + 8 * TILE_BYTES + 2048;                  // [dS-group warp][32 rows][256 B]
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int ntile = p.Spad / BT;
@@ -192,13 +213,17 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(&qdo_free[s], 1);
         }
         mbar_init(&s_full, 1);
-        mbar_init(&s_free, 8);  // one arrival per compute warp
         mbar_init(&dp_full, 1);
-        mbar_init(&p_ready, 8);  // one arrival per compute warp
-        mbar_init(&ds_ready, 8);  // one arrival per compute warp
+        mbar_init(&dv_done, 1);
         mbar_init(&dq_full, 1);
-        mbar_init(&dq_free, 8);  // one arrival per compute warp
         mbar_init(&all_done, 1);
+        // one arrival per warp of the group that signals
+        mbar_init(&s_free, 4);
+        mbar_init(&p_ready, 4);
+        mbar_init(&dp_free, 4);
+        mbar_init(&p_read, 4);
+        mbar_init(&ds_ready, 4);
+        mbar_init(&dq_free, 4);
         fence_barrier_init();
     }
     if (warp == 9) tmem_alloc(&tmem_slot, TMEM_COLS);
@@ -232,14 +257,15 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t IDESC_SS = idesc_bf16(BT, BT, 0, 0);  // S^T, dP^T: both operands K-major
-            constexpr uint32_t IDESC_TS = idesc_bf16(BT, DH, 0, 1);  // dV, dK: A in TMEM, B MN-major
+            constexpr uint32_t IDESC_KN = idesc_bf16(BT, DH, 0, 1);  // dV, dK: A K-major, B MN-major
             constexpr uint32_t IDESC_DQ = idesc_bf16(BT, DH, 1, 1);  // dQ: dS and K both MN-major
             // Descriptors are built once; K steps and ring stages add constants to the start-address
             // field (units of 16 bytes).
             constexpr uint64_t TILE16 = TILE_BYTES >> 4;
             const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16), dV = smem_desc_sw128(smem_u32(sV), 16);
             const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16), dG0 = smem_desc_sw128(smem_u32(sdO), 16);
-            const uint64_t dDS = smem_desc_sw128(smem_u32(sDS), TILE_BYTES);
+            const uint64_t dDSk = smem_desc_sw128(smem_u32(sDS), 16);          // dS as [keys][queries]: K-major A
+            const uint64_t dDSm = smem_desc_sw128(smem_u32(sDS), TILE_BYTES);  // dS as MN-major A (M = queries)
             auto issue_st = [&](int s) {
                 const uint64_t q = dQ0 + s * TILE16;
 #pragma unroll
@@ -262,150 +288,157 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int it = 0; it < niter; it++) {
                 const int s = it & 1, sn = s ^ 1;
                 const uint64_t q = dQ0 + s * TILE16, g = dG0 + s * TILE16;
-                mbar_wait_poll(&s_free, it & 1, guard, 504);
+                if (it + 1 < niter) {
+                    // next scores and next dP^T as soon as this iteration's have been read out
+                    mbar_wait_poll(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
+                    mbar_wait_poll(&s_free, it & 1, guard, 504);
+                    tc_fence_after();
+                    issue_st(sn);
+                    mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
+                    mbar_wait_poll(&dp_free, it & 1, guard, 510);
+                    tc_fence_after();
+                    issue_dp(sn);
+                }
                 mbar_wait_poll(&p_ready, it & 1, guard, 505);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i
-                    umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_TS, it > 0 || k > 0);
-                if (it + 1 < niter) {
-                    mbar_wait_poll(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
-                    tc_fence_after();
-                    issue_st(sn);  // its commit also covers the dV product above: P may then be rewritten
-                }
+                for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i   (A: P^T bf16 in TMEM)
+                    umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_KN, it > 0 || k > 0);
+                umma_commit(&dv_done);
                 mbar_wait_poll(&ds_ready, it & 1, guard, 507);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i
-                    umma_ts(tmem + COL_DK, tmem + COL_DP + 8 * k, q + 128 * k, IDESC_TS, it > 0 || k > 0);
+                for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i   (A: dS in smem, rows = keys, K = queries)
+                    umma_ss(tmem + COL_DK, dDSk + (k / 4) * TILE16 + 2 * (k % 4), q + 128 * k, IDESC_KN, it > 0 || k > 0);
                 umma_commit(&qdo_free[s]);
                 if (it > 0) {
                     mbar_wait_poll(&dq_free, (it - 1) & 1, guard, 508);
                     tc_fence_after();
                 }
 #pragma unroll
-                for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K
-                    umma_ss(tmem + COL_DQ, dDS + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
+                for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K       (A: the same tile read MN-major)
+                    umma_ss(tmem + COL_DQ, dDSm + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
                 umma_commit(&dq_full);
-                if (it + 1 < niter) {
-                    mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
-                    tc_fence_after();
-                    issue_dp(sn);  // its commit also covers dK and dQ above: dS may then be rewritten
-                }
             }
             umma_commit(&all_done);
         }
+    } else if (warp < 4) {
+        // ---------------- P group (warps 0-3): lane = key row, all 128 query columns ----------------
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const uint32_t tS = lane_base + COL_ST, tP = lane_base + COL_P;
+        for (int it = 0; it < niter; it++) {
+            const int s = it & 1;
+            mbar_wait(&q_full[s], (it / 2) & 1, guard, 601);  // lse2 of this query tile is in smem
+            const float* l2 = sStat + s * 256;
+            mbar_wait(&s_full, it & 1, guard, 602);
+            tc_fence_after();
+            uint32_t pk[64], va[32], vb[32];
+            tmem_ld32(tS, va);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                tmem_ld_wait();
+                if (c == 0 || c == 2) tmem_ld32(tS + 32 * (c + 1), vb);
+                if (c == 1) tmem_ld32(tS + 64, va);
+                if (c == 3) {  // all of S^T(it) is in registers: the next scores may overwrite it
+                    tc_fence_before();
+                    warp_arrive(&s_free, lane);
+                }
+                const uint32_t(&cur)[32] = (c & 1) ? vb : va;
+                if (it == 0) p_chunk<true>(cur, l2 + 32 * c, p.scale_log2, r, 32 * c, &pk[16 * c]);
+                else p_chunk<false>(cur, l2 + 32 * c, p.scale_log2, r, 32 * c, &pk[16 * c]);
+            }
+            if (it > 0) {  // P^T(it-1) has been read by its dV product and by the dS group
+                mbar_wait(&dv_done, (it - 1) & 1, guard, 603);
+                mbar_wait(&p_read, (it - 1) & 1, guard, 604);
+                tc_fence_after();
+            }
+            tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+            tmem_st32(tP + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+            tmem_st_wait();
+            tc_fence_before();
+            warp_arrive(&p_ready, lane);
+        }
+        // epilogue: dV of this key tile
+        mbar_wait(&all_done, 0, guard, 606);
+        tc_fence_after();
+        store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, b, h, p);
     } else {
-        // ---------------- compute warps: lane = key row, group w owns query columns 64w .. 64w+63 ----------------
-        const int w = warp / 4;
-        const int r = (warp % 4) * 32 + lane;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
-        // dQ tile -> this warp's staging block (its 32 query rows x its 32 columns) -> one bulk
-        // reduction into the matching 4 KB block of the accumulator.
-        uint8_t* stage = sStage + warp * 4096;
-        float* acc_base = p.dq_acc + (((int64_t)bh * ntile * 2 + w) * BT + (warp % 4) * 32) * 32;
+        // ---------------- dS group (warps 4-7): lane = key row, all 128 query columns ----------------
+        const int q4 = warp - 4;
+        const int r = q4 * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+        const uint32_t tP = lane_base + COL_P, tDP = lane_base + COL_DP, tDQ = lane_base + COL_DQ;
+        uint8_t* stage = sStage + q4 * 8192;
+        float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + q4 * 32) * DH;
+        // dQ tile rows of this warp -> staging block -> one 8 KB bulk reduction into the accumulator
         auto drain_dq = [&](int tile) {
-            uint32_t dq[32];
-            tmem_ld32(lane_base + COL_DQ + 32 * w, dq);
+            uint32_t d0[32], d1[32];
+            tmem_ld32(tDQ, d0);
+            tmem_ld32(tDQ + 32, d1);
             tmem_ld_wait();
             tc_fence_before();
             warp_arrive(&dq_free, lane);
             if (lane == 0) bulk_wait_read();  // the previous reduction has finished reading the block
             __syncwarp();
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                *reinterpret_cast<uint4*>(stage + lane * 128 + ((ch ^ (lane & 7)) * 16)) =
-                    make_uint4(dq[4 * ch], dq[4 * ch + 1], dq[4 * ch + 2], dq[4 * ch + 3]);
+            for (int ch = 0; ch < 8; ch++) {
+                *reinterpret_cast<uint4*>(stage + lane * 256 + ((ch ^ (lane & 7)) * 16)) =
+                    make_uint4(d0[4 * ch], d0[4 * ch + 1], d0[4 * ch + 2], d0[4 * ch + 3]);
+                *reinterpret_cast<uint4*>(stage + lane * 256 + (((8 + ch) ^ (lane & 7)) * 16)) =
+                    make_uint4(d1[4 * ch], d1[4 * ch + 1], d1[4 * ch + 2], d1[4 * ch + 3]);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)tile * 2 * BT * 32, stage, 4096);
+            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)tile * BT * DH, stage, 8192);
         };
         for (int it = 0; it < niter; it++) {
             const int s = it & 1;
-            const bool diag = it == 0;
-            mbar_wait(&q_full[s], (it / 2) & 1, guard, 601);
-            const float* l2 = sStat + s * 256 + 64 * w;
-            const float* dl = l2 + 128;
-            mbar_wait(&s_full, it & 1, guard, 602);
+            mbar_wait(&q_full[s], (it / 2) & 1, guard, 611);  // delta of this query tile is in smem
+            const float* dl = sStat + s * 256 + 128;
+            mbar_wait(&p_ready, it & 1, guard, 612);
+            mbar_wait(&dp_full, it & 1, guard, 613);
             tc_fence_after();
-            uint32_t v0[32], v1[32], pk[32];
-            tmem_ld32(lane_base + COL_ST + 64 * w, v0);
-            tmem_ld32(lane_base + COL_ST + 64 * w + 32, v1);
+            uint32_t pp[32], va[32], vb[32], ds[64];
+            tmem_ld32(tP, pp);
+            tmem_ld32(tDP, va);
+            tmem_ld32(tDP + 32, vb);
+            tmem_ld_wait();
+            ds_chunk(&pp[0], va, dl, &ds[0]);
+            ds_chunk(&pp[16], vb, dl + 32, &ds[16]);
+            tmem_ld32(tP + 32, pp);
+            tmem_ld32(tDP + 64, va);
+            tmem_ld32(tDP + 96, vb);
             tmem_ld_wait();
             tc_fence_before();
-            warp_arrive(&s_free, lane);
-            if (diag) make_p<true>(v0, v1, l2, p.scale_log2, r, 64 * w, pk);
-            else make_p<false>(v0, v1, l2, p.scale_log2, r, 64 * w, pk);
-            tmem_st32(lane_base + COL_P + 32 * w, pk);
-            tmem_st_wait();
-            tc_fence_before();
-            warp_arrive(&p_ready, lane);
-
-            if (it > 0) {
-                mbar_wait(&dq_full, (it - 1) & 1, guard, 603);
+            warp_arrive(&p_read, lane);   // P^T(it) and dP^T(it) are in registers
+            warp_arrive(&dp_free, lane);
+            ds_chunk(&pp[0], va, dl + 64, &ds[32]);
+            ds_chunk(&pp[16], vb, dl + 96, &ds[48]);
+            if (it > 0) {  // dK and dQ of the previous tile are done: dS smem is free, dQ is ready
+                mbar_wait(&dq_full, (it - 1) & 1, guard, 614);
                 tc_fence_after();
                 drain_dq(n + it - 1);
             }
-
-            mbar_wait(&dp_full, it & 1, guard, 604);
-            tc_fence_after();
-            tmem_ld32(lane_base + COL_DP + 64 * w, v0);
-            tmem_ld32(lane_base + COL_DP + 64 * w + 32, v1);
-            tmem_ld_wait();
-            compute_bar_sync();  // both groups hold their dP^T before anyone overwrites it with dS^T
-            uint32_t dsk[32];
-            const float4* d4 = reinterpret_cast<const float4*>(dl);
+            // row r of dS: two 128-byte rows (queries 0-63 | 64-127) with the 128-byte swizzle
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                const float4 da = d4[i / 4], db = d4[8 + i / 4];
-                dsk[i / 2] = ds_pair(pk[i / 2], __uint_as_float(v0[i]), __uint_as_float(v0[i + 1]), da.x, da.y);
-                dsk[i / 2 + 1] = ds_pair(pk[i / 2 + 1], __uint_as_float(v0[i + 2]), __uint_as_float(v0[i + 3]), da.z, da.w);
-                dsk[16 + i / 2] = ds_pair(pk[16 + i / 2], __uint_as_float(v1[i]), __uint_as_float(v1[i + 1]), db.x, db.y);
-                dsk[16 + i / 2 + 1] =
-                    ds_pair(pk[16 + i / 2 + 1], __uint_as_float(v1[i + 2]), __uint_as_float(v1[i + 3]), db.z, db.w);
-            }
-            tmem_st32(lane_base + COL_DP + 32 * w, dsk);
-            // the same 64 values as one 128-byte row of block w of the MN-major dS operand
-            uint8_t* row = sDS + w * TILE_BYTES + r * 128;
+            for (int blk = 0; blk < 2; blk++)
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) =
-                    make_uint4(dsk[4 * ch], dsk[4 * ch + 1], dsk[4 * ch + 2], dsk[4 * ch + 3]);
-            tmem_st_wait();
+                for (int ch = 0; ch < 8; ch++)
+                    *reinterpret_cast<uint4*>(sDS + blk * TILE_BYTES + r * 128 + ((ch ^ (r & 7)) * 16)) =
+                        make_uint4(ds[32 * blk + 4 * ch], ds[32 * blk + 4 * ch + 1], ds[32 * blk + 4 * ch + 2],
+                                   ds[32 * blk + 4 * ch + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
             warp_arrive(&ds_ready, lane);
         }
-        mbar_wait(&dq_full, (niter - 1) & 1, guard, 605);
+        mbar_wait(&dq_full, (niter - 1) & 1, guard, 615);
         tc_fence_after();
         drain_dq(n + niter - 1);
         if (lane == 0) bulk_wait_all();
-
-        // epilogue: group 0 stores dV, group 1 stores scale * dK
-        mbar_wait(&all_done, 0, guard, 606);
+        // epilogue: scale * dK of this key tile
+        mbar_wait(&all_done, 0, guard, 616);
         tc_fence_after();
-        uint32_t o0[32], o1[32];
-        const uint32_t col = w == 0 ? COL_DV : COL_DK;
-        tmem_ld32(lane_base + col, o0);
-        tmem_ld32(lane_base + col + 32, o1);
-        tmem_ld_wait();
-        const int key = k0 + r;
-        if (key < p.S) {
-            const float f = w == 0 ? 1.0f : p.scale;
-            __nv_bfloat16* out = (w == 0 ? p.dV : p.dK) + (int64_t)b * p.sb + (int64_t)key * p.ss + (int64_t)h * p.sh;
-            uint4* dst = reinterpret_cast<uint4*>(out);
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-                dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * f, __uint_as_float(o0[i + 1]) * f),
-                                        pack_bf16(__uint_as_float(o0[i + 2]) * f, __uint_as_float(o0[i + 3]) * f),
-                                        pack_bf16(__uint_as_float(o0[i + 4]) * f, __uint_as_float(o0[i + 5]) * f),
-                                        pack_bf16(__uint_as_float(o0[i + 6]) * f, __uint_as_float(o0[i + 7]) * f));
-                dst[4 + i / 8] = make_uint4(pack_bf16(__uint_as_float(o1[i]) * f, __uint_as_float(o1[i + 1]) * f),
-                                            pack_bf16(__uint_as_float(o1[i + 2]) * f, __uint_as_float(o1[i + 3]) * f),
-                                            pack_bf16(__uint_as_float(o1[i + 4]) * f, __uint_as_float(o1[i + 5]) * f),
-                                            pack_bf16(__uint_as_float(o1[i + 6]) * f, __uint_as_float(o1[i + 7]) * f));
-            }
-        }
+        store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, b, h, p);
     }
 
     tc_fence_before();

@@ -10,15 +10,16 @@
 //          warps 4-7  softmax group of tile 1
 //          warp  8    TMA producer: Q once, then K/V tiles of 128 keys through a 3-stage ring
 //          warp  9    MMA issuer (one elected thread) and TMEM owner
-//   TMEM = S0 | S1 (128 fp32 columns each) | O0 | O1 (64 columns each); P (bf16) overwrites the
-//          first 64 columns of its S and feeds the PV product directly from TMEM.
+//   TMEM = S0 | S1 (128 fp32 columns each) | O0 | O1 (64 columns each) | P0 | P1 (128 bf16 = 64
+//          columns each): all 512 columns.  P feeds the PV product directly from TMEM.
 //
 //   per KV tile j:   S_t = Q_t K_j^T   (SS MMA, 128x128x64)      -> softmax group t
 //                    P_t = exp2(c*S_t - m_t), l_t += rowsum      -> TMEM (bf16)
 //                    O_t += P_t V_j    (TS MMA, 128x64x128)
 //
-// The MMA warp interleaves the two tiles (PV0(j), S0(j+1), PV1(j), S1(j+1), ...) so one group's
-// exponentials overlap the other group's matrix products.  KV tiles above the causal diagonal
+// Because P has columns of its own, the next scores of a tile do not have to wait for its PV
+// product: the MMA warp issues S0(j+1), PV0(j), S1(j+1), PV1(j), ... so a softmax group gets its next
+// scores one product earlier, and one group's exponentials overlap the other group's products.  KV tiles above the causal diagonal
 // are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
 // when it grows by more than 8 (in log2 units), so the rescaling of O in TMEM is rare.
 #include "internal.cuh"
@@ -36,7 +37,7 @@ constexpr int STAGES = 3;
 constexpr int TILE_BYTES = BM * DH * 2;  // 16 KB: one 128 x 64 bf16 tile
 constexpr int NTHREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_S = 0, COL_O = 256;
+constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 constexpr size_t SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + 1024;  // + alignment slack
 
 struct FwdParams {
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], o_done[2];
+    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -84,7 +85,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int t = 0; t < 2; t++) {
             mbar_init(&s_full[t], 1);
             mbar_init(&p_full[t], 4);  // one arrival per softmax warp
-            mbar_init(&o_done[t], 1);
+            mbar_init(&pv_done[t], 1);
         }
         fence_barrier_init();
     }
@@ -132,7 +133,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             };
             auto issue_pv = [&](int t, int s, bool acc) {
                 const uint64_t vd = dV0 + s * TILE16;
-                const uint32_t d = tmem + COL_O + t * DH, a = tmem + COL_S + t * BN;
+                const uint32_t d = tmem + COL_O + t * DH, a = tmem + COL_P + t * 64;
                 umma_ts(d, a, vd, IDESC_O, acc);
 #pragma unroll
                 for (int k = 1; k < BN / 16; k++) umma_ts(d, a + 8 * k, vd + 128 * k, IDESC_O, true);
@@ -145,26 +146,24 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (has_t1) issue_s(1, 0);
             for (int j = 0; j < nkv; j++) {
                 const int s = j % STAGES, sn = (j + 1) % STAGES;
+                const bool more = j + 1 < nkv;
+                if (more) mbar_wait_poll(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
                 mbar_wait_poll(&v_full[s], (j / STAGES) & 1, guard, 203);
                 if (j <= last0) {
-                    mbar_wait_poll(&p_full[0], j & 1, guard, 204);
-                    tc_fence_after();
-                    issue_pv(0, s, j > 0);
-                    if (j == last0) umma_commit(&o_done[0]);
-                }
-                if (j + 1 < nkv) {
-                    mbar_wait_poll(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
+                    mbar_wait_poll(&p_full[0], j & 1, guard, 204);  // P0(j) written, S0(j) consumed
                     tc_fence_after();
                     if (j + 1 <= last0) issue_s(0, sn);
+                    issue_pv(0, s, j > 0);
+                    umma_commit(&pv_done[0]);
                 }
                 if (has_t1) {
                     mbar_wait_poll(&p_full[1], j & 1, guard, 206);
                     tc_fence_after();
+                    if (more) issue_s(1, sn);
                     issue_pv(1, s, j > 0);
-                    if (j == last1) umma_commit(&o_done[1]);
+                    umma_commit(&pv_done[1]);
                 }
                 umma_commit(&kv_empty[s]);
-                if (j + 1 < nkv && has_t1) issue_s(1, sn);
             }
         }
     } else {
@@ -174,6 +173,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
         const uint32_t tS = lane_base + COL_S + t * BN;
         const uint32_t tO = lane_base + COL_O + t * DH;
+        const uint32_t tP = lane_base + COL_P + t * 64;
         const int jlast = n0 + t;
         const bool active = t == 0 || has_t1;
         float m = -INFINITY, l = 0.f;
@@ -211,8 +211,10 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     const float pm = fmaxf(__low2float(pmax), __high2float(pmax));
                     slow = __any_sync(0xffffffffu, !(pm <= 256.0f));
                     if (!slow) {
-                        tmem_st32(tS, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
-                        tmem_st32(tS + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+                        mbar_wait(&pv_done[t], (j - 1) & 1, guard, 305 + t);  // PV_t(j-1) has read P_t
+                        tc_fence_after();
+                        tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+                        tmem_st32(tP + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
                         l += rs;
                     }
                 }
@@ -238,8 +240,11 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
                     const float m_use = raise ? m_new : m;
                     const float alpha = raise ? ex2(m - m_new) : 1.0f;
+                    if (j > 0) {
+                        mbar_wait(&pv_done[t], (j - 1) & 1, guard, 307 + t);  // O_t stable, P_t free
+                        tc_fence_after();
+                    }
                     if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                        // S_t(j) completing implies PV_t(j-1) has completed: O_t is stable here.
                         uint32_t o0[32], o1[32];
                         tmem_ld32(tO, o0);
                         tmem_ld32(tO + 32, o1);
@@ -254,8 +259,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         tmem_st_wait();
                     }
                     m = m_use;
-                    // pass 2: chunk c of P (64 values, 32 columns) only overwrites S columns that
-                    // have already been consumed.
+                    // pass 2
                     float rs = 0.f;
 #pragma unroll
                     for (int c = 0; c < 2; c++) {
@@ -279,7 +283,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                             pk[i / 2] = pack_bf16(a0, a1);
                             pk[16 + i / 2] = pack_bf16(b0, b1);
                         }
-                        tmem_st32(tS + 32 * c, pk);
+                        tmem_st32(tP + 32 * c, pk);
                     }
                     l = l * alpha + rs;
                 }
@@ -289,7 +293,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (lane == 0) mbar_arrive(&p_full[t]);
             }
             // epilogue: O_t / l -> bf16 -> global; lse
-            mbar_wait(&o_done[t], 0, guard, 311 + t);
+            mbar_wait(&pv_done[t], jlast & 1, guard, 311 + t);
             tc_fence_after();
             const int qr = q0 + t * BM + r;
             const float inv = 1.0f / l;

@@ -189,3 +189,49 @@ class Reference:
         self.lib.ref_kernel_attn_bwd_all(_p(Q), _p(K), _p(V), _p(O), _p(dO), _p(den),
                                          _p(dQ), _p(dK), _p(dV), B, S, D, E)
         return dQ, dK, dV
+
+
+class ReferenceCuda:
+    """The reference's own CUDA kernels (two_stage_cuda_kernels.cu, linear_cuda_kernels.cu compiled
+    unmodified for sm_100, see ref_cuda_wrap.cu), on torch CUDA float tensors.  Used by the GPU
+    tests as a second checker and by the benchmark to time the reference's serial-scan kernels."""
+
+    def __init__(self):
+        path = _build.build_reference_cuda()
+        if path is None:
+            raise FileNotFoundError("oracle/_ref/libref_cuda.so is not built and the reference tree is not mounted")
+        self.lib = C.CDLL(path)
+        vp = C.c_void_p
+        self.lib.refcuda_mha_fwd.argtypes = [vp] * 4 + [_z] * 4
+        self.lib.refcuda_mha_bwd.argtypes = [vp] * 8 + [_z] * 4
+        self.lib.refcuda_kernel_attn_fwd_bwd.argtypes = [vp] * 14 + [_z] * 4 + [C.c_int]
+        self.lib.refcuda_linear_fwd_bwd.argtypes = [vp] * 14 + [_z] * 4 + [C.c_int]
+
+    @staticmethod
+    def available():
+        return _build.build_reference_cuda() is not None
+
+    def mha_fwd(self, Q, K, V, O, B, S, H, Dh):
+        assert self.lib.refcuda_mha_fwd(*(t.data_ptr() for t in (Q, K, V, O)), B, S, H, Dh) == 0
+
+    def mha_bwd(self, Q, K, V, O, dO, dQ, dK, dV, B, S, H, Dh):
+        assert self.lib.refcuda_mha_bwd(*(t.data_ptr() for t in (Q, K, V, O, dO, dQ, dK, dV)), B, S, H, Dh) == 0
+
+    def scan_buffers(self, B, S, D, E, device):
+        """Outputs and scratch of one forward + backward of either linear flavour."""
+        import torch
+        N = B * S
+        f = lambda *s: torch.empty(*s, device=device, dtype=torch.float32)
+        return dict(O=f(N, E), den=f(N), dQ=f(N, D), dK=f(N, D), dV=f(N, E), zc=f(N, D), Sbuf=f(B * max(D, E), max(D, E)),
+                    zbuf=f(B, D), dnum=f(N, E), dden=f(N))
+
+    def _scan(self, fn, Q, K, V, dO, buf, B, S, D, E, bwd):
+        order = ("O", "den", "dQ", "dK", "dV", "zc", "Sbuf", "zbuf", "dnum", "dden")
+        ptrs = [t.data_ptr() for t in (Q, K, V, dO)] + [buf[k].data_ptr() for k in order]
+        assert fn(*ptrs, B, S, D, E, int(bwd)) == 0
+
+    def kernel_attn(self, Q, K, V, dO, buf, B, S, D, E, bwd=True):
+        self._scan(self.lib.refcuda_kernel_attn_fwd_bwd, Q, K, V, dO, buf, B, S, D, E, bwd)
+
+    def linear(self, Qp, Kp, V, dO, buf, B, S, D, E, bwd=True):
+        self._scan(self.lib.refcuda_linear_fwd_bwd, Qp, Kp, V, dO, buf, B, S, D, E, bwd)

@@ -71,6 +71,27 @@ def build_dropin_kernel_test(reference=DEFAULT_REFERENCE, force=False):
     return out
 
 
+def build_reference_cuda(reference=DEFAULT_REFERENCE, force=False):
+    """Compiles the reference's UNMODIFIED two_stage_cuda_kernels.cu and linear_cuda_kernels.cu for
+    sm_100 (with the TensorN stand-in) plus oracle/ref_cuda_wrap.cu into oracle/_ref/libref_cuda.so.
+    Returns its path, or None when neither the reference tree nor a previous build is available."""
+    root = os.path.dirname(HERE)
+    out_dir = os.path.join(HERE, "_ref")
+    out = os.path.join(out_dir, "libref_cuda.so")
+    srcs = [os.path.join(reference, "src", "TwoStage", "two_stage_cuda_kernels.cu"),
+            os.path.join(reference, "src", "LinearAttention", "linear_cuda_kernels.cu")]
+    if not all(os.path.exists(s) for s in srcs):
+        return out if os.path.exists(out) else None
+    wrap = os.path.join(HERE, "ref_cuda_wrap.cu")
+    compat = os.path.join(root, "cxx-gpt_b200", "compat")
+    if force or _stale(out, srcs + [wrap, os.path.join(compat, "TensorN.hpp")]):
+        os.makedirs(out_dir, exist_ok=True)
+        subprocess.check_call(["nvcc", "-gencode", "arch=compute_100,code=sm_100", "-O3", "-std=c++17",
+                               "-Xcompiler", "-fPIC", "-shared", "-Wno-deprecated-gpu-targets",
+                               "-I", compat, "-I", os.path.join(reference, "src"), "-o", out, wrap] + srcs)
+    return out
+
+
 if __name__ == "__main__":
     ref = DEFAULT_REFERENCE
     if "--reference" in sys.argv:
@@ -78,3 +99,4 @@ if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_reference(ref, force="--force" in sys.argv))
     print(build_dropin_kernel_test(ref, force="--force" in sys.argv))
+    print(build_reference_cuda(ref, force="--force" in sys.argv))
