@@ -10,6 +10,7 @@
 //          warps 4-7  softmax group of tile 1
 //          warp  8    TMA producer: Q once, then K/V tiles of 128 keys through a 3-stage ring
 //          warp  9    MMA issuer (one elected thread) and TMEM owner
+//          warps 10-11 idle; with warps 8-9 they release registers to the softmax warps (setmaxnreg)
 //   TMEM = S0 | S1 (128 fp32 columns each) | O0 | O1 (64 columns each) | P0 | P1 (128 bf16 = 64
 //          columns each): all 512 columns.  P feeds the PV product directly from TMEM.
 //
@@ -17,9 +18,9 @@
 //                    P_t = exp2(c*S_t - m_t), l_t += rowsum      -> TMEM (bf16)
 //                    O_t += P_t V_j    (TS MMA, 128x64x128)
 //
-// Because P has columns of its own, the next scores of a tile do not have to wait for its PV
-// product: the MMA warp issues S0(j+1), PV0(j), S1(j+1), PV1(j), ... so a softmax group gets its next
-// scores one product earlier, and one group's exponentials overlap the other group's products.  KV tiles above the causal diagonal
+// A softmax thread pulls its whole row of scores (128 values) into registers and releases the score
+// columns at once; since P has columns of its own, the MMA warp can then issue S_t(j+1) while the
+// exponentials of step j are still running, and a softmax group never waits for its next scores.  KV tiles above the causal diagonal
 // are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
 // when it grows by more than 8 (in log2 units), so the rescaling of O in TMEM is rare.
 #include "internal.cuh"
@@ -35,7 +36,7 @@ constexpr int BN = 128;       // keys per KV tile
 constexpr int DH = 64;        // head dimension
 constexpr int STAGES = 3;
 constexpr int TILE_BYTES = BM * DH * 2;  // 16 KB: one 128 x 64 bf16 tile
-constexpr int NTHREADS = 320;
+constexpr int NTHREADS = 384;  // 12 warps: 8 softmax, producer, MMA issuer, 2 idle (they only give up registers)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 constexpr size_t SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + 1024;  // + alignment slack
@@ -53,7 +54,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], p_full[2], pv_done[2];
+    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], s_free[2], p_full[2],
+        pv_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -84,6 +86,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(&s_full[t], 1);
+            mbar_init(&s_free[t], 4);  // one arrival per softmax warp
             mbar_init(&p_full[t], 4);  // one arrival per softmax warp
             mbar_init(&pv_done[t], 1);
         }
@@ -95,6 +98,12 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
+    // Register budget: the softmax warps keep a whole row of scores (128 values) in registers, so
+    // the other warp group hands most of its registers over.
+    if (warp >= 8) {
+        // Warps 8-11 form one warp group; all four execute this one instruction together.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    }
     if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -147,27 +156,41 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int j = 0; j < nkv; j++) {
                 const int s = j % STAGES, sn = (j + 1) % STAGES;
                 const bool more = j + 1 < nkv;
-                if (more) mbar_wait_poll(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
+                if (more) {
+                    // next scores of both tiles as soon as this step's have been read into registers
+                    mbar_wait_poll(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
+                    if (j + 1 <= last0) {
+                        mbar_wait_poll(&s_free[0], j & 1, guard, 207);
+                        tc_fence_after();
+                        issue_s(0, sn);
+                    }
+                    if (has_t1) {
+                        mbar_wait_poll(&s_free[1], j & 1, guard, 208);
+                        tc_fence_after();
+                        issue_s(1, sn);
+                    }
+                }
                 mbar_wait_poll(&v_full[s], (j / STAGES) & 1, guard, 203);
                 if (j <= last0) {
-                    mbar_wait_poll(&p_full[0], j & 1, guard, 204);  // P0(j) written, S0(j) consumed
+                    mbar_wait_poll(&p_full[0], j & 1, guard, 204);
                     tc_fence_after();
-                    if (j + 1 <= last0) issue_s(0, sn);
                     issue_pv(0, s, j > 0);
                     umma_commit(&pv_done[0]);
                 }
                 if (has_t1) {
                     mbar_wait_poll(&p_full[1], j & 1, guard, 206);
                     tc_fence_after();
-                    if (more) issue_s(1, sn);
                     issue_pv(1, s, j > 0);
                     umma_commit(&pv_done[1]);
                 }
                 umma_commit(&kv_empty[s]);
             }
         }
+    } else if (warp >= 10) {
+        // idle warps: they only take part in the register hand-over above
     } else {
         // ---------------- softmax groups ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         const int t = warp / 4;
         const int r = (warp % 4) * 32 + lane;  // row inside the tile == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
@@ -182,69 +205,40 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 mbar_wait(&s_full[t], j & 1, guard, 301 + t);
                 tc_fence_after();
                 const bool diag = j == jlast;
-                bool slow = j == 0 || diag;
-                if (!slow) {
-                    // Fast path (interior tiles): one pass against the current maximum m.  The 128
-                    // scores are read in four chunks, the next chunk's TMEM load in flight while
-                    // this one is exponentiated; P stays in registers until the whole row is known
-                    // to fit (max P <= 2^8), so S is still intact if the slow path has to take over.
-                    uint32_t pk[64], va[32], vb[32];
-                    float rs = 0.f;
-                    __nv_bfloat162 pmax = __floats2bfloat162_rn(0.f, 0.f);
-                    tmem_ld32(tS, va);
+                // The whole row of scores goes to registers at once, and the score columns are handed
+                // back right away: S_t(j+1) is computed while this step's exponentials run.
+                uint32_t sv[4][32];
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        tmem_ld_wait();
-                        if (c == 0 || c == 2) tmem_ld32(tS + 32 * (c + 1), vb);
-                        if (c == 1) tmem_ld32(tS + 64, va);
-                        const uint32_t(&cur)[32] = (c & 1) ? vb : va;
+                for (int c = 0; c < 4; c++) tmem_ld32(tS + 32 * c, sv[c]);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_free[t]);
+                // pass 1: row maximum; on the diagonal tile key column c is visible iff c <= r
+                float mx = -INFINITY;
+                if (diag) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float a0 = ex2(fmaf(__uint_as_float(cur[i]), p.scale_log2, -m));
-                            const float a1 = ex2(fmaf(__uint_as_float(cur[i + 1]), p.scale_log2, -m));
-                            rs += a0 + a1;
-                            const __nv_bfloat162 pp = __floats2bfloat162_rn(a0, a1);
-                            pmax = __hmax2(pmax, pp);
-                            pk[16 * c + i / 2] = *reinterpret_cast<const uint32_t*>(&pp);
-                        }
-                    }
-                    const float pm = fmaxf(__low2float(pmax), __high2float(pmax));
-                    slow = __any_sync(0xffffffffu, !(pm <= 256.0f));
-                    if (!slow) {
-                        mbar_wait(&pv_done[t], (j - 1) & 1, guard, 305 + t);  // PV_t(j-1) has read P_t
-                        tc_fence_after();
-                        tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
-                        tmem_st32(tP + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
-                        l += rs;
-                    }
-                }
-                if (slow) {
-                    // Slow path (first tile, diagonal tile, or a row whose maximum grows by more than
-                    // 2^8): pass 1 finds the masked row maximum, O is rescaled if needed, pass 2
-                    // exponentiates.  On the diagonal tile key column c is visible iff c <= r.
-                    float mx = -INFINITY;
-#pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        uint32_t v0[32], v1[32];
-                        tmem_ld32(tS + 64 * c, v0);
-                        tmem_ld32(tS + 64 * c + 32, v1);
-                        tmem_ld_wait();
+                    for (int c = 0; c < 4; c++)
 #pragma unroll
                         for (int i = 0; i < 32; i++) {
-                            const float a = (!diag || 64 * c + i <= r) ? __uint_as_float(v0[i]) : -INFINITY;
-                            const float bb = (!diag || 64 * c + 32 + i <= r) ? __uint_as_float(v1[i]) : -INFINITY;
-                            mx = fmaxf(mx, fmaxf(a, bb));
+                            if (32 * c + i > r) sv[c][i] = 0xff800000u;  // -inf
+                            mx = fmaxf(mx, __uint_as_float(sv[c][i]));
                         }
-                    }
-                    const float m_new = fmaxf(m, mx * p.scale_log2);
-                    const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
-                    const float m_use = raise ? m_new : m;
-                    const float alpha = raise ? ex2(m - m_new) : 1.0f;
-                    if (j > 0) {
-                        mbar_wait(&pv_done[t], (j - 1) & 1, guard, 307 + t);  // O_t stable, P_t free
-                        tc_fence_after();
-                    }
-                    if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            mx = fmaxf(mx, fmaxf(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])));
+                }
+                const float m_new = fmaxf(m, mx * p.scale_log2);
+                const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
+                const float m_use = raise ? m_new : m;
+                const float alpha = raise ? ex2(m - m_new) : 1.0f;
+                if (j > 0) {
+                    mbar_wait(&pv_done[t], (j - 1) & 1, guard, 305 + t);  // O_t stable, P_t free
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, raise)) {
                         uint32_t o0[32], o1[32];
                         tmem_ld32(tO, o0);
                         tmem_ld32(tO + 32, o1);
@@ -256,37 +250,27 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         }
                         tmem_st32(tO, o0);
                         tmem_st32(tO + 32, o1);
-                        tmem_st_wait();
                     }
-                    m = m_use;
-                    // pass 2
-                    float rs = 0.f;
-#pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        uint32_t v0[32], v1[32], pk[32];
-                        tmem_ld32(tS + 64 * c, v0);
-                        tmem_ld32(tS + 64 * c + 32, v1);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float a0 = ex2(fmaf(__uint_as_float(v0[i]), p.scale_log2, -m_use));
-                            float a1 = ex2(fmaf(__uint_as_float(v0[i + 1]), p.scale_log2, -m_use));
-                            float b0 = ex2(fmaf(__uint_as_float(v1[i]), p.scale_log2, -m_use));
-                            float b1 = ex2(fmaf(__uint_as_float(v1[i + 1]), p.scale_log2, -m_use));
-                            if (diag) {
-                                a0 = 64 * c + i <= r ? a0 : 0.f;
-                                a1 = 64 * c + i + 1 <= r ? a1 : 0.f;
-                                b0 = 64 * c + 32 + i <= r ? b0 : 0.f;
-                                b1 = 64 * c + 32 + i + 1 <= r ? b1 : 0.f;
-                            }
-                            rs += (a0 + a1) + (b0 + b1);
-                            pk[i / 2] = pack_bf16(a0, a1);
-                            pk[16 + i / 2] = pack_bf16(b0, b1);
-                        }
-                        tmem_st32(tP + 32 * c, pk);
-                    }
-                    l = l * alpha + rs;
                 }
+                m = m_use;
+                // pass 2: P = exp2(c*S - m) as bf16 pairs (masked scores are -inf and give 0)
+                float rs = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a0 = ex2(fmaf(__uint_as_float(sv[2 * c][i]), p.scale_log2, -m_use));
+                        const float a1 = ex2(fmaf(__uint_as_float(sv[2 * c][i + 1]), p.scale_log2, -m_use));
+                        const float b0 = ex2(fmaf(__uint_as_float(sv[2 * c + 1][i]), p.scale_log2, -m_use));
+                        const float b1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1][i + 1]), p.scale_log2, -m_use));
+                        rs += (a0 + a1) + (b0 + b1);
+                        pk[i / 2] = pack_bf16(a0, a1);
+                        pk[16 + i / 2] = pack_bf16(b0, b1);
+                    }
+                    tmem_st32(tP + 32 * c, pk);
+                }
+                l = l * alpha + rs;
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();

@@ -78,8 +78,9 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
     atomicCAS(g.status, 0, code);
 }
 
-// The same bounded wait for a role that is a single thread (the MMA issuer): it polls without the
-// suspend hint, so it reacts within a few cycles of the arrival; one polling thread costs nothing.
+// The same bounded wait for a role that is a single thread (the MMA issuer).  It polls without
+// the suspend hint but sleeps ~30 ns between polls: a tight polling loop would take issue slots
+// from the compute warps that share its scheduler, a hinted try_wait wakes up too late.
 __device__ __forceinline__ void mbar_wait_poll(uint64_t* bar, uint32_t parity, const Guard& g, int code) {
     const uint32_t addr = smem_u32(bar);
     uint64_t t0 = 0;
@@ -93,6 +94,7 @@ __device__ __forceinline__ void mbar_wait_poll(uint64_t* bar, uint32_t parity, c
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok) return;
+        __nanosleep(32);
         if ((i & 1023u) == 1023u) {
             if (*g.abort_flag) return;
             if (*reinterpret_cast<volatile int*>(g.status) != 0) break;
