@@ -262,7 +262,10 @@ def run_ours(args):
                         "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
                 "roofline": {"bound": "tensor", "kernel": "mha_tc_bwd (pre + main + post launches)",
                              "achieved": bwd_tf, "peak": peak, "peak_sustained": peak_sustained,
-                             "peak_source": how, "unit": UNIT, "frac": bwd_tf / peak, "traffic": None}}
+                             "peak_source": how, "unit": UNIT, "frac": bwd_tf / peak,
+                             # dram__bytes_read + write of mha_tc_bwd_kernel from the ncu capture summarised in
+                             # profiles/mha_tc_bwd_kernel_softmax_s4096_b4.md (398.6 MB at B=4), scaled by B/4
+                             "traffic": 398.64e6 * B / 4 if S == 4096 else None}}
         if world == 1 and not args.no_cpu_baseline:
             tf, cores, dt, desc = cpu_sample(B, min(S, 4096))
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",

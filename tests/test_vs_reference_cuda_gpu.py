@@ -59,9 +59,11 @@ def test_elu_kernel_attention_matches_reference_kernels(pkg, dev, refcuda, B, S,
         assert rel_err(mine[k].cpu().numpy(), buf[k].cpu().numpy(), floor=1e-3) < TOL, k
 
 
-@pytest.mark.parametrize("B,S,D,E", [(96, 256, 64, 64), (2, 128, 1024, 768), (3, 70, 32, 24)])
+@pytest.mark.parametrize("B,S,D,E", [(96, 256, 64, 64), (2, 128, 1024, 768), (3, 70, 32, 16)])
 def test_linear_gpt_scan_matches_reference_kernels(pkg, dev, refcuda, B, S, D, E):
-    """The LinearGPT flavour has no CPU code in the reference; its CUDA kernels are the only pin."""
+    """The LinearGPT flavour has no CPU code in the reference; its CUDA kernels are the only pin.
+    E is kept a power of two: the reference's step-1 kernel reduces over min(E, 256) threads with a
+    halving tree (linear_cuda_kernels.cu:127-131, 142), which drops terms for other block sizes."""
     N = B * S
     x_q, x_k = rnd(dev, 5, N, E, std=0.5), rnd(dev, 6, N, E, std=0.5)
     V, dO = rnd(dev, 7, N, E), rnd(dev, 8, N, E)
