@@ -25,7 +25,7 @@ SYMBOLS = [
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
     "cxxattn_sync_status", "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
-    "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity",
+    "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
 ]
 
 
@@ -78,6 +78,8 @@ def lib():
         L.cxxattn_rope.argtypes = [vp, vp, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
         L.cxxattn_sync_status.argtypes = [vp]
+        L.cxxattn_set_timing_events.argtypes = [vp, vp]
+        L.cxxattn_set_timing_events.restype = None
         L.cxxattn_linattn_fwd_noalloc.argtypes = [C.POINTER(LinDesc)] + [vp] * 6 + [vp]
         L.cxxattn_linattn_noalloc_capacity.restype = sz
         L.cxxattn_linattn_noalloc_capacity.argtypes = []
@@ -235,6 +237,13 @@ class HostPlan:
             self.close()
         except Exception:
             pass
+
+
+def set_timing_events(start, stop):
+    """torch.cuda.Event objects (enable_timing=True, already recorded once so that they exist) or
+    None, None: recorded around the main backward kernel by the following mha_bwd calls."""
+    lib().cxxattn_set_timing_events(start.cuda_event if start is not None else None,
+                                    stop.cuda_event if stop is not None else None)
 
 
 def sync_status():

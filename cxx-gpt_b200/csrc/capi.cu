@@ -97,7 +97,11 @@ int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void*
     if (desc->dtype == CXXATTN_F32)
         return linattn_f32_fwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (float*)O, den,
                                z_cache, workspace, workspace_bytes, st);
-    return CXXATTN_ERR_UNSUPPORTED;
+    if (desc->dtype == CXXATTN_BF16) {
+        if (z_cache != nullptr) return CXXATTN_ERR_UNSUPPORTED;  // the bf16 path keeps z on chip
+        return linattn_tc_fwd(*desc, Q, K, V, O, den, st);
+    }
+    return CXXATTN_ERR_INVALID;
 }
 
 int cxxattn_linattn_fwd_noalloc(const cxxattn_lin_desc* desc, const float* Q, const float* K, const float* V,
@@ -161,6 +165,10 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
     if ((!Q && !K) || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 2 || D % head_dim)
         return CXXATTN_ERR_INVALID;
     return rope(Q, K, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
+}
+
+void cxxattn_set_timing_events(void* start_event, void* stop_event) {
+    mha_tc_bwd_set_timing_events(start_event, stop_event);
 }
 
 int cxxattn_sync_status(cxxattn_stream_t stream) { return sync_status(static_cast<cudaStream_t>(stream)); }

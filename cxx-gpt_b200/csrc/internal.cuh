@@ -37,6 +37,13 @@ size_t mha_tc_bwd_workspace(const MhaShape& p, bool have_lse);
 int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, const void* O, const void* dO,
                const float* lse, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes, cudaStream_t st);
 
+void mha_tc_bwd_set_timing_events(void* start, void* stop);
+
+// ---- tcgen05 bf16 linear attention, D = E = 64 (linattn_tc_fwd.cu) ----
+bool linattn_tc_supported(const cxxattn_lin_desc& d);
+int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
+                   cudaStream_t st);
+
 // ---- diagnostics (umma_selftest.cu) ----
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);
 int sync_status(cudaStream_t st);

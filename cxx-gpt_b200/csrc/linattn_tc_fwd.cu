@@ -1,0 +1,335 @@
+// Causal linear attention forward on the tensor cores (tcgen05 + TMEM + TMA), bf16 tensors with
+// fp32 accumulation and fp32 running state, D = E = 64.
+//
+// Replaces the serial per-timestep scan of two_stage_cuda::kernel_attn_fwd
+// (src/TwoStage/two_stage_cuda_kernels.cu:889-976) and linear_cuda::causal_linear_attention_fwd
+// (src/LinearAttention/linear_cuda_kernels.cu:10-79) for dtype BF16.  One CTA owns one batch unit
+// and walks its sequence in chunks of 128 tokens; Q, K and V are read from HBM exactly once (TMA),
+// O and den are written once, and the running state never leaves the SM:
+//
+//   phi            the feature map (ELU+1 or none) is applied in place on the Q and K tiles in shared
+//                  memory, rows past the end of the sequence are zeroed
+//   A   = phiQ phiK^T                       (SS MMA 128x128x64)   -> TMEM, masked to s <= t by the
+//                                            compute warps, row sums taken, bf16 back to TMEM (P)
+//   O'  = phiQ [S_prev | z_prev]            (SS MMA 128x80x64: the state of all earlier chunks as a
+//                                            bf16 operand, its 65th column is z and yields phiQ.z)
+//   O' += P V                               (TS MMA 128x64x128)
+//   S  += phiK^T [V | 1]                    (SS MMA, 64 state rows (issued as M=128 with the operand
+//                                            block repeated), N=80: the constant column of ones makes
+//                                            column 64 the running z = sum phiK)
+//   O   = O'[:, :64] / (den + 1e-8),  den = rowsum(A masked) + O'[:, 64]
+//
+// The state S (fp32, 64 x 65) lives in TMEM for the whole sequence; after each chunk it is copied
+// as bf16 into shared memory to serve as the operand of the next chunk's inter-chunk product.
+#include "internal.cuh"
+#include "tc_common.cuh"
+
+namespace cxxattn {
+namespace {
+
+using namespace tc;
+
+constexpr int CH = 128;  // tokens per chunk
+constexpr int DE = 64;   // feature width (D = E)
+constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
+constexpr int NSTAGE = 2;
+constexpr int NTHREADS = 192;  // 4 compute warps, TMA producer, MMA issuer
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_A = 0, COL_P = 128, COL_O = 192, COL_SX = 288;
+// per stage Q | K | V, then the ones tile, then the bf16 state operand (2 blocks of 64 rows x 128 B)
+constexpr size_t SMEM_BYTES = NSTAGE * 3 * TILE_BYTES + TILE_BYTES + 2 * 8192 + 1024;
+
+struct LinFwdParams {
+    __nv_bfloat16* O;
+    float* den;
+    int* status;
+    int B, S;
+    int map_elu;     // 1: phi(x) = x > 0 ? x + 1 : exp(x) applied to Q and K; 0: inputs pre-mapped
+    int eps_in_den;  // 1: den stored with the 1e-8 added
+};
+
+__device__ __forceinline__ uint32_t phi2(uint32_t v) {  // two bf16 values -> phi -> two bf16 values
+    const float a = __uint_as_float(v << 16), b = __uint_as_float(v & 0xffff0000u);
+    const float pa = a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f);
+    const float pb = b > 0.f ? b + 1.f : ex2(b * 1.4426950408889634f);
+    return pack_bf16(pa, pb);
+}
+// In-place feature map of one 128-byte row of a tile (element order does not matter).
+__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu) {
+    uint4* p = reinterpret_cast<uint4*>(row);
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        uint4 v = p[ch];
+        if (!valid) v = make_uint4(0u, 0u, 0u, 0u);
+        else if (elu) v = make_uint4(phi2(v.x), phi2(v.y), phi2(v.z), phi2(v.w));
+        p[ch] = v;
+    }
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, LinFwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, a_full, p_ready, o_full, o_free, s_done, sprev_ready;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    auto sQ = [&](int st) { return smem + (st * 3 + 0) * TILE_BYTES; };
+    auto sK = [&](int st) { return smem + (st * 3 + 1) * TILE_BYTES; };
+    auto sV = [&](int st) { return smem + (st * 3 + 2) * TILE_BYTES; };
+    uint8_t* sOnes = smem + NSTAGE * 3 * TILE_BYTES;  // [128 tokens][64] bf16, column 0 = 1
+    uint8_t* sPrev = sOnes + TILE_BYTES;              // block 0: S_prev [64 d][64 e]; block 1: column 0 = z_prev
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int b = blockIdx.x;
+    const int nc = (p.S + CH - 1) / CH;
+    const Guard guard{&abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&stage_free[s], 1);
+        }
+        mbar_init(&a_full, 1);
+        mbar_init(&o_full, 1);
+        mbar_init(&s_done, 1);
+        mbar_init(&mapped, 4);  // one arrival per compute warp
+        mbar_init(&p_ready, 4);
+        mbar_init(&o_free, 4);
+        mbar_init(&sprev_ready, 4);
+        fence_barrier_init();
+    }
+    if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
+    // constant tiles: ones column, and an all-zero state operand for the first chunk
+    for (int i = threadIdx.x; i < (TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
+        reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    if (threadIdx.x < CH)  // element (row, 0) of the swizzled tile sits in 16-byte chunk (row & 7)
+        *reinterpret_cast<uint16_t*>(sOnes + threadIdx.x * 128 + (threadIdx.x & 7) * 16) = 0x3f80;  // bf16 1.0
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            prefetch_tmap(&tmQ);
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+            for (int c = 0; c < nc; c++) {
+                const int st = c % NSTAGE;
+                if (c >= NSTAGE) mbar_wait(&stage_free[st], ((c / NSTAGE) - 1) & 1, guard, 701);
+                mbar_expect_tx(&full[st], 3 * TILE_BYTES);
+                tma_load_4d(sQ(st), &tmQ, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, c * CH, b);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC_A = idesc_bf16(CH, CH, 0, 0);  // phiQ phiK^T: both K-major
+            constexpr uint32_t IDESC_I = idesc_bf16(CH, 80, 0, 1);  // phiQ [S_prev | z]: B MN-major
+            constexpr uint32_t IDESC_P = idesc_bf16(CH, DE, 0, 1);  // P V: A in TMEM, B MN-major
+            constexpr uint32_t IDESC_S = idesc_bf16(CH, 80, 1, 1);  // phiK^T [V | 1]: both MN-major
+            const uint64_t dPrev = smem_desc_sw128(smem_u32(sPrev), 8192);
+            for (int c = 0; c < nc; c++) {
+                const int st = c % NSTAGE;
+                const uint64_t dQ = smem_desc_sw128(smem_u32(sQ(st)), 16);
+                const uint64_t dK = smem_desc_sw128(smem_u32(sK(st)), 16);
+                // phiK as an MN-major A operand: 64 state rows; the second block of 64 rows (offset 0)
+                // repeats the first, its output lanes are never read
+                const uint64_t dKm = smem_desc_sw128(smem_u32(sK(st)), 0);
+                const uint64_t dV = smem_desc_sw128(smem_u32(sV(st)), 0);
+                // [V | 1]: the second block of 64 columns is the ones tile
+                const uint64_t dV1 = smem_desc_sw128(smem_u32(sV(st)), smem_u32(sOnes) - smem_u32(sV(st)));
+                mbar_wait_poll(&mapped, c & 1, guard, 711);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + COL_A, dQ + 2 * k, dK + 2 * k, IDESC_A, k > 0);
+                umma_commit(&a_full);
+                mbar_wait_poll(&sprev_ready, c & 1, guard, 712);
+                if (c > 0) mbar_wait_poll(&o_free, (c - 1) & 1, guard, 713);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + COL_O, dQ + 2 * k, dPrev + 128 * k, IDESC_I, k > 0);
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)
+                    umma_ss(tmem + COL_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
+                umma_commit(&s_done);
+                mbar_wait_poll(&p_ready, c & 1, guard, 714);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)
+                    umma_ts(tmem + COL_O, tmem + COL_P + 8 * k, dV + 128 * k, IDESC_P, true);
+                umma_commit(&o_full);
+                umma_commit(&stage_free[st]);
+            }
+        }
+    } else {
+        // ---------------- compute warps: thread r = token row r of the chunk = TMEM lane r ----------------
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        // the state operand of the first chunk is the zero tile written at start-up
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sprev_ready);
+        for (int c = 0; c < nc; c++) {
+            const int st = c % NSTAGE;
+            const int tok = c * CH + r;
+            const bool valid = tok < p.S;
+            // feature map, in place (with no map, rows past the end are already zero: TMA fills them)
+            mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 721);
+            if (p.map_elu) {
+                map_row(sQ(st) + r * 128, valid, true);
+                map_row(sK(st) + r * 128, valid, true);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&mapped);
+
+            // A -> causal mask inside the chunk (key column s visible iff s <= r), row sum, bf16 P
+            mbar_wait(&a_full, c & 1, guard, 722);
+            tc_fence_after();
+            float rowsum = 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint32_t v0[32], v1[32], pk[32];
+                // columns of a 32-wide block beyond this warp's last row are all masked: not even loaded
+                const bool need0 = 64 * h <= warp * 32 + 31, need1 = 64 * h + 32 <= warp * 32 + 31;
+                if (need0) tmem_ld32(lane_base + COL_A + 64 * h, v0);
+                if (need1) tmem_ld32(lane_base + COL_A + 64 * h + 32, v1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float a0 = (need0 && 64 * h + i <= r) ? __uint_as_float(v0[i]) : 0.f;
+                    const float a1 = (need0 && 64 * h + i + 1 <= r) ? __uint_as_float(v0[i + 1]) : 0.f;
+                    const float b0 = (need1 && 64 * h + 32 + i <= r) ? __uint_as_float(v1[i]) : 0.f;
+                    const float b1 = (need1 && 64 * h + 32 + i + 1 <= r) ? __uint_as_float(v1[i + 1]) : 0.f;
+                    rowsum += (a0 + a1) + (b0 + b1);
+                    pk[i / 2] = pack_bf16(a0, a1);
+                    pk[16 + i / 2] = pack_bf16(b0, b1);
+                }
+                tmem_st32(lane_base + COL_P + 32 * h, pk);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready);
+
+            // state after this chunk -> bf16 operand of the next chunk's inter-chunk product
+            mbar_wait(&s_done, c & 1, guard, 723);
+            tc_fence_after();
+            if (c + 1 < nc) {
+                if (warp < 2) {  // state rows d = 0..63 are TMEM lanes 0..63
+                    uint32_t s0[32], s1[32], s2[32];
+                    tmem_ld32(lane_base + COL_SX, s0);
+                    tmem_ld32(lane_base + COL_SX + 32, s1);
+                    tmem_ld32(lane_base + COL_SX + 64, s2);  // column 64 = z; the rest is not used
+                    tmem_ld_wait();
+                    uint8_t* row = sPrev + r * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) = make_uint4(
+                            pack_bf16(__uint_as_float(s0[8 * ch]), __uint_as_float(s0[8 * ch + 1])),
+                            pack_bf16(__uint_as_float(s0[8 * ch + 2]), __uint_as_float(s0[8 * ch + 3])),
+                            pack_bf16(__uint_as_float(s0[8 * ch + 4]), __uint_as_float(s0[8 * ch + 5])),
+                            pack_bf16(__uint_as_float(s0[8 * ch + 6]), __uint_as_float(s0[8 * ch + 7])));
+                        *reinterpret_cast<uint4*>(row + (((4 + ch) ^ (r & 7)) * 16)) = make_uint4(
+                            pack_bf16(__uint_as_float(s1[8 * ch]), __uint_as_float(s1[8 * ch + 1])),
+                            pack_bf16(__uint_as_float(s1[8 * ch + 2]), __uint_as_float(s1[8 * ch + 3])),
+                            pack_bf16(__uint_as_float(s1[8 * ch + 4]), __uint_as_float(s1[8 * ch + 5])),
+                            pack_bf16(__uint_as_float(s1[8 * ch + 6]), __uint_as_float(s1[8 * ch + 7])));
+                    }
+                    // block 1, logical chunk 0: {z, 0, ...}
+                    *reinterpret_cast<uint4*>(sPrev + 8192 + r * 128 + ((r & 7) * 16)) =
+                        make_uint4(pack_bf16(__uint_as_float(s2[0]), 0.f), 0u, 0u, 0u);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sprev_ready);
+            }
+
+            // output rows: O = O'[:, :64] / (den + 1e-8), den = rowsum + O'[:, 64]
+            mbar_wait(&o_full, c & 1, guard, 724);
+            tc_fence_after();
+            uint32_t o0[32], o1[32], o2[32];
+            tmem_ld32(lane_base + COL_O, o0);
+            tmem_ld32(lane_base + COL_O + 32, o1);
+            tmem_ld32(lane_base + COL_O + 64, o2);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free);
+            if (valid) {
+                const float den = rowsum + __uint_as_float(o2[0]);
+                const float inv = 1.0f / (den + 1e-8f);
+                const int64_t row = (int64_t)b * p.S + tok;
+                p.den[row] = p.eps_in_den ? den + 1e-8f : den;
+                uint4* dst = reinterpret_cast<uint4*>(p.O + row * DE);
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * inv, __uint_as_float(o0[i + 1]) * inv),
+                                            pack_bf16(__uint_as_float(o0[i + 2]) * inv, __uint_as_float(o0[i + 3]) * inv),
+                                            pack_bf16(__uint_as_float(o0[i + 4]) * inv, __uint_as_float(o0[i + 5]) * inv),
+                                            pack_bf16(__uint_as_float(o0[i + 6]) * inv, __uint_as_float(o0[i + 7]) * inv));
+                    dst[4 + i / 8] = make_uint4(pack_bf16(__uint_as_float(o1[i]) * inv, __uint_as_float(o1[i + 1]) * inv),
+                                                pack_bf16(__uint_as_float(o1[i + 2]) * inv, __uint_as_float(o1[i + 3]) * inv),
+                                                pack_bf16(__uint_as_float(o1[i + 4]) * inv, __uint_as_float(o1[i + 5]) * inv),
+                                                pack_bf16(__uint_as_float(o1[i + 6]) * inv, __uint_as_float(o1[i + 7]) * inv));
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+bool linattn_tc_supported(const cxxattn_lin_desc& d) { return d.D == DE && d.E == DE; }
+
+int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
+                   cudaStream_t st) {
+    if (!linattn_tc_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
+    for (const void* q : {Q, K, V, (const void*)O})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    CUtensorMap tmQ, tmK, tmV;
+    const int B = (int)d.B, S = (int)d.S;
+    if (!make_tmap_bhsd(&tmQ, Q, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH) ||
+        !make_tmap_bhsd(&tmK, K, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH) ||
+        !make_tmap_bhsd(&tmV, V, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH))
+        return CXXATTN_ERR_CUDA;
+    LinFwdParams p;
+    p.O = static_cast<__nv_bfloat16*>(O);
+    p.den = den;
+    p.status = status_word();
+    if (p.status == nullptr) return CXXATTN_ERR_CUDA;
+    p.B = B;
+    p.S = S;
+    p.map_elu = d.feature_map == CXXATTN_MAP_ELU1;
+    p.eps_in_den = d.eps_in_den;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(linattn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
+            cudaSuccess)
+            return CXXATTN_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    linattn_tc_fwd_kernel<<<(unsigned)B, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, p);
+    return check_launch();
+}
+
+}  // namespace cxxattn

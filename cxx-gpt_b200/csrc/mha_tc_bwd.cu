@@ -451,6 +451,14 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 }  // namespace
 
+// Optional CUDA events recorded right before and after the main backward kernel (see
+// cxxattn_set_timing_events); null = off.
+static thread_local cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
+void mha_tc_bwd_set_timing_events(void* start, void* stop) {
+    g_ev_start = static_cast<cudaEvent_t>(start);
+    g_ev_stop = static_cast<cudaEvent_t>(stop);
+}
+
 static size_t rows_bytes(const MhaShape& p) {
     const size_t spad = ((size_t)p.S + BT - 1) / BT * BT;
     return align_up((size_t)p.B * p.H * spad * sizeof(float), 256);
@@ -514,7 +522,9 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
         attr_set[dev] = true;
     }
     const int64_t grid = (int64_t)(Spad / BT) * p.B * p.H;
+    if (g_ev_start) cudaEventRecord(g_ev_start, st);
     mha_tc_bwd_kernel<<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);
+    if (g_ev_stop) cudaEventRecord(g_ev_stop, st);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
 
     const int64_t orows = (int64_t)p.B * p.H * p.S;

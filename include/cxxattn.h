@@ -197,6 +197,11 @@ int cxxattn_mha_fwd_bwd_host(cxxattn_host_plan* plan, const void* hQ, const void
  * cleared) or not (CXXATTN_OK).  Results of a launch that timed out are undefined. */
 int cxxattn_sync_status(cxxattn_stream_t stream);
 
+/* Measurement hook: two cudaEvent_t handles that later cxxattn_mha_bwd calls (dtype BF16) of the
+ * calling thread record on their stream right before and right after the main backward kernel,
+ * so that its duration can be read without the pre- and post-pass.  NULL, NULL switches it off. */
+void cxxattn_set_timing_events(void* start_event, void* stop_event);
+
 /* One-tile check of the tcgen05 operand conventions (bf16 device buffers, float result):
  *   mode 0: D[128x128] = A[128x64] B[128x64]^T;  mode 1: D[128x64] = A[128x128] B[128x64];
  *   mode 2: D[128x64]  = A[128x128]^T B[128x64]. */
