@@ -146,7 +146,8 @@ int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void*
         return linattn_f32_bwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (const float*)O,
                                (const float*)dO, den, (float*)dQ, (float*)dK, (float*)dV,
                                workspace, workspace_bytes, st);
-    return CXXATTN_ERR_UNSUPPORTED;
+    if (desc->dtype == CXXATTN_BF16) return linattn_tc_bwd(*desc, Q, K, V, O, dO, den, dQ, dK, dV, st);
+    return CXXATTN_ERR_INVALID;
 }
 
 int cxxattn_phi_elu_fwd(const float* x, float* phi, size_t N, size_t D, size_t E, cxxattn_stream_t stream) {

@@ -1,0 +1,598 @@
+// Causal linear attention backward on the tensor cores (tcgen05 + TMEM + TMA), bf16 tensors with
+// fp32 accumulation and fp32 running states, D = E = 64.
+//
+// Replaces, for dtype BF16, the three serial scans of the reference backward
+// (two_stage_cuda::kernel_attn_bwd_step1 / _dQ / _dKdV, src/TwoStage/two_stage_cuda_kernels.cu:
+// 1190-1809, and the linear_cuda:: counterparts, src/LinearAttention/linear_cuda_kernels.cu:
+// 101-298) with two chunked passes over the sequence, one CTA per batch unit, 128 tokens per chunk.
+// Step 1 (dnum = dO/den, dden = -(dO.O)/den) is fused into both passes: the dO tile is rescaled in
+// place in shared memory and dden goes into column 0 of a small side tile, so that a bias or a
+// rank-one term becomes one more K step of a matrix product:
+//
+//   pass 1 (chunks ascending, prefix state S = sum phiK (x) [V | 1], as in the forward):
+//     W    = dnum V^T + dden 1^T                      masked to s <= t, bf16 -> TMEM (P)
+//     dQ'  = [dnum | dden] [S_prev | z_prev]^T + P phiK
+//     dQ   = dQ' o phi'(Q)
+//   pass 2 (chunks descending, suffix state S* = sum phiQ (x) [dnum | dden]):
+//     A^T  = phiK phiQ^T,   W2 = V dnum^T + 1 dden^T   both masked to s >= t, bf16 -> TMEM (P1, P2)
+//     dV   = phiK S*_next + P1 dnum
+//     dK   = (V S*_next^T + z*_next + P2 phiQ) o phi'(K)
+//
+// As in the forward, the states stay in TMEM (fp32) for the whole sequence and are copied as bf16
+// into shared memory once per chunk to serve as matrix operands.
+#include "internal.cuh"
+#include "tc_common.cuh"
+
+namespace cxxattn {
+namespace {
+
+using namespace tc;
+
+constexpr int CH = 128;
+constexpr int DE = 64;
+constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
+constexpr int NSTAGE = 2;
+constexpr int NTHREADS = 192;  // 4 compute warps, TMA producer, MMA issuer
+constexpr uint32_t TMEM_COLS = 512;
+
+struct LinBwdParams {
+    const __nv_bfloat16* Q;  // raw inputs, read row-wise for phi'
+    const __nv_bfloat16* K;
+    const __nv_bfloat16* O;
+    const float* den;
+    __nv_bfloat16* dQ;
+    __nv_bfloat16* dK;
+    __nv_bfloat16* dV;
+    int* status;
+    int B, S;
+    int map_elu;
+};
+
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ float phi1(float a) { return a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f); }
+__device__ __forceinline__ float dphi1(float a) { return a > 0.f ? 1.f : ex2(a * 1.4426950408889634f); }
+__device__ __forceinline__ uint32_t phi2(uint32_t v) { return pack_bf16(phi1(bf_lo(v)), phi1(bf_hi(v))); }
+
+// In-place feature map of one 128-byte tile row (element order does not matter).
+__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu) {
+    uint4* p = reinterpret_cast<uint4*>(row);
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        uint4 v = p[ch];
+        if (!valid) v = make_uint4(0u, 0u, 0u, 0u);
+        else if (elu) v = make_uint4(phi2(v.x), phi2(v.y), phi2(v.z), phi2(v.w));
+        p[ch] = v;
+    }
+}
+
+// Step 1 for one token row: the dO tile row becomes dnum = dO / den in place, dden = -(dO . O) / den
+// is returned and also written (bf16) to element 0 of the row's side-tile entry.
+__device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16* o_row, float den, bool valid,
+                                           int swz, uint8_t* dden_slot) {
+    uint4* p = reinterpret_cast<uint4*>(do_row);
+    const uint4* o = reinterpret_cast<const uint4*>(o_row);
+    const float inv = valid ? 1.0f / den : 0.f;
+    float dot = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        // the tile row is stored with its 16-byte chunks permuted (chunk ch holds logical chunk
+        // ch ^ swz); the O row comes from global memory in logical order
+        uint4 g = p[ch];
+        const uint4 ov = valid ? o[ch ^ swz] : make_uint4(0u, 0u, 0u, 0u);
+        dot += bf_lo(g.x) * bf_lo(ov.x) + bf_hi(g.x) * bf_hi(ov.x) + bf_lo(g.y) * bf_lo(ov.y) + bf_hi(g.y) * bf_hi(ov.y) +
+               bf_lo(g.z) * bf_lo(ov.z) + bf_hi(g.z) * bf_hi(ov.z) + bf_lo(g.w) * bf_lo(ov.w) + bf_hi(g.w) * bf_hi(ov.w);
+        g = make_uint4(pack_bf16(bf_lo(g.x) * inv, bf_hi(g.x) * inv), pack_bf16(bf_lo(g.y) * inv, bf_hi(g.y) * inv),
+                       pack_bf16(bf_lo(g.z) * inv, bf_hi(g.z) * inv), pack_bf16(bf_lo(g.w) * inv, bf_hi(g.w) * inv));
+        p[ch] = g;
+    }
+    const float dden = -dot * inv;
+    *reinterpret_cast<uint16_t*>(dden_slot) = __bfloat16_as_ushort(__float2bfloat16_rn(dden));
+    return dden;
+}
+
+// fp32 state rows (TMEM lanes 0..63, 64 columns + z in column 64) -> bf16 operand tile in shared
+// memory: block 0 = [64 d][64 e], block 1 = column 0 holds z; optionally z also as fp32.
+__device__ __forceinline__ void state_to_smem(uint32_t taddr, uint8_t* sState, int r, float* zf32 = nullptr) {
+    uint32_t s0[32], s1[32], s2[32];
+    tmem_ld32(taddr, s0);
+    tmem_ld32(taddr + 32, s1);
+    tmem_ld32(taddr + 64, s2);  // column 64 = z; the rest is not used
+    tmem_ld_wait();
+    uint8_t* row = sState + r * 128;
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+        *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) =
+            make_uint4(pack_bf16(__uint_as_float(s0[8 * ch]), __uint_as_float(s0[8 * ch + 1])),
+                       pack_bf16(__uint_as_float(s0[8 * ch + 2]), __uint_as_float(s0[8 * ch + 3])),
+                       pack_bf16(__uint_as_float(s0[8 * ch + 4]), __uint_as_float(s0[8 * ch + 5])),
+                       pack_bf16(__uint_as_float(s0[8 * ch + 6]), __uint_as_float(s0[8 * ch + 7])));
+        *reinterpret_cast<uint4*>(row + (((4 + ch) ^ (r & 7)) * 16)) =
+            make_uint4(pack_bf16(__uint_as_float(s1[8 * ch]), __uint_as_float(s1[8 * ch + 1])),
+                       pack_bf16(__uint_as_float(s1[8 * ch + 2]), __uint_as_float(s1[8 * ch + 3])),
+                       pack_bf16(__uint_as_float(s1[8 * ch + 4]), __uint_as_float(s1[8 * ch + 5])),
+                       pack_bf16(__uint_as_float(s1[8 * ch + 6]), __uint_as_float(s1[8 * ch + 7])));
+    }
+    *reinterpret_cast<uint4*>(sState + 8192 + r * 128 + ((r & 7) * 16)) =
+        make_uint4(pack_bf16(__uint_as_float(s2[0]), 0.f), 0u, 0u, 0u);
+    if (zf32 != nullptr) zf32[r] = __uint_as_float(s2[0]);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// One gradient row: (acc + bias) * phi'(raw) -> bf16 -> global (128 bytes).  raw == nullptr: no
+// phi' factor (pre-mapped features); bias == nullptr: none.
+__device__ __forceinline__ void store_grad_row(__nv_bfloat16* dst, const __nv_bfloat16* raw, const uint32_t (&o0)[32],
+                                               const uint32_t (&o1)[32], const float* bias) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    const uint4* r4 = reinterpret_cast<const uint4*>(raw);
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int col = 8 * ch + i;
+            v[i] = __uint_as_float(col < 32 ? o0[col] : o1[col - 32]);
+            if (bias != nullptr) v[i] += bias[col];
+        }
+        if (raw != nullptr) {
+            const uint4 x = r4[ch];
+            v[0] *= dphi1(bf_lo(x.x)); v[1] *= dphi1(bf_hi(x.x));
+            v[2] *= dphi1(bf_lo(x.y)); v[3] *= dphi1(bf_hi(x.y));
+            v[4] *= dphi1(bf_lo(x.z)); v[5] *= dphi1(bf_hi(x.z));
+            v[6] *= dphi1(bf_lo(x.w)); v[7] *= dphi1(bf_hi(x.w));
+        }
+        d4[ch] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// pass 1: dQ
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t C1_W = 0, C1_DQ = 128, C1_SX = 192;  // W/P | dQ' | state (80 columns)
+// per stage K | V | dO, then ones tile, dden side tile, state operand (2 blocks x 8 KB)
+constexpr size_t SMEM1_BYTES = NSTAGE * 3 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 1024;
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                         const __grid_constant__ CUtensorMap tmG, LinBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, w_full, p_ready, o_full, o_free, s_done, sprev_ready;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    auto sK = [&](int st) { return smem + (st * 3 + 0) * TILE_BYTES; };
+    auto sV = [&](int st) { return smem + (st * 3 + 1) * TILE_BYTES; };
+    auto sG = [&](int st) { return smem + (st * 3 + 2) * TILE_BYTES; };  // dO, rescaled to dnum in place
+    uint8_t* sOnes = smem + NSTAGE * 3 * TILE_BYTES;  // [128][64] bf16, column 0 = 1
+    uint8_t* sDden = sOnes + TILE_BYTES;              // [128 tokens][64] bf16, column 0 = dden_t
+    uint8_t* sPrev = sDden + TILE_BYTES;              // block 0: S_prev [64 d][64 e]; block 1: column 0 = z_prev
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int b = blockIdx.x;
+    const int nc = (p.S + CH - 1) / CH;
+    const Guard guard{&abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&stage_free[s], 1);
+        }
+        mbar_init(&w_full, 1);
+        mbar_init(&o_full, 1);
+        mbar_init(&s_done, 1);
+        mbar_init(&mapped, 4);
+        mbar_init(&p_ready, 4);
+        mbar_init(&o_free, 4);
+        mbar_init(&sprev_ready, 4);
+        fence_barrier_init();
+    }
+    if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
+    for (int i = threadIdx.x; i < (2 * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
+        reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    if (threadIdx.x < CH)
+        *reinterpret_cast<uint16_t*>(sOnes + threadIdx.x * 128 + (threadIdx.x & 7) * 16) = 0x3f80;  // bf16 1.0
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+            prefetch_tmap(&tmG);
+            for (int c = 0; c < nc; c++) {
+                const int st = c % NSTAGE;
+                if (c >= NSTAGE) mbar_wait(&stage_free[st], ((c / NSTAGE) - 1) & 1, guard, 801);
+                mbar_expect_tx(&full[st], 3 * TILE_BYTES);
+                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sG(st), &tmG, &full[st], 0, 0, c * CH, b);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t IDESC_W = idesc_bf16(CH, CH, 0, 0);  // dnum V^T (+ dden 1^T): both K-major
+            constexpr uint32_t IDESC_I = idesc_bf16(CH, DE, 0, 0);  // [dnum|dden][S_prev|z]^T: both K-major
+            constexpr uint32_t IDESC_P = idesc_bf16(CH, DE, 0, 1);  // P phiK: A in TMEM, B MN-major
+            constexpr uint32_t IDESC_S = idesc_bf16(CH, 80, 1, 1);  // phiK^T [V | 1]: both MN-major
+            const uint64_t dOnes = smem_desc_sw128(smem_u32(sOnes), 16), dDd = smem_desc_sw128(smem_u32(sDden), 16);
+            const uint64_t dPrev0 = smem_desc_sw128(smem_u32(sPrev), 16), dPrev1 = smem_desc_sw128(smem_u32(sPrev) + 8192, 16);
+            for (int c = 0; c < nc; c++) {
+                const int st = c % NSTAGE;
+                const uint64_t dG = smem_desc_sw128(smem_u32(sG(st)), 16), dVk = smem_desc_sw128(smem_u32(sV(st)), 16);
+                const uint64_t dKm = smem_desc_sw128(smem_u32(sK(st)), 0);
+                const uint64_t dV1 = smem_desc_sw128(smem_u32(sV(st)), smem_u32(sOnes) - smem_u32(sV(st)));
+                mbar_wait_poll(&mapped, c & 1, guard, 811);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C1_W, dG + 2 * k, dVk + 2 * k, IDESC_W, k > 0);
+                umma_ss(tmem + C1_W, dDd, dOnes, IDESC_W, true);  // + dden_t for every column
+                umma_commit(&w_full);
+                mbar_wait_poll(&sprev_ready, c & 1, guard, 812);
+                if (c > 0) mbar_wait_poll(&o_free, (c - 1) & 1, guard, 813);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C1_DQ, dG + 2 * k, dPrev0 + 2 * k, IDESC_I, k > 0);
+                umma_ss(tmem + C1_DQ, dDd, dPrev1, IDESC_I, true);  // + dden_t z_prev
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)
+                    umma_ss(tmem + C1_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
+                umma_commit(&s_done);
+                mbar_wait_poll(&p_ready, c & 1, guard, 814);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)
+                    umma_ts(tmem + C1_DQ, tmem + C1_W + 8 * k, dKm + 128 * k, IDESC_P, true);
+                umma_commit(&o_full);
+                umma_commit(&stage_free[st]);
+            }
+        }
+    } else {
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sprev_ready);
+        for (int c = 0; c < nc; c++) {
+            const int st = c % NSTAGE;
+            const int tok = c * CH + r;
+            const bool valid = tok < p.S;
+            const int64_t row = (int64_t)b * p.S + tok;
+            const float den = valid ? p.den[row] : 1.f;
+            mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 821);
+            step1_row(sG(st) + r * 128, p.O + row * DE, den, valid, r & 7, sDden + r * 128 + (r & 7) * 16);
+            if (p.map_elu) map_row(sK(st) + r * 128, valid, true);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&mapped);
+
+            // W -> mask s <= t -> bf16 P, written over the first 64 columns of W (each thread only
+            // touches its own TMEM lane and has its whole row in registers before it stores)
+            mbar_wait(&w_full, c & 1, guard, 822);
+            tc_fence_after();
+            uint32_t pk[64];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint32_t v0[32], v1[32];
+                const bool need0 = 64 * h <= warp * 32 + 31, need1 = 64 * h + 32 <= warp * 32 + 31;
+                if (need0) tmem_ld32(lane_base + C1_W + 64 * h, v0);
+                if (need1) tmem_ld32(lane_base + C1_W + 64 * h + 32, v1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float a0 = (need0 && 64 * h + i <= r) ? __uint_as_float(v0[i]) : 0.f;
+                    const float a1 = (need0 && 64 * h + i + 1 <= r) ? __uint_as_float(v0[i + 1]) : 0.f;
+                    const float b0 = (need1 && 64 * h + 32 + i <= r) ? __uint_as_float(v1[i]) : 0.f;
+                    const float b1 = (need1 && 64 * h + 32 + i + 1 <= r) ? __uint_as_float(v1[i + 1]) : 0.f;
+                    pk[32 * h + i / 2] = pack_bf16(a0, a1);
+                    pk[32 * h + 16 + i / 2] = pack_bf16(b0, b1);
+                }
+            }
+            tmem_st32(lane_base + C1_W, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+            tmem_st32(lane_base + C1_W + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready);
+
+            mbar_wait(&s_done, c & 1, guard, 823);
+            tc_fence_after();
+            if (c + 1 < nc) {
+                if (warp < 2) state_to_smem(lane_base + C1_SX, sPrev, r);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sprev_ready);
+            }
+
+            mbar_wait(&o_full, c & 1, guard, 824);
+            tc_fence_after();
+            uint32_t o0[32], o1[32];
+            tmem_ld32(lane_base + C1_DQ, o0);
+            tmem_ld32(lane_base + C1_DQ + 32, o1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free);
+            if (valid) store_grad_row(p.dQ + row * DE, p.map_elu ? p.Q + row * DE : nullptr, o0, o1, nullptr);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// pass 2: dK, dV (chunks in descending order)
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t C2_AT = 0, C2_W = 128, C2_DV = 256, C2_DK = 320, C2_SX = 384;
+// per stage Q | K | V | dO, then ones tile, dden side tile, state operand (2 blocks x 8 KB)
+constexpr size_t SMEM2_BYTES = NSTAGE * 4 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 1024;
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
+                           LinBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, aw_full, p_ready, o_full, o_free, s_done, snext_ready;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ float zstar[DE];  // z*_next in fp32, added to dK in the epilogue
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    auto sQ = [&](int st) { return smem + (st * 4 + 0) * TILE_BYTES; };
+    auto sK = [&](int st) { return smem + (st * 4 + 1) * TILE_BYTES; };
+    auto sV = [&](int st) { return smem + (st * 4 + 2) * TILE_BYTES; };
+    auto sG = [&](int st) { return smem + (st * 4 + 3) * TILE_BYTES; };
+    uint8_t* sOnes = smem + NSTAGE * 4 * TILE_BYTES;
+    uint8_t* sDden = sOnes + TILE_BYTES;
+    uint8_t* sNext = sDden + TILE_BYTES;  // block 0: S*_next [64 d][64 e]; block 1: column 0 = z*_next
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int b = blockIdx.x;
+    const int nc = (p.S + CH - 1) / CH;
+    const Guard guard{&abort_flag, p.status};
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&stage_free[s], 1);
+        }
+        mbar_init(&aw_full, 1);
+        mbar_init(&o_full, 1);
+        mbar_init(&s_done, 1);
+        mbar_init(&mapped, 4);
+        mbar_init(&p_ready, 4);
+        mbar_init(&o_free, 4);
+        mbar_init(&snext_ready, 4);
+        fence_barrier_init();
+    }
+    if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
+    for (int i = threadIdx.x; i < (2 * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
+        reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x < DE) zstar[threadIdx.x] = 0.f;
+    __syncthreads();
+    if (threadIdx.x < CH)
+        *reinterpret_cast<uint16_t*>(sOnes + threadIdx.x * 128 + (threadIdx.x & 7) * 16) = 0x3f80;  // bf16 1.0
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    // iteration n = 0 .. nc-1 handles chunk c = nc-1-n
+    if (warp == 4) {
+        if (lane == 0) {
+            prefetch_tmap(&tmQ);
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+            prefetch_tmap(&tmG);
+            for (int n = 0; n < nc; n++) {
+                const int st = n % NSTAGE, c = nc - 1 - n;
+                if (n >= NSTAGE) mbar_wait(&stage_free[st], ((n / NSTAGE) - 1) & 1, guard, 901);
+                mbar_expect_tx(&full[st], 4 * TILE_BYTES);
+                tma_load_4d(sQ(st), &tmQ, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sG(st), &tmG, &full[st], 0, 0, c * CH, b);
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t IDESC_KK = idesc_bf16(CH, CH, 0, 0);  // A^T and W2: both operands K-major
+            constexpr uint32_t IDESC_KN = idesc_bf16(CH, DE, 0, 1);  // A K-major (or TMEM), B MN-major
+            constexpr uint32_t IDESC_K2 = idesc_bf16(CH, DE, 0, 0);  // V S*^T: both K-major
+            constexpr uint32_t IDESC_S = idesc_bf16(CH, 80, 1, 1);   // phiQ^T [dnum | dden]: both MN-major
+            const uint64_t dOnes = smem_desc_sw128(smem_u32(sOnes), 16), dDd = smem_desc_sw128(smem_u32(sDden), 16);
+            const uint64_t dNextK = smem_desc_sw128(smem_u32(sNext), 16);  // rows d, K = e   (for V S*^T)
+            const uint64_t dNextM = smem_desc_sw128(smem_u32(sNext), 0);   // rows = K = d, N = e (for phiK S*)
+            for (int n = 0; n < nc; n++) {
+                const int st = n % NSTAGE;
+                const uint64_t dQk = smem_desc_sw128(smem_u32(sQ(st)), 16), dKk = smem_desc_sw128(smem_u32(sK(st)), 16);
+                const uint64_t dVk = smem_desc_sw128(smem_u32(sV(st)), 16), dGk = smem_desc_sw128(smem_u32(sG(st)), 16);
+                const uint64_t dQm = smem_desc_sw128(smem_u32(sQ(st)), 0);  // phiQ MN-major (A of the state, B of dK)
+                const uint64_t dGm = smem_desc_sw128(smem_u32(sG(st)), 0);  // dnum MN-major (B of dV)
+                const uint64_t dG1 = smem_desc_sw128(smem_u32(sG(st)), smem_u32(sDden) - smem_u32(sG(st)));  // [dnum | dden]
+                mbar_wait_poll(&mapped, n & 1, guard, 911);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C2_AT, dKk + 2 * k, dQk + 2 * k, IDESC_KK, k > 0);
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C2_W, dVk + 2 * k, dGk + 2 * k, IDESC_KK, k > 0);
+                umma_ss(tmem + C2_W, dOnes, dDd, IDESC_KK, true);  // + dden_s for every row
+                umma_commit(&aw_full);
+                mbar_wait_poll(&snext_ready, n & 1, guard, 912);
+                if (n > 0) mbar_wait_poll(&o_free, (n - 1) & 1, guard, 913);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++)  // dV' = phiK S*_next
+                    umma_ss(tmem + C2_DV, dKk + 2 * k, dNextM + 128 * k, IDESC_KN, k > 0);
+#pragma unroll
+                for (int k = 0; k < DE / 16; k++)  // dK' = V S*_next^T
+                    umma_ss(tmem + C2_DK, dVk + 2 * k, dNextK + 2 * k, IDESC_K2, k > 0);
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)  // S* += phiQ^T [dnum | dden]
+                    umma_ss(tmem + C2_SX, dQm + 128 * k, dG1 + 128 * k, IDESC_S, n > 0 || k > 0);
+                umma_commit(&s_done);
+                mbar_wait_poll(&p_ready, n & 1, guard, 914);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)  // dV' += P1 dnum
+                    umma_ts(tmem + C2_DV, tmem + C2_AT + 8 * k, dGm + 128 * k, IDESC_KN, true);
+#pragma unroll
+                for (int k = 0; k < CH / 16; k++)  // dK' += P2 phiQ
+                    umma_ts(tmem + C2_DK, tmem + C2_W + 8 * k, dQm + 128 * k, IDESC_KN, true);
+                umma_commit(&o_full);
+                umma_commit(&stage_free[st]);
+            }
+        }
+    } else {
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&snext_ready);
+        for (int n = 0; n < nc; n++) {
+            const int st = n % NSTAGE, c = nc - 1 - n;
+            const int tok = c * CH + r;
+            const bool valid = tok < p.S;
+            const int64_t row = (int64_t)b * p.S + tok;
+            const float den = valid ? p.den[row] : 1.f;
+            mbar_wait(&full[st], (n / NSTAGE) & 1, guard, 921);
+            step1_row(sG(st) + r * 128, p.O + row * DE, den, valid, r & 7, sDden + r * 128 + (r & 7) * 16);
+            if (p.map_elu) {
+                map_row(sQ(st) + r * 128, valid, true);
+                map_row(sK(st) + r * 128, valid, true);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&mapped);
+
+            // A^T and W2 -> mask s >= t -> bf16 P1, P2 (each over the first 64 columns of its source)
+            mbar_wait(&aw_full, n & 1, guard, 922);
+            tc_fence_after();
+#pragma unroll
+            for (int m = 0; m < 2; m++) {
+                const uint32_t src = lane_base + (m == 0 ? C2_AT : C2_W);
+                uint32_t pk[64];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t v0[32], v1[32];
+                    // a 32-wide column block entirely below this warp's first row is all masked
+                    const bool need0 = 64 * h + 31 >= warp * 32, need1 = 64 * h + 63 >= warp * 32;
+                    if (need0) tmem_ld32(src + 64 * h, v0);
+                    if (need1) tmem_ld32(src + 64 * h + 32, v1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float a0 = (need0 && 64 * h + i >= r) ? __uint_as_float(v0[i]) : 0.f;
+                        const float a1 = (need0 && 64 * h + i + 1 >= r) ? __uint_as_float(v0[i + 1]) : 0.f;
+                        const float b0 = (need1 && 64 * h + 32 + i >= r) ? __uint_as_float(v1[i]) : 0.f;
+                        const float b1 = (need1 && 64 * h + 32 + i + 1 >= r) ? __uint_as_float(v1[i + 1]) : 0.f;
+                        pk[32 * h + i / 2] = pack_bf16(a0, a1);
+                        pk[32 * h + 16 + i / 2] = pack_bf16(b0, b1);
+                    }
+                }
+                tmem_st32(src, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+                tmem_st32(src + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready);
+
+            // output rows use z*_next of the chunks after this one: read it before it is replaced
+            float zb[DE];
+            if (valid) {
+#pragma unroll
+                for (int i = 0; i < DE; i++) zb[i] = zstar[i];
+            }
+            mbar_wait(&o_full, n & 1, guard, 924);
+            tc_fence_after();
+            uint32_t o0[32], o1[32];
+            tmem_ld32(lane_base + C2_DV, o0);
+            tmem_ld32(lane_base + C2_DV + 32, o1);
+            tmem_ld_wait();
+            if (valid) store_grad_row(p.dV + row * DE, nullptr, o0, o1, nullptr);
+            tmem_ld32(lane_base + C2_DK, o0);
+            tmem_ld32(lane_base + C2_DK + 32, o1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free);
+            if (valid) store_grad_row(p.dK + row * DE, p.map_elu ? p.K + row * DE : nullptr, o0, o1, zb);
+
+            // state after this chunk -> operand of the next (earlier) chunk; every compute thread has
+            // read zstar above (the arrivals below are after that in program order)
+            mbar_wait(&s_done, n & 1, guard, 923);
+            tc_fence_after();
+            if (n + 1 < nc) {
+                asm volatile("bar.sync 2, 128;" ::: "memory");  // all 4 compute warps are done with zstar
+                if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&snext_ready);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O,
+                   const void* dO, const float* den, void* dQ, void* dK, void* dV, cudaStream_t st) {
+    if (!linattn_tc_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
+    for (const void* q : {Q, K, V, O, dO, (const void*)dQ, (const void*)dK, (const void*)dV})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    const int B = (int)d.B, S = (int)d.S;
+    CUtensorMap tmQ, tmK, tmV, tmG;
+    if (!make_tmap_bhsd(&tmQ, Q, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH) ||
+        !make_tmap_bhsd(&tmK, K, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH) ||
+        !make_tmap_bhsd(&tmV, V, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH) ||
+        !make_tmap_bhsd(&tmG, dO, B, S, 1, DE, (int64_t)S * DE, DE, DE, CH))
+        return CXXATTN_ERR_CUDA;
+    LinBwdParams p;
+    p.Q = static_cast<const __nv_bfloat16*>(Q);
+    p.K = static_cast<const __nv_bfloat16*>(K);
+    p.O = static_cast<const __nv_bfloat16*>(O);
+    p.den = den;
+    p.dQ = static_cast<__nv_bfloat16*>(dQ);
+    p.dK = static_cast<__nv_bfloat16*>(dK);
+    p.dV = static_cast<__nv_bfloat16*>(dV);
+    p.status = status_word();
+    if (p.status == nullptr) return CXXATTN_ERR_CUDA;
+    p.B = B;
+    p.S = S;
+    p.map_elu = d.feature_map == CXXATTN_MAP_ELU1;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(linattn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SMEM1_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(linattn_tc_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SMEM2_BYTES) != cudaSuccess)
+            return CXXATTN_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    linattn_tc_bwd_dq_kernel<<<(unsigned)B, NTHREADS, SMEM1_BYTES, st>>>(tmK, tmV, tmG, p);
+    if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+    linattn_tc_bwd_dkdv_kernel<<<(unsigned)B, NTHREADS, SMEM2_BYTES, st>>>(tmQ, tmK, tmV, tmG, p);
+    return check_launch();
+}
+
+}  // namespace cxxattn

@@ -75,3 +75,55 @@ def test_unsupported_bf16_requests_are_refused(pkg, dev):
     rc = lib.cxxattn_linattn_fwd(C.byref(d), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), f.data_ptr(), None,
                                  None, 0, None)
     assert rc == -2  # D = E = 32 has no bf16 kernel: an error, not a detour through another path
+
+
+def run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, fmap, eps):
+    tq, tk, tv, tg = (x.to(dev) for x in (Q, K, V, dO))
+    O = torch.full_like(tv, float("nan"))
+    den = torch.full((B * S,), float("nan"), device=dev)
+    pkg.linattn_fwd(tq, tk, tv, O, den, None, B, S, 64, 64, fmap, eps)
+    dQ, dK, dV = (torch.full_like(tq, float("nan")) for _ in range(3))
+    pkg.linattn_bwd(tq, tk, tv, O, tg, den, dQ, dK, dV, B, S, 64, 64, fmap, eps)
+    pkg.sync_status()
+    return [t.float().cpu().numpy() for t in (O, den, dQ, dK, dV)]
+
+
+@pytest.mark.parametrize("B,S", [(1, 128), (2, 256), (2, 1000), (1, 77), (3, 2048)])
+def test_elu_backward_matches_oracle(pkg, dev, orc, B, S):
+    Q, K, V = inputs(21 + S, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(S)).bfloat16()
+    O, den, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    # the reference backward consumes the stored O and den of the forward under test
+    rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O, f[3], den, B, S, 64, 64, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert np.all(np.isfinite(a)), name
+        assert rel_err(a, b) < TOL_BF16, (name, rel_err(a, b))
+
+
+def test_premapped_backward_matches_oracle(pkg, dev, orc):
+    B, S = 2, 700
+    Q, K, V = inputs(31, B, S, 64, 64, positive=True)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(7)).bfloat16()
+    O, den, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_NONE, 1)
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    dnum, dden = orc.linattn_step1(O, f[3], den, f64=True)
+    rdQ, rdK, rdV = orc.linattn_bwd(f[0], f[1], f[2], dnum, dden, B, S, 64, 64, elu=False, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert rel_err(a, b) < TOL_BF16, (name, rel_err(a, b))
+
+
+def test_backward_long_sequence_linearity_and_subset_parity(pkg, dev, orc):
+    """S=4096: dX(4*dO) == 4*dX(dO) (a power of two is exact in bf16/fp32 up to the bf16 roundings
+    it moves), and parity on one unit."""
+    B, S = 4, 4096
+    Q, K, V = inputs(41, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(9)).bfloat16()
+    O, den, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+    _, _, dQ4, dK4, dV4 = run_fwd_bwd(pkg, dev, Q, K, V, dO * 4, B, S, pkg.MAP_ELU1, 0)
+    for a, b in ((dQ4, dQ), (dK4, dK), (dV4, dV)):
+        assert rel_err(a, 4 * b) < 1e-2
+    f = [x[:S].float().numpy() for x in (Q, K, V, dO)]
+    rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O[:S], f[3], den[:S], 1, S, 64, 64, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert rel_err(a[:S], b) < TOL_BF16, (name, rel_err(a[:S], b))
