@@ -308,7 +308,9 @@ def run_ours_linattn(args):
     B, D, E = B0 * H, DH, DH
     N = B * S
     gen = torch.Generator(device="cpu").manual_seed(3 + rank)
-    hQ, hK, hV, hdO = (torch.randn(N, D, generator=gen).pin_memory() for _ in range(4))
+    tdt = torch.bfloat16 if args.lin_dtype == "bf16" else torch.float32
+    w = 2 if args.lin_dtype == "bf16" else 4
+    hQ, hK, hV, hdO = (torch.randn(N, D, generator=gen).to(tdt).pin_memory() for _ in range(4))
     Q, K, V, dO = (t.to(dev) for t in (hQ, hK, hV, hdO))
     O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
     den = torch.empty(N, device=dev)
@@ -338,7 +340,7 @@ def run_ours_linattn(args):
     ms = e0.elapsed_time(e1) / args.steps
 
     # end to end: pinned host tensors in, host tensors out (plain copies around the same two calls)
-    hO, hdQ, hdK, hdV = (torch.empty(N, D).pin_memory() for _ in range(4))
+    hO, hdQ, hdK, hdV = (torch.empty(N, D, dtype=tdt).pin_memory() for _ in range(4))
     hden = torch.empty(N).pin_memory()
 
     def e2e_step():
@@ -364,16 +366,18 @@ def run_ours_linattn(args):
         if rank == 0 and oracle.ReferenceCuda.available():
             rc = oracle.ReferenceCuda()
             buf = rc.scan_buffers(B, S, D, E, dev)
-            rc.kernel_attn(Q, K, V, dO, buf, B, S, D, E)
+            Qf, Kf, Vf, dOf = (t.float() for t in (Q, K, V, dO))  # the same values, as the reference's fp32
+            rc.kernel_attn(Qf, Kf, Vf, dOf, buf, B, S, D, E)
             torch.cuda.synchronize()
             r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             r0.record()
             for _ in range(2):
-                rc.kernel_attn(Q, K, V, dO, buf, B, S, D, E)
+                rc.kernel_attn(Qf, Kf, Vf, dOf, buf, B, S, D, E)
             r1.record()
             torch.cuda.synchronize()
             ref_ms = r0.elapsed_time(r1) / 2
-            ref_err = float((buf["O"] - O).abs().max() / buf["O"].abs().max())
+            ref_err = float((buf["O"] - O.float()).abs().max() / buf["O"].abs().max())
+            del Qf, Kf, Vf, dOf
     except Exception as e:  # the baseline is optional; say why it is missing
         ref_ms, ref_err = None, repr(e)
 
@@ -382,7 +386,7 @@ def run_ours_linattn(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
     if rank == 0:
-        nbytes = lin_bytes_fwd_bwd(B, S, D, E)
+        nbytes = lin_bytes_fwd_bwd(B, S, D, E, w)
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
                 hbm, how = float(json.load(f)["hbm_gbs"]), "measured"
@@ -391,15 +395,18 @@ def run_ours_linattn(args):
         gbs = nbytes / (ms * 1e-3) / 1e9
         line = {"metric": LIN_METRIC, "value": world * gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "vs_baseline": None, "dtype": args.lin_dtype, "data": "synthetic",
                 "config": {"workload": args.workload, "units_per_gpu": B, "S": S, "D": D, "E": E,
                            "tokens_per_gpu": B0 * S, "feature_map": "elu+1",
-                           "l2": "9 tensors x %.0f MB per step exceed the 126 MB L2" % (N * D * 4 / 1e6)},
-                "tokens_per_s": world * B0 * S / (ms * 1e-3), "gpu_launches": args.steps * 12,
+                           "l2": "9 tensors x %.0f MB per step exceed the 126 MB L2" % (N * D * w / 1e6)},
+                "tokens_per_s": world * B0 * S / (ms * 1e-3),
+                "gpu_launches": args.steps * (3 if args.lin_dtype == "bf16" else 12),
                 "clocks": sampler.result(),
                 "e2e": {"value": world * nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": 4 * N * D * 4, "d2h_bytes_per_step": 4 * N * D * 4 + N * 4},
-                "roofline": {"bound": "hbm", "kernel": "chunk_state + chunk_scan + chunk_apply (fwd + bwd call)",
+                        "h2d_bytes_per_step": 4 * N * D * w, "d2h_bytes_per_step": 4 * N * D * w + N * 4},
+                "roofline": {"bound": "hbm",
+                             "kernel": ("linattn_tc_fwd + linattn_tc_bwd_dq + linattn_tc_bwd_dkdv" if w == 2 else
+                                        "chunk_state + chunk_scan + chunk_apply (fwd + bwd call)"),
                              "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s", "frac": gbs / hbm,
                              "traffic": None},
                 "reference_cuda": {"ms_per_step": ref_ms, "speedup": (ref_ms / ms) if ref_ms else None,
@@ -417,7 +424,7 @@ def run_ours_linattn(args):
             o, dn, _ = orc.linattn_fwd(q, k, v, units, s_eff, D, E)
             orc.kernel_attn_bwd(q, k, v, o, g_, dn, units, s_eff, D, E)
             dt = time.perf_counter() - t0
-            line["cpu_baseline"] = {"value": lin_bytes_fwd_bwd(units, s_eff, D, E) / dt / 1e9, "unit": "GB/s",
+            line["cpu_baseline"] = {"value": lin_bytes_fwd_bwd(units, s_eff, D, E, w) / dt / 1e9, "unit": "GB/s",
                                     "cores": units, "kind": "port",
                                     "sample": f"{units} of {B} units of S={s_eff}, fp32 oracle, fwd+bwd ({dt:.1f} s)"}
         print(json.dumps(line), flush=True)
@@ -433,6 +440,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
+                    help="element type of the linattn_* workloads (bf16: tensor-core kernels, f32: exact kernels)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = min(args.steps, 3)
