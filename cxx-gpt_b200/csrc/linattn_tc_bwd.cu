@@ -55,14 +55,17 @@ __device__ __forceinline__ float dphi1(float a) { return a > 0.f ? 1.f : ex2(a *
 __device__ __forceinline__ uint32_t phi2(uint32_t v) { return pack_bf16(phi1(bf_lo(v)), phi1(bf_hi(v))); }
 
 // In-place feature map of one 128-byte tile row (element order does not matter).
-__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu) {
+// Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
+// index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
+__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
     uint4* p = reinterpret_cast<uint4*>(row);
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        uint4 v = p[ch];
+        const int pc = ch ^ rot;
+        uint4 v = p[pc];
         if (!valid) v = make_uint4(0u, 0u, 0u, 0u);
         else if (elu) v = make_uint4(phi2(v.x), phi2(v.y), phi2(v.z), phi2(v.w));
-        p[ch] = v;
+        p[pc] = v;
     }
 }
 
@@ -76,15 +79,17 @@ __device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16*
     float dot = 0.f;
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        // the tile row is stored with its 16-byte chunks permuted (chunk ch holds logical chunk
-        // ch ^ swz); the O row comes from global memory in logical order
-        uint4 g = p[ch];
-        const uint4 ov = valid ? o[ch ^ swz] : make_uint4(0u, 0u, 0u, 0u);
+        // the tile row is stored with its 16-byte chunks permuted: logical chunk ch sits at
+        // position ch ^ swz (swz = row & 7, which also spreads the lanes of a warp over the banks);
+        // the O row comes from global memory in logical order
+        const int pc = ch ^ swz;
+        uint4 g = p[pc];
+        const uint4 ov = valid ? o[ch] : make_uint4(0u, 0u, 0u, 0u);
         dot += bf_lo(g.x) * bf_lo(ov.x) + bf_hi(g.x) * bf_hi(ov.x) + bf_lo(g.y) * bf_lo(ov.y) + bf_hi(g.y) * bf_hi(ov.y) +
                bf_lo(g.z) * bf_lo(ov.z) + bf_hi(g.z) * bf_hi(ov.z) + bf_lo(g.w) * bf_lo(ov.w) + bf_hi(g.w) * bf_hi(ov.w);
         g = make_uint4(pack_bf16(bf_lo(g.x) * inv, bf_hi(g.x) * inv), pack_bf16(bf_lo(g.y) * inv, bf_hi(g.y) * inv),
                        pack_bf16(bf_lo(g.z) * inv, bf_hi(g.z) * inv), pack_bf16(bf_lo(g.w) * inv, bf_hi(g.w) * inv));
-        p[ch] = g;
+        p[pc] = g;
     }
     const float dden = -dot * inv;
     *reinterpret_cast<uint16_t*>(dden_slot) = __bfloat16_as_ushort(__float2bfloat16_rn(dden));
@@ -258,18 +263,27 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
-        for (int c = 0; c < nc; c++) {
+        // step 1 and the feature map of chunk c; done one chunk ahead (after the previous chunk's
+        // products that read the dden side tile have completed) so that chunk c+1's products start
+        // while chunk c is being finished
+        auto prep_chunk = [&](int c) {
             const int st = c % NSTAGE;
             const int tok = c * CH + r;
-            const bool valid = tok < p.S;
+            const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
-            const float den = valid ? p.den[row] : 1.f;
+            const float den = ok ? p.den[row] : 1.f;
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 821);
-            step1_row(sG(st) + r * 128, p.O + row * DE, den, valid, r & 7, sDden + r * 128 + (r & 7) * 16);
-            if (p.map_elu) map_row(sK(st) + r * 128, valid, true);
+            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden + r * 128 + (r & 7) * 16);
+            if (p.map_elu) map_row(sK(st) + r * 128, ok, true, r & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped);
+        };
+        prep_chunk(0);
+        for (int c = 0; c < nc; c++) {
+            const int tok = c * CH + r;
+            const bool valid = tok < p.S;
+            const int64_t row = (int64_t)b * p.S + tok;
 
             // W -> mask s <= t -> bf16 P, written over the first 64 columns of W (each thread only
             // touches its own TMEM lane and has its whole row in registers before it stores)
@@ -300,13 +314,14 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready);
 
-            mbar_wait(&s_done, c & 1, guard, 823);
+            mbar_wait(&s_done, c & 1, guard, 823);  // also: this chunk's readers of the side tile are done
             tc_fence_after();
             if (c + 1 < nc) {
                 if (warp < 2) state_to_smem(lane_base + C1_SX, sPrev, r);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sprev_ready);
+                prep_chunk(c + 1);
             }
 
             mbar_wait(&o_full, c & 1, guard, 824);
@@ -344,7 +359,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, aw_full, p_ready, o_full, o_free, s_done, snext_ready;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ float zstar[DE];  // z*_next in fp32, added to dK in the epilogue
+    __shared__ float zstar[2][DE];  // z*_next in fp32 (double-buffered by iteration parity), added to dK
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     auto sQ = [&](int st) { return smem + (st * 4 + 0) * TILE_BYTES; };
@@ -378,7 +393,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
     for (int i = threadIdx.x; i < (2 * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
         reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (threadIdx.x < DE) zstar[threadIdx.x] = 0.f;
+    if (threadIdx.x < DE) zstar[0][threadIdx.x] = 0.f;
     __syncthreads();
     if (threadIdx.x < CH)
         *reinterpret_cast<uint16_t*>(sOnes + threadIdx.x * 128 + (threadIdx.x & 7) * 16) = 0x3f80;  // bf16 1.0
@@ -460,21 +475,28 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&snext_ready);
-        for (int n = 0; n < nc; n++) {
+        auto prep_chunk = [&](int n) {  // step 1 and feature maps of iteration n, one iteration ahead
             const int st = n % NSTAGE, c = nc - 1 - n;
             const int tok = c * CH + r;
-            const bool valid = tok < p.S;
+            const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
-            const float den = valid ? p.den[row] : 1.f;
+            const float den = ok ? p.den[row] : 1.f;
             mbar_wait(&full[st], (n / NSTAGE) & 1, guard, 921);
-            step1_row(sG(st) + r * 128, p.O + row * DE, den, valid, r & 7, sDden + r * 128 + (r & 7) * 16);
+            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden + r * 128 + (r & 7) * 16);
             if (p.map_elu) {
-                map_row(sQ(st) + r * 128, valid, true);
-                map_row(sK(st) + r * 128, valid, true);
+                map_row(sQ(st) + r * 128, ok, true, r & 7);
+                map_row(sK(st) + r * 128, ok, true, r & 7);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped);
+        };
+        prep_chunk(0);
+        for (int n = 0; n < nc; n++) {
+            const int c = nc - 1 - n;
+            const int tok = c * CH + r;
+            const bool valid = tok < p.S;
+            const int64_t row = (int64_t)b * p.S + tok;
 
             // A^T and W2 -> mask s >= t -> bf16 P1, P2 (each over the first 64 columns of its source)
             mbar_wait(&aw_full, n & 1, guard, 922);
@@ -509,12 +531,19 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready);
 
-            // output rows use z*_next of the chunks after this one: read it before it is replaced
-            float zb[DE];
-            if (valid) {
-#pragma unroll
-                for (int i = 0; i < DE; i++) zb[i] = zstar[i];
+            // state after this chunk -> operand of the next (earlier) chunk, then step 1 / maps of that
+            // chunk, so that its products start while this chunk's outputs are written.  z* goes to the
+            // other half of `zstar`: the epilogue below still reads this iteration's half.
+            mbar_wait(&s_done, n & 1, guard, 923);  // also: this chunk's readers of the side tile are done
+            tc_fence_after();
+            if (n + 1 < nc) {
+                if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar[(n + 1) & 1]);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&snext_ready);
+                prep_chunk(n + 1);
             }
+
             mbar_wait(&o_full, n & 1, guard, 924);
             tc_fence_after();
             uint32_t o0[32], o1[32];
@@ -528,19 +557,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&o_free);
-            if (valid) store_grad_row(p.dK + row * DE, p.map_elu ? p.K + row * DE : nullptr, o0, o1, zb);
-
-            // state after this chunk -> operand of the next (earlier) chunk; every compute thread has
-            // read zstar above (the arrivals below are after that in program order)
-            mbar_wait(&s_done, n & 1, guard, 923);
-            tc_fence_after();
-            if (n + 1 < nc) {
-                asm volatile("bar.sync 2, 128;" ::: "memory");  // all 4 compute warps are done with zstar
-                if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&snext_ready);
-            }
+            if (valid) store_grad_row(p.dK + row * DE, p.map_elu ? p.K + row * DE : nullptr, o0, o1, zstar[n & 1]);
         }
     }
     tc_fence_before();

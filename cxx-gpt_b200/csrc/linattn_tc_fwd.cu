@@ -55,14 +55,17 @@ __device__ __forceinline__ uint32_t phi2(uint32_t v) {  // two bf16 values -> ph
     return pack_bf16(pa, pb);
 }
 // In-place feature map of one 128-byte row of a tile (element order does not matter).
-__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu) {
+// Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
+// index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
+__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
     uint4* p = reinterpret_cast<uint4*>(row);
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        uint4 v = p[ch];
+        const int pc = ch ^ rot;
+        uint4 v = p[pc];
         if (!valid) v = make_uint4(0u, 0u, 0u, 0u);
         else if (elu) v = make_uint4(phi2(v.x), phi2(v.y), phi2(v.z), phi2(v.w));
-        p[ch] = v;
+        p[pc] = v;
     }
 }
 
@@ -178,19 +181,25 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
-        for (int c = 0; c < nc; c++) {
+        // feature map of chunk c, in place (with no map, rows past the end are already zero: TMA
+        // fills them).  It is done one chunk ahead, right after the P of the previous chunk has been
+        // handed over, so that the products of chunk c+1 start while chunk c is being finished.
+        auto map_chunk = [&](int c) {
             const int st = c % NSTAGE;
-            const int tok = c * CH + r;
-            const bool valid = tok < p.S;
-            // feature map, in place (with no map, rows past the end are already zero: TMA fills them)
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 721);
             if (p.map_elu) {
-                map_row(sQ(st) + r * 128, valid, true);
-                map_row(sK(st) + r * 128, valid, true);
+                const bool ok = c * CH + r < p.S;
+                map_row(sQ(st) + r * 128, ok, true, r & 7);
+                map_row(sK(st) + r * 128, ok, true, r & 7);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped);
+        };
+        map_chunk(0);
+        for (int c = 0; c < nc; c++) {
+            const int tok = c * CH + r;
+            const bool valid = tok < p.S;
 
             // A -> causal mask inside the chunk (key column s visible iff s <= r), row sum, bf16 P
             mbar_wait(&a_full, c & 1, guard, 722);
@@ -220,6 +229,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready);
+            if (c + 1 < nc) map_chunk(c + 1);
 
             // state after this chunk -> bf16 operand of the next chunk's inter-chunk product
             mbar_wait(&s_done, c & 1, guard, 723);
