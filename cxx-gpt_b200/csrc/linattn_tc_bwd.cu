@@ -32,7 +32,7 @@ constexpr int CH = 128;
 constexpr int DE = 64;
 constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
 constexpr int NSTAGE = 2;
-constexpr int NTHREADS = 192;  // 4 compute warps, TMA producer, MMA issuer
+constexpr int NTHREADS = 320;  // 4 compute warps, TMA producer, MMA issuer, 4 preparation warps (step 1, maps)
 constexpr uint32_t TMEM_COLS = 512;
 
 struct LinBwdParams {
@@ -52,21 +52,36 @@ __device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v <<
 __device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 __device__ __forceinline__ float phi1(float a) { return a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f); }
 __device__ __forceinline__ float dphi1(float a) { return a > 0.f ? 1.f : ex2(a * 1.4426950408889634f); }
-__device__ __forceinline__ uint32_t phi2(uint32_t v) { return pack_bf16(phi1(bf_lo(v)), phi1(bf_hi(v))); }
+// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e).  The product x*log2(e) is
+// rounded to bf16 before the exponential (relative effect ln2*|t|*2^-9 on values that are then
+// rounded to bf16 anyway); one MUFU operation serves two elements.
+__device__ __forceinline__ uint32_t phi2(uint32_t v) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
+    const __nv_bfloat162 t = __hmul2(x, __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
+    uint32_t e;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<const uint32_t*>(&t)));
+    const __nv_bfloat162 pos = __hadd2(x, __floats2bfloat162_rn(1.f, 1.f));
+    const uint32_t m = __hgt2_mask(x, __floats2bfloat162_rn(0.f, 0.f));  // 0xffff per half where x > 0
+    return (*reinterpret_cast<const uint32_t*>(&pos) & m) | (e & ~m);
+}
 
 // In-place feature map of one 128-byte tile row (element order does not matter).
 // Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
 // index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
 __device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
     uint4* p = reinterpret_cast<uint4*>(row);
+    uint4 v[8];
+    // all loads first, all stores last: with run-time chunk positions the compiler cannot reorder
+    // a load past an earlier store, and a lone warp would crawl through eight dependent round trips
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) v[ch] = p[ch ^ rot];
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        const int pc = ch ^ rot;
-        uint4 v = p[pc];
-        if (!valid) v = make_uint4(0u, 0u, 0u, 0u);
-        else if (elu) v = make_uint4(phi2(v.x), phi2(v.y), phi2(v.z), phi2(v.w));
-        p[pc] = v;
+        if (!valid) v[ch] = make_uint4(0u, 0u, 0u, 0u);
+        else if (elu) v[ch] = make_uint4(phi2(v[ch].x), phi2(v[ch].y), phi2(v[ch].z), phi2(v[ch].w));
     }
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) p[ch ^ rot] = v[ch];
 }
 
 // Step 1 for one token row: the dO tile row becomes dnum = dO / den in place, dden = -(dO . O) / den
@@ -76,21 +91,26 @@ __device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16*
     uint4* p = reinterpret_cast<uint4*>(do_row);
     const uint4* o = reinterpret_cast<const uint4*>(o_row);
     const float inv = valid ? 1.0f / den : 0.f;
+    // The tile row is stored with its 16-byte chunks permuted: logical chunk ch sits at position
+    // ch ^ swz (swz = row & 7, which also spreads the lanes of a warp over the banks); the O row comes
+    // from global memory in logical order.  All loads first, all stores last.
+    uint4 g[8], ov[8];
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        g[ch] = p[ch ^ swz];
+        ov[ch] = valid ? o[ch] : make_uint4(0u, 0u, 0u, 0u);
+    }
     float dot = 0.f;
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        // the tile row is stored with its 16-byte chunks permuted: logical chunk ch sits at
-        // position ch ^ swz (swz = row & 7, which also spreads the lanes of a warp over the banks);
-        // the O row comes from global memory in logical order
-        const int pc = ch ^ swz;
-        uint4 g = p[pc];
-        const uint4 ov = valid ? o[ch] : make_uint4(0u, 0u, 0u, 0u);
-        dot += bf_lo(g.x) * bf_lo(ov.x) + bf_hi(g.x) * bf_hi(ov.x) + bf_lo(g.y) * bf_lo(ov.y) + bf_hi(g.y) * bf_hi(ov.y) +
-               bf_lo(g.z) * bf_lo(ov.z) + bf_hi(g.z) * bf_hi(ov.z) + bf_lo(g.w) * bf_lo(ov.w) + bf_hi(g.w) * bf_hi(ov.w);
-        g = make_uint4(pack_bf16(bf_lo(g.x) * inv, bf_hi(g.x) * inv), pack_bf16(bf_lo(g.y) * inv, bf_hi(g.y) * inv),
-                       pack_bf16(bf_lo(g.z) * inv, bf_hi(g.z) * inv), pack_bf16(bf_lo(g.w) * inv, bf_hi(g.w) * inv));
-        p[pc] = g;
+        const uint4 a = g[ch], c = ov[ch];
+        dot += bf_lo(a.x) * bf_lo(c.x) + bf_hi(a.x) * bf_hi(c.x) + bf_lo(a.y) * bf_lo(c.y) + bf_hi(a.y) * bf_hi(c.y) +
+               bf_lo(a.z) * bf_lo(c.z) + bf_hi(a.z) * bf_hi(c.z) + bf_lo(a.w) * bf_lo(c.w) + bf_hi(a.w) * bf_hi(c.w);
+        g[ch] = make_uint4(pack_bf16(bf_lo(a.x) * inv, bf_hi(a.x) * inv), pack_bf16(bf_lo(a.y) * inv, bf_hi(a.y) * inv),
+                           pack_bf16(bf_lo(a.z) * inv, bf_hi(a.z) * inv), pack_bf16(bf_lo(a.w) * inv, bf_hi(a.w) * inv));
     }
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) p[ch ^ swz] = g[ch];
     const float dden = -dot * inv;
     *reinterpret_cast<uint16_t*>(dden_slot) = __bfloat16_as_ushort(__float2bfloat16_rn(dden));
     return dden;
@@ -154,8 +174,8 @@ __device__ __forceinline__ void store_grad_row(__nv_bfloat16* dst, const __nv_bf
 // pass 1: dQ
 // ---------------------------------------------------------------------------------------------
 constexpr uint32_t C1_W = 0, C1_DQ = 128, C1_SX = 192;  // W/P | dQ' | state (80 columns)
-// per stage K | V | dO, then ones tile, dden side tile, state operand (2 blocks x 8 KB)
-constexpr size_t SMEM1_BYTES = NSTAGE * 3 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 1024;
+// per stage K | V | dO, then ones tile, dden side tile per stage, state operand (2 blocks x 8 KB)
+constexpr size_t SMEM1_BYTES = NSTAGE * 3 * TILE_BYTES + (1 + NSTAGE) * TILE_BYTES + 2 * 8192 + 1024;
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -170,8 +190,8 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     auto sV = [&](int st) { return smem + (st * 3 + 1) * TILE_BYTES; };
     auto sG = [&](int st) { return smem + (st * 3 + 2) * TILE_BYTES; };  // dO, rescaled to dnum in place
     uint8_t* sOnes = smem + NSTAGE * 3 * TILE_BYTES;  // [128][64] bf16, column 0 = 1
-    uint8_t* sDden = sOnes + TILE_BYTES;              // [128 tokens][64] bf16, column 0 = dden_t
-    uint8_t* sPrev = sDden + TILE_BYTES;              // block 0: S_prev [64 d][64 e]; block 1: column 0 = z_prev
+    auto sDden = [&](int st) { return sOnes + (1 + st) * TILE_BYTES; };  // [128 tokens][64] bf16, column 0 = dden_t
+    uint8_t* sPrev = sOnes + (1 + NSTAGE) * TILE_BYTES;  // block 0: S_prev [64 d][64 e]; block 1: column 0 = z_prev
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int b = blockIdx.x;
@@ -194,7 +214,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         fence_barrier_init();
     }
     if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
-    for (int i = threadIdx.x; i < (2 * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
+    for (int i = threadIdx.x; i < ((1 + NSTAGE) * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
         reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     if (threadIdx.x < CH)
@@ -225,10 +245,11 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             constexpr uint32_t IDESC_I = idesc_bf16(CH, DE, 0, 0);  // [dnum|dden][S_prev|z]^T: both K-major
             constexpr uint32_t IDESC_P = idesc_bf16(CH, DE, 0, 1);  // P phiK: A in TMEM, B MN-major
             constexpr uint32_t IDESC_S = idesc_bf16(CH, 80, 1, 1);  // phiK^T [V | 1]: both MN-major
-            const uint64_t dOnes = smem_desc_sw128(smem_u32(sOnes), 16), dDd = smem_desc_sw128(smem_u32(sDden), 16);
+            const uint64_t dOnes = smem_desc_sw128(smem_u32(sOnes), 16);
             const uint64_t dPrev0 = smem_desc_sw128(smem_u32(sPrev), 16), dPrev1 = smem_desc_sw128(smem_u32(sPrev) + 8192, 16);
             for (int c = 0; c < nc; c++) {
                 const int st = c % NSTAGE;
+                const uint64_t dDd = smem_desc_sw128(smem_u32(sDden(st)), 16);
                 const uint64_t dG = smem_desc_sw128(smem_u32(sG(st)), 16), dVk = smem_desc_sw128(smem_u32(sV(st)), 16);
                 const uint64_t dKm = smem_desc_sw128(smem_u32(sK(st)), 0);
                 const uint64_t dV1 = smem_desc_sw128(smem_u32(sV(st)), smem_u32(sOnes) - smem_u32(sV(st)));
@@ -257,29 +278,28 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 umma_commit(&stage_free[st]);
             }
         }
-    } else {
-        const int r = warp * 32 + lane;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sprev_ready);
-        // step 1 and the feature map of chunk c; done one chunk ahead (after the previous chunk's
-        // products that read the dden side tile have completed) so that chunk c+1's products start
-        // while chunk c is being finished
-        auto prep_chunk = [&](int c) {
+    } else if (warp >= 6) {
+        // ---------------- preparation warps: step 1 and the feature map, as soon as a chunk has landed ----------------
+        const int r = (warp - 6) * 32 + lane;
+        for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
             const int tok = c * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = ok ? p.den[row] : 1.f;
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 821);
-            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden + r * 128 + (r & 7) * 16);
+            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
             if (p.map_elu) map_row(sK(st) + r * 128, ok, true, r & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped);
-        };
-        prep_chunk(0);
+        }
+    } else {
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sprev_ready);
         for (int c = 0; c < nc; c++) {
             const int tok = c * CH + r;
             const bool valid = tok < p.S;
@@ -314,14 +334,13 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready);
 
-            mbar_wait(&s_done, c & 1, guard, 823);  // also: this chunk's readers of the side tile are done
+            mbar_wait(&s_done, c & 1, guard, 823);
             tc_fence_after();
             if (c + 1 < nc) {
                 if (warp < 2) state_to_smem(lane_base + C1_SX, sPrev, r);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sprev_ready);
-                prep_chunk(c + 1);
             }
 
             mbar_wait(&o_full, c & 1, guard, 824);
@@ -349,7 +368,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // ---------------------------------------------------------------------------------------------
 constexpr uint32_t C2_AT = 0, C2_W = 128, C2_DV = 256, C2_DK = 320, C2_SX = 384;
 // per stage Q | K | V | dO, then ones tile, dden side tile, state operand (2 blocks x 8 KB)
-constexpr size_t SMEM2_BYTES = NSTAGE * 4 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 1024;
+constexpr size_t SMEM2_BYTES = NSTAGE * 4 * TILE_BYTES + (1 + NSTAGE) * TILE_BYTES + 2 * 8192 + 1024;
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -367,8 +386,8 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     auto sV = [&](int st) { return smem + (st * 4 + 2) * TILE_BYTES; };
     auto sG = [&](int st) { return smem + (st * 4 + 3) * TILE_BYTES; };
     uint8_t* sOnes = smem + NSTAGE * 4 * TILE_BYTES;
-    uint8_t* sDden = sOnes + TILE_BYTES;
-    uint8_t* sNext = sDden + TILE_BYTES;  // block 0: S*_next [64 d][64 e]; block 1: column 0 = z*_next
+    auto sDden = [&](int st) { return sOnes + (1 + st) * TILE_BYTES; };
+    uint8_t* sNext = sOnes + (1 + NSTAGE) * TILE_BYTES;  // block 0: S*_next [64 d][64 e]; block 1: column 0 = z*_next
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int b = blockIdx.x;
@@ -391,7 +410,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         fence_barrier_init();
     }
     if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
-    for (int i = threadIdx.x; i < (2 * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
+    for (int i = threadIdx.x; i < ((1 + NSTAGE) * TILE_BYTES + 2 * 8192) / 16; i += NTHREADS)
         reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (threadIdx.x < DE) zstar[0][threadIdx.x] = 0.f;
     __syncthreads();
@@ -426,7 +445,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             constexpr uint32_t IDESC_KN = idesc_bf16(CH, DE, 0, 1);  // A K-major (or TMEM), B MN-major
             constexpr uint32_t IDESC_K2 = idesc_bf16(CH, DE, 0, 0);  // V S*^T: both K-major
             constexpr uint32_t IDESC_S = idesc_bf16(CH, 80, 1, 1);   // phiQ^T [dnum | dden]: both MN-major
-            const uint64_t dOnes = smem_desc_sw128(smem_u32(sOnes), 16), dDd = smem_desc_sw128(smem_u32(sDden), 16);
+            const uint64_t dOnes = smem_desc_sw128(smem_u32(sOnes), 16);
             const uint64_t dNextK = smem_desc_sw128(smem_u32(sNext), 16);  // rows d, K = e   (for V S*^T)
             const uint64_t dNextM = smem_desc_sw128(smem_u32(sNext), 0);   // rows = K = d, N = e (for phiK S*)
             for (int n = 0; n < nc; n++) {
@@ -435,7 +454,8 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                 const uint64_t dVk = smem_desc_sw128(smem_u32(sV(st)), 16), dGk = smem_desc_sw128(smem_u32(sG(st)), 16);
                 const uint64_t dQm = smem_desc_sw128(smem_u32(sQ(st)), 0);  // phiQ MN-major (A of the state, B of dK)
                 const uint64_t dGm = smem_desc_sw128(smem_u32(sG(st)), 0);  // dnum MN-major (B of dV)
-                const uint64_t dG1 = smem_desc_sw128(smem_u32(sG(st)), smem_u32(sDden) - smem_u32(sG(st)));  // [dnum | dden]
+                const uint64_t dDd = smem_desc_sw128(smem_u32(sDden(st)), 16);
+                const uint64_t dG1 = smem_desc_sw128(smem_u32(sG(st)), smem_u32(sDden(st)) - smem_u32(sG(st)));  // [dnum | dden]
                 mbar_wait_poll(&mapped, n & 1, guard, 911);
                 tc_fence_after();
 #pragma unroll
@@ -469,20 +489,17 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                 umma_commit(&stage_free[st]);
             }
         }
-    } else {
-        const int r = warp * 32 + lane;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&snext_ready);
-        auto prep_chunk = [&](int n) {  // step 1 and feature maps of iteration n, one iteration ahead
+    } else if (warp >= 6) {
+        // ---------------- preparation warps: step 1 and the feature maps of Q and K ----------------
+        const int r = (warp - 6) * 32 + lane;
+        for (int n = 0; n < nc; n++) {
             const int st = n % NSTAGE, c = nc - 1 - n;
             const int tok = c * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = ok ? p.den[row] : 1.f;
             mbar_wait(&full[st], (n / NSTAGE) & 1, guard, 921);
-            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden + r * 128 + (r & 7) * 16);
+            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
             if (p.map_elu) {
                 map_row(sQ(st) + r * 128, ok, true, r & 7);
                 map_row(sK(st) + r * 128, ok, true, r & 7);
@@ -490,8 +507,13 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped);
-        };
-        prep_chunk(0);
+        }
+    } else {
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&snext_ready);
         for (int n = 0; n < nc; n++) {
             const int c = nc - 1 - n;
             const int tok = c * CH + r;
@@ -534,14 +556,13 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             // state after this chunk -> operand of the next (earlier) chunk, then step 1 / maps of that
             // chunk, so that its products start while this chunk's outputs are written.  z* goes to the
             // other half of `zstar`: the epilogue below still reads this iteration's half.
-            mbar_wait(&s_done, n & 1, guard, 923);  // also: this chunk's readers of the side tile are done
+            mbar_wait(&s_done, n & 1, guard, 923);
             tc_fence_after();
             if (n + 1 < nc) {
                 if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar[(n + 1) & 1]);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&snext_ready);
-                prep_chunk(n + 1);
             }
 
             mbar_wait(&o_full, n & 1, guard, 924);

@@ -8,7 +8,7 @@
 // O and den are written once, and the running state never leaves the SM:
 //
 //   phi            the feature map (ELU+1 or none) is applied in place on the Q and K tiles in shared
-//                  memory, rows past the end of the sequence are zeroed
+//                  memory by four dedicated warps, rows past the end of the sequence are zeroed
 //   A   = phiQ phiK^T                       (SS MMA 128x128x64)   -> TMEM, masked to s <= t by the
 //                                            compute warps, row sums taken, bf16 back to TMEM (P)
 //   O'  = phiQ [S_prev | z_prev]            (SS MMA 128x80x64: the state of all earlier chunks as a
@@ -33,7 +33,7 @@ constexpr int CH = 128;  // tokens per chunk
 constexpr int DE = 64;   // feature width (D = E)
 constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
 constexpr int NSTAGE = 2;
-constexpr int NTHREADS = 192;  // 4 compute warps, TMA producer, MMA issuer
+constexpr int NTHREADS = 320;  // 4 compute warps, TMA producer, MMA issuer, 4 feature-map warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_A = 0, COL_P = 128, COL_O = 192, COL_SX = 288;
 // per stage Q | K | V, then the ones tile, then the bf16 state operand (2 blocks of 64 rows x 128 B)
@@ -48,25 +48,35 @@ struct LinFwdParams {
     int eps_in_den;  // 1: den stored with the 1e-8 added
 };
 
-__device__ __forceinline__ uint32_t phi2(uint32_t v) {  // two bf16 values -> phi -> two bf16 values
-    const float a = __uint_as_float(v << 16), b = __uint_as_float(v & 0xffff0000u);
-    const float pa = a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f);
-    const float pb = b > 0.f ? b + 1.f : ex2(b * 1.4426950408889634f);
-    return pack_bf16(pa, pb);
+// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e).  The product x*log2(e) is
+// rounded to bf16 before the exponential (relative effect ln2*|t|*2^-9 on values that are then
+// rounded to bf16 anyway); one MUFU operation serves two elements.
+__device__ __forceinline__ uint32_t phi2(uint32_t v) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
+    const __nv_bfloat162 t = __hmul2(x, __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
+    uint32_t e;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<const uint32_t*>(&t)));
+    const __nv_bfloat162 pos = __hadd2(x, __floats2bfloat162_rn(1.f, 1.f));
+    const uint32_t m = __hgt2_mask(x, __floats2bfloat162_rn(0.f, 0.f));  // 0xffff per half where x > 0
+    return (*reinterpret_cast<const uint32_t*>(&pos) & m) | (e & ~m);
 }
 // In-place feature map of one 128-byte row of a tile (element order does not matter).
 // Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
 // index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
 __device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
     uint4* p = reinterpret_cast<uint4*>(row);
+    uint4 v[8];
+    // all loads first, all stores last: with run-time chunk positions the compiler cannot reorder
+    // a load past an earlier store, and a lone warp would crawl through eight dependent round trips
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) v[ch] = p[ch ^ rot];
 #pragma unroll
     for (int ch = 0; ch < 8; ch++) {
-        const int pc = ch ^ rot;
-        uint4 v = p[pc];
-        if (!valid) v = make_uint4(0u, 0u, 0u, 0u);
-        else if (elu) v = make_uint4(phi2(v.x), phi2(v.y), phi2(v.z), phi2(v.w));
-        p[pc] = v;
+        if (!valid) v[ch] = make_uint4(0u, 0u, 0u, 0u);
+        else if (elu) v[ch] = make_uint4(phi2(v[ch].x), phi2(v[ch].y), phi2(v[ch].z), phi2(v[ch].w));
     }
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) p[ch ^ rot] = v[ch];
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -173,18 +183,13 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 umma_commit(&stage_free[st]);
             }
         }
-    } else {
-        // ---------------- compute warps: thread r = token row r of the chunk = TMEM lane r ----------------
-        const int r = warp * 32 + lane;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        // the state operand of the first chunk is the zero tile written at start-up
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sprev_ready);
-        // feature map of chunk c, in place (with no map, rows past the end are already zero: TMA
-        // fills them).  It is done one chunk ahead, right after the P of the previous chunk has been
-        // handed over, so that the products of chunk c+1 start while chunk c is being finished.
-        auto map_chunk = [&](int c) {
+    } else if (warp >= 6) {
+        // ---------------- feature-map warps: thread r = row r of the Q and K tiles ----------------
+        // The map is applied in place as soon as a chunk has landed (with no map there is nothing to
+        // do: rows past the end are already zero, TMA fills them), independently of the compute
+        // warps, which are still busy with the previous chunk.
+        const int r = (warp - 6) * 32 + lane;
+        for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 721);
             if (p.map_elu) {
@@ -195,8 +200,15 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped);
-        };
-        map_chunk(0);
+        }
+    } else {
+        // ---------------- compute warps: thread r = token row r of the chunk = TMEM lane r ----------------
+        const int r = warp * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        // the state operand of the first chunk is the zero tile written at start-up
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sprev_ready);
         for (int c = 0; c < nc; c++) {
             const int tok = c * CH + r;
             const bool valid = tok < p.S;
@@ -229,7 +241,6 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready);
-            if (c + 1 < nc) map_chunk(c + 1);
 
             // state after this chunk -> bf16 operand of the next chunk's inter-chunk product
             mbar_wait(&s_done, c & 1, guard, 723);
