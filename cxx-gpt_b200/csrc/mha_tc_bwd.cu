@@ -9,17 +9,18 @@
 //
 //   S^T  = K Q_i^T                 (SS MMA, keys on the 128 TMEM lanes, queries on 128 columns)
 //   dP^T = V dO_i^T                (SS MMA)
-//   P^T  = exp2(c S^T - lse2_q)    (warps 0-3, lane = key row)  -> bf16 in TMEM
-//   dS^T = P^T o (dP^T - delta_q)  (warps 4-7, lane = key row)  -> bf16 in shared memory, one tile that
-//                                  is both a K-major operand [keys][queries] and an MN-major one
+//   P^T  = exp2(c S^T - lse2_q)    (lane = key row)  -> bf16 in registers and in TMEM
+//   dS^T = P^T o (dP^T - delta_q)  -> bf16 in shared memory, one tile that is both a K-major operand
+//                                  [keys][queries] and an MN-major one
 //   dV  += P^T dO_i                (TS MMA: P^T from TMEM, dO_i as an MN-major operand)
 //   dK  += dS^T Q_i                (SS MMA: dS read K-major, Q_i MN-major)
 //   dQ_i = dS K                    (SS MMA: dS read MN-major), drained from TMEM through shared memory
 //                                  with one bulk reduce-add per warp into an fp32 accumulator
 //
-// The two warp groups work on different phases of the pipeline (the P group is already on tile i+1
-// while the dS group finishes tile i), and the MMA warp issues S^T(i+1) and dP^T(i+1) as soon as
-// tile i's have been read out of TMEM, so the tensor pipe does not wait for the exponentials.
+// Two compute warp groups take the query tiles alternately (group 0 the even ones, group 1 the odd
+// ones) and each does both halves of its tile, so P^T never has to be read back; the MMA warp issues
+// S^T(i+1) and dP^T(i+1) as soon as tile i's have been read out of TMEM, so one group is in the
+// first half of tile i+1 while the other is in the second half of tile i.
 //
 // Three launches per call: a row pre-pass (delta = dO.O, lse in log2 units padded to whole tiles,
 // accumulator cleared), the main kernel, and a pass turning the accumulator into bf16 dQ.
@@ -39,7 +40,7 @@ constexpr int NTHREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_ST = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_P = 448;
 // K | V | Q x2 | dO x2 | dS (2 blocks) | (lse2, delta) x2 | dQ staging
-constexpr int STAGE_BYTES = 4 * 8192;  // dQ staging: 32 rows x 64 fp32 per warp of the dS group
+constexpr int STAGE_BYTES = 8 * 8192;  // dQ staging: 32 rows x 64 fp32 per compute warp
 constexpr size_t SMEM_BYTES = 8 * TILE_BYTES + 2 * 1024 + STAGE_BYTES + 1024;
 
 struct BwdParams {
@@ -180,8 +181,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t kv_full, q_full[2], do_full[2], qdo_free[2], s_full, s_free, dp_full, dp_free, p_ready, p_read,
-        dv_done, ds_ready, dq_full, dq_free, all_done;
+    __shared__ uint64_t kv_full, q_full[2], do_full[2], qdo_free[2], s_full[2], dp_full[2], dv_done[2], dq_full[2], s_free,
+        dp_free, p_ready, ds_ready, dq_free, all_done;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -192,7 +193,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* sdO = smem + 4 * TILE_BYTES;  // 2 stages
     uint8_t* sDS = smem + 6 * TILE_BYTES;  // 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
     float* sStat = reinterpret_cast<float*>(smem + 8 * TILE_BYTES);  // [stage][lse2 | delta][128]
-    uint8_t* sStage = smem + 8 * TILE_BYTES + 2048;                  // [dS-group warp][32 rows][256 B]
+    uint8_t* sStage = smem + 8 * TILE_BYTES + 2048;                  // [compute warp][32 rows][256 B]
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int ntile = p.Spad / BT;
@@ -212,16 +213,17 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(&do_full[s], 1);
             mbar_init(&qdo_free[s], 1);
         }
-        mbar_init(&s_full, 1);
-        mbar_init(&dp_full, 1);
-        mbar_init(&dv_done, 1);
-        mbar_init(&dq_full, 1);
+        for (int s = 0; s < 2; s++) {  // waited on by the compute group that owns tiles of this parity
+            mbar_init(&s_full[s], 1);
+            mbar_init(&dp_full[s], 1);
+            mbar_init(&dv_done[s], 1);
+            mbar_init(&dq_full[s], 1);
+        }
         mbar_init(&all_done, 1);
-        // one arrival per warp of the group that signals
+        // waited on by the MMA thread, tile after tile; one arrival per warp of the group that signals
         mbar_init(&s_free, 4);
         mbar_init(&p_ready, 4);
         mbar_init(&dp_free, 4);
-        mbar_init(&p_read, 4);
         mbar_init(&ds_ready, 4);
         mbar_init(&dq_free, 4);
         fence_barrier_init();
@@ -270,13 +272,13 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const uint64_t q = dQ0 + s * TILE16;
 #pragma unroll
                 for (int k = 0; k < DH / 16; k++) umma_ss(tmem + COL_ST, dK + 2 * k, q + 2 * k, IDESC_SS, k > 0);
-                umma_commit(&s_full);
+                umma_commit(&s_full[s]);
             };
             auto issue_dp = [&](int s) {
                 const uint64_t g = dG0 + s * TILE16;
 #pragma unroll
                 for (int k = 0; k < DH / 16; k++) umma_ss(tmem + COL_DP, dV + 2 * k, g + 2 * k, IDESC_SS, k > 0);
-                umma_commit(&dp_full);
+                umma_commit(&dp_full[s]);
             };
             mbar_wait_poll(&kv_full, 0, guard, 501);
             mbar_wait_poll(&q_full[0], 0, guard, 502);
@@ -288,23 +290,24 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int it = 0; it < niter; it++) {
                 const int s = it & 1, sn = s ^ 1;
                 const uint64_t q = dQ0 + s * TILE16, g = dG0 + s * TILE16;
-                if (it + 1 < niter) {
-                    // next scores and next dP^T as soon as this iteration's have been read out
+                if (it + 1 < niter) {  // next scores as soon as this tile's are in registers
                     mbar_wait_poll(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
                     mbar_wait_poll(&s_free, it & 1, guard, 504);
                     tc_fence_after();
                     issue_st(sn);
-                    mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
-                    mbar_wait_poll(&dp_free, it & 1, guard, 510);
-                    tc_fence_after();
-                    issue_dp(sn);
                 }
                 mbar_wait_poll(&p_ready, it & 1, guard, 505);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i   (A: P^T bf16 in TMEM)
                     umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_KN, it > 0 || k > 0);
-                umma_commit(&dv_done);
+                umma_commit(&dv_done[s]);
+                if (it + 1 < niter) {  // next dP^T as soon as this tile's is in registers
+                    mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
+                    mbar_wait_poll(&dp_free, it & 1, guard, 510);
+                    tc_fence_after();
+                    issue_dp(sn);
+                }
                 mbar_wait_poll(&ds_ready, it & 1, guard, 507);
                 tc_fence_after();
 #pragma unroll
@@ -318,20 +321,50 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K       (A: the same tile read MN-major)
                     umma_ss(tmem + COL_DQ, dDSm + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
-                umma_commit(&dq_full);
+                umma_commit(&dq_full[s]);
             }
             umma_commit(&all_done);
         }
-    } else if (warp < 4) {
-        // ---------------- P group (warps 0-3): lane = key row, all 128 query columns ----------------
-        const int r = warp * 32 + lane;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        const uint32_t tS = lane_base + COL_ST, tP = lane_base + COL_P;
-        for (int it = 0; it < niter; it++) {
-            const int s = it & 1;
-            mbar_wait(&q_full[s], (it / 2) & 1, guard, 601);  // lse2 of this query tile is in smem
-            const float* l2 = sStat + s * 256;
-            mbar_wait(&s_full, it & 1, guard, 602);
+    } else {
+        // ---------------- compute groups: group g (warps 4g..4g+3) owns the query tiles it = g, g+2, ... ----------------
+        // lane = key row; a thread turns its row of S^T into P^T (bf16, kept in registers and copied to
+        // TMEM for the dV product), then P^T and dP^T into dS^T.  While one group is in the second
+        // half of tile i the other is already in the first half of tile i+1.
+        const int g = warp / 4;
+        const int q4 = warp % 4;
+        const int r = q4 * 32 + lane;
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+        const uint32_t tS = lane_base + COL_ST, tP = lane_base + COL_P, tDP = lane_base + COL_DP, tDQ = lane_base + COL_DQ;
+        // dQ tile it-1 (written by the other group's dS): this group's warps drain it, rows 32*q4.., all
+        // 64 columns in two 4 KB pieces
+        float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + q4 * 32) * DH;
+        auto drain_dq = [&](int tile) {
+            uint32_t d0[32], d1[32];
+            tmem_ld32(tDQ, d0);
+            tmem_ld32(tDQ + 32, d1);
+            tmem_ld_wait();
+            tc_fence_before();
+            warp_arrive(&dq_free, lane);
+            if (lane == 0) bulk_wait_read();  // the previous reduction has finished reading the block
+            __syncwarp();
+            uint8_t* blk = sStage + warp * 8192;
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                *reinterpret_cast<uint4*>(blk + lane * 256 + ((ch ^ (lane & 7)) * 16)) =
+                    make_uint4(d0[4 * ch], d0[4 * ch + 1], d0[4 * ch + 2], d0[4 * ch + 3]);
+                *reinterpret_cast<uint4*>(blk + lane * 256 + (((8 + ch) ^ (lane & 7)) * 16)) =
+                    make_uint4(d1[4 * ch], d1[4 * ch + 1], d1[4 * ch + 2], d1[4 * ch + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)tile * BT * DH, blk, 8192);
+        };
+        for (int it = g; it < niter; it += 2) {
+            const int ph = (it >> 1) & 1;  // phase parity of the per-group barriers
+            mbar_wait(&q_full[g], ph, guard, 601);  // lse2 / delta of this query tile are in smem
+            const float* l2 = sStat + g * 256;
+            const float* dl = l2 + 128;
+            mbar_wait(&s_full[g], ph, guard, 602);
             tc_fence_after();
             uint32_t pk[64], va[32], vb[32];
             tmem_ld32(tS, va);
@@ -348,9 +381,8 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (it == 0) p_chunk<true>(cur, l2 + 32 * c, p.scale_log2, r, 32 * c, &pk[16 * c]);
                 else p_chunk<false>(cur, l2 + 32 * c, p.scale_log2, r, 32 * c, &pk[16 * c]);
             }
-            if (it > 0) {  // P^T(it-1) has been read by its dV product and by the dS group
-                mbar_wait(&dv_done, (it - 1) & 1, guard, 603);
-                mbar_wait(&p_read, (it - 1) & 1, guard, 604);
+            if (it > 0) {  // the dV product of tile it-1 has read P^T(it-1)
+                mbar_wait(&dv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 603);
                 tc_fence_after();
             }
             tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
@@ -358,65 +390,24 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_st_wait();
             tc_fence_before();
             warp_arrive(&p_ready, lane);
-        }
-        // epilogue: dV of this key tile
-        mbar_wait(&all_done, 0, guard, 606);
-        tc_fence_after();
-        store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, b, h, p);
-    } else {
-        // ---------------- dS group (warps 4-7): lane = key row, all 128 query columns ----------------
-        const int q4 = warp - 4;
-        const int r = q4 * 32 + lane;
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
-        const uint32_t tP = lane_base + COL_P, tDP = lane_base + COL_DP, tDQ = lane_base + COL_DQ;
-        uint8_t* stage = sStage + q4 * 8192;
-        float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + q4 * 32) * DH;
-        // dQ tile rows of this warp -> staging block -> one 8 KB bulk reduction into the accumulator
-        auto drain_dq = [&](int tile) {
-            uint32_t d0[32], d1[32];
-            tmem_ld32(tDQ, d0);
-            tmem_ld32(tDQ + 32, d1);
-            tmem_ld_wait();
-            tc_fence_before();
-            warp_arrive(&dq_free, lane);
-            if (lane == 0) bulk_wait_read();  // the previous reduction has finished reading the block
-            __syncwarp();
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                *reinterpret_cast<uint4*>(stage + lane * 256 + ((ch ^ (lane & 7)) * 16)) =
-                    make_uint4(d0[4 * ch], d0[4 * ch + 1], d0[4 * ch + 2], d0[4 * ch + 3]);
-                *reinterpret_cast<uint4*>(stage + lane * 256 + (((8 + ch) ^ (lane & 7)) * 16)) =
-                    make_uint4(d1[4 * ch], d1[4 * ch + 1], d1[4 * ch + 2], d1[4 * ch + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)tile * BT * DH, stage, 8192);
-        };
-        for (int it = 0; it < niter; it++) {
-            const int s = it & 1;
-            mbar_wait(&q_full[s], (it / 2) & 1, guard, 611);  // delta of this query tile is in smem
-            const float* dl = sStat + s * 256 + 128;
-            mbar_wait(&p_ready, it & 1, guard, 612);
-            mbar_wait(&dp_full, it & 1, guard, 613);
+
+            // second half: dS^T = P^T o (dP^T - delta), written over pk in place
+            mbar_wait(&dp_full[g], ph, guard, 613);
             tc_fence_after();
-            uint32_t pp[32], va[32], vb[32], ds[64];
-            tmem_ld32(tP, pp);
             tmem_ld32(tDP, va);
             tmem_ld32(tDP + 32, vb);
             tmem_ld_wait();
-            ds_chunk(&pp[0], va, dl, &ds[0]);
-            ds_chunk(&pp[16], vb, dl + 32, &ds[16]);
-            tmem_ld32(tP + 32, pp);
+            ds_chunk(&pk[0], va, dl, &pk[0]);
+            ds_chunk(&pk[16], vb, dl + 32, &pk[16]);
             tmem_ld32(tDP + 64, va);
             tmem_ld32(tDP + 96, vb);
             tmem_ld_wait();
             tc_fence_before();
-            warp_arrive(&p_read, lane);   // P^T(it) and dP^T(it) are in registers
-            warp_arrive(&dp_free, lane);
-            ds_chunk(&pp[0], va, dl + 64, &ds[32]);
-            ds_chunk(&pp[16], vb, dl + 96, &ds[48]);
-            if (it > 0) {  // dK and dQ of the previous tile are done: dS smem is free, dQ is ready
-                mbar_wait(&dq_full, (it - 1) & 1, guard, 614);
+            warp_arrive(&dp_free, lane);  // dP^T(it) is in registers
+            ds_chunk(&pk[32], va, dl + 64, &pk[32]);
+            ds_chunk(&pk[48], vb, dl + 96, &pk[48]);
+            if (it > 0) {  // dK and dQ of tile it-1 are done: the dS tile in smem is free, dQ(it-1) is ready
+                mbar_wait(&dq_full[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 614);
                 tc_fence_after();
                 drain_dq(n + it - 1);
             }
@@ -426,19 +417,23 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++)
                     *reinterpret_cast<uint4*>(sDS + blk * TILE_BYTES + r * 128 + ((ch ^ (r & 7)) * 16)) =
-                        make_uint4(ds[32 * blk + 4 * ch], ds[32 * blk + 4 * ch + 1], ds[32 * blk + 4 * ch + 2],
-                                   ds[32 * blk + 4 * ch + 3]);
+                        make_uint4(pk[32 * blk + 4 * ch], pk[32 * blk + 4 * ch + 1], pk[32 * blk + 4 * ch + 2],
+                                   pk[32 * blk + 4 * ch + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             warp_arrive(&ds_ready, lane);
         }
-        mbar_wait(&dq_full, (niter - 1) & 1, guard, 615);
-        tc_fence_after();
-        drain_dq(n + niter - 1);
+        // the last tile's dQ is drained by the group that did not produce it (as every other tile's)
+        if (g == (niter & 1)) {
+            mbar_wait(&dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, guard, 615);
+            tc_fence_after();
+            drain_dq(n + niter - 1);
+        }
         if (lane == 0) bulk_wait_all();
-        // epilogue: scale * dK of this key tile
+        // epilogue: group 0 stores dV, group 1 stores scale * dK
         mbar_wait(&all_done, 0, guard, 616);
         tc_fence_after();
-        store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, b, h, p);
+        if (g == 0) store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, b, h, p);
+        else store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, b, h, p);
     }
 
     tc_fence_before();
