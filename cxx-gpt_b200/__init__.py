@@ -23,7 +23,7 @@ SYMBOLS = [
     "cxxattn_linattn_workspace_bytes", "cxxattn_linattn_fwd", "cxxattn_linattn_bwd_step1",
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
-    "cxxattn_sync_status", "cxxattn_selftest_umma",
+    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
 ]
@@ -248,7 +248,9 @@ def set_timing_events(start, stop):
 
 def sync_status():
     """Synchronises the current stream and raises if a tensor-core kernel gave up a bounded wait."""
-    check(lib().cxxattn_sync_status(_stream()), "cxxattn_sync_status")
+    rc = lib().cxxattn_sync_status(_stream())
+    if rc != 0:
+        raise CxxAttnError(rc, "cxxattn_sync_status (wait site %d)" % lib().cxxattn_last_timeout_site())
 
 
 def selftest_umma(mode, A, B, D):

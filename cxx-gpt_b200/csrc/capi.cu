@@ -173,6 +173,7 @@ void cxxattn_set_timing_events(void* start_event, void* stop_event) {
 }
 
 int cxxattn_sync_status(cxxattn_stream_t stream) { return sync_status(static_cast<cudaStream_t>(stream)); }
+int cxxattn_last_timeout_site(void) { return last_timeout_site(); }
 
 int cxxattn_selftest_umma(int mode, const void* A, const void* B, float* D, cxxattn_stream_t stream) {
     if (!A || !B || !D) return CXXATTN_ERR_INVALID;

@@ -49,6 +49,7 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
 // ---- diagnostics (umma_selftest.cu) ----
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);
 int sync_status(cudaStream_t st);
+int last_timeout_site();
 
 // ---- exact fp32 chunk-parallel linear attention (linattn_f32.cu) ----
 size_t linattn_f32_workspace(const cxxattn_lin_desc& d);

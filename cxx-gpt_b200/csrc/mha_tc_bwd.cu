@@ -36,12 +36,14 @@ using namespace tc;
 constexpr int BT = 128;  // rows per tile (queries and keys)
 constexpr int DH = 64;
 constexpr int TILE_BYTES = BT * DH * 2;  // 16 KB
-constexpr int NTHREADS = 320;
+constexpr int NTHREADS = 384;  // warps 0-7 compute, 8 producer, 9 MMA issuer, 10-11 only hand registers over
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_ST = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_P = 448;
-// K | V | Q x2 | dO x2 | dS (2 blocks) | (lse2, delta) x2 | dQ staging
-constexpr int STAGE_BYTES = 8 * 8192;  // dQ staging: 32 rows x 64 fp32 per compute warp
-constexpr size_t SMEM_BYTES = 8 * TILE_BYTES + 2 * 1024 + STAGE_BYTES + 1024;
+// K | V | Q x3 | dO x2 | dS x2 (2 blocks each) | (lse2, delta) x3 | dQ staging
+constexpr int NQ = 3;                  // Q stages: Q_i is read first (S^T) and last (dK) in a tile's life
+constexpr int NTILES = 2 + NQ + 2 + 4;
+constexpr int STAGE_BYTES = 4 * 8192;  // dQ staging: 32 rows x 64 fp32 per warp of the draining group
+constexpr size_t SMEM_BYTES = NTILES * TILE_BYTES + NQ * 1024 + STAGE_BYTES + 1024;
 
 struct BwdParams {
     const float* lse2;   // [BH][Spad]  lse * log2(e), +inf on padding rows
@@ -181,19 +183,19 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t kv_full, q_full[2], do_full[2], qdo_free[2], s_full[2], dp_full[2], dv_done[2], dq_full[2], s_free,
-        dp_free, p_ready, ds_ready, dq_free, all_done;
+    __shared__ uint64_t kv_full, q_full[NQ], q_free[NQ], do_full[2], s_full[2], dp_full[2], dv_done[2], dq_full[2], s_free,
+        dp_free, p_ready, ds_ready[2], dq_free, stage_free[4], all_done;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem;
     uint8_t* sV = smem + TILE_BYTES;
-    uint8_t* sQ = smem + 2 * TILE_BYTES;   // 2 stages
-    uint8_t* sdO = smem + 4 * TILE_BYTES;  // 2 stages
-    uint8_t* sDS = smem + 6 * TILE_BYTES;  // 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
-    float* sStat = reinterpret_cast<float*>(smem + 8 * TILE_BYTES);  // [stage][lse2 | delta][128]
-    uint8_t* sStage = smem + 8 * TILE_BYTES + 2048;                  // [compute warp][32 rows][256 B]
+    uint8_t* sQ = smem + 2 * TILE_BYTES;          // NQ stages
+    uint8_t* sdO = smem + (2 + NQ) * TILE_BYTES;  // 2 stages
+    uint8_t* sDS = smem + (4 + NQ) * TILE_BYTES;  // 2 buffers x 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
+    float* sStat = reinterpret_cast<float*>(smem + NTILES * TILE_BYTES);  // [Q stage][lse2 | delta][128]
+    uint8_t* sStage = smem + NTILES * TILE_BYTES + NQ * 1024;             // [warp % 4][32 rows][256 B]
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int ntile = p.Spad / BT;
@@ -208,24 +210,27 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (threadIdx.x == 0) {
         abort_flag = 0;
         mbar_init(&kv_full, 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < NQ; s++) {
             mbar_init(&q_full[s], 1);
-            mbar_init(&do_full[s], 1);
-            mbar_init(&qdo_free[s], 1);
+            mbar_init(&q_free[s], 1);
         }
-        for (int s = 0; s < 2; s++) {  // waited on by the compute group that owns tiles of this parity
+        for (int s = 0; s < 2; s++) {  // indexed by the parity of the query tile
+            mbar_init(&do_full[s], 1);
             mbar_init(&s_full[s], 1);
             mbar_init(&dp_full[s], 1);
             mbar_init(&dv_done[s], 1);
             mbar_init(&dq_full[s], 1);
         }
         mbar_init(&all_done, 1);
-        // waited on by the MMA thread, tile after tile; one arrival per warp of the group that signals
+        // waited on by the MMA warp, tile after tile; one arrival per warp of the group that signals
         mbar_init(&s_free, 4);
         mbar_init(&p_ready, 4);
         mbar_init(&dp_free, 4);
-        mbar_init(&ds_ready, 4);
+        // dS^T(i+1) may be complete before dS^T(i) is (it waits for neither dK(i) nor dQ(i)): one barrier per group
+        mbar_init(&ds_ready[0], 4);
+        mbar_init(&ds_ready[1], 4);
         mbar_init(&dq_free, 4);
+        for (int w = 0; w < 4; w++) mbar_init(&stage_free[w], 1);
         fence_barrier_init();
     }
     if (warp == 9) tmem_alloc(&tmem_slot, TMEM_COLS);
@@ -234,6 +239,11 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
+    if (warp >= 8) {
+        // Warps 8-11 form one warp group; all four execute this one instruction together and hand
+        // most of their registers to the compute groups.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    }
     if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -245,109 +255,126 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tma_load_4d(sK, &tmK, &kv_full, 0, h, k0, b);
             tma_load_4d(sV, &tmV, &kv_full, 0, h, k0, b);
             for (int it = 0; it < niter; it++) {
-                const int s = it & 1, q0 = (n + it) * BT;
-                if (it >= 2) mbar_wait(&qdo_free[s], ((it / 2) - 1) & 1, guard, 401);
-                mbar_expect_tx(&q_full[s], TILE_BYTES + 1024);
-                tma_load_4d(sQ + s * TILE_BYTES, &tmQ, &q_full[s], 0, h, q0, b);
-                bulk_load_1d(sStat + s * 256, p.lse2 + (int64_t)bh * p.Spad + q0, 512, &q_full[s]);
-                bulk_load_1d(sStat + s * 256 + 128, p.delta + (int64_t)bh * p.Spad + q0, 512, &q_full[s]);
+                const int qs = it % NQ, s = it & 1, q0 = (n + it) * BT;
+                // Q (with the row statistics) is held until dK(it) has read it; dO until dV(it) has
+                if (it >= NQ) mbar_wait(&q_free[qs], ((it / NQ) - 1) & 1, guard, 401);
+                mbar_expect_tx(&q_full[qs], TILE_BYTES + 1024);
+                tma_load_4d(sQ + qs * TILE_BYTES, &tmQ, &q_full[qs], 0, h, q0, b);
+                bulk_load_1d(sStat + qs * 256, p.lse2 + (int64_t)bh * p.Spad + q0, 512, &q_full[qs]);
+                bulk_load_1d(sStat + qs * 256 + 128, p.delta + (int64_t)bh * p.Spad + q0, 512, &q_full[qs]);
+                if (it >= 2) mbar_wait(&dv_done[s], ((it / 2) - 1) & 1, guard, 402);
                 mbar_expect_tx(&do_full[s], TILE_BYTES);
                 tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &do_full[s], 0, h, q0, b);
             }
         }
     } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t IDESC_SS = idesc_bf16(BT, BT, 0, 0);  // S^T, dP^T: both operands K-major
-            constexpr uint32_t IDESC_KN = idesc_bf16(BT, DH, 0, 1);  // dV, dK: A K-major, B MN-major
-            constexpr uint32_t IDESC_DQ = idesc_bf16(BT, DH, 1, 1);  // dQ: dS and K both MN-major
-            // Descriptors are built once; K steps and ring stages add constants to the start-address
-            // field (units of 16 bytes).
-            constexpr uint64_t TILE16 = TILE_BYTES >> 4;
-            const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16), dV = smem_desc_sw128(smem_u32(sV), 16);
-            const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16), dG0 = smem_desc_sw128(smem_u32(sdO), 16);
-            const uint64_t dDSk = smem_desc_sw128(smem_u32(sDS), 16);          // dS as [keys][queries]: K-major A
-            const uint64_t dDSm = smem_desc_sw128(smem_u32(sDS), TILE_BYTES);  // dS as MN-major A (M = queries)
-            auto issue_st = [&](int s) {
-                const uint64_t q = dQ0 + s * TILE16;
+        // the whole warp runs the loop (uniform control flow and operands); one elected lane issues
+        const uint32_t el = elect_one();
+        constexpr uint32_t IDESC_SS = idesc_bf16(BT, BT, 0, 0);  // S^T, dP^T: both operands K-major
+        constexpr uint32_t IDESC_KN = idesc_bf16(BT, DH, 0, 1);  // dV, dK: A K-major, B MN-major
+        constexpr uint32_t IDESC_DQ = idesc_bf16(BT, DH, 1, 1);  // dQ: dS and K both MN-major
+        // Descriptors are built once; K steps and ring stages add constants to the start-address
+        // field (units of 16 bytes).
+        constexpr uint64_t TILE16 = TILE_BYTES >> 4;
+        const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16), dV = smem_desc_sw128(smem_u32(sV), 16);
+        const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16), dG0 = smem_desc_sw128(smem_u32(sdO), 16);
+        const uint64_t dDSk = smem_desc_sw128(smem_u32(sDS), 16);          // dS as [keys][queries]: K-major A
+        const uint64_t dDSm = smem_desc_sw128(smem_u32(sDS), TILE_BYTES);  // dS as MN-major A (M = queries)
+        auto issue_st = [&](int s, int qs) {
+            const uint64_t q = dQ0 + qs * TILE16;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++) umma_ss(tmem + COL_ST, dK + 2 * k, q + 2 * k, IDESC_SS, k > 0);
-                umma_commit(&s_full[s]);
-            };
-            auto issue_dp = [&](int s) {
-                const uint64_t g = dG0 + s * TILE16;
+            for (int k = 0; k < DH / 16; k++) umma_ss_e(el, tmem + COL_ST, dK + 2 * k, q + 2 * k, IDESC_SS, k > 0);
+            umma_commit_e(el, &s_full[s]);
+        };
+        auto issue_dp = [&](int s) {
+            const uint64_t g = dG0 + s * TILE16;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++) umma_ss(tmem + COL_DP, dV + 2 * k, g + 2 * k, IDESC_SS, k > 0);
-                umma_commit(&dp_full[s]);
-            };
-            mbar_wait_poll(&kv_full, 0, guard, 501);
-            mbar_wait_poll(&q_full[0], 0, guard, 502);
-            tc_fence_after();
-            issue_st(0);
-            mbar_wait_poll(&do_full[0], 0, guard, 503);
-            tc_fence_after();
-            issue_dp(0);
-            for (int it = 0; it < niter; it++) {
-                const int s = it & 1, sn = s ^ 1;
-                const uint64_t q = dQ0 + s * TILE16, g = dG0 + s * TILE16;
-                if (it + 1 < niter) {  // next scores as soon as this tile's are in registers
-                    mbar_wait_poll(&q_full[sn], ((it + 1) / 2) & 1, guard, 506);
-                    mbar_wait_poll(&s_free, it & 1, guard, 504);
-                    tc_fence_after();
-                    issue_st(sn);
-                }
-                mbar_wait_poll(&p_ready, it & 1, guard, 505);
+            for (int k = 0; k < DH / 16; k++) umma_ss_e(el, tmem + COL_DP, dV + 2 * k, g + 2 * k, IDESC_SS, k > 0);
+            umma_commit_e(el, &dp_full[s]);
+        };
+        mbar_wait_poll(&kv_full, 0, guard, 501);
+        mbar_wait_poll(&q_full[0], 0, guard, 502);
+        tc_fence_after();
+        issue_st(0, 0);
+        mbar_wait_poll(&do_full[0], 0, guard, 503);
+        tc_fence_after();
+        issue_dp(0);
+        int qs = 0;  // it % NQ
+        for (int it = 0; it < niter; it++) {
+            const int s = it & 1, sn = s ^ 1;
+            const int qn = qs + 1 == NQ ? 0 : qs + 1;
+            const uint64_t q = dQ0 + qs * TILE16, g = dG0 + s * TILE16;
+            const uint64_t dsk = dDSk + s * 2 * TILE16, dsm = dDSm + s * 2 * TILE16;
+            if (it + 1 < niter) {  // next scores as soon as this tile's are in registers
+                mbar_wait_poll(&q_full[qn], ((it + 1) / NQ) & 1, guard, 506);
+                mbar_wait_poll(&s_free, it & 1, guard, 504);
                 tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i   (A: P^T bf16 in TMEM)
-                    umma_ts(tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_KN, it > 0 || k > 0);
-                umma_commit(&dv_done[s]);
-                if (it + 1 < niter) {  // next dP^T as soon as this tile's is in registers
-                    mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
-                    mbar_wait_poll(&dp_free, it & 1, guard, 510);
-                    tc_fence_after();
-                    issue_dp(sn);
-                }
-                mbar_wait_poll(&ds_ready, it & 1, guard, 507);
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i   (A: dS in smem, rows = keys, K = queries)
-                    umma_ss(tmem + COL_DK, dDSk + (k / 4) * TILE16 + 2 * (k % 4), q + 128 * k, IDESC_KN, it > 0 || k > 0);
-                umma_commit(&qdo_free[s]);
-                if (it > 0) {
-                    mbar_wait_poll(&dq_free, (it - 1) & 1, guard, 508);
-                    tc_fence_after();
-                }
-#pragma unroll
-                for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K       (A: the same tile read MN-major)
-                    umma_ss(tmem + COL_DQ, dDSm + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
-                umma_commit(&dq_full[s]);
+                issue_st(sn, qn);
             }
-            umma_commit(&all_done);
+            mbar_wait_poll(&p_ready, it & 1, guard, 505);
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i   (A: P^T bf16 in TMEM)
+                umma_ts_e(el, tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_KN, it > 0 || k > 0);
+            umma_commit_e(el, &dv_done[s]);  // P^T may be overwritten, and this dO stage refilled
+            if (it + 1 < niter) {  // next dP^T as soon as this tile's is in registers
+                mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
+                mbar_wait_poll(&dp_free, it & 1, guard, 510);
+                tc_fence_after();
+                issue_dp(sn);
+            }
+            mbar_wait_poll(&ds_ready[s], (it >> 1) & 1, guard, 507);
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i   (A: dS in smem, rows = keys, K = queries)
+                umma_ss_e(el, tmem + COL_DK, dsk + (k / 4) * TILE16 + 2 * (k % 4), q + 128 * k, IDESC_KN, it > 0 || k > 0);
+            umma_commit_e(el, &q_free[qs]);
+            if (it > 0) {
+                mbar_wait_poll(&dq_free, (it - 1) & 1, guard, 508);
+                tc_fence_after();
+            }
+#pragma unroll
+            for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K       (A: the same tile read MN-major)
+                umma_ss_e(el, tmem + COL_DQ, dsm + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
+            umma_commit_e(el, &dq_full[s]);  // dQ_i is ready, and this dS buffer may be overwritten
+            qs = qn;
         }
+        umma_commit_e(el, &all_done);
+    } else if (warp >= 10) {
+        // idle warps: they only take part in the register hand-over above
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ---------------- compute groups: group g (warps 4g..4g+3) owns the query tiles it = g, g+2, ... ----------------
         // lane = key row; a thread turns its row of S^T into P^T (bf16, kept in registers and copied to
-        // TMEM for the dV product), then P^T and dP^T into dS^T.  While one group is in the second
-        // half of tile i the other is already in the first half of tile i+1.
+        // TMEM for the dV product), then P^T and dP^T into dS^T, and last drains dQ of the tile before
+        // (the other group's).  While one group is in the second half of tile i the other is already
+        // in the first half of tile i+1.
         const int g = warp / 4;
         const int q4 = warp % 4;
         const int r = q4 * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
         const uint32_t tS = lane_base + COL_ST, tP = lane_base + COL_P, tDP = lane_base + COL_DP, tDQ = lane_base + COL_DQ;
-        // dQ tile it-1 (written by the other group's dS): this group's warps drain it, rows 32*q4.., all
-        // 64 columns in two 4 KB pieces
         float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + q4 * 32) * DH;
-        auto drain_dq = [&](int tile) {
+        uint8_t* blk = sStage + q4 * 8192;  // shared with the same warp of the other group, drain after drain
+        bool pending = false;               // this warp's last bulk reduction may still be reading blk
+        // the staging block goes back to the other group once this warp's reduction has read it
+        auto release_stage = [&]() {
+            if (pending && lane == 0) {
+                bulk_wait_read();
+                mbar_arrive(&stage_free[q4]);
+            }
+            pending = false;
+        };
+        // dQ of query tile d (relative to n): rows 32*q4.., all 64 columns, one 8 KB reduction
+        auto drain_dq = [&](int d) {
             uint32_t d0[32], d1[32];
             tmem_ld32(tDQ, d0);
             tmem_ld32(tDQ + 32, d1);
             tmem_ld_wait();
             tc_fence_before();
             warp_arrive(&dq_free, lane);
-            if (lane == 0) bulk_wait_read();  // the previous reduction has finished reading the block
-            __syncwarp();
-            uint8_t* blk = sStage + warp * 8192;
+            if (d > 0) mbar_wait(&stage_free[q4], (d - 1) & 1, guard, 617);
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
                 *reinterpret_cast<uint4*>(blk + lane * 256 + ((ch ^ (lane & 7)) * 16)) =
@@ -357,29 +384,41 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)tile * BT * DH, blk, 8192);
+            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)(n + d) * BT * DH, blk, 8192);
+            pending = true;
         };
         for (int it = g; it < niter; it += 2) {
-            const int ph = (it >> 1) & 1;  // phase parity of the per-group barriers
-            mbar_wait(&q_full[g], ph, guard, 601);  // lse2 / delta of this query tile are in smem
-            const float* l2 = sStat + g * 256;
+            const int ph = (it >> 1) & 1;  // phase parity of the barriers indexed by tile parity
+            const int qs = it % NQ;
+            mbar_wait(&q_full[qs], (it / NQ) & 1, guard, 601);  // lse2 / delta of this query tile are in smem
+            const float* l2 = sStat + qs * 256;
             const float* dl = l2 + 128;
             mbar_wait(&s_full[g], ph, guard, 602);
             tc_fence_after();
-            uint32_t pk[64], va[32], vb[32];
-            tmem_ld32(tS, va);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
+            uint32_t pk[64];
+            {
+                // the whole row of S^T goes to registers first, so the next scores can be issued while
+                // this tile's exponentials run
+                uint32_t s0[32], s1[32], s2[32], s3[32];
+                tmem_ld32(tS, s0);
+                tmem_ld32(tS + 32, s1);
+                tmem_ld32(tS + 64, s2);
+                tmem_ld32(tS + 96, s3);
                 tmem_ld_wait();
-                if (c == 0 || c == 2) tmem_ld32(tS + 32 * (c + 1), vb);
-                if (c == 1) tmem_ld32(tS + 64, va);
-                if (c == 3) {  // all of S^T(it) is in registers: the next scores may overwrite it
-                    tc_fence_before();
-                    warp_arrive(&s_free, lane);
+                tc_fence_before();
+                warp_arrive(&s_free, lane);
+                release_stage();
+                if (it == 0) {
+                    p_chunk<true>(s0, l2, p.scale_log2, r, 0, &pk[0]);
+                    p_chunk<true>(s1, l2 + 32, p.scale_log2, r, 32, &pk[16]);
+                    p_chunk<true>(s2, l2 + 64, p.scale_log2, r, 64, &pk[32]);
+                    p_chunk<true>(s3, l2 + 96, p.scale_log2, r, 96, &pk[48]);
+                } else {
+                    p_chunk<false>(s0, l2, p.scale_log2, r, 0, &pk[0]);
+                    p_chunk<false>(s1, l2 + 32, p.scale_log2, r, 32, &pk[16]);
+                    p_chunk<false>(s2, l2 + 64, p.scale_log2, r, 64, &pk[32]);
+                    p_chunk<false>(s3, l2 + 96, p.scale_log2, r, 96, &pk[48]);
                 }
-                const uint32_t(&cur)[32] = (c & 1) ? vb : va;
-                if (it == 0) p_chunk<true>(cur, l2 + 32 * c, p.scale_log2, r, 32 * c, &pk[16 * c]);
-                else p_chunk<false>(cur, l2 + 32 * c, p.scale_log2, r, 32 * c, &pk[16 * c]);
             }
             if (it > 0) {  // the dV product of tile it-1 has read P^T(it-1)
                 mbar_wait(&dv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 603);
@@ -392,6 +431,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             warp_arrive(&p_ready, lane);
 
             // second half: dS^T = P^T o (dP^T - delta), written over pk in place
+            uint32_t va[32], vb[32];
             mbar_wait(&dp_full[g], ph, guard, 613);
             tc_fence_after();
             tmem_ld32(tDP, va);
@@ -406,31 +446,35 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             warp_arrive(&dp_free, lane);  // dP^T(it) is in registers
             ds_chunk(&pk[32], va, dl + 64, &pk[32]);
             ds_chunk(&pk[48], vb, dl + 96, &pk[48]);
-            if (it > 0) {  // dK and dQ of tile it-1 are done: the dS tile in smem is free, dQ(it-1) is ready
-                mbar_wait(&dq_full[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 614);
-                tc_fence_after();
-                drain_dq(n + it - 1);
-            }
+            if (it >= 2)  // dK and dQ of tile it-2 have read this dS buffer
+                mbar_wait(&dq_full[g], ((it - 2) >> 1) & 1, guard, 614);
             // row r of dS: two 128-byte rows (queries 0-63 | 64-127) with the 128-byte swizzle
+            uint8_t* ds_row = sDS + g * 2 * TILE_BYTES + r * 128;
 #pragma unroll
-            for (int blk = 0; blk < 2; blk++)
+            for (int half = 0; half < 2; half++)
 #pragma unroll
                 for (int ch = 0; ch < 8; ch++)
-                    *reinterpret_cast<uint4*>(sDS + blk * TILE_BYTES + r * 128 + ((ch ^ (r & 7)) * 16)) =
-                        make_uint4(pk[32 * blk + 4 * ch], pk[32 * blk + 4 * ch + 1], pk[32 * blk + 4 * ch + 2],
-                                   pk[32 * blk + 4 * ch + 3]);
+                    *reinterpret_cast<uint4*>(ds_row + half * TILE_BYTES + ((ch ^ (r & 7)) * 16)) =
+                        make_uint4(pk[32 * half + 4 * ch], pk[32 * half + 4 * ch + 1], pk[32 * half + 4 * ch + 2],
+                                   pk[32 * half + 4 * ch + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            warp_arrive(&ds_ready, lane);
+            warp_arrive(&ds_ready[g], lane);
+            if (it > 0) {  // dQ of the tile before (the other group's) leaves TMEM through this group
+                mbar_wait(&dq_full[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 615);
+                tc_fence_after();
+                drain_dq(it - 1);
+            }
         }
+        release_stage();
         // the last tile's dQ is drained by the group that did not produce it (as every other tile's)
         if (g == (niter & 1)) {
-            mbar_wait(&dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, guard, 615);
+            mbar_wait(&dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, guard, 616);
             tc_fence_after();
-            drain_dq(n + niter - 1);
+            drain_dq(niter - 1);
         }
         if (lane == 0) bulk_wait_all();
         // epilogue: group 0 stores dV, group 1 stores scale * dK
-        mbar_wait(&all_done, 0, guard, 616);
+        mbar_wait(&all_done, 0, guard, 618);
         tc_fence_after();
         if (g == 0) store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, b, h, p);
         else store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, b, h, p);

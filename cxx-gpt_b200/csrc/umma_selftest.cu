@@ -129,6 +129,9 @@ int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t
     return check_launch();
 }
 
+static int g_last_site = 0;
+int last_timeout_site() { return g_last_site; }
+
 int sync_status(cudaStream_t st) {
     int* status = status_word();
     if (status == nullptr) return CXXATTN_ERR_CUDA;
@@ -136,6 +139,7 @@ int sync_status(cudaStream_t st) {
     if (cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return CXXATTN_ERR_CUDA;
     if (cudaStreamSynchronize(st) != cudaSuccess) return CXXATTN_ERR_CUDA;
     if (host != 0) {
+        g_last_site = host;
         cudaMemsetAsync(status, 0, sizeof(int), st);
         cudaStreamSynchronize(st);
         return CXXATTN_ERR_TIMEOUT;

@@ -197,6 +197,10 @@ int cxxattn_mha_fwd_bwd_host(cxxattn_host_plan* plan, const void* hQ, const void
  * cleared) or not (CXXATTN_OK).  Results of a launch that timed out are undefined. */
 int cxxattn_sync_status(cxxattn_stream_t stream);
 
+/* The wait site (a small kernel-specific number, for bug reports) of the last timeout that
+ * cxxattn_sync_status reported in this process; 0 if none. */
+int cxxattn_last_timeout_site(void);
+
 /* Measurement hook: two cudaEvent_t handles that later cxxattn_mha_bwd calls (dtype BF16) of the
  * calling thread record on their stream right before and right after the main backward kernel,
  * so that its duration can be read without the pre- and post-pass.  NULL, NULL switches it off. */
