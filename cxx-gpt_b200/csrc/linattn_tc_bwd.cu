@@ -240,7 +240,9 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {
+        // MMA issuer: the whole warp runs the loop (uniform control flow and operands); one elected lane issues
+        {
+            const uint32_t el = elect_one();
             constexpr uint32_t IDESC_W = idesc_bf16(CH, CH, 0, 0);  // dnum V^T (+ dden 1^T): both K-major
             constexpr uint32_t IDESC_I = idesc_bf16(CH, DE, 0, 0);  // [dnum|dden][S_prev|z]^T: both K-major
             constexpr uint32_t IDESC_P = idesc_bf16(CH, DE, 0, 1);  // P phiK: A in TMEM, B MN-major
@@ -256,26 +258,26 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 mbar_wait_poll(&mapped, c & 1, guard, 811);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C1_W, dG + 2 * k, dVk + 2 * k, IDESC_W, k > 0);
-                umma_ss(tmem + C1_W, dDd, dOnes, IDESC_W, true);  // + dden_t for every column
-                umma_commit(&w_full);
+                for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + C1_W, dG + 2 * k, dVk + 2 * k, IDESC_W, k > 0);
+                umma_ss_e(el, tmem + C1_W, dDd, dOnes, IDESC_W, true);  // + dden_t for every column
+                umma_commit_e(el, &w_full);
                 mbar_wait_poll(&sprev_ready, c & 1, guard, 812);
                 if (c > 0) mbar_wait_poll(&o_free, (c - 1) & 1, guard, 813);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C1_DQ, dG + 2 * k, dPrev0 + 2 * k, IDESC_I, k > 0);
-                umma_ss(tmem + C1_DQ, dDd, dPrev1, IDESC_I, true);  // + dden_t z_prev
+                for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + C1_DQ, dG + 2 * k, dPrev0 + 2 * k, IDESC_I, k > 0);
+                umma_ss_e(el, tmem + C1_DQ, dDd, dPrev1, IDESC_I, true);  // + dden_t z_prev
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)
-                    umma_ss(tmem + C1_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
-                umma_commit(&s_done);
+                    umma_ss_e(el, tmem + C1_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
+                umma_commit_e(el, &s_done);
                 mbar_wait_poll(&p_ready, c & 1, guard, 814);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)
-                    umma_ts(tmem + C1_DQ, tmem + C1_W + 8 * k, dKm + 128 * k, IDESC_P, true);
-                umma_commit(&o_full);
-                umma_commit(&stage_free[st]);
+                    umma_ts_e(el, tmem + C1_DQ, tmem + C1_W + 8 * k, dKm + 128 * k, IDESC_P, true);
+                umma_commit_e(el, &o_full);
+                umma_commit_e(el, &stage_free[st]);
             }
         }
     } else if (warp >= 6) {
@@ -440,7 +442,9 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {
+        // MMA issuer: the whole warp runs the loop (uniform control flow and operands); one elected lane issues
+        {
+            const uint32_t el = elect_one();
             constexpr uint32_t IDESC_KK = idesc_bf16(CH, CH, 0, 0);  // A^T and W2: both operands K-major
             constexpr uint32_t IDESC_KN = idesc_bf16(CH, DE, 0, 1);  // A K-major (or TMEM), B MN-major
             constexpr uint32_t IDESC_K2 = idesc_bf16(CH, DE, 0, 0);  // V S*^T: both K-major
@@ -459,34 +463,34 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                 mbar_wait_poll(&mapped, n & 1, guard, 911);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C2_AT, dKk + 2 * k, dQk + 2 * k, IDESC_KK, k > 0);
+                for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + C2_AT, dKk + 2 * k, dQk + 2 * k, IDESC_KK, k > 0);
 #pragma unroll
-                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + C2_W, dVk + 2 * k, dGk + 2 * k, IDESC_KK, k > 0);
-                umma_ss(tmem + C2_W, dOnes, dDd, IDESC_KK, true);  // + dden_s for every row
-                umma_commit(&aw_full);
+                for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + C2_W, dVk + 2 * k, dGk + 2 * k, IDESC_KK, k > 0);
+                umma_ss_e(el, tmem + C2_W, dOnes, dDd, IDESC_KK, true);  // + dden_s for every row
+                umma_commit_e(el, &aw_full);
                 mbar_wait_poll(&snext_ready, n & 1, guard, 912);
                 if (n > 0) mbar_wait_poll(&o_free, (n - 1) & 1, guard, 913);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < DE / 16; k++)  // dV' = phiK S*_next
-                    umma_ss(tmem + C2_DV, dKk + 2 * k, dNextM + 128 * k, IDESC_KN, k > 0);
+                    umma_ss_e(el, tmem + C2_DV, dKk + 2 * k, dNextM + 128 * k, IDESC_KN, k > 0);
 #pragma unroll
                 for (int k = 0; k < DE / 16; k++)  // dK' = V S*_next^T
-                    umma_ss(tmem + C2_DK, dVk + 2 * k, dNextK + 2 * k, IDESC_K2, k > 0);
+                    umma_ss_e(el, tmem + C2_DK, dVk + 2 * k, dNextK + 2 * k, IDESC_K2, k > 0);
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)  // S* += phiQ^T [dnum | dden]
-                    umma_ss(tmem + C2_SX, dQm + 128 * k, dG1 + 128 * k, IDESC_S, n > 0 || k > 0);
-                umma_commit(&s_done);
+                    umma_ss_e(el, tmem + C2_SX, dQm + 128 * k, dG1 + 128 * k, IDESC_S, n > 0 || k > 0);
+                umma_commit_e(el, &s_done);
                 mbar_wait_poll(&p_ready, n & 1, guard, 914);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)  // dV' += P1 dnum
-                    umma_ts(tmem + C2_DV, tmem + C2_AT + 8 * k, dGm + 128 * k, IDESC_KN, true);
+                    umma_ts_e(el, tmem + C2_DV, tmem + C2_AT + 8 * k, dGm + 128 * k, IDESC_KN, true);
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)  // dK' += P2 phiQ
-                    umma_ts(tmem + C2_DK, tmem + C2_W + 8 * k, dQm + 128 * k, IDESC_KN, true);
-                umma_commit(&o_full);
-                umma_commit(&stage_free[st]);
+                    umma_ts_e(el, tmem + C2_DK, tmem + C2_W + 8 * k, dQm + 128 * k, IDESC_KN, true);
+                umma_commit_e(el, &o_full);
+                umma_commit_e(el, &stage_free[st]);
             }
         }
     } else if (warp >= 6) {

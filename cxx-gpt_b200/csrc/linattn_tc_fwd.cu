@@ -144,7 +144,9 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // the whole warp runs the loop (uniform control flow and operands); one elected lane issues
+        {
+            const uint32_t el = elect_one();
             constexpr uint32_t IDESC_A = idesc_bf16(CH, CH, 0, 0);  // phiQ phiK^T: both K-major
             constexpr uint32_t IDESC_I = idesc_bf16(CH, 80, 0, 1);  // phiQ [S_prev | z]: B MN-major
             constexpr uint32_t IDESC_P = idesc_bf16(CH, DE, 0, 1);  // P V: A in TMEM, B MN-major
@@ -163,24 +165,24 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 mbar_wait_poll(&mapped, c & 1, guard, 711);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + COL_A, dQ + 2 * k, dK + 2 * k, IDESC_A, k > 0);
-                umma_commit(&a_full);
+                for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + COL_A, dQ + 2 * k, dK + 2 * k, IDESC_A, k > 0);
+                umma_commit_e(el, &a_full);
                 mbar_wait_poll(&sprev_ready, c & 1, guard, 712);
                 if (c > 0) mbar_wait_poll(&o_free, (c - 1) & 1, guard, 713);
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < DE / 16; k++) umma_ss(tmem + COL_O, dQ + 2 * k, dPrev + 128 * k, IDESC_I, k > 0);
+                for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + COL_O, dQ + 2 * k, dPrev + 128 * k, IDESC_I, k > 0);
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)
-                    umma_ss(tmem + COL_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
-                umma_commit(&s_done);
+                    umma_ss_e(el, tmem + COL_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
+                umma_commit_e(el, &s_done);
                 mbar_wait_poll(&p_ready, c & 1, guard, 714);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)
-                    umma_ts(tmem + COL_O, tmem + COL_P + 8 * k, dV + 128 * k, IDESC_P, true);
-                umma_commit(&o_full);
-                umma_commit(&stage_free[st]);
+                    umma_ts_e(el, tmem + COL_O, tmem + COL_P + 8 * k, dV + 128 * k, IDESC_P, true);
+                umma_commit_e(el, &o_full);
+                umma_commit_e(el, &stage_free[st]);
             }
         }
     } else if (warp >= 6) {

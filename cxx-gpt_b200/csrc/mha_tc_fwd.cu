@@ -124,7 +124,9 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
     } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // the whole warp runs the loop (uniform control flow and operands); one elected lane issues
+        {
+            const uint32_t el = elect_one();
             constexpr uint32_t IDESC_S = idesc_bf16(BM, BN, 0, 0);  // Q, K both K-major
             constexpr uint32_t IDESC_O = idesc_bf16(BM, DH, 0, 1);  // P from TMEM, V MN-major
             // Descriptors are built once; a K step or a ring stage only adds a constant to the
@@ -137,15 +139,15 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const uint64_t qd = dQ0 + t * TILE16, kd = dK0 + s * TILE16;
                 const uint32_t d = tmem + COL_S + t * BN;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++) umma_ss(d, qd + 2 * k, kd + 2 * k, IDESC_S, k > 0);
-                umma_commit(&s_full[t]);
+                for (int k = 0; k < DH / 16; k++) umma_ss_e(el, d, qd + 2 * k, kd + 2 * k, IDESC_S, k > 0);
+                umma_commit_e(el, &s_full[t]);
             };
             auto issue_pv = [&](int t, int s, bool acc) {
                 const uint64_t vd = dV0 + s * TILE16;
                 const uint32_t d = tmem + COL_O + t * DH, a = tmem + COL_P + t * 64;
-                umma_ts(d, a, vd, IDESC_O, acc);
+                umma_ts_e(el, d, a, vd, IDESC_O, acc);
 #pragma unroll
-                for (int k = 1; k < BN / 16; k++) umma_ts(d, a + 8 * k, vd + 128 * k, IDESC_O, true);
+                for (int k = 1; k < BN / 16; k++) umma_ts_e(el, d, a + 8 * k, vd + 128 * k, IDESC_O, true);
             };
             const int last0 = n0, last1 = n0 + 1;  // last KV tile of each query tile
             mbar_wait_poll(&q_full, 0, guard, 201);
@@ -175,15 +177,15 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     mbar_wait_poll(&p_full[0], j & 1, guard, 204);
                     tc_fence_after();
                     issue_pv(0, s, j > 0);
-                    umma_commit(&pv_done[0]);
+                    umma_commit_e(el, &pv_done[0]);
                 }
                 if (has_t1) {
                     mbar_wait_poll(&p_full[1], j & 1, guard, 206);
                     tc_fence_after();
                     issue_pv(1, s, j > 0);
-                    umma_commit(&pv_done[1]);
+                    umma_commit_e(el, &pv_done[1]);
                 }
-                umma_commit(&kv_empty[s]);
+                umma_commit_e(el, &kv_empty[s]);
             }
         }
     } else if (warp >= 10) {
