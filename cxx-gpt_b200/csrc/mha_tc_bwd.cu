@@ -36,19 +36,21 @@ using namespace tc;
 constexpr int BT = 128;  // rows per tile (queries and keys)
 constexpr int DH = 64;
 constexpr int TILE_BYTES = BT * DH * 2;  // 16 KB
-constexpr int NTHREADS = 384;  // warps 0-7 compute, 8 producer, 9 MMA issuer, 10-11 only hand registers over
+constexpr int NTHREADS = 640;  // warps 0-15 compute, 16 producer, 17 MMA issuer, 18-19 only hand registers over
+constexpr int W_PROD = 16, W_MMA = 17;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_ST = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_P = 448;
 // K | V | Q x3 | dO x2 | dS x2 (2 blocks each) | (lse2, delta) x3 | dQ staging
 constexpr int NQ = 3;                  // Q stages: Q_i is read first (S^T) and last (dK) in a tile's life
 constexpr int NTILES = 2 + NQ + 2 + 4;
-constexpr int STAGE_BYTES = 4 * 8192;  // dQ staging: 32 rows x 64 fp32 per warp of the draining group
+constexpr int STAGE_BYTES = 8 * 4096;  // dQ staging: 32 rows x 32 fp32 per warp of the draining group
 constexpr size_t SMEM_BYTES = NTILES * TILE_BYTES + NQ * 1024 + STAGE_BYTES + 1024;
 
 struct BwdParams {
     const float* lse2;   // [BH][Spad]  lse * log2(e), +inf on padding rows
     const float* delta;  // [BH][Spad]
-    float* dq_acc;       // [BH][Spad][64]; the 16-byte chunk ch of a row is stored at chunk ch ^ (row & 7)
+    float* dq_acc;       // [BH][Spad/128] tiles of [row / 32][column / 32][row % 32][32]; the 16-byte chunk ch
+                         // of such a 128-byte row is stored at chunk ch ^ (row & 7)
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
     int* status;
@@ -91,10 +93,11 @@ __global__ void mha_tc_bwd_post_kernel(const float* __restrict__ dq_acc, __nv_bf
     if (row >= (int64_t)B * H * S) return;
     const int s = row % S;
     const int bh = row / S;
-    // accumulator layout of the main kernel: row-major [bh][Spad][64] with the 16-byte chunk ch of a
-    // row stored at chunk position ch ^ (row & 7)
-    const int pos = (((lane / 2) ^ (s & 7)) * 4) + (2 * lane) % 4;
-    const float2 a = *reinterpret_cast<const float2*>(dq_acc + ((int64_t)bh * Spad + s) * DH + pos);
+    // accumulator layout of the main kernel: per tile of 128 rows, blocks [row / 32][column / 32] of
+    // 32 rows x 32 floats, the 16-byte chunk ch of a row stored at chunk position ch ^ (row & 7)
+    const int rt = s % BT, col = (2 * lane) % 32;
+    const int64_t blk = ((int64_t)bh * (Spad / BT) + s / BT) * (BT * DH) + ((rt / 32) * 2 + lane / 16) * 1024;
+    const float2 a = *reinterpret_cast<const float2*>(dq_acc + blk + (rt % 32) * 32 + (((col / 4) ^ (rt & 7)) * 4) + col % 4);
     const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
     reinterpret_cast<__nv_bfloat162*>(dQ + off)[lane] = __floats2bfloat162_rn(a.x * scale, a.y * scale);
 }
@@ -122,61 +125,62 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 // P^T for 32 query columns of one key row: exp2(c*S - lse2_q) as 16 bf16 pairs; on the diagonal
 // tile key row r is visible to query column qc iff r <= qc.
 template <bool DIAG>
-__device__ __forceinline__ void p_chunk(const uint32_t (&v)[32], const float* l2, float c, int r, int qc0,
-                                        uint32_t* pk) {
+__device__ __forceinline__ void p_chunk(uint32_t (&v)[32], const float* l2, float c, int r, int qc0, uint32_t* pk) {
+    // three passes over the 32 values (arguments, exponentials, packing) keep many independent
+    // operations in flight: the warp has few partners to hide latencies behind
     const float4* l4 = reinterpret_cast<const float4*>(l2);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
         const float4 la = l4[i / 4];
-        float a0 = ex2(fmaf(__uint_as_float(v[i]), c, -la.x));
-        float a1 = ex2(fmaf(__uint_as_float(v[i + 1]), c, -la.y));
-        float a2 = ex2(fmaf(__uint_as_float(v[i + 2]), c, -la.z));
-        float a3 = ex2(fmaf(__uint_as_float(v[i + 3]), c, -la.w));
-        if (DIAG) {
-            a0 = r <= qc0 + i ? a0 : 0.f;
-            a1 = r <= qc0 + i + 1 ? a1 : 0.f;
-            a2 = r <= qc0 + i + 2 ? a2 : 0.f;
-            a3 = r <= qc0 + i + 3 ? a3 : 0.f;
-        }
-        pk[i / 2] = pack_bf16(a0, a1);
-        pk[i / 2 + 1] = pack_bf16(a2, a3);
+        v[i] = __float_as_uint(fmaf(__uint_as_float(v[i]), c, -la.x));
+        v[i + 1] = __float_as_uint(fmaf(__uint_as_float(v[i + 1]), c, -la.y));
+        v[i + 2] = __float_as_uint(fmaf(__uint_as_float(v[i + 2]), c, -la.z));
+        v[i + 3] = __float_as_uint(fmaf(__uint_as_float(v[i + 3]), c, -la.w));
     }
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        float a = ex2(__uint_as_float(v[i]));
+        if (DIAG) a = r <= qc0 + i ? a : 0.f;
+        v[i] = __float_as_uint(a);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) pk[i / 2] = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
 }
 // dS^T = P^T o (dP^T - delta_q) for 32 query columns, in packed bf16 arithmetic (the result is a
 // bf16 MMA operand anyway).
-__device__ __forceinline__ void ds_chunk(const uint32_t* p16, const uint32_t (&v)[32], const float* dl, uint32_t* ds) {
+__device__ __forceinline__ void ds_chunk(const uint32_t* p16, uint32_t (&v)[32], const float* dl, uint32_t* ds) {
     const float4* d4 = reinterpret_cast<const float4*>(dl);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
         const float4 d = d4[i / 4];
-        const __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[i]) - d.x, __uint_as_float(v[i + 1]) - d.y);
-        const __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[i + 2]) - d.z, __uint_as_float(v[i + 3]) - d.w);
-        const __nv_bfloat162 r0 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p16[i / 2]), t0);
-        const __nv_bfloat162 r1 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p16[i / 2 + 1]), t1);
-        ds[i / 2] = *reinterpret_cast<const uint32_t*>(&r0);
-        ds[i / 2 + 1] = *reinterpret_cast<const uint32_t*>(&r1);
+        v[i] = __float_as_uint(__uint_as_float(v[i]) - d.x);
+        v[i + 1] = __float_as_uint(__uint_as_float(v[i + 1]) - d.y);
+        v[i + 2] = __float_as_uint(__uint_as_float(v[i + 2]) - d.z);
+        v[i + 3] = __float_as_uint(__uint_as_float(v[i + 3]) - d.w);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) v[i / 2] = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const __nv_bfloat162 r0 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p16[i]),
+                                          *reinterpret_cast<const __nv_bfloat162*>(&v[i]));
+        ds[i] = *reinterpret_cast<const uint32_t*>(&r0);
     }
 }
-// One key row (64 fp32 TMEM columns of this lane) -> scaled bf16 -> global.
-__device__ __forceinline__ void store_rows(uint32_t taddr, __nv_bfloat16* base, float f, int key, int b, int h,
+// Half a key row (32 fp32 TMEM columns of this lane, columns c0..c0+31) -> scaled bf16 -> global.
+__device__ __forceinline__ void store_rows(uint32_t taddr, __nv_bfloat16* base, float f, int key, int c0, int b, int h,
                                            const BwdParams& p) {
-    uint32_t o0[32], o1[32];
-    tmem_ld32(taddr, o0);
-    tmem_ld32(taddr + 32, o1);
+    uint32_t o0[32];
+    tmem_ld32(taddr + c0, o0);
     tmem_ld_wait();
     if (key >= p.S) return;
-    uint4* dst = reinterpret_cast<uint4*>(base + (int64_t)b * p.sb + (int64_t)key * p.ss + (int64_t)h * p.sh);
+    uint4* dst = reinterpret_cast<uint4*>(base + (int64_t)b * p.sb + (int64_t)key * p.ss + (int64_t)h * p.sh + c0);
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
+    for (int i = 0; i < 32; i += 8)
         dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * f, __uint_as_float(o0[i + 1]) * f),
                                 pack_bf16(__uint_as_float(o0[i + 2]) * f, __uint_as_float(o0[i + 3]) * f),
                                 pack_bf16(__uint_as_float(o0[i + 4]) * f, __uint_as_float(o0[i + 5]) * f),
                                 pack_bf16(__uint_as_float(o0[i + 6]) * f, __uint_as_float(o0[i + 7]) * f));
-        dst[4 + i / 8] = make_uint4(pack_bf16(__uint_as_float(o1[i]) * f, __uint_as_float(o1[i + 1]) * f),
-                                    pack_bf16(__uint_as_float(o1[i + 2]) * f, __uint_as_float(o1[i + 3]) * f),
-                                    pack_bf16(__uint_as_float(o1[i + 4]) * f, __uint_as_float(o1[i + 5]) * f),
-                                    pack_bf16(__uint_as_float(o1[i + 6]) * f, __uint_as_float(o1[i + 7]) * f));
-    }
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -184,7 +188,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t kv_full, q_full[NQ], q_free[NQ], do_full[2], s_full[2], dp_full[2], dv_done[2], dq_full[2], s_free,
-        dp_free, p_ready, ds_ready[2], dq_free, stage_free[4], all_done;
+        dp_free, p_ready, ds_ready[2], dq_free, stage_free[8], all_done;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -195,7 +199,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* sdO = smem + (2 + NQ) * TILE_BYTES;  // 2 stages
     uint8_t* sDS = smem + (4 + NQ) * TILE_BYTES;  // 2 buffers x 2 blocks of 64 queries: [128 keys][64 queries] bf16 each
     float* sStat = reinterpret_cast<float*>(smem + NTILES * TILE_BYTES);  // [Q stage][lse2 | delta][128]
-    uint8_t* sStage = smem + NTILES * TILE_BYTES + NQ * 1024;             // [warp % 4][32 rows][256 B]
+    uint8_t* sStage = smem + NTILES * TILE_BYTES + NQ * 1024;             // [warp % 8][32 rows][128 B]
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int ntile = p.Spad / BT;
@@ -223,28 +227,28 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         mbar_init(&all_done, 1);
         // waited on by the MMA warp, tile after tile; one arrival per warp of the group that signals
-        mbar_init(&s_free, 4);
-        mbar_init(&p_ready, 4);
-        mbar_init(&dp_free, 4);
+        mbar_init(&s_free, 8);
+        mbar_init(&p_ready, 8);
+        mbar_init(&dp_free, 8);
         // dS^T(i+1) may be complete before dS^T(i) is (it waits for neither dK(i) nor dQ(i)): one barrier per group
-        mbar_init(&ds_ready[0], 4);
-        mbar_init(&ds_ready[1], 4);
-        mbar_init(&dq_free, 4);
-        for (int w = 0; w < 4; w++) mbar_init(&stage_free[w], 1);
+        mbar_init(&ds_ready[0], 8);
+        mbar_init(&ds_ready[1], 8);
+        mbar_init(&dq_free, 8);
+        for (int w = 0; w < 8; w++) mbar_init(&stage_free[w], 1);
         fence_barrier_init();
     }
-    if (warp == 9) tmem_alloc(&tmem_slot, TMEM_COLS);
+    if (warp == W_MMA) tmem_alloc(&tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    if (warp >= 8) {
-        // Warps 8-11 form one warp group; all four execute this one instruction together and hand
-        // most of their registers to the compute groups.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp >= W_PROD) {
+        // Warps 16-19 form one warp group; all four execute this one instruction together and hand
+        // most of their registers to the compute warps.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     }
-    if (warp == 8) {
+    if (warp == W_PROD) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             prefetch_tmap(&tmQ);
@@ -267,7 +271,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &do_full[s], 0, h, q0, b);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == W_MMA) {
         // ---------------- MMA issuer ----------------
         // the whole warp runs the loop (uniform control flow and operands); one elected lane issues
         const uint32_t el = elect_one();
@@ -341,83 +345,80 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             qs = qn;
         }
         umma_commit_e(el, &all_done);
-    } else if (warp >= 10) {
+    } else if (warp > W_MMA) {
         // idle warps: they only take part in the register hand-over above
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-        // ---------------- compute groups: group g (warps 4g..4g+3) owns the query tiles it = g, g+2, ... ----------------
-        // lane = key row; a thread turns its row of S^T into P^T (bf16, kept in registers and copied to
-        // TMEM for the dV product), then P^T and dP^T into dS^T, and last drains dQ of the tile before
-        // (the other group's).  While one group is in the second half of tile i the other is already
-        // in the first half of tile i+1.
-        const int g = warp / 4;
+        // The increase is served from the registers the CTA got at launch (640 threads x 96) and blocks
+        // until they are there: 16 warps x 32 x (104 - 96) must not exceed what warps 16-19 gave back,
+        // 4 x 32 x (96 - 40).
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        // ---------------- compute warps ----------------
+        // Group g = warp / 8 owns the query tiles it = g, g+2, ...; inside a group, warp % 4 selects the
+        // 32 key rows (TMEM lanes) and c = (warp / 4) % 2 the half of the 128 query columns.  lane = key
+        // row: a thread turns its half row of S^T into P^T (bf16, kept in registers and copied to TMEM
+        // for the dV product), then P^T and dP^T into dS^T, and last drains its part of dQ of the tile
+        // before (the other group's).  While one group is in the second half of tile i the other is
+        // already in the first half of tile i+1.
+        const int g = warp / 8;
+        const int c = (warp / 4) & 1;
         const int q4 = warp % 4;
         const int r = q4 * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
-        const uint32_t tS = lane_base + COL_ST, tP = lane_base + COL_P, tDP = lane_base + COL_DP, tDQ = lane_base + COL_DQ;
-        float* acc_base = p.dq_acc + ((int64_t)bh * p.Spad + q4 * 32) * DH;
-        uint8_t* blk = sStage + q4 * 8192;  // shared with the same warp of the other group, drain after drain
-        bool pending = false;               // this warp's last bulk reduction may still be reading blk
+        const uint32_t tS = lane_base + COL_ST + 64 * c, tP = lane_base + COL_P + 32 * c;
+        const uint32_t tDP = lane_base + COL_DP + 64 * c, tDQ = lane_base + COL_DQ + 32 * c;
+        const int sb = warp % 8;  // staging block, shared with the same warp of the other group, drain after drain
+        float* acc_base = p.dq_acc + (int64_t)bh * p.Spad * DH + (q4 * 2 + c) * 1024;
+        uint8_t* blk = sStage + sb * 4096;
+        bool pending = false;  // this warp's last bulk reduction may still be reading blk
         // the staging block goes back to the other group once this warp's reduction has read it
         auto release_stage = [&]() {
             if (pending && lane == 0) {
                 bulk_wait_read();
-                mbar_arrive(&stage_free[q4]);
+                mbar_arrive(&stage_free[sb]);
             }
             pending = false;
         };
-        // dQ of query tile d (relative to n): rows 32*q4.., all 64 columns, one 8 KB reduction
+        // dQ of query tile d (relative to n): rows 32*q4.., columns 32*c.., one 4 KB reduction
         auto drain_dq = [&](int d) {
-            uint32_t d0[32], d1[32];
+            uint32_t d0[32];
             tmem_ld32(tDQ, d0);
-            tmem_ld32(tDQ + 32, d1);
             tmem_ld_wait();
             tc_fence_before();
             warp_arrive(&dq_free, lane);
-            if (d > 0) mbar_wait(&stage_free[q4], (d - 1) & 1, guard, 617);
+            if (d > 0) mbar_wait(&stage_free[sb], (d - 1) & 1, guard, 617);
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                *reinterpret_cast<uint4*>(blk + lane * 256 + ((ch ^ (lane & 7)) * 16)) =
+            for (int ch = 0; ch < 8; ch++)
+                *reinterpret_cast<uint4*>(blk + lane * 128 + ((ch ^ (lane & 7)) * 16)) =
                     make_uint4(d0[4 * ch], d0[4 * ch + 1], d0[4 * ch + 2], d0[4 * ch + 3]);
-                *reinterpret_cast<uint4*>(blk + lane * 256 + (((8 + ch) ^ (lane & 7)) * 16)) =
-                    make_uint4(d1[4 * ch], d1[4 * ch + 1], d1[4 * ch + 2], d1[4 * ch + 3]);
-            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)(n + d) * BT * DH, blk, 8192);
+            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)(n + d) * BT * DH, blk, 4096);
             pending = true;
         };
         for (int it = g; it < niter; it += 2) {
             const int ph = (it >> 1) & 1;  // phase parity of the barriers indexed by tile parity
             const int qs = it % NQ;
             mbar_wait(&q_full[qs], (it / NQ) & 1, guard, 601);  // lse2 / delta of this query tile are in smem
-            const float* l2 = sStat + qs * 256;
+            const float* l2 = sStat + qs * 256 + 64 * c;
             const float* dl = l2 + 128;
             mbar_wait(&s_full[g], ph, guard, 602);
             tc_fence_after();
-            uint32_t pk[64];
+            uint32_t pk[32];
             {
-                // the whole row of S^T goes to registers first, so the next scores can be issued while
+                // the half row of S^T goes to registers first, so the next scores can be issued while
                 // this tile's exponentials run
-                uint32_t s0[32], s1[32], s2[32], s3[32];
+                uint32_t s0[32], s1[32];
                 tmem_ld32(tS, s0);
                 tmem_ld32(tS + 32, s1);
-                tmem_ld32(tS + 64, s2);
-                tmem_ld32(tS + 96, s3);
                 tmem_ld_wait();
                 tc_fence_before();
                 warp_arrive(&s_free, lane);
-                release_stage();
                 if (it == 0) {
-                    p_chunk<true>(s0, l2, p.scale_log2, r, 0, &pk[0]);
-                    p_chunk<true>(s1, l2 + 32, p.scale_log2, r, 32, &pk[16]);
-                    p_chunk<true>(s2, l2 + 64, p.scale_log2, r, 64, &pk[32]);
-                    p_chunk<true>(s3, l2 + 96, p.scale_log2, r, 96, &pk[48]);
+                    p_chunk<true>(s0, l2, p.scale_log2, r, 64 * c, &pk[0]);
+                    p_chunk<true>(s1, l2 + 32, p.scale_log2, r, 64 * c + 32, &pk[16]);
                 } else {
                     p_chunk<false>(s0, l2, p.scale_log2, r, 0, &pk[0]);
-                    p_chunk<false>(s1, l2 + 32, p.scale_log2, r, 32, &pk[16]);
-                    p_chunk<false>(s2, l2 + 64, p.scale_log2, r, 64, &pk[32]);
-                    p_chunk<false>(s3, l2 + 96, p.scale_log2, r, 96, &pk[48]);
+                    p_chunk<false>(s1, l2 + 32, p.scale_log2, r, 0, &pk[16]);
                 }
             }
             if (it > 0) {  // the dV product of tile it-1 has read P^T(it-1)
@@ -425,38 +426,33 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tc_fence_after();
             }
             tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
-            tmem_st32(tP + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
             tmem_st_wait();
             tc_fence_before();
             warp_arrive(&p_ready, lane);
+            release_stage();  // long after the reduction was issued: costs no waiting
 
             // second half: dS^T = P^T o (dP^T - delta), written over pk in place
-            uint32_t va[32], vb[32];
-            mbar_wait(&dp_full[g], ph, guard, 613);
-            tc_fence_after();
-            tmem_ld32(tDP, va);
-            tmem_ld32(tDP + 32, vb);
-            tmem_ld_wait();
-            ds_chunk(&pk[0], va, dl, &pk[0]);
-            ds_chunk(&pk[16], vb, dl + 32, &pk[16]);
-            tmem_ld32(tDP + 64, va);
-            tmem_ld32(tDP + 96, vb);
-            tmem_ld_wait();
-            tc_fence_before();
-            warp_arrive(&dp_free, lane);  // dP^T(it) is in registers
-            ds_chunk(&pk[32], va, dl + 64, &pk[32]);
-            ds_chunk(&pk[48], vb, dl + 96, &pk[48]);
+            {
+                uint32_t va[32];
+                mbar_wait(&dp_full[g], ph, guard, 613);
+                tc_fence_after();
+                tmem_ld32(tDP, va);
+                tmem_ld_wait();
+                ds_chunk(&pk[0], va, dl, &pk[0]);
+                tmem_ld32(tDP + 32, va);
+                tmem_ld_wait();
+                tc_fence_before();
+                warp_arrive(&dp_free, lane);  // dP^T(it) is in registers
+                ds_chunk(&pk[16], va, dl + 32, &pk[16]);
+            }
             if (it >= 2)  // dK and dQ of tile it-2 have read this dS buffer
                 mbar_wait(&dq_full[g], ((it - 2) >> 1) & 1, guard, 614);
-            // row r of dS: two 128-byte rows (queries 0-63 | 64-127) with the 128-byte swizzle
-            uint8_t* ds_row = sDS + g * 2 * TILE_BYTES + r * 128;
+            // this thread's part of row r of dS: one 128-byte row (queries 64c..64c+63) with the 128-byte swizzle
+            uint8_t* ds_row = sDS + (g * 2 + c) * TILE_BYTES + r * 128;
 #pragma unroll
-            for (int half = 0; half < 2; half++)
-#pragma unroll
-                for (int ch = 0; ch < 8; ch++)
-                    *reinterpret_cast<uint4*>(ds_row + half * TILE_BYTES + ((ch ^ (r & 7)) * 16)) =
-                        make_uint4(pk[32 * half + 4 * ch], pk[32 * half + 4 * ch + 1], pk[32 * half + 4 * ch + 2],
-                                   pk[32 * half + 4 * ch + 3]);
+            for (int ch = 0; ch < 8; ch++)
+                *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) * 16)) =
+                    make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             warp_arrive(&ds_ready[g], lane);
             if (it > 0) {  // dQ of the tile before (the other group's) leaves TMEM through this group
@@ -476,13 +472,13 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // epilogue: group 0 stores dV, group 1 stores scale * dK
         mbar_wait(&all_done, 0, guard, 618);
         tc_fence_after();
-        if (g == 0) store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, b, h, p);
-        else store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, b, h, p);
+        if (g == 0) store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, 32 * c, b, h, p);
+        else store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, 32 * c, b, h, p);
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == W_MMA) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
