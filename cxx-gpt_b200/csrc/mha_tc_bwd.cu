@@ -59,47 +59,61 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
-// One warp per (batch*head, row < Spad): delta, lse2, and a cleared accumulator row.
+// Eight threads per (batch*head, row < Spad), 16 bytes of O and dO each: delta, lse2, and a cleared
+// accumulator row.
 __global__ void mha_tc_bwd_pre_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
                                       const float* __restrict__ lse, float* __restrict__ lse2,
                                       float* __restrict__ delta, float* __restrict__ dq_acc, int B, int S, int H,
                                       int Spad, int64_t sb, int64_t ss, int64_t sh) {
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-    const int lane = threadIdx.x % 32;
-    if (row >= (int64_t)B * H * Spad) return;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 8;
+    const int part = threadIdx.x % 8;
+    if (row >= (int64_t)B * H * Spad) return;  // whole groups of 8 threads leave together
     const int s = row % Spad;
     const int bh = row / Spad;
-    reinterpret_cast<float2*>(dq_acc + row * DH)[lane] = make_float2(0.f, 0.f);
+    float4* z = reinterpret_cast<float4*>(dq_acc + row * DH + part * 8);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
     float acc = 0.f;
     if (s < S) {
-        const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
-        const float2 o = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(O + off)[lane]);
-        const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dO + off)[lane]);
-        acc = o.x * g.x + o.y * g.y;
+        const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh + part * 8;
+        const uint4 o = *reinterpret_cast<const uint4*>(O + off);
+        const uint4 g = *reinterpret_cast<const uint4*>(dO + off);
+        const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[i]));
+            const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+            acc = fmaf(a.x, c.x, fmaf(a.y, c.y, acc));
+        }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
+    for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (part == 0) {
         delta[row] = acc;
         lse2[row] = s < S ? lse[(int64_t)bh * S + s] * 1.4426950408889634f : INFINITY;
     }
 }
 
-// dQ[b,s,h,:] = bf16(scale * acc[bh][s][:]); one warp per row.
+// dQ[b,s,h,:] = bf16(scale * acc[bh][s][:]); eight threads per row, 8 columns each.
 __global__ void mha_tc_bwd_post_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dQ, int B,
                                        int S, int H, int Spad, int64_t sb, int64_t ss, int64_t sh, float scale) {
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-    const int lane = threadIdx.x % 32;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 8;
+    const int part = threadIdx.x % 8;
     if (row >= (int64_t)B * H * S) return;
     const int s = row % S;
     const int bh = row / S;
     // accumulator layout of the main kernel: per tile of 128 rows, blocks [row / 32][column / 32] of
     // 32 rows x 32 floats, the 16-byte chunk ch of a row stored at chunk position ch ^ (row & 7)
-    const int rt = s % BT, col = (2 * lane) % 32;
-    const int64_t blk = ((int64_t)bh * (Spad / BT) + s / BT) * (BT * DH) + ((rt / 32) * 2 + lane / 16) * 1024;
-    const float2 a = *reinterpret_cast<const float2*>(dq_acc + blk + (rt % 32) * 32 + (((col / 4) ^ (rt & 7)) * 4) + col % 4);
-    const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh;
-    reinterpret_cast<__nv_bfloat162*>(dQ + off)[lane] = __floats2bfloat162_rn(a.x * scale, a.y * scale);
+    const int rt = s % BT;
+    const float* src = dq_acc + ((int64_t)bh * (Spad / BT) + s / BT) * (BT * DH) + ((rt / 32) * 2 + part / 4) * 1024 +
+                       (rt % 32) * 32;
+    const int ch = 2 * (part % 4);
+    const float4 a = *reinterpret_cast<const float4*>(src + ((ch ^ (rt & 7)) * 4));
+    const float4 c = *reinterpret_cast<const float4*>(src + (((ch + 1) ^ (rt & 7)) * 4));
+    const int64_t off = (int64_t)(bh / H) * sb + (int64_t)s * ss + (int64_t)(bh % H) * sh + part * 8;
+    *reinterpret_cast<uint4*>(dQ + off) =
+        make_uint4(pack_bf16(a.x * scale, a.y * scale), pack_bf16(a.z * scale, a.w * scale),
+                   pack_bf16(c.x * scale, c.y * scale), pack_bf16(c.z * scale, c.w * scale));
 }
 
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -376,6 +390,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 bulk_wait_read();
                 mbar_arrive(&stage_free[sb]);
             }
+            __syncwarp();  // without it lane 0 may run on its own for a long stretch
             pending = false;
         };
         // dQ of query tile d (relative to n): rows 32*q4.., columns 32*c.., one 4 KB reduction
@@ -413,6 +428,7 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tmem_ld_wait();
                 tc_fence_before();
                 warp_arrive(&s_free, lane);
+                release_stage();  // the other group's next drain waits for this: do it early
                 if (it == 0) {
                     p_chunk<true>(s0, l2, p.scale_log2, r, 64 * c, &pk[0]);
                     p_chunk<true>(s1, l2 + 32, p.scale_log2, r, 64 * c + 32, &pk[16]);
@@ -429,7 +445,6 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_st_wait();
             tc_fence_before();
             warp_arrive(&p_ready, lane);
-            release_stage();  // long after the reduction was issued: costs no waiting
 
             // second half: dS^T = P^T o (dP^T - delta), written over pk in place
             {
@@ -526,7 +541,7 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
         lse = tmp;
     }
     const int64_t nrows = (int64_t)p.B * p.H * Spad;
-    mha_tc_bwd_pre_kernel<<<(unsigned)((nrows + 7) / 8), 256, 0, st>>>(
+    mha_tc_bwd_pre_kernel<<<(unsigned)((nrows + 31) / 32), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(O), static_cast<const __nv_bfloat16*>(dO), lse, lse2, delta, dq_acc, p.B,
         p.S, p.H, Spad, p.sb, p.ss, p.sh);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
@@ -563,7 +578,7 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
 
     const int64_t orows = (int64_t)p.B * p.H * p.S;
-    mha_tc_bwd_post_kernel<<<(unsigned)((orows + 7) / 8), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dQ), p.B,
+    mha_tc_bwd_post_kernel<<<(unsigned)((orows + 31) / 32), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dQ), p.B,
                                                                       p.S, p.H, Spad, p.sb, p.ss, p.sh, p.scale);
     return check_launch();
 }
