@@ -57,31 +57,42 @@ def measured_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs.
+    NVML is initialised in the constructor, so the first sample falls inside even a short region."""
 
     def __init__(self, index):
         super().__init__(daemon=True)
         self.index, self.stop_flag, self.samples, self.reasons, self.max_mhz = index, False, [], set(), None
-
-    def run(self):
+        self.nv = self.h = None
         try:
             import pynvml as nv
             nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
-            names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
-                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
-                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
-                     nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
-            while not self.stop_flag:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                for bit, name in names.items():
-                    if r & bit:
-                        self.reasons.add(name)
-                time.sleep(0.02)
+            self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
         except Exception as e:  # NVML missing: report that instead of clocks
             self.reasons.add("nvml_unavailable:" + type(e).__name__)
+
+    def sample(self):
+        nv = self.nv
+        names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                 nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+        self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        for bit, name in names.items():
+            if r & bit:
+                self.reasons.add(name)
+
+    def run(self):
+        if self.nv is None:
+            return
+        try:
+            while not self.stop_flag:
+                self.sample()
+                time.sleep(0.005)
+        except Exception as e:
+            self.reasons.add("nvml_error:" + type(e).__name__)
 
     def result(self):
         s = sorted(self.samples)
@@ -271,7 +282,7 @@ def run_ours(args):
                              "peak_source": how, "unit": UNIT, "frac": main_tf / peak,
                              # dram__bytes_read + write of mha_tc_bwd_kernel from the ncu capture summarised in
                              # profiles/mha_tc_bwd_kernel_softmax_s4096_b4.md (398.6 MB at B=4), scaled by B/4
-                             "traffic": 398.64e6 * B / 4 if S == 4096 else None}}
+                             "traffic": 391.9e6 * B / 4 if S == 4096 else None}}
         if world == 1 and not args.no_cpu_baseline:
             tf, cores, dt, desc = cpu_sample(B, min(S, 4096))
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",
@@ -363,7 +374,7 @@ def run_ours_linattn(args):
     ref_ms = None
     try:
         import oracle
-        if rank == 0 and oracle.ReferenceCuda.available():
+        if rank == 0 and not args.no_reference_cuda and oracle.ReferenceCuda.available():
             rc = oracle.ReferenceCuda()
             buf = rc.scan_buffers(B, S, D, E, dev)
             Qf, Kf, Vf, dOf = (t.float() for t in (Q, K, V, dO))  # the same values, as the reference's fp32
@@ -440,6 +451,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
     ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
                     help="element type of the linattn_* workloads (bf16: tensor-core kernels, f32: exact kernels)")
     args = ap.parse_args()
