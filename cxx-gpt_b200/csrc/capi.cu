@@ -86,6 +86,7 @@ int cxxattn_mha_bwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, 
 size_t cxxattn_linattn_workspace_bytes(const cxxattn_lin_desc* desc) {
     if (!lin_ok(desc)) return 0;
     if (desc->dtype == CXXATTN_F32) return linattn_f32_workspace(*desc);
+    if (desc->dtype == CXXATTN_BF16) return linattn_tc_workspace(*desc);
     return 0;
 }
 
@@ -99,7 +100,7 @@ int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void*
                                z_cache, workspace, workspace_bytes, st);
     if (desc->dtype == CXXATTN_BF16) {
         if (z_cache != nullptr) return CXXATTN_ERR_UNSUPPORTED;  // the bf16 path keeps z on chip
-        return linattn_tc_fwd(*desc, Q, K, V, O, den, st);
+        return linattn_tc_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
     }
     return CXXATTN_ERR_INVALID;
 }
@@ -146,7 +147,8 @@ int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void*
         return linattn_f32_bwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (const float*)O,
                                (const float*)dO, den, (float*)dQ, (float*)dK, (float*)dV,
                                workspace, workspace_bytes, st);
-    if (desc->dtype == CXXATTN_BF16) return linattn_tc_bwd(*desc, Q, K, V, O, dO, den, dQ, dK, dV, st);
+    if (desc->dtype == CXXATTN_BF16)
+        return linattn_tc_bwd(*desc, Q, K, V, O, dO, den, dQ, dK, dV, workspace, workspace_bytes, st);
     return CXXATTN_ERR_INVALID;
 }
 

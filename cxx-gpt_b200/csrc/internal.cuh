@@ -41,10 +41,14 @@ void mha_tc_bwd_set_timing_events(void* start, void* stop);
 
 // ---- tcgen05 bf16 linear attention, D = E = 64 (linattn_tc_fwd.cu) ----
 bool linattn_tc_supported(const cxxattn_lin_desc& d);
+// Workspace (optional): group states for cutting a unit's sequence over several CTAs; without it
+// one CTA walks a whole unit.
+size_t linattn_tc_workspace(const cxxattn_lin_desc& d);
 int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
-                   cudaStream_t st);
+                   void* ws, size_t ws_bytes, cudaStream_t st);
 int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O,
-                   const void* dO, const float* den, void* dQ, void* dK, void* dV, cudaStream_t st);
+                   const void* dO, const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes,
+                   cudaStream_t st);
 
 // ---- diagnostics (umma_selftest.cu) ----
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);

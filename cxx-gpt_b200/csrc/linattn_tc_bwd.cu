@@ -20,17 +20,14 @@
 //
 // As in the forward, the states stay in TMEM (fp32) for the whole sequence and are copied as bf16
 // into shared memory once per chunk to serve as matrix operands.
-#include "internal.cuh"
-#include "tc_common.cuh"
+#include "linattn_tc_common.cuh"
 
 namespace cxxattn {
 namespace {
 
 using namespace tc;
+using namespace lintc;
 
-constexpr int CH = 128;
-constexpr int DE = 64;
-constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
 constexpr int NSTAGE = 2;
 constexpr int NTHREADS = 320;  // 4 compute warps, TMA producer, MMA issuer, 4 preparation warps (step 1, maps)
 constexpr uint32_t TMEM_COLS = 512;
@@ -46,103 +43,9 @@ struct LinBwdParams {
     int* status;
     int B, S;
     int map_elu;
+    SeqGroups sgp;  // prefix group states (dQ pass); G = 1: one CTA per unit
+    SeqGroups sgs;  // suffix group states (dK/dV pass)
 };
-
-__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
-__device__ __forceinline__ float phi1(float a) { return a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f); }
-__device__ __forceinline__ float dphi1(float a) { return a > 0.f ? 1.f : ex2(a * 1.4426950408889634f); }
-// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e).  The product x*log2(e) is
-// rounded to bf16 before the exponential (relative effect ln2*|t|*2^-9 on values that are then
-// rounded to bf16 anyway); one MUFU operation serves two elements.
-__device__ __forceinline__ uint32_t phi2(uint32_t v) {
-    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
-    const __nv_bfloat162 t = __hmul2(x, __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
-    uint32_t e;
-    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<const uint32_t*>(&t)));
-    const __nv_bfloat162 pos = __hadd2(x, __floats2bfloat162_rn(1.f, 1.f));
-    const uint32_t m = __hgt2_mask(x, __floats2bfloat162_rn(0.f, 0.f));  // 0xffff per half where x > 0
-    return (*reinterpret_cast<const uint32_t*>(&pos) & m) | (e & ~m);
-}
-
-// In-place feature map of one 128-byte tile row (element order does not matter).
-// Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
-// index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
-__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
-    uint4* p = reinterpret_cast<uint4*>(row);
-    uint4 v[8];
-    // all loads first, all stores last: with run-time chunk positions the compiler cannot reorder
-    // a load past an earlier store, and a lone warp would crawl through eight dependent round trips
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) v[ch] = p[ch ^ rot];
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
-        if (!valid) v[ch] = make_uint4(0u, 0u, 0u, 0u);
-        else if (elu) v[ch] = make_uint4(phi2(v[ch].x), phi2(v[ch].y), phi2(v[ch].z), phi2(v[ch].w));
-    }
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) p[ch ^ rot] = v[ch];
-}
-
-// Step 1 for one token row: the dO tile row becomes dnum = dO / den in place, dden = -(dO . O) / den
-// is returned and also written (bf16) to element 0 of the row's side-tile entry.
-__device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16* o_row, float den, bool valid,
-                                           int swz, uint8_t* dden_slot) {
-    uint4* p = reinterpret_cast<uint4*>(do_row);
-    const uint4* o = reinterpret_cast<const uint4*>(o_row);
-    const float inv = valid ? 1.0f / den : 0.f;
-    // The tile row is stored with its 16-byte chunks permuted: logical chunk ch sits at position
-    // ch ^ swz (swz = row & 7, which also spreads the lanes of a warp over the banks); the O row comes
-    // from global memory in logical order.  All loads first, all stores last.
-    uint4 g[8], ov[8];
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
-        g[ch] = p[ch ^ swz];
-        ov[ch] = valid ? o[ch] : make_uint4(0u, 0u, 0u, 0u);
-    }
-    float dot = 0.f;
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
-        const uint4 a = g[ch], c = ov[ch];
-        dot += bf_lo(a.x) * bf_lo(c.x) + bf_hi(a.x) * bf_hi(c.x) + bf_lo(a.y) * bf_lo(c.y) + bf_hi(a.y) * bf_hi(c.y) +
-               bf_lo(a.z) * bf_lo(c.z) + bf_hi(a.z) * bf_hi(c.z) + bf_lo(a.w) * bf_lo(c.w) + bf_hi(a.w) * bf_hi(c.w);
-        g[ch] = make_uint4(pack_bf16(bf_lo(a.x) * inv, bf_hi(a.x) * inv), pack_bf16(bf_lo(a.y) * inv, bf_hi(a.y) * inv),
-                           pack_bf16(bf_lo(a.z) * inv, bf_hi(a.z) * inv), pack_bf16(bf_lo(a.w) * inv, bf_hi(a.w) * inv));
-    }
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) p[ch ^ swz] = g[ch];
-    const float dden = -dot * inv;
-    *reinterpret_cast<uint16_t*>(dden_slot) = __bfloat16_as_ushort(__float2bfloat16_rn(dden));
-    return dden;
-}
-
-// fp32 state rows (TMEM lanes 0..63, 64 columns + z in column 64) -> bf16 operand tile in shared
-// memory: block 0 = [64 d][64 e], block 1 = column 0 holds z; optionally z also as fp32.
-__device__ __forceinline__ void state_to_smem(uint32_t taddr, uint8_t* sState, int r, float* zf32 = nullptr) {
-    uint32_t s0[32], s1[32], s2[32];
-    tmem_ld32(taddr, s0);
-    tmem_ld32(taddr + 32, s1);
-    tmem_ld32(taddr + 64, s2);  // column 64 = z; the rest is not used
-    tmem_ld_wait();
-    uint8_t* row = sState + r * 128;
-#pragma unroll
-    for (int ch = 0; ch < 4; ch++) {
-        *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) =
-            make_uint4(pack_bf16(__uint_as_float(s0[8 * ch]), __uint_as_float(s0[8 * ch + 1])),
-                       pack_bf16(__uint_as_float(s0[8 * ch + 2]), __uint_as_float(s0[8 * ch + 3])),
-                       pack_bf16(__uint_as_float(s0[8 * ch + 4]), __uint_as_float(s0[8 * ch + 5])),
-                       pack_bf16(__uint_as_float(s0[8 * ch + 6]), __uint_as_float(s0[8 * ch + 7])));
-        *reinterpret_cast<uint4*>(row + (((4 + ch) ^ (r & 7)) * 16)) =
-            make_uint4(pack_bf16(__uint_as_float(s1[8 * ch]), __uint_as_float(s1[8 * ch + 1])),
-                       pack_bf16(__uint_as_float(s1[8 * ch + 2]), __uint_as_float(s1[8 * ch + 3])),
-                       pack_bf16(__uint_as_float(s1[8 * ch + 4]), __uint_as_float(s1[8 * ch + 5])),
-                       pack_bf16(__uint_as_float(s1[8 * ch + 6]), __uint_as_float(s1[8 * ch + 7])));
-    }
-    *reinterpret_cast<uint4*>(sState + 8192 + r * 128 + ((r & 7) * 16)) =
-        make_uint4(pack_bf16(__uint_as_float(s2[0]), 0.f), 0u, 0u, 0u);
-    if (zf32 != nullptr) zf32[r] = __uint_as_float(s2[0]);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 
 // One gradient row: (acc + bias) * phi'(raw) -> bf16 -> global (128 bytes).  raw == nullptr: no
 // phi' factor (pre-mapped features); bias == nullptr: none.
@@ -194,8 +97,9 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     uint8_t* sPrev = sOnes + (1 + NSTAGE) * TILE_BYTES;  // block 0: S_prev [64 d][64 e]; block 1: column 0 = z_prev
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int b = blockIdx.x;
-    const int nc = (p.S + CH - 1) / CH;
+    const int b = blockIdx.x / p.sgp.G, g = blockIdx.x % p.sgp.G;  // batch unit, sequence group
+    const int c0 = g * p.sgp.gc;                                    // first chunk of the group
+    const int nc = min((p.S + CH - 1) / CH, c0 + p.sgp.gc) - c0;    // chunks of the group
     const Guard guard{&abort_flag, p.status};
 
     if (threadIdx.x == 0) {
@@ -234,9 +138,9 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 const int st = c % NSTAGE;
                 if (c >= NSTAGE) mbar_wait(&stage_free[st], ((c / NSTAGE) - 1) & 1, guard, 801);
                 mbar_expect_tx(&full[st], 3 * TILE_BYTES);
-                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, c * CH, b);
-                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, c * CH, b);
-                tma_load_4d(sG(st), &tmG, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, (c0 + c) * CH, b);
+                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, (c0 + c) * CH, b);
+                tma_load_4d(sG(st), &tmG, &full[st], 0, 0, (c0 + c) * CH, b);
             }
         }
     } else if (warp == 5) {
@@ -269,7 +173,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 umma_ss_e(el, tmem + C1_DQ, dDd, dPrev1, IDESC_I, true);  // + dden_t z_prev
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)
-                    umma_ss_e(el, tmem + C1_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
+                    umma_ss_e(el, tmem + C1_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, g > 0 || c > 0 || k > 0);
                 umma_commit_e(el, &s_done);
                 mbar_wait_poll(&p_ready, c & 1, guard, 814);
                 tc_fence_after();
@@ -285,7 +189,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         const int r = (warp - 6) * 32 + lane;
         for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
-            const int tok = c * CH + r;
+            const int tok = (c0 + c) * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = ok ? p.den[row] : 1.f;
@@ -299,11 +203,13 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     } else {
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        // a later sequence group starts from the sum of the states of the groups before it
+        if (g > 0 && warp < 2) init_state_row(p.sgp, b, 0, g, r, lane_base + C1_SX, sPrev);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
         for (int c = 0; c < nc; c++) {
-            const int tok = c * CH + r;
+            const int tok = (c0 + c) * CH + r;
             const bool valid = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
 
@@ -392,8 +298,10 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     uint8_t* sNext = sOnes + (1 + NSTAGE) * TILE_BYTES;  // block 0: S*_next [64 d][64 e]; block 1: column 0 = z*_next
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int b = blockIdx.x;
-    const int nc = (p.S + CH - 1) / CH;
+    const int b = blockIdx.x / p.sgs.G, g = blockIdx.x % p.sgs.G;  // batch unit, sequence group
+    const int c0 = g * p.sgs.gc;                                    // first chunk of the group
+    const int nc = min((p.S + CH - 1) / CH, c0 + p.sgs.gc) - c0;    // chunks of the group
+    const bool seeded = g + 1 < p.sgs.G;                            // later groups exist: start from their states
     const Guard guard{&abort_flag, p.status};
 
     if (threadIdx.x == 0) {
@@ -424,7 +332,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    // iteration n = 0 .. nc-1 handles chunk c = nc-1-n
+    // iteration n = 0 .. nc-1 handles chunk c = c0 + nc-1-n
     if (warp == 4) {
         if (lane == 0) {
             prefetch_tmap(&tmQ);
@@ -432,7 +340,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             prefetch_tmap(&tmV);
             prefetch_tmap(&tmG);
             for (int n = 0; n < nc; n++) {
-                const int st = n % NSTAGE, c = nc - 1 - n;
+                const int st = n % NSTAGE, c = c0 + nc - 1 - n;
                 if (n >= NSTAGE) mbar_wait(&stage_free[st], ((n / NSTAGE) - 1) & 1, guard, 901);
                 mbar_expect_tx(&full[st], 4 * TILE_BYTES);
                 tma_load_4d(sQ(st), &tmQ, &full[st], 0, 0, c * CH, b);
@@ -479,7 +387,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                     umma_ss_e(el, tmem + C2_DK, dVk + 2 * k, dNextK + 2 * k, IDESC_K2, k > 0);
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)  // S* += phiQ^T [dnum | dden]
-                    umma_ss_e(el, tmem + C2_SX, dQm + 128 * k, dG1 + 128 * k, IDESC_S, n > 0 || k > 0);
+                    umma_ss_e(el, tmem + C2_SX, dQm + 128 * k, dG1 + 128 * k, IDESC_S, seeded || n > 0 || k > 0);
                 umma_commit_e(el, &s_done);
                 mbar_wait_poll(&p_ready, n & 1, guard, 914);
                 tc_fence_after();
@@ -497,7 +405,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         // ---------------- preparation warps: step 1 and the feature maps of Q and K ----------------
         const int r = (warp - 6) * 32 + lane;
         for (int n = 0; n < nc; n++) {
-            const int st = n % NSTAGE, c = nc - 1 - n;
+            const int st = n % NSTAGE, c = c0 + nc - 1 - n;
             const int tok = c * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
@@ -515,11 +423,13 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     } else {
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        // an earlier sequence group starts from the sum of the states of the groups after it
+        if (seeded && warp < 2) init_state_row(p.sgs, b, g + 1, p.sgs.G, r, lane_base + C2_SX, sNext, zstar[0]);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&snext_ready);
         for (int n = 0; n < nc; n++) {
-            const int c = nc - 1 - n;
+            const int c = c0 + nc - 1 - n;
             const int tok = c * CH + r;
             const bool valid = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
@@ -596,7 +506,8 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 }  // namespace
 
 int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O,
-                   const void* dO, const float* den, void* dQ, void* dK, void* dV, cudaStream_t st) {
+                   const void* dO, const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes,
+                   cudaStream_t st) {
     if (!linattn_tc_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
     for (const void* q : {Q, K, V, O, dO, (const void*)dQ, (const void*)dK, (const void*)dV})
         if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
@@ -620,6 +531,19 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
     p.B = B;
     p.S = S;
     p.map_elu = d.feature_map == CXXATTN_MAP_ELU1;
+    // sequence groups when the units alone would leave SMs idle and the caller brought the workspace
+    LinGroupPlan plan = linattn_tc_plan(B, S);
+    if (plan.G > 1 && (ws == nullptr || ws_bytes < 2 * plan.state_bytes || reinterpret_cast<uintptr_t>(ws) % 16))
+        plan = LinGroupPlan{1, (S + CH - 1) / CH, 0};
+    float* gsp = static_cast<float*>(ws);
+    float* gss = plan.G > 1 ? reinterpret_cast<float*>(static_cast<char*>(ws) + plan.state_bytes) : nullptr;
+    p.sgp = SeqGroups{gsp, plan.G, plan.gc};
+    p.sgs = SeqGroups{gss, plan.G, plan.gc};
+    if (plan.G > 1) {
+        int rc = linattn_tc_group_states(0, plan, B, S, p.map_elu, K, V, nullptr, nullptr, gsp, st);
+        if (rc == CXXATTN_OK) rc = linattn_tc_group_states(1, plan, B, S, p.map_elu, Q, dO, O, den, gss, st);
+        if (rc != CXXATTN_OK) return rc;
+    }
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -631,9 +555,9 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
             return CXXATTN_ERR_CUDA;
         attr_set[dev] = true;
     }
-    linattn_tc_bwd_dq_kernel<<<(unsigned)B, NTHREADS, SMEM1_BYTES, st>>>(tmK, tmV, tmG, p);
+    linattn_tc_bwd_dq_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM1_BYTES, st>>>(tmK, tmV, tmG, p);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
-    linattn_tc_bwd_dkdv_kernel<<<(unsigned)B, NTHREADS, SMEM2_BYTES, st>>>(tmQ, tmK, tmV, tmG, p);
+    linattn_tc_bwd_dkdv_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM2_BYTES, st>>>(tmQ, tmK, tmV, tmG, p);
     return check_launch();
 }
 

@@ -1,0 +1,170 @@
+// Pieces shared by the bf16 tensor-core linear-attention kernels (forward, the two backward passes
+// and the group-state pre-pass): tile constants, the packed feature map, step 1 on a tile row, the
+// state row <-> operand tile conversion, and the sequence-group bookkeeping.
+#pragma once
+#include "internal.cuh"
+#include "tc_common.cuh"
+
+namespace cxxattn {
+namespace lintc {
+
+using namespace tc;
+
+constexpr int CH = 128;  // tokens per chunk
+constexpr int DE = 64;   // feature width (D = E)
+constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
+
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ float phi1(float a) { return a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f); }
+__device__ __forceinline__ float dphi1(float a) { return a > 0.f ? 1.f : ex2(a * 1.4426950408889634f); }
+// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e).  The product x*log2(e) is
+// rounded to bf16 before the exponential (relative effect ln2*|t|*2^-9 on values that are then
+// rounded to bf16 anyway); one MUFU operation serves two elements.
+__device__ __forceinline__ uint32_t phi2(uint32_t v) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
+    const __nv_bfloat162 t = __hmul2(x, __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
+    uint32_t e;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<const uint32_t*>(&t)));
+    const __nv_bfloat162 pos = __hadd2(x, __floats2bfloat162_rn(1.f, 1.f));
+    const uint32_t m = __hgt2_mask(x, __floats2bfloat162_rn(0.f, 0.f));  // 0xffff per half where x > 0
+    return (*reinterpret_cast<const uint32_t*>(&pos) & m) | (e & ~m);
+}
+
+// In-place feature map of one 128-byte tile row (element order does not matter).
+// Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
+// index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
+__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
+    uint4* p = reinterpret_cast<uint4*>(row);
+    uint4 v[8];
+    // all loads first, all stores last: with run-time chunk positions the compiler cannot reorder
+    // a load past an earlier store, and a lone warp would crawl through eight dependent round trips
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) v[ch] = p[ch ^ rot];
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        if (!valid) v[ch] = make_uint4(0u, 0u, 0u, 0u);
+        else if (elu) v[ch] = make_uint4(phi2(v[ch].x), phi2(v[ch].y), phi2(v[ch].z), phi2(v[ch].w));
+    }
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) p[ch ^ rot] = v[ch];
+}
+
+// Step 1 for one token row: the dO tile row becomes dnum = dO / den in place, dden = -(dO . O) / den
+// is returned and also written (bf16) to element 0 of the row's side-tile entry.
+__device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16* o_row, float den, bool valid,
+                                           int swz, uint8_t* dden_slot) {
+    uint4* p = reinterpret_cast<uint4*>(do_row);
+    const uint4* o = reinterpret_cast<const uint4*>(o_row);
+    const float inv = valid ? 1.0f / den : 0.f;
+    // The tile row is stored with its 16-byte chunks permuted: logical chunk ch sits at position
+    // ch ^ swz (swz = row & 7, which also spreads the lanes of a warp over the banks); the O row comes
+    // from global memory in logical order.  All loads first, all stores last.
+    uint4 g[8], ov[8];
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        g[ch] = p[ch ^ swz];
+        ov[ch] = valid ? o[ch] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) {
+        const uint4 a = g[ch], c = ov[ch];
+        dot += bf_lo(a.x) * bf_lo(c.x) + bf_hi(a.x) * bf_hi(c.x) + bf_lo(a.y) * bf_lo(c.y) + bf_hi(a.y) * bf_hi(c.y) +
+               bf_lo(a.z) * bf_lo(c.z) + bf_hi(a.z) * bf_hi(c.z) + bf_lo(a.w) * bf_lo(c.w) + bf_hi(a.w) * bf_hi(c.w);
+        g[ch] = make_uint4(pack_bf16(bf_lo(a.x) * inv, bf_hi(a.x) * inv), pack_bf16(bf_lo(a.y) * inv, bf_hi(a.y) * inv),
+                           pack_bf16(bf_lo(a.z) * inv, bf_hi(a.z) * inv), pack_bf16(bf_lo(a.w) * inv, bf_hi(a.w) * inv));
+    }
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++) p[ch ^ swz] = g[ch];
+    const float dden = -dot * inv;
+    *reinterpret_cast<uint16_t*>(dden_slot) = __bfloat16_as_ushort(__float2bfloat16_rn(dden));
+    return dden;
+}
+
+// One fp32 state row in registers (64 columns + z) -> bf16 operand tile in shared memory: block 0 =
+// [64 d][64 e], block 1 = column 0 holds z; optionally z also as fp32.
+__device__ __forceinline__ void state_regs_to_smem(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float z,
+                                                   uint8_t* sState, int r, float* zf32 = nullptr) {
+    uint8_t* row = sState + r * 128;
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+        *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) =
+            make_uint4(pack_bf16(__uint_as_float(s0[8 * ch]), __uint_as_float(s0[8 * ch + 1])),
+                       pack_bf16(__uint_as_float(s0[8 * ch + 2]), __uint_as_float(s0[8 * ch + 3])),
+                       pack_bf16(__uint_as_float(s0[8 * ch + 4]), __uint_as_float(s0[8 * ch + 5])),
+                       pack_bf16(__uint_as_float(s0[8 * ch + 6]), __uint_as_float(s0[8 * ch + 7])));
+        *reinterpret_cast<uint4*>(row + (((4 + ch) ^ (r & 7)) * 16)) =
+            make_uint4(pack_bf16(__uint_as_float(s1[8 * ch]), __uint_as_float(s1[8 * ch + 1])),
+                       pack_bf16(__uint_as_float(s1[8 * ch + 2]), __uint_as_float(s1[8 * ch + 3])),
+                       pack_bf16(__uint_as_float(s1[8 * ch + 4]), __uint_as_float(s1[8 * ch + 5])),
+                       pack_bf16(__uint_as_float(s1[8 * ch + 6]), __uint_as_float(s1[8 * ch + 7])));
+    }
+    *reinterpret_cast<uint4*>(sState + 8192 + r * 128 + ((r & 7) * 16)) = make_uint4(pack_bf16(z, 0.f), 0u, 0u, 0u);
+    if (zf32 != nullptr) zf32[r] = z;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// The same from the fp32 state in TMEM (lanes 0..63, 64 columns + z in column 64).
+__device__ __forceinline__ void state_to_smem(uint32_t taddr, uint8_t* sState, int r, float* zf32 = nullptr) {
+    uint32_t s0[32], s1[32], s2[32];
+    tmem_ld32(taddr, s0);
+    tmem_ld32(taddr + 32, s1);
+    tmem_ld32(taddr + 64, s2);  // column 64 = z; the rest is not used
+    tmem_ld_wait();
+    state_regs_to_smem(s0, s1, __uint_as_float(s2[0]), sState, r, zf32);
+}
+
+// ---- sequence groups ---------------------------------------------------------------------------
+// When there are fewer batch units than SMs, the sequence of a unit is cut into G groups of `gc`
+// chunks and one CTA takes one (unit, group).  A pre-pass (linattn_tc_state.cu) leaves the state sum
+// of every group in `gstate` [unit][group][64 rows][GS_ROW floats] (64 columns + z); a CTA starts
+// from the sum over the groups before it (prefix states) or after it (suffix states).
+constexpr int GS_ROW = 68;  // floats per state row in global memory (16-byte aligned rows)
+struct SeqGroups {
+    const float* gstate;  // null: one group
+    int G, gc;
+};
+// Row r (< 64) of the initial state of group g: sum over groups [g0, g1) -> TMEM (fp32) and the bf16
+// operand tile.  Called by the two warps that own TMEM lanes 0..63.
+__device__ __forceinline__ void init_state_row(const SeqGroups& sg, int unit, int g0, int g1, int r, uint32_t taddr,
+                                               uint8_t* sState, float* zf32 = nullptr) {
+    float acc[GS_ROW];
+#pragma unroll
+    for (int i = 0; i < GS_ROW; i++) acc[i] = 0.f;
+    for (int g = g0; g < g1; g++) {
+        const float4* src = reinterpret_cast<const float4*>(sg.gstate + (((int64_t)unit * sg.G + g) * DE + r) * GS_ROW);
+#pragma unroll
+        for (int i = 0; i < GS_ROW / 4; i++) {
+            const float4 v = src[i];
+            acc[4 * i] += v.x; acc[4 * i + 1] += v.y; acc[4 * i + 2] += v.z; acc[4 * i + 3] += v.w;
+        }
+    }
+    uint32_t s0[32], s1[32], s2[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        s0[i] = __float_as_uint(acc[i]);
+        s1[i] = __float_as_uint(acc[32 + i]);
+        s2[i] = i == 0 ? __float_as_uint(acc[64]) : 0u;
+    }
+    tmem_st32(taddr, s0);
+    tmem_st32(taddr + 32, s1);
+    tmem_st32(taddr + 64, s2);
+    tmem_st_wait();
+    state_regs_to_smem(s0, s1, acc[64], sState, r, zf32);
+}
+
+}  // namespace lintc
+
+// Host side: how a launch is cut into sequence groups (G = 1: not at all), the workspace that takes,
+// and the pre-pass that fills the group states.
+struct LinGroupPlan {
+    int G, gc;           // groups per unit, chunks per group
+    size_t state_bytes;  // one set of group states
+};
+LinGroupPlan linattn_tc_plan(int B, int S);
+// mode 0: prefix states sum phiK (x) [V | 1] of groups 0..G-2; mode 1: suffix states
+// sum phiQ (x) [dnum | dden] of groups 1..G-1 (step 1 fused: needs O, dO, den).
+int linattn_tc_group_states(int mode, const LinGroupPlan& plan, int B, int S, int map_elu, const void* A, const void* Bm,
+                            const void* O, const float* den, float* gstate, cudaStream_t st);
+
+}  // namespace cxxattn

@@ -21,17 +21,14 @@
 //
 // The state S (fp32, 64 x 65) lives in TMEM for the whole sequence; after each chunk it is copied
 // as bf16 into shared memory to serve as the operand of the next chunk's inter-chunk product.
-#include "internal.cuh"
-#include "tc_common.cuh"
+#include "linattn_tc_common.cuh"
 
 namespace cxxattn {
 namespace {
 
 using namespace tc;
+using namespace lintc;
 
-constexpr int CH = 128;  // tokens per chunk
-constexpr int DE = 64;   // feature width (D = E)
-constexpr int TILE_BYTES = CH * DE * 2;  // 16 KB
 constexpr int NSTAGE = 2;
 constexpr int NTHREADS = 320;  // 4 compute warps, TMA producer, MMA issuer, 4 feature-map warps
 constexpr uint32_t TMEM_COLS = 512;
@@ -46,38 +43,8 @@ struct LinFwdParams {
     int B, S;
     int map_elu;     // 1: phi(x) = x > 0 ? x + 1 : exp(x) applied to Q and K; 0: inputs pre-mapped
     int eps_in_den;  // 1: den stored with the 1e-8 added
+    SeqGroups sg;    // sequence groups (G = 1: one CTA per unit)
 };
-
-// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e).  The product x*log2(e) is
-// rounded to bf16 before the exponential (relative effect ln2*|t|*2^-9 on values that are then
-// rounded to bf16 anyway); one MUFU operation serves two elements.
-__device__ __forceinline__ uint32_t phi2(uint32_t v) {
-    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
-    const __nv_bfloat162 t = __hmul2(x, __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
-    uint32_t e;
-    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<const uint32_t*>(&t)));
-    const __nv_bfloat162 pos = __hadd2(x, __floats2bfloat162_rn(1.f, 1.f));
-    const uint32_t m = __hgt2_mask(x, __floats2bfloat162_rn(0.f, 0.f));  // 0xffff per half where x > 0
-    return (*reinterpret_cast<const uint32_t*>(&pos) & m) | (e & ~m);
-}
-// In-place feature map of one 128-byte row of a tile (element order does not matter).
-// Rows are 128 bytes apart, so the lanes of a warp must not all touch the same 16-byte chunk
-// index at once (that would be a 32-way bank conflict): lane l starts at chunk l & 7.
-__device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int rot) {
-    uint4* p = reinterpret_cast<uint4*>(row);
-    uint4 v[8];
-    // all loads first, all stores last: with run-time chunk positions the compiler cannot reorder
-    // a load past an earlier store, and a lone warp would crawl through eight dependent round trips
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) v[ch] = p[ch ^ rot];
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
-        if (!valid) v[ch] = make_uint4(0u, 0u, 0u, 0u);
-        else if (elu) v[ch] = make_uint4(phi2(v[ch].x), phi2(v[ch].y), phi2(v[ch].z), phi2(v[ch].w));
-    }
-#pragma unroll
-    for (int ch = 0; ch < 8; ch++) p[ch ^ rot] = v[ch];
-}
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -95,8 +62,9 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint8_t* sPrev = sOnes + TILE_BYTES;              // block 0: S_prev [64 d][64 e]; block 1: column 0 = z_prev
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int b = blockIdx.x;
-    const int nc = (p.S + CH - 1) / CH;
+    const int b = blockIdx.x / p.sg.G, g = blockIdx.x % p.sg.G;  // batch unit, sequence group
+    const int c0 = g * p.sg.gc;                                   // first chunk of the group
+    const int nc = min((p.S + CH - 1) / CH, c0 + p.sg.gc) - c0;   // chunks of the group
     const Guard guard{&abort_flag, p.status};
 
     if (threadIdx.x == 0) {
@@ -137,9 +105,9 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const int st = c % NSTAGE;
                 if (c >= NSTAGE) mbar_wait(&stage_free[st], ((c / NSTAGE) - 1) & 1, guard, 701);
                 mbar_expect_tx(&full[st], 3 * TILE_BYTES);
-                tma_load_4d(sQ(st), &tmQ, &full[st], 0, 0, c * CH, b);
-                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, c * CH, b);
-                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, c * CH, b);
+                tma_load_4d(sQ(st), &tmQ, &full[st], 0, 0, (c0 + c) * CH, b);
+                tma_load_4d(sK(st), &tmK, &full[st], 0, 0, (c0 + c) * CH, b);
+                tma_load_4d(sV(st), &tmV, &full[st], 0, 0, (c0 + c) * CH, b);
             }
         }
     } else if (warp == 5) {
@@ -174,7 +142,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + COL_O, dQ + 2 * k, dPrev + 128 * k, IDESC_I, k > 0);
 #pragma unroll
                 for (int k = 0; k < CH / 16; k++)
-                    umma_ss_e(el, tmem + COL_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, c > 0 || k > 0);
+                    umma_ss_e(el, tmem + COL_SX, dKm + 128 * k, dV1 + 128 * k, IDESC_S, g > 0 || c > 0 || k > 0);
                 umma_commit_e(el, &s_done);
                 mbar_wait_poll(&p_ready, c & 1, guard, 714);
                 tc_fence_after();
@@ -195,7 +163,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const int st = c % NSTAGE;
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 721);
             if (p.map_elu) {
-                const bool ok = c * CH + r < p.S;
+                const bool ok = (c0 + c) * CH + r < p.S;
                 map_row(sQ(st) + r * 128, ok, true, r & 7);
                 map_row(sK(st) + r * 128, ok, true, r & 7);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -207,12 +175,14 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // ---------------- compute warps: thread r = token row r of the chunk = TMEM lane r ----------------
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        // the state operand of the first chunk is the zero tile written at start-up
+        // the state operand of the first chunk is the zero tile written at start-up, or, for a later
+        // sequence group, the sum of the states of the groups before it (which also seeds TMEM)
+        if (g > 0 && warp < 2) init_state_row(p.sg, b, 0, g, r, lane_base + COL_SX, sPrev);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
         for (int c = 0; c < nc; c++) {
-            const int tok = c * CH + r;
+            const int tok = (c0 + c) * CH + r;
             const bool valid = tok < p.S;
 
             // A -> causal mask inside the chunk (key column s visible iff s <= r), row sum, bf16 P
@@ -322,8 +292,13 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 bool linattn_tc_supported(const cxxattn_lin_desc& d) { return d.D == DE && d.E == DE; }
 
+size_t linattn_tc_workspace(const cxxattn_lin_desc& d) {
+    if (!linattn_tc_supported(d)) return 0;
+    return 2 * linattn_tc_plan((int)d.B, (int)d.S).state_bytes;  // prefix and suffix group states
+}
+
 int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
-                   cudaStream_t st) {
+                   void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!linattn_tc_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
     for (const void* q : {Q, K, V, (const void*)O})
         if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
@@ -342,6 +317,15 @@ int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
     p.S = S;
     p.map_elu = d.feature_map == CXXATTN_MAP_ELU1;
     p.eps_in_den = d.eps_in_den;
+    // sequence groups when the units alone would leave SMs idle and the caller brought the workspace
+    LinGroupPlan plan = linattn_tc_plan(B, S);
+    if (plan.G > 1 && (ws == nullptr || ws_bytes < plan.state_bytes || reinterpret_cast<uintptr_t>(ws) % 16))
+        plan = LinGroupPlan{1, (S + CH - 1) / CH, 0};
+    p.sg = SeqGroups{static_cast<const float*>(ws), plan.G, plan.gc};
+    if (plan.G > 1) {
+        const int rc = linattn_tc_group_states(0, plan, B, S, p.map_elu, K, V, nullptr, nullptr, static_cast<float*>(ws), st);
+        if (rc != CXXATTN_OK) return rc;
+    }
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -351,7 +335,7 @@ int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
             return CXXATTN_ERR_CUDA;
         attr_set[dev] = true;
     }
-    linattn_tc_fwd_kernel<<<(unsigned)B, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, p);
+    linattn_tc_fwd_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, p);
     return check_launch();
 }
 

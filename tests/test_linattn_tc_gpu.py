@@ -127,3 +127,56 @@ def test_backward_long_sequence_linearity_and_subset_parity(pkg, dev, orc):
     rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O[:S], f[3], den[:S], 1, S, 64, 64, f64=True)
     for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
         assert rel_err(a[:S], b) < TOL_BF16, (name, rel_err(a[:S], b))
+
+
+def test_sequence_groups_agree_with_single_pass(pkg, dev, orc):
+    """Few units: the sequence is cut into groups of chunks that run as separate CTAs, seeded by a
+    state pre-pass (the workspace holds the group states).  Without a workspace one CTA walks the
+    whole unit.  Both must match the oracle, and each other closely; 11 chunks give groups of
+    unequal length, the last chunk is ragged."""
+    import ctypes as C
+    B, S = 3, 1300
+    Q, K, V = inputs(51, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(3)).bfloat16()
+    d = pkg.lin_desc(B, S, 64, 64, pkg.BF16, pkg.MAP_ELU1, 0)
+    assert pkg.lib().cxxattn_linattn_workspace_bytes(C.byref(d)) > 0  # groups are planned for this shape
+    grouped = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+
+    tq, tk, tv, tg = (x.to(dev) for x in (Q, K, V, dO))
+    O = torch.full_like(tv, float("nan"))
+    den = torch.full((B * S,), float("nan"), device=dev)
+    dQ, dK, dV = (torch.full_like(tq, float("nan")) for _ in range(3))
+    lib = pkg.lib()
+    assert lib.cxxattn_linattn_fwd(C.byref(d), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), O.data_ptr(),
+                                   den.data_ptr(), None, None, 0, None) == 0
+    torch.cuda.synchronize()
+    assert lib.cxxattn_linattn_bwd(C.byref(d), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), O.data_ptr(),
+                                   tg.data_ptr(), den.data_ptr(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(),
+                                   None, 0, None) == 0
+    pkg.sync_status()
+    single = [t.float().cpu().numpy() for t in (O, den, dQ, dK, dV)]
+    for name, a, b in zip(("O", "den", "dQ", "dK", "dV"), grouped, single):
+        assert np.all(np.isfinite(a)) and np.all(np.isfinite(b)), name
+        assert rel_err(a, b) < 1e-2, (name, rel_err(a, b))
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    rO, rden, _ = orc.linattn_fwd(f[0], f[1], f[2], B, S, 64, 64, elu=True, f64=True)
+    for got in (grouped, single):
+        assert rel_err(got[0], rO) < TOL_BF16 and rel_err(got[1], rden) < TOL_BF16
+        rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], got[0], f[3], got[1], B, S, 64, 64, f64=True)
+        for name, a, b in (("dQ", got[2], rdQ), ("dK", got[3], rdK), ("dV", got[4], rdV)):
+            assert rel_err(a, b) < TOL_BF16, (name, rel_err(a, b))
+
+
+def test_many_units_take_one_group(pkg, dev, orc):
+    """With more units than SMs nothing is cut (no workspace is asked for) and the results are the
+    single-pass ones."""
+    import ctypes as C
+    B, S = 320, 256
+    d = pkg.lin_desc(B, S, 64, 64, pkg.BF16, pkg.MAP_ELU1, 0)
+    assert pkg.lib().cxxattn_linattn_workspace_bytes(C.byref(d)) == 0
+    Q, K, V = inputs(61, B, S, 64, 64)
+    O, den = run(pkg, dev, Q, K, V, B, S, pkg.MAP_ELU1, 0)
+    n = 4 * S
+    rO, rden, _ = orc.linattn_fwd(Q[:n].float().numpy(), K[:n].float().numpy(), V[:n].float().numpy(), 4, S, 64, 64,
+                                  elu=True, f64=True)
+    assert rel_err(O[:n], rO) < TOL_BF16 and rel_err(den[:n], rden) < TOL_BF16
