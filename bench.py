@@ -100,13 +100,22 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons)}
 
 
+def host_threads():
+    """All host threads this process may use (launchers such as torchrun set OMP_NUM_THREADS=1,
+    which is not what a CPU baseline should run on)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_sample(B, S, threads=None, units=None):
     """Times the CPU oracle (fp32, the reference's operation order) on `units` (batch, head) units
     of the workload, one per host thread by default.  Returns (TFLOP/s, cores, description)."""
     import numpy as np
     import oracle
     orc = oracle.Oracle()
-    cores = threads or orc.num_threads()
+    cores = threads or host_threads()
     orc.set_threads(cores)
     units = units or cores
     rng = np.random.default_rng(3)
@@ -134,7 +143,8 @@ def run_reference(args):
         import numpy as np
         import oracle
         orc = oracle.Oracle()
-        units = orc.num_threads()
+        units = host_threads()
+        orc.set_threads(units)
         rng = np.random.default_rng(3)
         q, k, v, g_ = (rng.standard_normal((units * s_len, DH)).astype(np.float32) for _ in range(4))
         t0 = time.perf_counter()
@@ -427,7 +437,8 @@ def run_ours_linattn(args):
             import numpy as np
             import oracle
             orc = oracle.Oracle()
-            units = orc.num_threads()
+            units = host_threads()
+            orc.set_threads(units)
             s_eff = min(S, 4096)
             rng = np.random.default_rng(3)
             q, k, v, g_ = (rng.standard_normal((units * s_eff, D)).astype(np.float32) for _ in range(4))
