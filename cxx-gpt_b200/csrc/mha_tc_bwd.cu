@@ -25,6 +25,9 @@
 // Three launches per call: a row pre-pass (delta = dO.O, lse in log2 units padded to whole tiles,
 // accumulator cleared), the main kernel, and a pass turning the accumulator into bf16 dQ.
 // dQ is summed with atomics, so its low bits depend on the order in which CTAs arrive.
+#include <algorithm>
+#include <cstdlib>
+
 #include "internal.cuh"
 #include "tc_common.cuh"
 
@@ -54,6 +57,7 @@ struct BwdParams {
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
     int* status;
+    int* counter;  // next work item; zero at launch
     int B, S, H, Spad;
     int64_t sb, ss, sh;
     float scale, scale_log2;
@@ -63,8 +67,8 @@ struct BwdParams {
 // accumulator row.
 __global__ void mha_tc_bwd_pre_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
                                       const float* __restrict__ lse, float* __restrict__ lse2,
-                                      float* __restrict__ delta, float* __restrict__ dq_acc, int B, int S, int H,
-                                      int Spad, int64_t sb, int64_t ss, int64_t sh) {
+                                      float* __restrict__ delta, float* __restrict__ dq_acc, int* __restrict__ counter,
+                                      int B, int S, int H, int Spad, int64_t sb, int64_t ss, int64_t sh) {
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 8;
     const int part = threadIdx.x % 8;
     if (row >= (int64_t)B * H * Spad) return;  // whole groups of 8 threads leave together
@@ -88,6 +92,7 @@ __global__ void mha_tc_bwd_pre_kernel(const __nv_bfloat16* __restrict__ O, const
     }
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (row == 0 && part == 0) *counter = 0;  // the main kernel's work-item counter
     if (part == 0) {
         delta[row] = acc;
         lse2[row] = s < S ? lse[(int64_t)bh * S + s] * 1.4426950408889634f : INFINITY;
@@ -197,12 +202,49 @@ __device__ __forceinline__ void store_rows(uint32_t taddr, __nv_bfloat16* base, 
                                 pack_bf16(__uint_as_float(o0[i + 6]) * f, __uint_as_float(o0[i + 7]) * f));
 }
 
+// One work item = one (key tile, batch*head).  Items are numbered heavy first (key tile 0 meets every
+// query tile) and handed out through a global counter, so a CTA that finishes early takes the next
+// one.  The producer thread draws the numbers and passes them to the other roles of its CTA through a
+// two-entry ring in shared memory; all roles therefore walk the same list.
+struct Item {
+    int n, bh, niter;  // key tile, batch*head, query tiles to visit (n .. ntile-1)
+};
+struct ItemRing {
+    int slot[2];
+    uint64_t full[2], empty[2];
+};
+__device__ __forceinline__ bool decode_item(int id, int ntile, int nbh, Item& w) {
+    if (id < 0 || id >= ntile * nbh) return false;
+    w.n = id / nbh;
+    w.bh = id % nbh;
+    w.niter = ntile - w.n;
+    return true;
+}
+// The k-th item of this CTA, for every role but the producer: all lanes of the warp read the entry,
+// then the warp gives it back.
+__device__ __forceinline__ bool next_item(ItemRing& ring, int k, int lane, int ntile, int nbh, Item& w,
+                                          const Guard& guard) {
+    mbar_wait(&ring.full[k & 1], (k >> 1) & 1, guard, 701);
+    const int id = *reinterpret_cast<volatile int*>(&ring.slot[k & 1]);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ring.empty[k & 1]);
+    // after a timed-out wait the ring no longer means anything: every role leaves its item loop
+    if (*reinterpret_cast<volatile int*>(guard.abort_flag)) return false;
+    return decode_item(id, ntile, nbh, w);
+}
+
+// PERSIST: CTAs draw work items from the global counter until none is left (worth it when items are
+// short: the fill and drain of the pipeline overlap between items).  Otherwise CTA i does item i and
+// the item bookkeeping folds away.
+template <bool PERSIST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t kv_full, q_full[NQ], q_free[NQ], do_full[2], s_full[2], dp_full[2], dv_done[2], dq_full[2], s_free,
-        dp_free, p_ready, ds_ready[2], dq_free, stage_free[8], all_done;
+        dp_free, p_ready, ds_ready[2], dq_free, stage_free[8], item_done, acc_free;
+    __shared__ ItemRing ring;
+    __shared__ int item_stash[16][8];  // per compute warp: what it needs of its current item only between tiles
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -218,12 +260,9 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int ntile = p.Spad / BT;
     const int nbh = p.B * p.H;
-    const int n = blockIdx.x / nbh;  // key tile; tile 0 meets every query tile, so it is scheduled first
-    const int bh = blockIdx.x % nbh;
-    const int b = bh / p.H, h = bh % p.H;
-    const int niter = ntile - n;
-    const int k0 = n * BT;
     const Guard guard{&abort_flag, p.status};
+    // Query tiles are counted through all items of the CTA: tile T (global index) uses Q stage T % NQ,
+    // dO stage / dS buffer / compute group T & 1, and every ring keeps its phase across item borders.
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -239,7 +278,8 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(&dv_done[s], 1);
             mbar_init(&dq_full[s], 1);
         }
-        mbar_init(&all_done, 1);
+        mbar_init(&item_done, 1);
+        mbar_init(&acc_free, 16);  // every compute warp, once per item
         // waited on by the MMA warp, tile after tile; one arrival per warp of the group that signals
         mbar_init(&s_free, 8);
         mbar_init(&p_ready, 8);
@@ -249,6 +289,10 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_init(&ds_ready[1], 8);
         mbar_init(&dq_free, 8);
         for (int w = 0; w < 8; w++) mbar_init(&stage_free[w], 1);
+        for (int e = 0; e < 2; e++) {
+            mbar_init(&ring.full[e], 1);
+            mbar_init(&ring.empty[e], 17);  // 16 compute warps and the MMA warp
+        }
         fence_barrier_init();
     }
     if (warp == W_MMA) tmem_alloc(&tmem_slot, TMEM_COLS);
@@ -259,8 +303,8 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (warp >= W_PROD) {
         // Warps 16-19 form one warp group; all four execute this one instruction together and hand
-        // most of their registers to the compute warps.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        // part of their registers to the compute warps.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     }
     if (warp == W_PROD) {
         // ---------------- TMA producer ----------------
@@ -269,20 +313,40 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             prefetch_tmap(&tmK);
             prefetch_tmap(&tmV);
             prefetch_tmap(&tmdO);
-            mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
-            tma_load_4d(sK, &tmK, &kv_full, 0, h, k0, b);
-            tma_load_4d(sV, &tmV, &kv_full, 0, h, k0, b);
-            for (int it = 0; it < niter; it++) {
-                const int qs = it % NQ, s = it & 1, q0 = (n + it) * BT;
-                // Q (with the row statistics) is held until dK(it) has read it; dO until dV(it) has
-                if (it >= NQ) mbar_wait(&q_free[qs], ((it / NQ) - 1) & 1, guard, 401);
-                mbar_expect_tx(&q_full[qs], TILE_BYTES + 1024);
-                tma_load_4d(sQ + qs * TILE_BYTES, &tmQ, &q_full[qs], 0, h, q0, b);
-                bulk_load_1d(sStat + qs * 256, p.lse2 + (int64_t)bh * p.Spad + q0, 512, &q_full[qs]);
-                bulk_load_1d(sStat + qs * 256 + 128, p.delta + (int64_t)bh * p.Spad + q0, 512, &q_full[qs]);
-                if (it >= 2) mbar_wait(&dv_done[s], ((it / 2) - 1) & 1, guard, 402);
-                mbar_expect_tx(&do_full[s], TILE_BYTES);
-                tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &do_full[s], 0, h, q0, b);
+            int T = 0;
+            Item w;
+            int next = PERSIST ? atomicAdd(p.counter, 1) : (int)blockIdx.x;
+            for (int k = 0; PERSIST || k == 0; k++) {
+                const int id = next;
+                const bool more = decode_item(id, ntile, nbh, w);
+                const int b = w.bh / p.H, h = w.bh % p.H;
+                if (PERSIST) {
+                    if (more) next = atomicAdd(p.counter, 1);  // drawn one item ahead: its latency is hidden
+                    if (k >= 2) mbar_wait(&ring.empty[k & 1], ((k >> 1) - 1) & 1, guard, 404);
+                    ring.slot[k & 1] = more ? id : -1;
+                    mbar_arrive(&ring.full[k & 1]);
+                }
+                if (!more || *reinterpret_cast<volatile int*>(&abort_flag)) break;
+                for (int it = 0; it < w.niter; it++, T++) {
+                    const int qs = T % NQ, s = T & 1, q0 = (w.n + it) * BT;
+                    // Q (with the row statistics) is held until dK of its tile has read it; dO until dV has
+                    if (T >= NQ) mbar_wait(&q_free[qs], ((T / NQ) - 1) & 1, guard, 401);
+                    mbar_expect_tx(&q_full[qs], TILE_BYTES + 1024);
+                    tma_load_4d(sQ + qs * TILE_BYTES, &tmQ, &q_full[qs], 0, h, q0, b);
+                    bulk_load_1d(sStat + qs * 256, p.lse2 + (int64_t)w.bh * p.Spad + q0, 512, &q_full[qs]);
+                    bulk_load_1d(sStat + qs * 256 + 128, p.delta + (int64_t)w.bh * p.Spad + q0, 512, &q_full[qs]);
+                    if (T >= 2) mbar_wait(&dv_done[s], ((T / 2) - 1) & 1, guard, 402);
+                    mbar_expect_tx(&do_full[s], TILE_BYTES);
+                    tma_load_4d(sdO + s * TILE_BYTES, &tmdO, &do_full[s], 0, h, q0, b);
+                    if (it == 0) {
+                        // K and V of this item, once every product of the item before has read the old ones
+                        // (the first Q and dO tiles above are already on their way)
+                        if (k > 0) mbar_wait(&item_done, (k - 1) & 1, guard, 403);
+                        mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
+                        tma_load_4d(sK, &tmK, &kv_full, 0, h, w.n * BT, b);
+                        tma_load_4d(sV, &tmV, &kv_full, 0, h, w.n * BT, b);
+                    }
+                }
             }
         }
     } else if (warp == W_MMA) {
@@ -311,60 +375,75 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int k = 0; k < DH / 16; k++) umma_ss_e(el, tmem + COL_DP, dV + 2 * k, g + 2 * k, IDESC_SS, k > 0);
             umma_commit_e(el, &dp_full[s]);
         };
-        mbar_wait_poll(&kv_full, 0, guard, 501);
-        mbar_wait_poll(&q_full[0], 0, guard, 502);
-        tc_fence_after();
-        issue_st(0, 0);
-        mbar_wait_poll(&do_full[0], 0, guard, 503);
-        tc_fence_after();
-        issue_dp(0);
-        int qs = 0;  // it % NQ
-        for (int it = 0; it < niter; it++) {
-            const int s = it & 1, sn = s ^ 1;
-            const int qn = qs + 1 == NQ ? 0 : qs + 1;
-            const uint64_t q = dQ0 + qs * TILE16, g = dG0 + s * TILE16;
-            const uint64_t dsk = dDSk + s * 2 * TILE16, dsm = dDSm + s * 2 * TILE16;
-            if (it + 1 < niter) {  // next scores as soon as this tile's are in registers
-                mbar_wait_poll(&q_full[qn], ((it + 1) / NQ) & 1, guard, 506);
-                mbar_wait_poll(&s_free, it & 1, guard, 504);
+        int T = 0;
+        Item w;
+        for (int k = 0; PERSIST ? next_item(ring, k, lane, ntile, nbh, w, guard)
+                                : (k == 0 && decode_item(blockIdx.x, ntile, nbh, w));
+             k++) {
+            mbar_wait_poll(&kv_full, k & 1, guard, 501);
+            {
+                // first tile of the item: its scores and dP^T need the new K and V, so they cannot be
+                // issued during the tile before, as all later ones are
+                const int s = T & 1, qs = T % NQ;
+                mbar_wait_poll(&q_full[qs], (T / NQ) & 1, guard, 502);
+                if (T > 0) mbar_wait_poll(&s_free, (T - 1) & 1, guard, 511);
                 tc_fence_after();
-                issue_st(sn, qn);
-            }
-            mbar_wait_poll(&p_ready, it & 1, guard, 505);
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < BT / 16; k++)  // dV += P^T dO_i   (A: P^T bf16 in TMEM)
-                umma_ts_e(el, tmem + COL_DV, tmem + COL_P + 8 * k, g + 128 * k, IDESC_KN, it > 0 || k > 0);
-            umma_commit_e(el, &dv_done[s]);  // P^T may be overwritten, and this dO stage refilled
-            if (it + 1 < niter) {  // next dP^T as soon as this tile's is in registers
-                mbar_wait_poll(&do_full[sn], ((it + 1) / 2) & 1, guard, 509);
-                mbar_wait_poll(&dp_free, it & 1, guard, 510);
+                issue_st(s, qs);
+                mbar_wait_poll(&do_full[s], (T >> 1) & 1, guard, 503);
+                if (T > 0) mbar_wait_poll(&dp_free, (T - 1) & 1, guard, 512);
                 tc_fence_after();
-                issue_dp(sn);
+                issue_dp(s);
             }
-            mbar_wait_poll(&ds_ready[s], (it >> 1) & 1, guard, 507);
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < BT / 16; k++)  // dK += dS^T Q_i   (A: dS in smem, rows = keys, K = queries)
-                umma_ss_e(el, tmem + COL_DK, dsk + (k / 4) * TILE16 + 2 * (k % 4), q + 128 * k, IDESC_KN, it > 0 || k > 0);
-            umma_commit_e(el, &q_free[qs]);
-            if (it > 0) {
-                mbar_wait_poll(&dq_free, (it - 1) & 1, guard, 508);
+            for (int it = 0; it < w.niter; it++, T++) {
+                const int s = T & 1, sn = s ^ 1;
+                const int qs = T % NQ, qn = (T + 1) % NQ;
+                const uint64_t q = dQ0 + qs * TILE16, g = dG0 + s * TILE16;
+                const uint64_t dsk = dDSk + s * 2 * TILE16, dsm = dDSm + s * 2 * TILE16;
+                if (it + 1 < w.niter) {  // next scores as soon as this tile's are in registers
+                    mbar_wait_poll(&q_full[qn], ((T + 1) / NQ) & 1, guard, 506);
+                    mbar_wait_poll(&s_free, T & 1, guard, 504);
+                    tc_fence_after();
+                    issue_st(sn, qn);
+                }
+                mbar_wait_poll(&p_ready, T & 1, guard, 505);
+                // dV and dK of the item before have left TMEM
+                if (it == 0 && k > 0) mbar_wait_poll(&acc_free, (k - 1) & 1, guard, 513);
                 tc_fence_after();
-            }
 #pragma unroll
-            for (int k = 0; k < BT / 16; k++)  // dQ_i = dS K       (A: the same tile read MN-major)
-                umma_ss_e(el, tmem + COL_DQ, dsm + 128 * k, dK + 128 * k, IDESC_DQ, k > 0);
-            umma_commit_e(el, &dq_full[s]);  // dQ_i is ready, and this dS buffer may be overwritten
-            qs = qn;
+                for (int kk = 0; kk < BT / 16; kk++)  // dV += P^T dO_i   (A: P^T bf16 in TMEM)
+                    umma_ts_e(el, tmem + COL_DV, tmem + COL_P + 8 * kk, g + 128 * kk, IDESC_KN, it > 0 || kk > 0);
+                umma_commit_e(el, &dv_done[s]);  // P^T may be overwritten, and this dO stage refilled
+                if (it + 1 < w.niter) {  // next dP^T as soon as this tile's is in registers
+                    mbar_wait_poll(&do_full[sn], ((T + 1) >> 1) & 1, guard, 509);
+                    mbar_wait_poll(&dp_free, T & 1, guard, 510);
+                    tc_fence_after();
+                    issue_dp(sn);
+                }
+                mbar_wait_poll(&ds_ready[s], (T >> 1) & 1, guard, 507);
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < BT / 16; kk++)  // dK += dS^T Q_i   (A: dS in smem, rows = keys, K = queries)
+                    umma_ss_e(el, tmem + COL_DK, dsk + (kk / 4) * TILE16 + 2 * (kk % 4), q + 128 * kk, IDESC_KN,
+                              it > 0 || kk > 0);
+                umma_commit_e(el, &q_free[qs]);
+                if (T > 0) {
+                    mbar_wait_poll(&dq_free, (T - 1) & 1, guard, 508);
+                    tc_fence_after();
+                }
+#pragma unroll
+                for (int kk = 0; kk < BT / 16; kk++)  // dQ_i = dS K       (A: the same tile read MN-major)
+                    umma_ss_e(el, tmem + COL_DQ, dsm + 128 * kk, dK + 128 * kk, IDESC_DQ, kk > 0);
+                umma_commit_e(el, &dq_full[s]);  // dQ_i is ready, and this dS buffer may be overwritten
+            }
+            // every product of the item: K and V may be replaced, dK and dV read out
+            umma_commit_e(el, &item_done);
         }
-        umma_commit_e(el, &all_done);
     } else if (warp > W_MMA) {
         // idle warps: they only take part in the register hand-over above
     } else {
         // The increase is served from the registers the CTA got at launch (640 threads x 96) and blocks
         // until they are there: 16 warps x 32 x (104 - 96) must not exceed what warps 16-19 gave back,
-        // 4 x 32 x (96 - 40).
+        // 4 x 32 x (96 - 56).
         asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         // ---------------- compute warps ----------------
         // Group g = warp / 8 owns the query tiles it = g, g+2, ...; inside a group, warp % 4 selects the
@@ -381,7 +460,6 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t tS = lane_base + COL_ST + 64 * c, tP = lane_base + COL_P + 32 * c;
         const uint32_t tDP = lane_base + COL_DP + 64 * c, tDQ = lane_base + COL_DQ + 32 * c;
         const int sb = warp % 8;  // staging block, shared with the same warp of the other group, drain after drain
-        float* acc_base = p.dq_acc + (int64_t)bh * p.Spad * DH + (q4 * 2 + c) * 1024;
         uint8_t* blk = sStage + sb * 4096;
         bool pending = false;  // this warp's last bulk reduction may still be reading blk
         // the staging block goes back to the other group once this warp's reduction has read it
@@ -393,8 +471,9 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             __syncwarp();  // without it lane 0 may run on its own for a long stretch
             pending = false;
         };
-        // dQ of query tile d (relative to n): rows 32*q4.., columns 32*c.., one 4 KB reduction
-        auto drain_dq = [&](int d) {
+        // dQ of the query tile with global index d (tile `qt` of batch*head `bh`): rows 32*q4.., columns
+        // 32*c.., one 4 KB reduction
+        auto drain_dq = [&](int d, int bh, int qt) {
             uint32_t d0[32];
             tmem_ld32(tDQ, d0);
             tmem_ld_wait();
@@ -407,88 +486,123 @@ mha_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     make_uint4(d0[4 * ch], d0[4 * ch + 1], d0[4 * ch + 2], d0[4 * ch + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) bulk_reduce_add_f32(acc_base + (int64_t)(n + d) * BT * DH, blk, 4096);
+            if (lane == 0)
+                bulk_reduce_add_f32(p.dq_acc + ((int64_t)bh * p.Spad + (int64_t)qt * BT) * DH + (q4 * 2 + c) * 1024, blk, 4096);
             pending = true;
         };
-        for (int it = g; it < niter; it += 2) {
-            const int ph = (it >> 1) & 1;  // phase parity of the barriers indexed by tile parity
-            const int qs = it % NQ;
-            mbar_wait(&q_full[qs], (it / NQ) & 1, guard, 601);  // lse2 / delta of this query tile are in smem
-            const float* l2 = sStat + qs * 256 + 64 * c;
-            const float* dl = l2 + 128;
-            mbar_wait(&s_full[g], ph, guard, 602);
-            tc_fence_after();
-            uint32_t pk[32];
-            {
-                // the half row of S^T goes to registers first, so the next scores can be issued while
-                // this tile's exponentials run
-                uint32_t s0[32], s1[32];
-                tmem_ld32(tS, s0);
-                tmem_ld32(tS + 32, s1);
-                tmem_ld_wait();
+        // Between tiles a warp needs little of its item; the rest (key tile, batch*head, the item
+        // before, the item count) waits in shared memory so that the tile loop keeps its registers
+        // for the score rows.
+        volatile int* stash = item_stash[warp];
+        int Tb = 0;  // global index of the first query tile of the current item
+        if (lane == 0) stash[2] = 0;
+        for (int k = 0; PERSIST || k == 0;) {
+            Item w;
+            if (PERSIST ? !next_item(ring, k, lane, ntile, nbh, w, guard) : !decode_item(blockIdx.x, ntile, nbh, w)) break;
+            const int niter = w.niter;
+            if (PERSIST) {
+                if (lane == 0) {
+                    stash[0] = w.n;
+                    stash[1] = w.bh;  // stash[2] holds the batch*head of the item before
+                    stash[3] = k;
+                    stash[4] = Tb + niter;
+                }
+                __syncwarp();
+            }
+            for (int it = (g ^ Tb) & 1; it < niter; it += 2) {  // this group's tiles: global index of parity g
+                const int T = Tb + it;
+                const int ph = (T >> 1) & 1;  // phase parity of the barriers indexed by tile parity
+                const int qs = T % NQ;
+                mbar_wait(&q_full[qs], (T / NQ) & 1, guard, 601);  // lse2 / delta of this query tile are in smem
+                const float* l2 = sStat + qs * 256 + 64 * c;
+                const float* dl = l2 + 128;
+                mbar_wait(&s_full[g], ph, guard, 602);
+                tc_fence_after();
+                uint32_t pk[32];
+                {
+                    // the half row of S^T goes to registers first, so the next scores can be issued while
+                    // this tile's exponentials run
+                    uint32_t s0[32], s1[32];
+                    tmem_ld32(tS, s0);
+                    tmem_ld32(tS + 32, s1);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    warp_arrive(&s_free, lane);
+                    release_stage();  // the other group's next drain waits for this: do it early
+                    if (it == 0) {  // the diagonal tile
+                        p_chunk<true>(s0, l2, p.scale_log2, r, 64 * c, &pk[0]);
+                        p_chunk<true>(s1, l2 + 32, p.scale_log2, r, 64 * c + 32, &pk[16]);
+                    } else {
+                        p_chunk<false>(s0, l2, p.scale_log2, r, 0, &pk[0]);
+                        p_chunk<false>(s1, l2 + 32, p.scale_log2, r, 0, &pk[16]);
+                    }
+                }
+                if (T > 0) {  // the dV product of the tile before has read its P^T
+                    mbar_wait(&dv_done[(T - 1) & 1], ((T - 1) >> 1) & 1, guard, 603);
+                    tc_fence_after();
+                }
+                tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+                tmem_st_wait();
                 tc_fence_before();
-                warp_arrive(&s_free, lane);
-                release_stage();  // the other group's next drain waits for this: do it early
-                if (it == 0) {
-                    p_chunk<true>(s0, l2, p.scale_log2, r, 64 * c, &pk[0]);
-                    p_chunk<true>(s1, l2 + 32, p.scale_log2, r, 64 * c + 32, &pk[16]);
-                } else {
-                    p_chunk<false>(s0, l2, p.scale_log2, r, 0, &pk[0]);
-                    p_chunk<false>(s1, l2 + 32, p.scale_log2, r, 0, &pk[16]);
+                warp_arrive(&p_ready, lane);
+
+                // second half: dS^T = P^T o (dP^T - delta), written over pk in place
+                {
+                    uint32_t va[32];
+                    mbar_wait(&dp_full[g], ph, guard, 613);
+                    tc_fence_after();
+                    tmem_ld32(tDP, va);
+                    tmem_ld_wait();
+                    ds_chunk(&pk[0], va, dl, &pk[0]);
+                    tmem_ld32(tDP + 32, va);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    warp_arrive(&dp_free, lane);  // dP^T of this tile is in registers
+                    ds_chunk(&pk[16], va, dl + 32, &pk[16]);
+                }
+                if (T >= 2)  // dK and dQ of this group's tile before have read this dS buffer
+                    mbar_wait(&dq_full[g], ((T - 2) >> 1) & 1, guard, 614);
+                // this thread's part of row r of dS: one 128-byte row (queries 64c..64c+63) with the 128-byte swizzle
+                uint8_t* ds_row = sDS + (g * 2 + c) * TILE_BYTES + r * 128;
+#pragma unroll
+                for (int ch = 0; ch < 8; ch++)
+                    *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) * 16)) =
+                        make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                warp_arrive(&ds_ready[g], lane);
+                if (T > 0) {  // dQ of the tile before (the other group's) leaves TMEM through this group
+                    mbar_wait(&dq_full[(T - 1) & 1], ((T - 1) >> 1) & 1, guard, 615);
+                    tc_fence_after();
+                    // that tile is this item's query tile n + it - 1, or the last one of the item before
+                    if (it > 0) drain_dq(T - 1, PERSIST ? stash[1] : w.bh, (PERSIST ? stash[0] : w.n) + it - 1);
+                    else drain_dq(T - 1, stash[2], ntile - 1);
                 }
             }
-            if (it > 0) {  // the dV product of tile it-1 has read P^T(it-1)
-                mbar_wait(&dv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 603);
-                tc_fence_after();
-            }
-            tmem_st32(tP, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
-            tmem_st_wait();
-            tc_fence_before();
-            warp_arrive(&p_ready, lane);
-
-            // second half: dS^T = P^T o (dP^T - delta), written over pk in place
-            {
-                uint32_t va[32];
-                mbar_wait(&dp_full[g], ph, guard, 613);
-                tc_fence_after();
-                tmem_ld32(tDP, va);
-                tmem_ld_wait();
-                ds_chunk(&pk[0], va, dl, &pk[0]);
-                tmem_ld32(tDP + 32, va);
-                tmem_ld_wait();
-                tc_fence_before();
-                warp_arrive(&dp_free, lane);  // dP^T(it) is in registers
-                ds_chunk(&pk[16], va, dl + 32, &pk[16]);
-            }
-            if (it >= 2)  // dK and dQ of tile it-2 have read this dS buffer
-                mbar_wait(&dq_full[g], ((it - 2) >> 1) & 1, guard, 614);
-            // this thread's part of row r of dS: one 128-byte row (queries 64c..64c+63) with the 128-byte swizzle
-            uint8_t* ds_row = sDS + (g * 2 + c) * TILE_BYTES + r * 128;
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) * 16)) =
-                    make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            warp_arrive(&ds_ready[g], lane);
-            if (it > 0) {  // dQ of the tile before (the other group's) leaves TMEM through this group
-                mbar_wait(&dq_full[(it - 1) & 1], ((it - 1) >> 1) & 1, guard, 615);
-                tc_fence_after();
-                drain_dq(it - 1);
-            }
-        }
-        release_stage();
-        // the last tile's dQ is drained by the group that did not produce it (as every other tile's)
-        if (g == (niter & 1)) {
-            mbar_wait(&dq_full[(niter - 1) & 1], ((niter - 1) >> 1) & 1, guard, 616);
+            // end of the item for this group: group 0 stores dV, group 1 stores scale * dK, and the
+            // accumulators go back to the MMA warp
+            release_stage();
+            if (PERSIST) k = stash[3];
+            const int n = PERSIST ? stash[0] : w.n, bh = PERSIST ? stash[1] : w.bh;
+            Tb = PERSIST ? stash[4] : niter;
+            mbar_wait(&item_done, k & 1, guard, 618);
             tc_fence_after();
-            drain_dq(niter - 1);
+            if (g == 0) store_rows(lane_base + COL_DV, p.dV, 1.0f, n * BT + r, 32 * c, bh / p.H, bh % p.H, p);
+            else store_rows(lane_base + COL_DK, p.dK, p.scale, n * BT + r, 32 * c, bh / p.H, bh % p.H, p);
+            tc_fence_before();
+            warp_arrive(&acc_free, lane);
+            if (lane == 0) stash[2] = bh;
+            __syncwarp();
+            k++;
+        }
+        const int prev_bh = stash[2];
+        release_stage();
+        // the very last tile's dQ is drained by the group that would own the next tile
+        if (Tb > 0 && g == (Tb & 1)) {
+            mbar_wait(&dq_full[(Tb - 1) & 1], ((Tb - 1) >> 1) & 1, guard, 616);
+            tc_fence_after();
+            drain_dq(Tb - 1, prev_bh, ntile - 1);
         }
         if (lane == 0) bulk_wait_all();
-        // epilogue: group 0 stores dV, group 1 stores scale * dK
-        mbar_wait(&all_done, 0, guard, 618);
-        tc_fence_after();
-        if (g == 0) store_rows(lane_base + COL_DV, p.dV, 1.0f, k0 + r, 32 * c, b, h, p);
-        else store_rows(lane_base + COL_DK, p.dK, p.scale, k0 + r, 32 * c, b, h, p);
     }
 
     tc_fence_before();
@@ -516,7 +630,8 @@ static size_t rows_bytes(const MhaShape& p) {
 
 size_t mha_tc_bwd_workspace(const MhaShape& p, bool have_lse) {
     const size_t rows = rows_bytes(p);
-    return 2 * rows + rows * DH + (have_lse ? 0 : align_up((size_t)p.B * p.H * p.S * sizeof(float), 256));
+    // lse2 | delta | dQ accumulator | work-item counter | (row statistics when the caller has none)
+    return 2 * rows + rows * DH + 256 + (have_lse ? 0 : align_up((size_t)p.B * p.H * p.S * sizeof(float), 256));
 }
 
 int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, const void* O, const void* dO,
@@ -532,17 +647,18 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
     float* lse2 = reinterpret_cast<float*>(base);
     float* delta = reinterpret_cast<float*>(base + rows);
     float* dq_acc = reinterpret_cast<float*>(base + 2 * rows);
+    int* counter = reinterpret_cast<int*>(base + 2 * rows + rows * DH);
     if (lse == nullptr) {
         // The reference backward recomputes the row statistics from Q and K; so does this pre-pass
         // (the forward kernel with its output store switched off).
-        float* tmp = reinterpret_cast<float*>(base + 2 * rows + rows * DH);
+        float* tmp = reinterpret_cast<float*>(base + 2 * rows + rows * DH + 256);
         const int rc = mha_tc_fwd(p, Q, K, V, nullptr, tmp, st);
         if (rc != CXXATTN_OK) return rc;
         lse = tmp;
     }
     const int64_t nrows = (int64_t)p.B * p.H * Spad;
     mha_tc_bwd_pre_kernel<<<(unsigned)((nrows + 31) / 32), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(O), static_cast<const __nv_bfloat16*>(dO), lse, lse2, delta, dq_acc, p.B,
+        static_cast<const __nv_bfloat16*>(O), static_cast<const __nv_bfloat16*>(dO), lse, lse2, delta, dq_acc, counter, p.B,
         p.S, p.H, Spad, p.sb, p.ss, p.sh);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
 
@@ -556,6 +672,7 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
     bp.lse2 = lse2; bp.delta = delta; bp.dq_acc = dq_acc;
     bp.dK = static_cast<__nv_bfloat16*>(dK);
     bp.dV = static_cast<__nv_bfloat16*>(dV);
+    bp.counter = counter;
     bp.status = status_word();
     if (bp.status == nullptr) return CXXATTN_ERR_CUDA;
     bp.B = p.B; bp.S = p.S; bp.H = p.H; bp.Spad = Spad;
@@ -566,14 +683,27 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(mha_tc_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(mha_tc_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(mha_tc_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SMEM_BYTES) != cudaSuccess)
             return CXXATTN_ERR_CUDA;
         attr_set[dev] = true;
     }
-    const int64_t grid = (int64_t)(Spad / BT) * p.B * p.H;
+    // persistent CTAs, one per SM, each walking its share of the (key tile, batch*head) items
+    static int nsm[64] = {};
+    if (dev >= 0 && dev < 64 && nsm[dev] == 0 &&
+        cudaDeviceGetAttribute(&nsm[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        nsm[dev] = 148;
+    const int64_t items = (int64_t)(Spad / BT) * p.B * p.H;
+    // Short sequences (few query tiles per item): persistent CTAs; long ones: one CTA per item, whose
+    // tile loop compiles a little tighter.  Tuning knob: CXXATTN_BWD_PERSIST=0/1 forces the choice.
+    static const int forced = [] { const char* e = std::getenv("CXXATTN_BWD_PERSIST"); return e ? std::atoi(e) : -1; }();
+    const bool persist = forced >= 0 ? forced != 0 : Spad / BT <= 32;
+    const int64_t grid = persist ? std::min<int64_t>(items, (dev >= 0 && dev < 64 && nsm[dev] > 0) ? nsm[dev] : 148) : items;
     if (g_ev_start) cudaEventRecord(g_ev_start, st);
-    mha_tc_bwd_kernel<<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);
+    if (persist) mha_tc_bwd_kernel<true><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);
+    else mha_tc_bwd_kernel<false><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);
     if (g_ev_stop) cudaEventRecord(g_ev_stop, st);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
 
