@@ -23,6 +23,8 @@
 // exponentials of step j are still running, and a softmax group never waits for its next scores.  KV tiles above the causal diagonal
 // are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
 // when it grows by more than 8 (in log2 units), so the rescaling of O in TMEM is rare.
+#include <algorithm>
+
 #include "internal.cuh"
 #include "tc_common.cuh"
 
@@ -39,7 +41,7 @@ constexpr int TILE_BYTES = BM * DH * 2;  // 16 KB: one 128 x 64 bf16 tile
 constexpr int NTHREADS = 384;  // 12 warps: 8 softmax, producer, MMA issuer, 2 idle (they only give up registers)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
-constexpr size_t SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + 1024;  // + alignment slack
+constexpr size_t SMEM_BYTES = (4 + 2 * STAGES) * TILE_BYTES + 1024;  // Q x2 (2 tiles each), K/V ring, alignment slack
 
 struct FwdParams {
     __nv_bfloat16* O;
@@ -50,35 +52,53 @@ struct FwdParams {
     float scale_log2;  // 1/sqrt(Dh) * log2(e)
 };
 
+// One work item = one pair of query tiles of one (batch, head).  Items are numbered heavy first (the
+// last pair of a sequence meets every KV tile); the persistent CTA j of P takes item j of the first
+// round, P-1-j of the second, j of the third, ..., so that every CTA gets a similar mix.  All roles of
+// a CTA walk the same list, and every ring of barriers keeps its phase across item borders, so the
+// next item's Q load and first scores overlap the last steps and the epilogue of the current one.
+struct Item {
+    int q0, bh, n0, nkv;
+    bool has_t1;
+};
+__device__ __forceinline__ bool get_item(int round, int npairs, int nbh, int S, Item& w) {
+    const int P = gridDim.x, j = blockIdx.x;
+    const int id = round * P + ((round & 1) ? P - 1 - j : j);
+    if (id >= npairs * nbh) return false;
+    const int pair = npairs - 1 - id / nbh;
+    w.bh = id % nbh;
+    w.q0 = pair * 2 * BM;
+    w.has_t1 = w.q0 + BM < S;
+    w.n0 = w.q0 / BN;  // diagonal KV tile of query tile 0
+    w.nkv = w.has_t1 ? w.n0 + 2 : w.n0 + 1;
+    return true;
+}
+
 __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], s_free[2], p_full[2],
-        pv_done[2];
+    __shared__ uint64_t q_full[2], q_free[2], k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[2], s_free[2],
+        p_full[2], pv_done[2], o_free[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;                                // 2 tiles
-    uint8_t* sK = smem + 2 * TILE_BYTES;               // STAGES tiles
-    uint8_t* sV = smem + (2 + STAGES) * TILE_BYTES;    // STAGES tiles
+    uint8_t* sQ = smem;                                // 2 buffers x 2 tiles
+    uint8_t* sK = smem + 4 * TILE_BYTES;               // STAGES tiles
+    uint8_t* sV = smem + (4 + STAGES) * TILE_BYTES;    // STAGES tiles
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
     const int nbh = p.B * p.H;
-    const int pair = npairs - 1 - (int)(blockIdx.x / nbh);  // longest CTAs first
-    const int bh = blockIdx.x % nbh;
-    const int b = bh / p.H, h = bh % p.H;
-    const int q0 = pair * 2 * BM;
-    const bool has_t1 = q0 + BM < p.S;
-    const int n0 = q0 / BN;                  // diagonal KV tile of query tile 0
-    const int nkv = has_t1 ? n0 + 2 : n0 + 1;
     const Guard guard{&abort_flag, p.status};
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        mbar_init(&q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&q_full[s], 1);
+            mbar_init(&q_free[s], 1);
+        }
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
@@ -87,8 +107,9 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int t = 0; t < 2; t++) {
             mbar_init(&s_full[t], 1);
             mbar_init(&s_free[t], 4);  // one arrival per softmax warp
-            mbar_init(&p_full[t], 4);  // one arrival per softmax warp
+            mbar_init(&p_full[t], 4);
             mbar_init(&pv_done[t], 1);
+            mbar_init(&o_free[t], 4);  // the output accumulator has been read out (once per item)
         }
         fence_barrier_init();
     }
@@ -110,101 +131,135 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             prefetch_tmap(&tmQ);
             prefetch_tmap(&tmK);
             prefetch_tmap(&tmV);
-            mbar_expect_tx(&q_full, 2 * TILE_BYTES);
-            tma_load_4d(sQ, &tmQ, &q_full, 0, h, q0, b);
-            tma_load_4d(sQ + TILE_BYTES, &tmQ, &q_full, 0, h, q0 + BM, b);
-            for (int j = 0; j < nkv; j++) {
-                const int s = j % STAGES;
-                if (j >= STAGES) mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, guard, 101);
-                mbar_expect_tx(&k_full[s], TILE_BYTES);
-                tma_load_4d(sK + s * TILE_BYTES, &tmK, &k_full[s], 0, h, j * BN, b);
-                mbar_expect_tx(&v_full[s], TILE_BYTES);
-                tma_load_4d(sV + s * TILE_BYTES, &tmV, &v_full[s], 0, h, j * BN, b);
+            int J = 0;  // KV steps so far, over all items: the ring stage is J % STAGES
+            Item w;
+            for (int k = 0; get_item(k, npairs, nbh, p.S, w); k++) {
+                const int b = w.bh / p.H, h = w.bh % p.H, qb = k & 1;
+                // the scores of the item two before have read this Q buffer
+                if (k >= 2) mbar_wait(&q_free[qb], ((k >> 1) - 1) & 1, guard, 102);
+                mbar_expect_tx(&q_full[qb], 2 * TILE_BYTES);
+                tma_load_4d(sQ + qb * 2 * TILE_BYTES, &tmQ, &q_full[qb], 0, h, w.q0, b);
+                tma_load_4d(sQ + (qb * 2 + 1) * TILE_BYTES, &tmQ, &q_full[qb], 0, h, w.q0 + BM, b);
+                for (int j = 0; j < w.nkv; j++, J++) {
+                    const int s = J % STAGES;
+                    if (J >= STAGES) mbar_wait(&kv_empty[s], ((J / STAGES) - 1) & 1, guard, 101);
+                    mbar_expect_tx(&k_full[s], TILE_BYTES);
+                    tma_load_4d(sK + s * TILE_BYTES, &tmK, &k_full[s], 0, h, j * BN, b);
+                    mbar_expect_tx(&v_full[s], TILE_BYTES);
+                    tma_load_4d(sV + s * TILE_BYTES, &tmV, &v_full[s], 0, h, j * BN, b);
+                }
             }
         }
     } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         // the whole warp runs the loop (uniform control flow and operands); one elected lane issues
-        {
-            const uint32_t el = elect_one();
-            constexpr uint32_t IDESC_S = idesc_bf16(BM, BN, 0, 0);  // Q, K both K-major
-            constexpr uint32_t IDESC_O = idesc_bf16(BM, DH, 0, 1);  // P from TMEM, V MN-major
-            // Descriptors are built once; a K step or a ring stage only adds a constant to the
-            // 14-bit start-address field (units of 16 bytes), which cannot carry out of it.
-            const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16);
-            const uint64_t dK0 = smem_desc_sw128(smem_u32(sK), 16);
-            const uint64_t dV0 = smem_desc_sw128(smem_u32(sV), 0);
-            constexpr uint64_t TILE16 = TILE_BYTES >> 4;
-            auto issue_s = [&](int t, int s) {
-                const uint64_t qd = dQ0 + t * TILE16, kd = dK0 + s * TILE16;
-                const uint32_t d = tmem + COL_S + t * BN;
+        const uint32_t el = elect_one();
+        constexpr uint32_t IDESC_S = idesc_bf16(BM, BN, 0, 0);  // Q, K both K-major
+        constexpr uint32_t IDESC_O = idesc_bf16(BM, DH, 0, 1);  // P from TMEM, V MN-major
+        // Descriptors are built once; a K step or a ring stage only adds a constant to the
+        // 14-bit start-address field (units of 16 bytes), which cannot carry out of it.
+        const uint64_t dQ0 = smem_desc_sw128(smem_u32(sQ), 16);
+        const uint64_t dK0 = smem_desc_sw128(smem_u32(sK), 16);
+        const uint64_t dV0 = smem_desc_sw128(smem_u32(sV), 0);
+        constexpr uint64_t TILE16 = TILE_BYTES >> 4;
+        auto issue_s = [&](int t, int s, int qb) {
+            const uint64_t qd = dQ0 + (qb * 2 + t) * TILE16, kd = dK0 + s * TILE16;
+            const uint32_t d = tmem + COL_S + t * BN;
 #pragma unroll
-                for (int k = 0; k < DH / 16; k++) umma_ss_e(el, d, qd + 2 * k, kd + 2 * k, IDESC_S, k > 0);
-                umma_commit_e(el, &s_full[t]);
-            };
-            auto issue_pv = [&](int t, int s, bool acc) {
-                const uint64_t vd = dV0 + s * TILE16;
-                const uint32_t d = tmem + COL_O + t * DH, a = tmem + COL_P + t * 64;
-                umma_ts_e(el, d, a, vd, IDESC_O, acc);
+            for (int kk = 0; kk < DH / 16; kk++) umma_ss_e(el, d, qd + 2 * kk, kd + 2 * kk, IDESC_S, kk > 0);
+            umma_commit_e(el, &s_full[t]);
+        };
+        auto issue_pv = [&](int t, int s, bool acc) {
+            const uint64_t vd = dV0 + s * TILE16;
+            const uint32_t d = tmem + COL_O + t * DH, a = tmem + COL_P + t * 64;
+            umma_ts_e(el, d, a, vd, IDESC_O, acc);
 #pragma unroll
-                for (int k = 1; k < BN / 16; k++) umma_ts_e(el, d, a + 8 * k, vd + 128 * k, IDESC_O, true);
-            };
-            const int last0 = n0, last1 = n0 + 1;  // last KV tile of each query tile
-            mbar_wait_poll(&q_full, 0, guard, 201);
-            mbar_wait_poll(&k_full[0], 0, guard, 202);
+            for (int kk = 1; kk < BN / 16; kk++) umma_ts_e(el, d, a + 8 * kk, vd + 128 * kk, IDESC_O, true);
+        };
+        int J = 0;             // KV steps so far (ring position)
+        int c0 = 0, c1 = 0;    // steps so far of query tile 0 / 1 (phases of their barriers)
+        int i0 = 0, i1 = 0;    // items so far in which tile 0 / 1 took part
+        Item w;
+        for (int k = 0; get_item(k, npairs, nbh, p.S, w); k++) {
+            const int qb = k & 1;
+            const int last0 = w.n0;  // last KV tile of query tile 0; tile 1 runs to nkv - 1
+            mbar_wait_poll(&q_full[qb], (k >> 1) & 1, guard, 201);
+            mbar_wait_poll(&k_full[J % STAGES], (J / STAGES) & 1, guard, 202);
+            // first scores of the item, as soon as the last ones of the item before have been read
+            if (c0 > 0) mbar_wait_poll(&s_free[0], (c0 - 1) & 1, guard, 209);
             tc_fence_after();
-            issue_s(0, 0);
-            if (has_t1) issue_s(1, 0);
-            for (int j = 0; j < nkv; j++) {
-                const int s = j % STAGES, sn = (j + 1) % STAGES;
-                const bool more = j + 1 < nkv;
-                if (more) {
+            issue_s(0, J % STAGES, qb);
+            if (w.has_t1) {
+                if (c1 > 0) mbar_wait_poll(&s_free[1], (c1 - 1) & 1, guard, 210);
+                tc_fence_after();
+                issue_s(1, J % STAGES, qb);
+            }
+            if (w.nkv == 1) umma_commit_e(el, &q_free[qb]);
+            for (int j = 0; j < w.nkv; j++) {
+                const int s = (J + j) % STAGES, sn = (J + j + 1) % STAGES;
+                if (j + 1 < w.nkv) {
                     // next scores of both tiles as soon as this step's have been read into registers
-                    mbar_wait_poll(&k_full[sn], ((j + 1) / STAGES) & 1, guard, 205);
+                    mbar_wait_poll(&k_full[sn], ((J + j + 1) / STAGES) & 1, guard, 205);
                     if (j + 1 <= last0) {
-                        mbar_wait_poll(&s_free[0], j & 1, guard, 207);
+                        mbar_wait_poll(&s_free[0], (c0 + j) & 1, guard, 207);
                         tc_fence_after();
-                        issue_s(0, sn);
+                        issue_s(0, sn, qb);
                     }
-                    if (has_t1) {
-                        mbar_wait_poll(&s_free[1], j & 1, guard, 208);
+                    if (w.has_t1) {
+                        mbar_wait_poll(&s_free[1], (c1 + j) & 1, guard, 208);
                         tc_fence_after();
-                        issue_s(1, sn);
+                        issue_s(1, sn, qb);
                     }
+                    if (j + 2 == w.nkv) umma_commit_e(el, &q_free[qb]);  // the item's last scores are issued
                 }
-                mbar_wait_poll(&v_full[s], (j / STAGES) & 1, guard, 203);
+                mbar_wait_poll(&v_full[s], ((J + j) / STAGES) & 1, guard, 203);
                 if (j <= last0) {
-                    mbar_wait_poll(&p_full[0], j & 1, guard, 204);
+                    mbar_wait_poll(&p_full[0], (c0 + j) & 1, guard, 204);
+                    // the output of the item before has left the accumulator
+                    if (j == 0 && i0 > 0) mbar_wait_poll(&o_free[0], (i0 - 1) & 1, guard, 211);
                     tc_fence_after();
                     issue_pv(0, s, j > 0);
                     umma_commit_e(el, &pv_done[0]);
                 }
-                if (has_t1) {
-                    mbar_wait_poll(&p_full[1], j & 1, guard, 206);
+                if (w.has_t1) {
+                    mbar_wait_poll(&p_full[1], (c1 + j) & 1, guard, 206);
+                    if (j == 0 && i1 > 0) mbar_wait_poll(&o_free[1], (i1 - 1) & 1, guard, 212);
                     tc_fence_after();
                     issue_pv(1, s, j > 0);
                     umma_commit_e(el, &pv_done[1]);
                 }
                 umma_commit_e(el, &kv_empty[s]);
             }
+            J += w.nkv;
+            c0 += last0 + 1;
+            i0++;
+            if (w.has_t1) {
+                c1 += w.nkv;
+                i1++;
+            }
         }
     } else if (warp >= 10) {
         // idle warps: they only take part in the register hand-over above
     } else {
         // ---------------- softmax groups ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        // served from what warps 8-11 gave back: 8 warps x 32 x (224 - 168) <= 4 x 32 x (168 - 40); a larger
+        // request would block forever
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int t = warp / 4;
         const int r = (warp % 4) * 32 + lane;  // row inside the tile == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
         const uint32_t tS = lane_base + COL_S + t * BN;
         const uint32_t tO = lane_base + COL_O + t * DH;
         const uint32_t tP = lane_base + COL_P + t * 64;
-        const int jlast = n0 + t;
-        const bool active = t == 0 || has_t1;
-        float m = -INFINITY, l = 0.f;
-        if (active) {
+        int ct = 0;  // steps so far of this group's query tile, over all items (phases of its barriers)
+        Item w;
+        for (int k = 0; get_item(k, npairs, nbh, p.S, w); k++) {
+            if (t == 1 && !w.has_t1) continue;  // a ragged last pair has no second tile
+            const int jlast = w.n0 + t;
+            float m = -INFINITY, l = 0.f;
             for (int j = 0; j <= jlast; j++) {
-                mbar_wait(&s_full[t], j & 1, guard, 301 + t);
+                const int cj = ct + j;
+                mbar_wait(&s_full[t], cj & 1, guard, 301 + t);
                 tc_fence_after();
                 const bool diag = j == jlast;
                 // The whole row of scores goes to registers at once, and the score columns are handed
@@ -238,7 +293,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const float m_use = raise ? m_new : m;
                 const float alpha = raise ? ex2(m - m_new) : 1.0f;
                 if (j > 0) {
-                    mbar_wait(&pv_done[t], (j - 1) & 1, guard, 305 + t);  // O_t stable, P_t free
+                    mbar_wait(&pv_done[t], (cj - 1) & 1, guard, 305 + t);  // O_t stable, P_t free
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, raise)) {
                         uint32_t o0[32], o1[32];
@@ -254,6 +309,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         tmem_st32(tO + 32, o1);
                     }
                 }
+                // (j == 0: P_t is free since the epilogue of the item before waited for its last PV)
                 m = m_use;
                 // pass 2: P = exp2(c*S - m) as bf16 pairs (masked scores are -inf and give 0)
                 float rs = 0.f;
@@ -278,15 +334,21 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_full[t]);
             }
-            // epilogue: O_t / l -> bf16 -> global; lse
-            mbar_wait(&pv_done[t], jlast & 1, guard, 311 + t);
+            // epilogue: O_t / l -> bf16 -> global; lse.  The accumulator goes back to the MMA warp as
+            // soon as it is in registers.
+            mbar_wait(&pv_done[t], (ct + jlast) & 1, guard, 311 + t);
             tc_fence_after();
-            const int qr = q0 + t * BM + r;
+            ct += jlast + 1;
+            const int qr = w.q0 + t * BM + r;
             const float inv = 1.0f / l;
             uint32_t o[2][32];
             tmem_ld32(tO, o[0]);
             tmem_ld32(tO + 32, o[1]);
             tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free[t]);
+            const int b = w.bh / p.H, h = w.bh % p.H;
             if (qr < p.S && p.O != nullptr) {
                 uint4* dst = reinterpret_cast<uint4*>(p.O + (int64_t)b * p.sb + (int64_t)qr * p.ss + (int64_t)h * p.sh);
 #pragma unroll
@@ -300,10 +362,8 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         v.w = pack_bf16(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
                         dst[(c * 32 + i) / 8] = v;
                     }
-                }
-            if (qr < p.S) {
-                if (p.lse != nullptr) p.lse[(int64_t)bh * p.S + qr] = (m + log2f(l)) * 0.6931471805599453f;
             }
+            if (qr < p.S && p.lse != nullptr) p.lse[(int64_t)w.bh * p.S + qr] = (m + log2f(l)) * 0.6931471805599453f;
         }
     }
 
@@ -348,8 +408,14 @@ int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, v
             return CXXATTN_ERR_CUDA;
         attr_set[dev] = true;
     }
+    // persistent CTAs, one per SM, each walking its share of the (query-tile pair, batch*head) items
+    static int nsm[64] = {};
+    if (dev >= 0 && dev < 64 && nsm[dev] == 0 &&
+        cudaDeviceGetAttribute(&nsm[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        nsm[dev] = 148;
     const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
-    const int64_t grid = (int64_t)npairs * p.B * p.H;
+    const int64_t items = (int64_t)npairs * p.B * p.H;
+    const int64_t grid = std::min<int64_t>(items, (dev >= 0 && dev < 64 && nsm[dev] > 0) ? nsm[dev] : 148);
     mha_tc_fwd_kernel<<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
     return check_launch();
 }
