@@ -17,10 +17,14 @@
 //   dQ_i = dS K                    (SS MMA: dS read MN-major), drained from TMEM through shared memory
 //                                  with one bulk reduce-add per warp into an fp32 accumulator
 //
-// Two compute warp groups take the query tiles alternately (group 0 the even ones, group 1 the odd
-// ones) and each does both halves of its tile, so P^T never has to be read back; the MMA warp issues
-// S^T(i+1) and dP^T(i+1) as soon as tile i's have been read out of TMEM, so one group is in the
-// first half of tile i+1 while the other is in the second half of tile i.
+// 16 compute warps in two groups take the query tiles alternately (by the parity of the tile's running
+// index); inside a group a warp owns 32 key rows (its TMEM lanes) and one half of the 128 query
+// columns, and does both halves of the tile's work on them, so P^T never has to be read back; the MMA
+// warp issues S^T(i+1) and dP^T(i+1) as soon as tile i's have been read out of TMEM, so one group is in
+// the first half of tile i+1 while the other is in the second half of tile i.  For sequences of up to
+// 32 tiles the CTAs are persistent (one per SM) and draw (key tile, batch*head) items from a global
+// counter; the rings of barriers keep their phase across items, so the next item's first loads and
+// the epilogue of the current one overlap instead of paying the pipeline's fill and drain per CTA.
 //
 // Three launches per call: a row pre-pass (delta = dO.O, lse in log2 units padded to whole tiles,
 // accumulator cleared), the main kernel, and a pass turning the accumulator into bf16 dQ.

@@ -5,11 +5,13 @@
 // dtype BF16.  Where the reference gives one warp one query row and walks the keys one at a
 // time with shuffle reductions, this kernel is a FlashAttention pipeline:
 //
-//   CTA  = 2 query tiles of 128 rows (rows q0 .. q0+255 of one (batch, head)), 10 warps:
+//   CTA  = persistent, one per SM; a work item = 2 query tiles of 128 rows (rows q0 .. q0+255 of one
+//          (batch, head)); 12 warps:
 //          warps 0-3  softmax group of tile 0  (thread i <-> query row i <-> TMEM lane i)
 //          warps 4-7  softmax group of tile 1
-//          warp  8    TMA producer: Q once, then K/V tiles of 128 keys through a 3-stage ring
-//          warp  9    MMA issuer (one elected thread) and TMEM owner
+//          warp  8    TMA producer: Q of the item (two buffers, so the next item's Q is already
+//                     there), then K/V tiles of 128 keys through a 3-stage ring
+//          warp  9    MMA issuer (the warp runs uniformly, one elected lane issues) and TMEM owner
 //          warps 10-11 idle; with warps 8-9 they release registers to the softmax warps (setmaxnreg)
 //   TMEM = S0 | S1 (128 fp32 columns each) | O0 | O1 (64 columns each) | P0 | P1 (128 bf16 = 64
 //          columns each): all 512 columns.  P feeds the PV product directly from TMEM.
