@@ -313,23 +313,32 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
                 // (j == 0: P_t is free since the epilogue of the item before waited for its last PV)
                 m = m_use;
-                // pass 2: P = exp2(c*S - m) as bf16 pairs (masked scores are -inf and give 0)
-                float rs = 0.f;
+                // pass 2: P = exp2(c*S - m) as bf16 pairs (masked scores are -inf and give 0); the
+                // arguments and the row sum are formed two at a time in packed fp32
+                const uint64_t c2 = pack2(p.scale_log2, p.scale_log2), m2 = pack2(-m_use, -m_use);
+                uint64_t rs2 = pack2(0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
                     uint32_t pk[32];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const float a0 = ex2(fmaf(__uint_as_float(sv[2 * c][i]), p.scale_log2, -m_use));
-                        const float a1 = ex2(fmaf(__uint_as_float(sv[2 * c][i + 1]), p.scale_log2, -m_use));
-                        const float b0 = ex2(fmaf(__uint_as_float(sv[2 * c + 1][i]), p.scale_log2, -m_use));
-                        const float b1 = ex2(fmaf(__uint_as_float(sv[2 * c + 1][i + 1]), p.scale_log2, -m_use));
-                        rs += (a0 + a1) + (b0 + b1);
+                        float a0, a1, b0, b1;
+                        unpack2(fma2(pack2(__uint_as_float(sv[2 * c][i]), __uint_as_float(sv[2 * c][i + 1])), c2, m2), a0, a1);
+                        unpack2(fma2(pack2(__uint_as_float(sv[2 * c + 1][i]), __uint_as_float(sv[2 * c + 1][i + 1])), c2, m2),
+                                b0, b1);
+                        a0 = ex2(a0);
+                        a1 = ex2(a1);
+                        b0 = ex2(b0);
+                        b1 = ex2(b1);
+                        rs2 = add2(rs2, add2(pack2(a0, a1), pack2(b0, b1)));
                         pk[i / 2] = pack_bf16(a0, a1);
                         pk[16 + i / 2] = pack_bf16(b0, b1);
                     }
                     tmem_st32(tP + 32 * c, pk);
                 }
+                float rs, rs_hi;
+                unpack2(rs2, rs, rs_hi);
+                rs += rs_hi;
                 l = l * alpha + rs;
                 tmem_st_wait();
                 tc_fence_before();
