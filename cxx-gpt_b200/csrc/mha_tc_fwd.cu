@@ -288,7 +288,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     for (int c = 0; c < 4; c++)
 #pragma unroll
                         for (int i = 0; i < 32; i += 2)
-                            mx = fmaxf(mx, fmaxf(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])));
+                            mx = max3(mx, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
                 }
                 const float m_new = fmaxf(m, mx * p.scale_log2);
                 const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
