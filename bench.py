@@ -247,7 +247,7 @@ def run_ours(args):
     pkg.set_timing_events(None, None)
 
     # ---- end to end: host buffers in, host buffers out, through the C-ABI host entry point ----
-    plan = pkg.HostPlan(B, S, H, DH, pkg.BF16, max(1, B // 8))
+    plan = pkg.HostPlan(B, S, H, DH, pkg.BF16, max(1, B // 16))  # 16 chunks: short pipeline fill and drain
     for _ in range(2):
         plan.fwd_bwd(hQ, hK, hV, hdO, hO, hdQ, hdK, hdV)
     barrier()

@@ -47,7 +47,7 @@ int cxxattn_host_plan_create(cxxattn_host_plan** out, const cxxattn_mha_desc* de
     p->desc = *desc;
     p->chunk_b = batch_per_chunk > desc->B ? (int)desc->B : batch_per_chunk;
     const int nchunks = (int)((desc->B + p->chunk_b - 1) / p->chunk_b);
-    p->nslots = nchunks < 3 ? nchunks : 3;
+    p->nslots = nchunks < 4 ? nchunks : 4;
     p->elem = desc->dtype == CXXATTN_BF16 ? 2 : 4;
     p->chunk_elems = (size_t)p->chunk_b * desc->S * desc->H * desc->Dh;
     cxxattn_mha_desc cd = *desc;
