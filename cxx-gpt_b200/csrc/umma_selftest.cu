@@ -26,7 +26,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;             // 2 tiles (mode 2 uses both)
     uint8_t* sB = smem + 2 * TILE;  // 1 tile
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, r = threadIdx.x;
+    const int warp = threadIdx.x / 32, r = threadIdx.x;
     const Guard guard{&abort_flag, status};
 
     if (threadIdx.x == 0) {
