@@ -23,7 +23,7 @@ SYMBOLS = [
     "cxxattn_linattn_workspace_bytes", "cxxattn_linattn_fwd", "cxxattn_linattn_bwd_step1",
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
-    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_selftest_umma",
+    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_cast", "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
 ]

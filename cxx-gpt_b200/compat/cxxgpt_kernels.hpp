@@ -6,6 +6,12 @@
 #pragma once
 #include "TensorN.hpp"
 
+// Not in the reference: lets the kept fp32 softmax signatures run on the bf16 tensor-core kernels
+// (head dimension 64; tolerance 2e-2 instead of 1e-5).  Default: off, or CXXATTN_COMPAT_PRECISION=tensorcore.
+namespace cxxattn_compat {
+void set_tensorcore(bool on);
+}
+
 namespace two_stage_cuda {
 using TensorN::CudaTensor;
 typedef const CudaTensor<float>& In;

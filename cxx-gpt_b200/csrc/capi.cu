@@ -182,6 +182,11 @@ int cxxattn_selftest_umma(int mode, const void* A, const void* B, float* D, cxxa
     return umma_selftest(mode, A, B, D, static_cast<cudaStream_t>(stream));
 }
 
+int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cxxattn_stream_t stream) {
+    if (!src || !dst || n == 0) return CXXATTN_ERR_INVALID;
+    return cast(src, src_dtype, dst, dst_dtype, n, static_cast<cudaStream_t>(stream));
+}
+
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {
     if (!A || !C || n == 0) return CXXATTN_ERR_INVALID;
     return gelu_exact(A, C, n, deriv != 0, static_cast<cudaStream_t>(stream));

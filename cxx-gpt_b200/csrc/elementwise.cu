@@ -115,6 +115,42 @@ int rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t hd, float sign
     return check_launch();
 }
 
+// fp32 <-> bf16, four elements per thread where the count allows
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n / 4; i += stride) {
+        const float4 v = reinterpret_cast<const float4*>(src)[i];
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        reinterpret_cast<uint2*>(dst)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+    for (size_t i = n / 4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dst[i] = __float2bfloat16_rn(src[i]);
+}
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n / 4; i += stride) {
+        const uint2 v = reinterpret_cast<const uint2*>(src)[i];
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+        reinterpret_cast<float4*>(dst)[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
+    }
+    for (size_t i = n / 4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dst[i] = __bfloat162float(src[i]);
+}
+
+int cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cudaStream_t st) {
+    if (reinterpret_cast<uintptr_t>(src) % 16 || reinterpret_cast<uintptr_t>(dst) % 16) return CXXATTN_ERR_ALIGNMENT;
+    if (src_dtype == CXXATTN_F32 && dst_dtype == CXXATTN_BF16)
+        cast_f32_bf16_kernel<<<flat_grid(n / 4 + 1), 256, 0, st>>>(static_cast<const float*>(src),
+                                                                  static_cast<__nv_bfloat16*>(dst), n);
+    else if (src_dtype == CXXATTN_BF16 && dst_dtype == CXXATTN_F32)
+        cast_bf16_f32_kernel<<<flat_grid(n / 4 + 1), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(src),
+                                                                  static_cast<float*>(dst), n);
+    else
+        return CXXATTN_ERR_UNSUPPORTED;
+    return check_launch();
+}
+
 int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st) {
     gelu_kernel<<<flat_grid(n), 256, 0, st>>>(A, C, n, deriv);
     return check_launch();

@@ -176,6 +176,10 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
 /* erf-GELU (deriv=0) and its derivative (deriv=1).  two_stage_cuda::gelu_exact /
  * gelu_exact_deriv (ts.cuh:84-85, ts.cu:1888-1924). */
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream);
+/* Dense element-wise conversion between CXXATTN_F32 and CXXATTN_BF16 (round to nearest even), for
+ * callers that hold the reference's fp32 tensors and want the tensor-core kernels; 16-byte aligned
+ * pointers. */
+int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cxxattn_stream_t stream);
 
 /* ---- host-buffer entry points ------------------------------------------------------------- */
 

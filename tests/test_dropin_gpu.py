@@ -36,3 +36,31 @@ def test_reference_kernel_test_program_passes_on_this_library():
         if not (v == v and v < limit):
             bad.append((name, val))
     assert not bad, (bad, out.stdout)
+
+
+def test_reference_kernel_test_program_in_tensorcore_mode():
+    """The same unmodified program with the adapter's opt-in switch: the fp32 signatures of the softmax
+    attention run on the bf16 tensor-core kernels where the head dimension is 64 (the "big S=256"
+    block); everything else stays on the exact path.  Inputs there are uniform in [-1, 1] (outputs and
+    gradients of order one), so 2e-2 absolute is the bf16 bar."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "kernel_test_dropin")
+    if not os.path.exists(exe):
+        import oracle
+        if oracle.build.build_dropin_kernel_test() is None:
+            pytest.skip("kernel_test_dropin not built and reference tree not mounted")
+    env = dict(os.environ, CXXATTN_COMPAT_PRECISION="tensorcore")
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = re.findall(r"^(.*\S)\s+maxdiff\s*=\s*([-+0-9.eE]+|nan|inf)\s*$", out.stdout, flags=re.M)
+    assert len(lines) == 34, out.stdout
+    big = [(n, float(v)) for n, v in lines if n.startswith("big S=256")]
+    assert len(big) == 4, lines
+    for name, v in big:
+        # above the fp32 path's error (so the tensor-core kernels really ran), below the bf16 bar
+        assert 2e-5 < v < 2e-2, (name, v)
+    for name, val in lines:
+        if name.startswith("big S=256"):
+            continue
+        v = float(val)
+        limit = 1e-2 if name.split()[-1] == "den" else 2e-5
+        assert v == v and v < limit, (name, val)
