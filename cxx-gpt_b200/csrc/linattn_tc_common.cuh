@@ -18,17 +18,18 @@ __device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v <<
 __device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 __device__ __forceinline__ float phi1(float a) { return a > 0.f ? a + 1.f : ex2(a * 1.4426950408889634f); }
 __device__ __forceinline__ float dphi1(float a) { return a > 0.f ? 1.f : ex2(a * 1.4426950408889634f); }
-// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e).  The product x*log2(e) is
-// rounded to bf16 before the exponential (relative effect ln2*|t|*2^-9 on values that are then
-// rounded to bf16 anyway); one MUFU operation serves two elements.
+// phi on a bf16 pair in packed arithmetic: x > 0 ? x + 1 : 2^(x log2 e), written without a select as
+// max(x, 0) + 2^(min(x, 0) log2 e) (for x > 0 the second term is exactly 1, for x <= 0 the first is
+// exactly 0).  The product with log2(e) is rounded to bf16 before the exponential (relative effect
+// ln2*|t|*2^-9 on values that are then rounded to bf16 anyway).
 __device__ __forceinline__ uint32_t phi2(uint32_t v) {
     const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&v);
-    const __nv_bfloat162 t = __hmul2(x, __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
+    const __nv_bfloat162 zero = __floats2bfloat162_rn(0.f, 0.f);
+    const __nv_bfloat162 t = __hmul2(__hmin2(x, zero), __floats2bfloat162_rn(1.4426950408889634f, 1.4426950408889634f));
     uint32_t e;
     asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(e) : "r"(*reinterpret_cast<const uint32_t*>(&t)));
-    const __nv_bfloat162 pos = __hadd2(x, __floats2bfloat162_rn(1.f, 1.f));
-    const uint32_t m = __hgt2_mask(x, __floats2bfloat162_rn(0.f, 0.f));  // 0xffff per half where x > 0
-    return (*reinterpret_cast<const uint32_t*>(&pos) & m) | (e & ~m);
+    const __nv_bfloat162 r = __hadd2(__hmax2(x, zero), *reinterpret_cast<const __nv_bfloat162*>(&e));
+    return *reinterpret_cast<const uint32_t*>(&r);
 }
 
 // In-place feature map of one 128-byte tile row (element order does not matter).

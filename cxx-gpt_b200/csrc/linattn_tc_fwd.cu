@@ -29,8 +29,8 @@ namespace {
 using namespace tc;
 using namespace lintc;
 
-constexpr int NSTAGE = 2;
-constexpr int NTHREADS = 320;  // 4 compute warps, TMA producer, MMA issuer, 4 feature-map warps
+constexpr int NSTAGE = 3;  // the feature-map warps work up to two chunks ahead of the products
+constexpr int NTHREADS = 512;  // 4 compute warps, TMA producer, MMA issuer, 8 feature-map warps (4 for Q, 4 for K), 2 idle
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_A = 0, COL_P = 128, COL_O = 192, COL_SX = 288;
 // per stage Q | K | V, then the ones tile, then the bf16 state operand (2 blocks of 64 rows x 128 B)
@@ -50,9 +50,10 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, LinFwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, a_full, p_ready, o_full, o_free, s_done, sprev_ready;
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped[NSTAGE], a_full, p_ready, o_full, o_free, s_done, sprev_ready;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ float s_rowsum[2][CH];  // row sums of the masked A, from the compute warps to the output warps
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     auto sQ = [&](int st) { return smem + (st * 3 + 0) * TILE_BYTES; };
@@ -76,9 +77,9 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(&a_full, 1);
         mbar_init(&o_full, 1);
         mbar_init(&s_done, 1);
-        mbar_init(&mapped, 4);  // one arrival per compute warp
+        for (int s = 0; s < NSTAGE; s++) mbar_init(&mapped[s], 8);  // one arrival per feature-map warp
         mbar_init(&p_ready, 4);
-        mbar_init(&o_free, 4);
+        mbar_init(&o_free, 8);  // the eight output (feature-map) warps
         mbar_init(&sprev_ready, 4);
         fence_barrier_init();
     }
@@ -94,6 +95,11 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+
+    // Register budget (512 threads x 128 at launch): the compute warps hold whole score rows, every
+    // other warp group gives registers back.  The increase blocks until they are there:
+    // 4 x 32 x (208 - 128) <= 12 x 32 x (128 - 96).
+    if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
 
     if (warp == 4) {
         // ---------------- TMA producer ----------------
@@ -130,7 +136,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const uint64_t dV = smem_desc_sw128(smem_u32(sV(st)), 0);
                 // [V | 1]: the second block of 64 columns is the ones tile
                 const uint64_t dV1 = smem_desc_sw128(smem_u32(sV(st)), smem_u32(sOnes) - smem_u32(sV(st)));
-                mbar_wait_poll(&mapped, c & 1, guard, 711);
+                mbar_wait_poll(&mapped[st], (c / NSTAGE) & 1, guard, 711);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + COL_A, dQ + 2 * k, dK + 2 * k, IDESC_A, k > 0);
@@ -153,26 +159,63 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 umma_commit_e(el, &stage_free[st]);
             }
         }
+    } else if (warp >= 14) {
+        // idle warps: they only take part in the register hand-over
     } else if (warp >= 6) {
         // ---------------- feature-map warps: thread r = row r of the Q and K tiles ----------------
         // The map is applied in place as soon as a chunk has landed (with no map there is nothing to
         // do: rows past the end are already zero, TMA fills them), independently of the compute
         // warps, which are still busy with the previous chunk.
-        const int r = (warp - 6) * 32 + lane;
+        // Warps 6-9 take the Q tile, warps 10-13 the K tile: one warp per scheduler alone is too slow
+        // (a row is ~450 dependent instructions) and would set the pace of the whole kernel.
+        // The same warps write the outputs, one chunk behind: O = O'[:, :64] / (den + 1e-8), den = rowsum
+        // + O'[:, 64]; a warp owns the 32 rows of its TMEM lane quarter and one half of the 64 columns.
+        const int r = ((warp - 6) % 4) * 32 + lane;  // warps 6..13 sit on lane quarters 2,3,0,1,2,3,0,1
+        const bool k_tile = warp >= 10;
+        const int rq = (warp % 4) * 32 + lane;  // row of this thread's TMEM lane
+        const uint32_t lane_q = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
+        const int half = k_tile ? 1 : 0;
+        auto write_output = [&](int c) {
+            mbar_wait(&o_full, c & 1, guard, 724);
+            tc_fence_after();
+            uint32_t o0[32], o2[32];
+            tmem_ld32(lane_q + COL_O + 32 * half, o0);
+            tmem_ld32(lane_q + COL_O + 64, o2);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free);
+            const int tok = (c0 + c) * CH + rq;
+            if (tok < p.S) {
+                const float den = s_rowsum[c & 1][rq] + __uint_as_float(o2[0]);
+                const float inv = 1.0f / (den + 1e-8f);
+                const int64_t row = (int64_t)b * p.S + tok;
+                if (half == 0) p.den[row] = p.eps_in_den ? den + 1e-8f : den;
+                uint4* dst = reinterpret_cast<uint4*>(p.O + row * DE + 32 * half);
+#pragma unroll
+                for (int i = 0; i < 32; i += 8)
+                    dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * inv, __uint_as_float(o0[i + 1]) * inv),
+                                            pack_bf16(__uint_as_float(o0[i + 2]) * inv, __uint_as_float(o0[i + 3]) * inv),
+                                            pack_bf16(__uint_as_float(o0[i + 4]) * inv, __uint_as_float(o0[i + 5]) * inv),
+                                            pack_bf16(__uint_as_float(o0[i + 6]) * inv, __uint_as_float(o0[i + 7]) * inv));
+            }
+        };
         for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 721);
             if (p.map_elu) {
                 const bool ok = (c0 + c) * CH + r < p.S;
-                map_row(sQ(st) + r * 128, ok, true, r & 7);
-                map_row(sK(st) + r * 128, ok, true, r & 7);
+                map_row((k_tile ? sK(st) : sQ(st)) + r * 128, ok, true, r & 7);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&mapped);
+            if (lane == 0) mbar_arrive(&mapped[st]);
+            if (c > 0) write_output(c - 1);
         }
+        write_output(nc - 1);
     } else {
         // ---------------- compute warps: thread r = token row r of the chunk = TMEM lane r ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         // the state operand of the first chunk is the zero tile written at start-up, or, for a later
@@ -182,9 +225,6 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
         for (int c = 0; c < nc; c++) {
-            const int tok = (c0 + c) * CH + r;
-            const bool valid = tok < p.S;
-
             // A -> causal mask inside the chunk (key column s visible iff s <= r), row sum, bf16 P
             mbar_wait(&a_full, c & 1, guard, 722);
             tc_fence_after();
@@ -210,6 +250,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tmem_st32(lane_base + COL_P + 32 * h, pk);
             }
             tmem_st_wait();
+            s_rowsum[c & 1][r] = rowsum;  // read by the output warps after o_full(c), which follows p_ready(c)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready);
@@ -248,35 +289,6 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (lane == 0) mbar_arrive(&sprev_ready);
             }
 
-            // output rows: O = O'[:, :64] / (den + 1e-8), den = rowsum + O'[:, 64]
-            mbar_wait(&o_full, c & 1, guard, 724);
-            tc_fence_after();
-            uint32_t o0[32], o1[32], o2[32];
-            tmem_ld32(lane_base + COL_O, o0);
-            tmem_ld32(lane_base + COL_O + 32, o1);
-            tmem_ld32(lane_base + COL_O + 64, o2);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&o_free);
-            if (valid) {
-                const float den = rowsum + __uint_as_float(o2[0]);
-                const float inv = 1.0f / (den + 1e-8f);
-                const int64_t row = (int64_t)b * p.S + tok;
-                p.den[row] = p.eps_in_den ? den + 1e-8f : den;
-                uint4* dst = reinterpret_cast<uint4*>(p.O + row * DE);
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    dst[i / 8] = make_uint4(pack_bf16(__uint_as_float(o0[i]) * inv, __uint_as_float(o0[i + 1]) * inv),
-                                            pack_bf16(__uint_as_float(o0[i + 2]) * inv, __uint_as_float(o0[i + 3]) * inv),
-                                            pack_bf16(__uint_as_float(o0[i + 4]) * inv, __uint_as_float(o0[i + 5]) * inv),
-                                            pack_bf16(__uint_as_float(o0[i + 6]) * inv, __uint_as_float(o0[i + 7]) * inv));
-                    dst[4 + i / 8] = make_uint4(pack_bf16(__uint_as_float(o1[i]) * inv, __uint_as_float(o1[i + 1]) * inv),
-                                                pack_bf16(__uint_as_float(o1[i + 2]) * inv, __uint_as_float(o1[i + 3]) * inv),
-                                                pack_bf16(__uint_as_float(o1[i + 4]) * inv, __uint_as_float(o1[i + 5]) * inv),
-                                                pack_bf16(__uint_as_float(o1[i + 6]) * inv, __uint_as_float(o1[i + 7]) * inv));
-                }
-            }
         }
     }
 
