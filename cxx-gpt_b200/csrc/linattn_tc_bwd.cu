@@ -29,7 +29,7 @@ using namespace tc;
 using namespace lintc;
 
 constexpr int NSTAGE = 2;
-constexpr int NTHREADS = 320;  // 4 compute warps, TMA producer, MMA issuer, 4 preparation warps (step 1, maps)
+constexpr int NTHREADS = 512;  // 4 compute warps, TMA producer, MMA issuer, 8 preparation warps (step 1, maps), 2 idle
 constexpr uint32_t TMEM_COLS = 512;
 
 struct LinBwdParams {
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmG, LinBwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, w_full, p_ready, o_full, o_free, s_done, sprev_ready;
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped[NSTAGE], w_full, p_ready, o_full, o_free, s_done, sprev_ready;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -111,7 +111,8 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         mbar_init(&w_full, 1);
         mbar_init(&o_full, 1);
         mbar_init(&s_done, 1);
-        mbar_init(&mapped, 4);
+        // one barrier per stage: the two halves of the preparation warps may be a chunk apart
+        for (int s = 0; s < NSTAGE; s++) mbar_init(&mapped[s], 8);  // one arrival per preparation warp
         mbar_init(&p_ready, 4);
         mbar_init(&o_free, 4);
         mbar_init(&sprev_ready, 4);
@@ -128,6 +129,10 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+
+    // Register budget (512 threads x 128 at launch): the compute warps hold whole rows, every other
+    // warp group gives registers back; 4 x 32 x (208 - 128) <= 12 x 32 x (128 - 96).
+    if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
 
     if (warp == 4) {
         if (lane == 0) {
@@ -159,7 +164,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 const uint64_t dG = smem_desc_sw128(smem_u32(sG(st)), 16), dVk = smem_desc_sw128(smem_u32(sV(st)), 16);
                 const uint64_t dKm = smem_desc_sw128(smem_u32(sK(st)), 0);
                 const uint64_t dV1 = smem_desc_sw128(smem_u32(sV(st)), smem_u32(sOnes) - smem_u32(sV(st)));
-                mbar_wait_poll(&mapped, c & 1, guard, 811);
+                mbar_wait_poll(&mapped[st], (c / NSTAGE) & 1, guard, 811);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + C1_W, dG + 2 * k, dVk + 2 * k, IDESC_W, k > 0);
@@ -184,23 +189,31 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 umma_commit_e(el, &stage_free[st]);
             }
         }
+    } else if (warp >= 14) {
+        // idle warps: they only take part in the register hand-over
     } else if (warp >= 6) {
         // ---------------- preparation warps: step 1 and the feature map, as soon as a chunk has landed ----------------
-        const int r = (warp - 6) * 32 + lane;
+        // warps 6-9: step 1 on the dO tile; warps 10-13: the feature map of the K tile (a lone warp per
+        // scheduler doing both would set the pace of the kernel)
+        const int r = ((warp - 6) % 4) * 32 + lane;
+        const bool second = warp >= 10;
         for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
             const int tok = (c0 + c) * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
-            const float den = ok ? p.den[row] : 1.f;
+            const float den = (!second && ok) ? p.den[row] : 1.f;
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 821);
-            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
-            if (p.map_elu) map_row(sK(st) + r * 128, ok, true, r & 7);
+            if (!second)
+                step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
+            else if (p.map_elu)
+                map_row(sK(st) + r * 128, ok, true, r & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&mapped);
+            if (lane == 0) mbar_arrive(&mapped[st]);
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         // a later sequence group starts from the sum of the states of the groups before it
@@ -283,7 +296,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
                            LinBwdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, aw_full, p_ready, o_full, o_free, s_done, snext_ready;
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped[NSTAGE], aw_full, p_ready, o_full, o_free, s_done, snext_ready;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float zstar[2][DE];  // z*_next in fp32 (double-buffered by iteration parity), added to dK
@@ -313,7 +326,8 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         mbar_init(&aw_full, 1);
         mbar_init(&o_full, 1);
         mbar_init(&s_done, 1);
-        mbar_init(&mapped, 4);
+        // one barrier per stage: the two halves of the preparation warps may be a chunk apart
+        for (int s = 0; s < NSTAGE; s++) mbar_init(&mapped[s], 8);  // one arrival per preparation warp
         mbar_init(&p_ready, 4);
         mbar_init(&o_free, 4);
         mbar_init(&snext_ready, 4);
@@ -331,6 +345,9 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+
+    // Register budget as in the first pass.
+    if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
 
     // iteration n = 0 .. nc-1 handles chunk c = c0 + nc-1-n
     if (warp == 4) {
@@ -368,7 +385,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                 const uint64_t dGm = smem_desc_sw128(smem_u32(sG(st)), 0);  // dnum MN-major (B of dV)
                 const uint64_t dDd = smem_desc_sw128(smem_u32(sDden(st)), 16);
                 const uint64_t dG1 = smem_desc_sw128(smem_u32(sG(st)), smem_u32(sDden(st)) - smem_u32(sG(st)));  // [dnum | dden]
-                mbar_wait_poll(&mapped, n & 1, guard, 911);
+                mbar_wait_poll(&mapped[st], (n / NSTAGE) & 1, guard, 911);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < DE / 16; k++) umma_ss_e(el, tmem + C2_AT, dKk + 2 * k, dQk + 2 * k, IDESC_KK, k > 0);
@@ -401,26 +418,32 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
                 umma_commit_e(el, &stage_free[st]);
             }
         }
+    } else if (warp >= 14) {
+        // idle warps: they only take part in the register hand-over
     } else if (warp >= 6) {
         // ---------------- preparation warps: step 1 and the feature maps of Q and K ----------------
-        const int r = (warp - 6) * 32 + lane;
+        // warps 6-9: step 1 on the dO tile and the map of the Q tile; warps 10-13: the map of the K tile
+        const int r = ((warp - 6) % 4) * 32 + lane;
+        const bool second = warp >= 10;
         for (int n = 0; n < nc; n++) {
             const int st = n % NSTAGE, c = c0 + nc - 1 - n;
             const int tok = c * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
-            const float den = ok ? p.den[row] : 1.f;
+            const float den = (!second && ok) ? p.den[row] : 1.f;
             mbar_wait(&full[st], (n / NSTAGE) & 1, guard, 921);
-            step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
-            if (p.map_elu) {
-                map_row(sQ(st) + r * 128, ok, true, r & 7);
+            if (!second) {
+                step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
+                if (p.map_elu) map_row(sQ(st) + r * 128, ok, true, r & 7);
+            } else if (p.map_elu) {
                 map_row(sK(st) + r * 128, ok, true, r & 7);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&mapped);
+            if (lane == 0) mbar_arrive(&mapped[st]);
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         // an earlier sequence group starts from the sum of the states of the groups after it

@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         LinStateParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped, done;
+    __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped[NSTAGE], done;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -69,7 +69,8 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             mbar_init(&full[s], 1);
             mbar_init(&stage_free[s], 1);
         }
-        mbar_init(&mapped, 4);
+        // one barrier per stage, so that a warp that runs a chunk ahead cannot complete an earlier phase
+        for (int s = 0; s < NSTAGE; s++) mbar_init(&mapped[s], 4);
         mbar_init(&done, 1);
         fence_barrier_init();
     }
@@ -114,7 +115,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const uint64_t dAm = smem_desc_sw128(smem_u32(sA(st)), 0);
             const uint32_t second = MODE == 0 ? smem_u32(sOnes) : smem_u32(sSide(st));
             const uint64_t dB1 = smem_desc_sw128(smem_u32(sB(st)), second - smem_u32(sB(st)));
-            mbar_wait_poll(&mapped, c & 1, guard, 1011);
+            mbar_wait_poll(&mapped[st], (c / NSTAGE) & 1, guard, 1011);
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < CH / 16; k++) umma_ss_e(el, tmem, dAm + 128 * k, dB1 + 128 * k, IDESC_S, c > 0 || k > 0);
@@ -137,7 +138,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             if (p.map_elu) map_row(sA(st) + r * 128, ok, true, r & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&mapped);
+            if (lane == 0) mbar_arrive(&mapped[st]);
         }
         // the group's state: TMEM lanes 0..63, 64 columns + z in column 64 -> global fp32
         mbar_wait(&done, 0, guard, 1022);
