@@ -195,8 +195,26 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         // ---------------- preparation warps: step 1 and the feature map, as soon as a chunk has landed ----------------
         // warps 6-9: step 1 on the dO tile; warps 10-13: the feature map of the K tile (a lone warp per
         // scheduler doing both would set the pace of the kernel)
+        // The second group also writes the dQ rows, one chunk behind (its warps 10-13 sit on the TMEM
+        // lane quarters 2, 3, 0, 1): dQ = dQ' o phi'(Q).
         const int r = ((warp - 6) % 4) * 32 + lane;
         const bool second = warp >= 10;
+        const int rq = (warp % 4) * 32 + lane;  // row of this thread's TMEM lane
+        const uint32_t lane_q = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
+        auto write_dq = [&](int c) {
+            mbar_wait(&o_full, c & 1, guard, 824);
+            tc_fence_after();
+            uint32_t o0[32], o1[32];
+            tmem_ld32(lane_q + C1_DQ, o0);
+            tmem_ld32(lane_q + C1_DQ + 32, o1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free);
+            const int tok = (c0 + c) * CH + rq;
+            const int64_t row = (int64_t)b * p.S + tok;
+            if (tok < p.S) store_grad_row(p.dQ + row * DE, p.map_elu ? p.Q + row * DE : nullptr, o0, o1, nullptr);
+        };
         for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
             const int tok = (c0 + c) * CH + r;
@@ -211,7 +229,9 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped[st]);
+            if (second && c > 0) write_dq(c - 1);
         }
+        if (second) write_dq(nc - 1);
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         const int r = warp * 32 + lane;
@@ -222,10 +242,6 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
         for (int c = 0; c < nc; c++) {
-            const int tok = (c0 + c) * CH + r;
-            const bool valid = tok < p.S;
-            const int64_t row = (int64_t)b * p.S + tok;
-
             // W -> mask s <= t -> bf16 P, written over the first 64 columns of W (each thread only
             // touches its own TMEM lane and has its whole row in registers before it stores)
             mbar_wait(&w_full, c & 1, guard, 822);
@@ -264,16 +280,6 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 if (lane == 0) mbar_arrive(&sprev_ready);
             }
 
-            mbar_wait(&o_full, c & 1, guard, 824);
-            tc_fence_after();
-            uint32_t o0[32], o1[32];
-            tmem_ld32(lane_base + C1_DQ, o0);
-            tmem_ld32(lane_base + C1_DQ + 32, o1);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&o_free);
-            if (valid) store_grad_row(p.dQ + row * DE, p.map_elu ? p.Q + row * DE : nullptr, o0, o1, nullptr);
         }
     }
     tc_fence_before();
@@ -299,7 +305,8 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped[NSTAGE], aw_full, p_ready, o_full, o_free, s_done, snext_ready;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ float zstar[2][DE];  // z*_next in fp32 (double-buffered by iteration parity), added to dK
+    __shared__ float zstar[3][DE];  // z*_next in fp32, added to dK; three buffers: written in iteration n for n + 1,
+                                    // read by the output warps until iteration n + 2 is under way
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     auto sQ = [&](int st) { return smem + (st * 4 + 0) * TILE_BYTES; };
@@ -423,8 +430,31 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     } else if (warp >= 6) {
         // ---------------- preparation warps: step 1 and the feature maps of Q and K ----------------
         // warps 6-9: step 1 on the dO tile and the map of the Q tile; warps 10-13: the map of the K tile
+        // The second group also writes the dV and dK rows, one chunk behind (its warps 10-13 sit on the
+        // TMEM lane quarters 2, 3, 0, 1): dV = dV', dK = (dK' + z*_next) o phi'(K).
         const int r = ((warp - 6) % 4) * 32 + lane;
         const bool second = warp >= 10;
+        const int rq = (warp % 4) * 32 + lane;  // row of this thread's TMEM lane
+        const uint32_t lane_q = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
+        auto write_dkdv = [&](int n) {
+            const int tok = (c0 + nc - 1 - n) * CH + rq;
+            const bool valid = tok < p.S;
+            const int64_t row = (int64_t)b * p.S + tok;
+            mbar_wait(&o_full, n & 1, guard, 924);
+            tc_fence_after();
+            uint32_t o0[32], o1[32];
+            tmem_ld32(lane_q + C2_DV, o0);
+            tmem_ld32(lane_q + C2_DV + 32, o1);
+            tmem_ld_wait();
+            if (valid) store_grad_row(p.dV + row * DE, nullptr, o0, o1, nullptr);
+            tmem_ld32(lane_q + C2_DK, o0);
+            tmem_ld32(lane_q + C2_DK + 32, o1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free);
+            if (valid) store_grad_row(p.dK + row * DE, p.map_elu ? p.K + row * DE : nullptr, o0, o1, zstar[n % 3]);
+        };
         for (int n = 0; n < nc; n++) {
             const int st = n % NSTAGE, c = c0 + nc - 1 - n;
             const int tok = c * CH + r;
@@ -441,7 +471,9 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped[st]);
+            if (second && n > 0) write_dkdv(n - 1);
         }
+        if (second) write_dkdv(nc - 1);
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         const int r = warp * 32 + lane;
@@ -452,11 +484,6 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(&snext_ready);
         for (int n = 0; n < nc; n++) {
-            const int c = c0 + nc - 1 - n;
-            const int tok = c * CH + r;
-            const bool valid = tok < p.S;
-            const int64_t row = (int64_t)b * p.S + tok;
-
             // A^T and W2 -> mask s >= t -> bf16 P1, P2 (each over the first 64 columns of its source)
             mbar_wait(&aw_full, n & 1, guard, 922);
             tc_fence_after();
@@ -496,26 +523,12 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             mbar_wait(&s_done, n & 1, guard, 923);
             tc_fence_after();
             if (n + 1 < nc) {
-                if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar[(n + 1) & 1]);
+                if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar[(n + 1) % 3]);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&snext_ready);
             }
 
-            mbar_wait(&o_full, n & 1, guard, 924);
-            tc_fence_after();
-            uint32_t o0[32], o1[32];
-            tmem_ld32(lane_base + C2_DV, o0);
-            tmem_ld32(lane_base + C2_DV + 32, o1);
-            tmem_ld_wait();
-            if (valid) store_grad_row(p.dV + row * DE, nullptr, o0, o1, nullptr);
-            tmem_ld32(lane_base + C2_DK, o0);
-            tmem_ld32(lane_base + C2_DK + 32, o1);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&o_free);
-            if (valid) store_grad_row(p.dK + row * DE, p.map_elu ? p.K + row * DE : nullptr, o0, o1, zstar[n & 1]);
         }
     }
     tc_fence_before();
