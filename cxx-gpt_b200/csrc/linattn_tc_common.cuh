@@ -51,6 +51,22 @@ __device__ __forceinline__ void map_row(uint8_t* row, bool valid, bool elu, int 
     for (int ch = 0; ch < 8; ch++) p[ch ^ rot] = v[ch];
 }
 
+// The same for half a row: chunks 4*half .. 4*half+3 (in the rotated order), so that two threads can
+// share a row.
+__device__ __forceinline__ void map_half_row(uint8_t* row, bool valid, int rot, int half) {
+    uint4* p = reinterpret_cast<uint4*>(row);
+    uint4 v[4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) v[ch] = p[(ch + 4 * half) ^ rot];
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+        if (!valid) v[ch] = make_uint4(0u, 0u, 0u, 0u);
+        else v[ch] = make_uint4(phi2(v[ch].x), phi2(v[ch].y), phi2(v[ch].z), phi2(v[ch].w));
+    }
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) p[(ch + 4 * half) ^ rot] = v[ch];
+}
+
 // Step 1 for one token row: the dO tile row becomes dnum = dO / den in place, dden = -(dO . O) / den
 // is returned and also written (bf16) to element 0 of the row's side-tile entry.
 __device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16* o_row, float den, bool valid,

@@ -26,7 +26,8 @@ using namespace tc;
 using namespace lintc;
 
 constexpr int NSTAGE = 2;
-constexpr int NTHREADS = 192;  // 4 preparation warps, TMA producer, MMA issuer
+constexpr int NTHREADS = 320;  // 8 preparation warps, TMA producer, MMA issuer
+constexpr int W_PROD = 8, W_MMA = 9;
 constexpr uint32_t TMEM_COLS = 128;
 // per stage A | B | side tile, then the constant ones tile
 constexpr size_t SMEM_BYTES = (NSTAGE * 3 + 1) * TILE_BYTES + 1024;
@@ -70,11 +71,11 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             mbar_init(&stage_free[s], 1);
         }
         // one barrier per stage, so that a warp that runs a chunk ahead cannot complete an earlier phase
-        for (int s = 0; s < NSTAGE; s++) mbar_init(&mapped[s], 4);
+        for (int s = 0; s < NSTAGE; s++) mbar_init(&mapped[s], 8);
         mbar_init(&done, 1);
         fence_barrier_init();
     }
-    if (warp == 5) tmem_alloc(&tmem_slot, TMEM_COLS);
+    if (warp == W_MMA) tmem_alloc(&tmem_slot, TMEM_COLS);
     // side tiles and the ones tile start as zero; only column 0 is ever written
     for (int st = 0; st < NSTAGE; st++)
         for (int i = threadIdx.x; i < TILE_BYTES / 16; i += NTHREADS)
@@ -90,7 +91,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    if (warp == 4) {
+    if (warp == W_PROD) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             prefetch_tmap(&tmA);
@@ -103,7 +104,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 tma_load_4d(sB(st), &tmB, &full[st], 0, 0, (c0 + c) * CH, b);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == W_MMA) {
         // ---------------- MMA issuer (warp-uniform; one elected lane issues) ----------------
         const uint32_t el = elect_one();
         constexpr uint32_t IDESC_S = idesc_bf16(CH, 80, 1, 1);  // both operands MN-major
@@ -123,19 +124,27 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
         umma_commit_e(el, &done);
     } else {
-        // ---------------- preparation warps: thread r = token row r of the chunk ----------------
-        const int r = warp * 32 + lane;
+        // ---------------- preparation warps: two threads per token row of the chunk ----------------
+        // mode 0: each maps half a row of K; mode 1: warps 0-3 do step 1 on the dO tile, warps 4-7 map Q
+        // (a lone warp per scheduler doing everything would set the pace of the kernel)
+        const int r = (warp % 4) * 32 + lane;
+        const int second = warp / 4;
         for (int c = 0; c < ng; c++) {
             const int st = c % NSTAGE;
             const int tok = (c0 + c) * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             float den = 1.f;
-            if (MODE == 1 && ok) den = p.den[row];
+            if (MODE == 1 && !second && ok) den = p.den[row];
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 1021);
-            if (MODE == 1)
-                step1_row(sB(st) + r * 128, p.O + row * DE, den, ok, r & 7, sSide(st) + r * 128 + (r & 7) * 16);
-            if (p.map_elu) map_row(sA(st) + r * 128, ok, true, r & 7);
+            if (MODE == 1) {
+                if (!second)
+                    step1_row(sB(st) + r * 128, p.O + row * DE, den, ok, r & 7, sSide(st) + r * 128 + (r & 7) * 16);
+                else if (p.map_elu)
+                    map_row(sA(st) + r * 128, ok, true, r & 7);
+            } else if (p.map_elu) {
+                map_half_row(sA(st) + r * 128, ok, r & 7, second);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&mapped[st]);
@@ -164,7 +173,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == W_MMA) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
@@ -173,7 +182,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 }  // namespace
 
 // Groups are worth it when the batch units leave SMs idle.  The cost model counts chunk-times: a main
-// CTA costs its chunks plus a fixed fill/drain of about two, a pre-pass CTA about a third of that
+// CTA costs its chunks plus a fixed fill/drain of about two, a pre-pass CTA about a quarter of that
 // per chunk; CTAs run in waves of one per SM.
 LinGroupPlan linattn_tc_plan(int B, int S) {
     static int sms[64] = {};
@@ -200,7 +209,7 @@ LinGroupPlan linattn_tc_plan(int B, int S) {
     for (int G = 2; G <= 16 && G <= nc; G++) {
         const int gc = (nc + G - 1) / G;
         if ((nc + gc - 1) / gc != G) continue;  // this G leaves an empty last group: a smaller G covers it
-        const double cost = waves((int64_t)B * G) * (gc + 2.0) + waves((int64_t)B * (G - 1)) * (0.35 * gc + 1.5);
+        const double cost = waves((int64_t)B * G) * (gc + 2.0) + waves((int64_t)B * (G - 1)) * (0.25 * gc + 1.0);
         if (cost < 0.95 * best_cost) {
             best_cost = cost;
             best = LinGroupPlan{G, gc, (size_t)B * G * lintc::DE * lintc::GS_ROW * sizeof(float)};
