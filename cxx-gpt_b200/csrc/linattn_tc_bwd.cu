@@ -237,7 +237,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         // a later sequence group starts from the sum of the states of the groups before it
-        if (g > 0 && warp < 2) init_state_row(p.sgp, b, 0, g, r, lane_base + C1_SX, sPrev);
+        if (g > 0) init_state_row(p.sgp, b, 0, g, r, lane_base + C1_SX, sPrev);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
@@ -274,7 +274,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             mbar_wait(&s_done, c & 1, guard, 823);
             tc_fence_after();
             if (c + 1 < nc) {
-                if (warp < 2) state_to_smem(lane_base + C1_SX, sPrev, r);
+                state_to_smem(lane_base + C1_SX, sPrev, r);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sprev_ready);
@@ -479,7 +479,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         const int r = warp * 32 + lane;
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         // an earlier sequence group starts from the sum of the states of the groups after it
-        if (seeded && warp < 2) init_state_row(p.sgs, b, g + 1, p.sgs.G, r, lane_base + C2_SX, sNext, zstar[0]);
+        if (seeded) init_state_row(p.sgs, b, g + 1, p.sgs.G, r, lane_base + C2_SX, sNext, zstar[0]);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&snext_ready);
@@ -523,7 +523,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             mbar_wait(&s_done, n & 1, guard, 923);
             tc_fence_after();
             if (n + 1 < nc) {
-                if (warp < 2) state_to_smem(lane_base + C2_SX, sNext, r, zstar[(n + 1) % 3]);
+                state_to_smem(lane_base + C2_SX, sNext, r, zstar[(n + 1) % 3]);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&snext_ready);

@@ -99,36 +99,36 @@ __device__ __forceinline__ float step1_row(uint8_t* do_row, const __nv_bfloat16*
     return dden;
 }
 
-// One fp32 state row in registers (64 columns + z) -> bf16 operand tile in shared memory: block 0 =
-// [64 d][64 e], block 1 = column 0 holds z; optionally z also as fp32.
-__device__ __forceinline__ void state_regs_to_smem(const uint32_t (&s0)[32], const uint32_t (&s1)[32], float z,
-                                                   uint8_t* sState, int r, float* zf32 = nullptr) {
-    uint8_t* row = sState + r * 128;
+// The fp32 state lives in TMEM lanes 0..63 (row d, 64 columns + z in column 64); lanes 64..127 hold an
+// identical copy (the state product is issued as M = 128 with its 64-row operand block repeated).
+// The four compute warps share the conversion to the bf16 operand tile in shared memory (block 0 =
+// [64 d][64 e], block 1 = column 0 holds z): thread r takes row d = r % 64, columns 0..31 if r < 64,
+// columns 32..63 and z otherwise.  `half` is one 32-column half of the row in registers.
+__device__ __forceinline__ void state_half_to_smem(const uint32_t (&h)[32], float z, uint8_t* sState, int r,
+                                                   float* zf32 = nullptr) {
+    const int d = r & 63, upper = r >> 6;
+    uint8_t* row = sState + d * 128;
 #pragma unroll
-    for (int ch = 0; ch < 4; ch++) {
-        *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) =
-            make_uint4(pack_bf16(__uint_as_float(s0[8 * ch]), __uint_as_float(s0[8 * ch + 1])),
-                       pack_bf16(__uint_as_float(s0[8 * ch + 2]), __uint_as_float(s0[8 * ch + 3])),
-                       pack_bf16(__uint_as_float(s0[8 * ch + 4]), __uint_as_float(s0[8 * ch + 5])),
-                       pack_bf16(__uint_as_float(s0[8 * ch + 6]), __uint_as_float(s0[8 * ch + 7])));
-        *reinterpret_cast<uint4*>(row + (((4 + ch) ^ (r & 7)) * 16)) =
-            make_uint4(pack_bf16(__uint_as_float(s1[8 * ch]), __uint_as_float(s1[8 * ch + 1])),
-                       pack_bf16(__uint_as_float(s1[8 * ch + 2]), __uint_as_float(s1[8 * ch + 3])),
-                       pack_bf16(__uint_as_float(s1[8 * ch + 4]), __uint_as_float(s1[8 * ch + 5])),
-                       pack_bf16(__uint_as_float(s1[8 * ch + 6]), __uint_as_float(s1[8 * ch + 7])));
+    for (int ch = 0; ch < 4; ch++)
+        *reinterpret_cast<uint4*>(row + (((4 * upper + ch) ^ (d & 7)) * 16)) =
+            make_uint4(pack_bf16(__uint_as_float(h[8 * ch]), __uint_as_float(h[8 * ch + 1])),
+                       pack_bf16(__uint_as_float(h[8 * ch + 2]), __uint_as_float(h[8 * ch + 3])),
+                       pack_bf16(__uint_as_float(h[8 * ch + 4]), __uint_as_float(h[8 * ch + 5])),
+                       pack_bf16(__uint_as_float(h[8 * ch + 6]), __uint_as_float(h[8 * ch + 7])));
+    if (upper) {
+        *reinterpret_cast<uint4*>(sState + 8192 + d * 128 + ((d & 7) * 16)) = make_uint4(pack_bf16(z, 0.f), 0u, 0u, 0u);
+        if (zf32 != nullptr) zf32[d] = z;
     }
-    *reinterpret_cast<uint4*>(sState + 8192 + r * 128 + ((r & 7) * 16)) = make_uint4(pack_bf16(z, 0.f), 0u, 0u, 0u);
-    if (zf32 != nullptr) zf32[r] = z;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-// The same from the fp32 state in TMEM (lanes 0..63, 64 columns + z in column 64).
+// Called by all four compute warps with `taddr` = the state region at the warp's own TMEM lanes.
 __device__ __forceinline__ void state_to_smem(uint32_t taddr, uint8_t* sState, int r, float* zf32 = nullptr) {
-    uint32_t s0[32], s1[32], s2[32];
-    tmem_ld32(taddr, s0);
-    tmem_ld32(taddr + 32, s1);
-    tmem_ld32(taddr + 64, s2);  // column 64 = z; the rest is not used
+    const int upper = r >> 6;
+    uint32_t h[32], s2[32];
+    tmem_ld32(taddr + 32 * upper, h);
+    if (upper) tmem_ld32(taddr + 64, s2);  // column 64 = z; the rest is not used
     tmem_ld_wait();
-    state_regs_to_smem(s0, s1, __uint_as_float(s2[0]), sState, r, zf32);
+    state_half_to_smem(h, upper ? __uint_as_float(s2[0]) : 0.f, sState, r, zf32);
 }
 
 // ---- sequence groups ---------------------------------------------------------------------------
@@ -141,15 +141,17 @@ struct SeqGroups {
     const float* gstate;  // null: one group
     int G, gc;
 };
-// Row r (< 64) of the initial state of group g: sum over groups [g0, g1) -> TMEM (fp32) and the bf16
-// operand tile.  Called by the two warps that own TMEM lanes 0..63.
+// The initial state of a group: the sum over groups [g0, g1).  Called by all four compute warps: thread
+// r seeds its own TMEM lane with row d = r % 64 (both copies must start equal) and writes its half of
+// the bf16 operand tile.
 __device__ __forceinline__ void init_state_row(const SeqGroups& sg, int unit, int g0, int g1, int r, uint32_t taddr,
                                                uint8_t* sState, float* zf32 = nullptr) {
+    const int d = r & 63, upper = r >> 6;
     float acc[GS_ROW];
 #pragma unroll
     for (int i = 0; i < GS_ROW; i++) acc[i] = 0.f;
     for (int g = g0; g < g1; g++) {
-        const float4* src = reinterpret_cast<const float4*>(sg.gstate + (((int64_t)unit * sg.G + g) * DE + r) * GS_ROW);
+        const float4* src = reinterpret_cast<const float4*>(sg.gstate + (((int64_t)unit * sg.G + g) * DE + d) * GS_ROW);
 #pragma unroll
         for (int i = 0; i < GS_ROW / 4; i++) {
             const float4 v = src[i];
@@ -167,7 +169,8 @@ __device__ __forceinline__ void init_state_row(const SeqGroups& sg, int unit, in
     tmem_st32(taddr + 32, s1);
     tmem_st32(taddr + 64, s2);
     tmem_st_wait();
-    state_regs_to_smem(s0, s1, acc[64], sState, r, zf32);
+    if (upper) state_half_to_smem(s1, acc[64], sState, r, zf32);
+    else state_half_to_smem(s0, 0.f, sState, r, zf32);
 }
 
 }  // namespace lintc

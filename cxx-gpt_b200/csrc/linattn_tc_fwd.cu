@@ -220,7 +220,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         // the state operand of the first chunk is the zero tile written at start-up, or, for a later
         // sequence group, the sum of the states of the groups before it (which also seeds TMEM)
-        if (g > 0 && warp < 2) init_state_row(p.sg, b, 0, g, r, lane_base + COL_SX, sPrev);
+        if (g > 0) init_state_row(p.sg, b, 0, g, r, lane_base + COL_SX, sPrev);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sprev_ready);
@@ -259,31 +259,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             mbar_wait(&s_done, c & 1, guard, 723);
             tc_fence_after();
             if (c + 1 < nc) {
-                if (warp < 2) {  // state rows d = 0..63 are TMEM lanes 0..63
-                    uint32_t s0[32], s1[32], s2[32];
-                    tmem_ld32(lane_base + COL_SX, s0);
-                    tmem_ld32(lane_base + COL_SX + 32, s1);
-                    tmem_ld32(lane_base + COL_SX + 64, s2);  // column 64 = z; the rest is not used
-                    tmem_ld_wait();
-                    uint8_t* row = sPrev + r * 128;
-#pragma unroll
-                    for (int ch = 0; ch < 4; ch++) {
-                        *reinterpret_cast<uint4*>(row + ((ch ^ (r & 7)) * 16)) = make_uint4(
-                            pack_bf16(__uint_as_float(s0[8 * ch]), __uint_as_float(s0[8 * ch + 1])),
-                            pack_bf16(__uint_as_float(s0[8 * ch + 2]), __uint_as_float(s0[8 * ch + 3])),
-                            pack_bf16(__uint_as_float(s0[8 * ch + 4]), __uint_as_float(s0[8 * ch + 5])),
-                            pack_bf16(__uint_as_float(s0[8 * ch + 6]), __uint_as_float(s0[8 * ch + 7])));
-                        *reinterpret_cast<uint4*>(row + (((4 + ch) ^ (r & 7)) * 16)) = make_uint4(
-                            pack_bf16(__uint_as_float(s1[8 * ch]), __uint_as_float(s1[8 * ch + 1])),
-                            pack_bf16(__uint_as_float(s1[8 * ch + 2]), __uint_as_float(s1[8 * ch + 3])),
-                            pack_bf16(__uint_as_float(s1[8 * ch + 4]), __uint_as_float(s1[8 * ch + 5])),
-                            pack_bf16(__uint_as_float(s1[8 * ch + 6]), __uint_as_float(s1[8 * ch + 7])));
-                    }
-                    // block 1, logical chunk 0: {z, 0, ...}
-                    *reinterpret_cast<uint4*>(sPrev + 8192 + r * 128 + ((r & 7) * 16)) =
-                        make_uint4(pack_bf16(__uint_as_float(s2[0]), 0.f), 0u, 0u, 0u);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                }
+                state_to_smem(lane_base + COL_SX, sPrev, r);  // shared by the four warps
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sprev_ready);
