@@ -292,7 +292,7 @@ def run_ours(args):
                              "peak_source": how, "unit": UNIT, "frac": main_tf / peak,
                              # dram__bytes_read + write of mha_tc_bwd_kernel from the ncu capture summarised in
                              # profiles/mha_tc_bwd_kernel_softmax_s4096_b4.md (398.6 MB at B=4), scaled by B/4
-                             "traffic": 383.8e6 * B / 4 if S == 4096 else None}}
+                             "traffic": 385.0e6 * B / 4 if S == 4096 else None}}
         if world == 1 and not args.no_cpu_baseline:
             tf, cores, dt, desc = cpu_sample(B, min(S, 4096))
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",
