@@ -221,6 +221,7 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = (!second && ok) ? p.den[row] : 1.f;
+            if (ok) prefetch_row(second ? p.Q + row * DE : p.O + row * DE);  // read by write_dq / step 1 below
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 821);
             if (!second)
                 step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
@@ -461,6 +462,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = (!second && ok) ? p.den[row] : 1.f;
+            if (ok) prefetch_row(second ? p.K + row * DE : p.O + row * DE);  // read by write_dkdv / step 1 below
             mbar_wait(&full[st], (n / NSTAGE) & 1, guard, 921);
             if (!second) {
                 step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);

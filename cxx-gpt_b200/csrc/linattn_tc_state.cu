@@ -135,7 +135,10 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             float den = 1.f;
-            if (MODE == 1 && !second && ok) den = p.den[row];
+            if (MODE == 1 && !second && ok) {
+                den = p.den[row];
+                prefetch_row(p.O + row * DE);
+            }
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 1021);
             if (MODE == 1) {
                 if (!second)
