@@ -54,22 +54,35 @@ __device__ __forceinline__ void store_grad_row(__nv_bfloat16* dst, const __nv_bf
     uint4* d4 = reinterpret_cast<uint4*>(dst);
     const uint4* r4 = reinterpret_cast<const uint4*>(raw);
 #pragma unroll
-    for (int ch = 0; ch < 8; ch++) {
-        float v[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int col = 8 * ch + i;
-            v[i] = __uint_as_float(col < 32 ? o0[col] : o1[col - 32]);
-            if (bias != nullptr) v[i] += bias[col];
-        }
+    for (int half = 0; half < 2; half++) {
+        // the four raw chunks of this half are requested together: one round trip, not four
+        uint4 x[4];
         if (raw != nullptr) {
-            const uint4 x = r4[ch];
-            v[0] *= dphi1(bf_lo(x.x)); v[1] *= dphi1(bf_hi(x.x));
-            v[2] *= dphi1(bf_lo(x.y)); v[3] *= dphi1(bf_hi(x.y));
-            v[4] *= dphi1(bf_lo(x.z)); v[5] *= dphi1(bf_hi(x.z));
-            v[6] *= dphi1(bf_lo(x.w)); v[7] *= dphi1(bf_hi(x.w));
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) x[c4] = r4[4 * half + c4];
         }
-        d4[ch] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {
+            const int ch = 4 * half + c4;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int col = 8 * ch + i;
+                v[i] = __uint_as_float(col < 32 ? o0[col] : o1[col - 32]);
+            }
+            if (bias != nullptr) {
+                const float4 b0 = reinterpret_cast<const float4*>(bias)[2 * ch], b1 = reinterpret_cast<const float4*>(bias)[2 * ch + 1];
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+            }
+            if (raw != nullptr) {
+                v[0] *= dphi1(bf_lo(x[c4].x)); v[1] *= dphi1(bf_hi(x[c4].x));
+                v[2] *= dphi1(bf_lo(x[c4].y)); v[3] *= dphi1(bf_hi(x[c4].y));
+                v[4] *= dphi1(bf_lo(x[c4].z)); v[5] *= dphi1(bf_hi(x[c4].z));
+                v[6] *= dphi1(bf_lo(x[c4].w)); v[7] *= dphi1(bf_hi(x[c4].w));
+            }
+            d4[ch] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
     }
 }
 
@@ -306,7 +319,7 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     __shared__ uint64_t full[NSTAGE], stage_free[NSTAGE], mapped[NSTAGE], aw_full, p_ready, o_full, o_free, s_done, snext_ready;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ float zstar[3][DE];  // z*_next in fp32, added to dK; three buffers: written in iteration n for n + 1,
+    __shared__ __align__(16) float zstar[3][DE];  // z*_next in fp32, added to dK; three buffers: written in iteration n for n + 1,
                                     // read by the output warps until iteration n + 2 is under way
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
