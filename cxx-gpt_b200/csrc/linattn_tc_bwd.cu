@@ -228,13 +228,16 @@ linattn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const int64_t row = (int64_t)b * p.S + tok;
             if (tok < p.S) store_grad_row(p.dQ + row * DE, p.map_elu ? p.Q + row * DE : nullptr, o0, o1, nullptr);
         };
+        for (int k = 0; k < 2 && k < nc; k++)  // the first two chunks' rows: nobody asked for them yet
+            if ((c0 + k) * CH + r < p.S) prefetch_row((second ? p.Q : p.O) + ((int64_t)b * p.S + (c0 + k) * CH + r) * DE);
         for (int c = 0; c < nc; c++) {
             const int st = c % NSTAGE;
             const int tok = (c0 + c) * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = (!second && ok) ? p.den[row] : 1.f;
-            if (ok) prefetch_row(second ? p.Q + row * DE : p.O + row * DE);  // read by write_dq / step 1 below
+            if (tok + 2 * CH < p.S)  // the rows step 1 / write_dq will read two chunks from now
+                prefetch_row((second ? p.Q : p.O) + (row + 2 * CH) * DE);
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 821);
             if (!second)
                 step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);
@@ -469,13 +472,17 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
             if (lane == 0) mbar_arrive(&o_free);
             if (valid) store_grad_row(p.dK + row * DE, p.map_elu ? p.K + row * DE : nullptr, o0, o1, zstar[n % 3]);
         };
+        for (int k = 0; k < 2 && k < nc; k++)  // the first two chunks' rows: nobody asked for them yet
+            if ((c0 + nc - 1 - k) * CH + r < p.S)
+                prefetch_row((second ? p.K : p.O) + ((int64_t)b * p.S + (c0 + nc - 1 - k) * CH + r) * DE);
         for (int n = 0; n < nc; n++) {
             const int st = n % NSTAGE, c = c0 + nc - 1 - n;
             const int tok = c * CH + r;
             const bool ok = tok < p.S;
             const int64_t row = (int64_t)b * p.S + tok;
             const float den = (!second && ok) ? p.den[row] : 1.f;
-            if (ok) prefetch_row(second ? p.K + row * DE : p.O + row * DE);  // read by write_dkdv / step 1 below
+            if (tok >= 2 * CH)  // the rows step 1 / write_dkdv will read two chunks from now
+                prefetch_row((second ? p.K : p.O) + (row - 2 * CH) * DE);
             mbar_wait(&full[st], (n / NSTAGE) & 1, guard, 921);
             if (!second) {
                 step1_row(sG(st) + r * 128, p.O + row * DE, den, ok, r & 7, sDden(st) + r * 128 + (r & 7) * 16);

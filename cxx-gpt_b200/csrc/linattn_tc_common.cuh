@@ -67,10 +67,11 @@ __device__ __forceinline__ void map_half_row(uint8_t* row, bool valid, int rot, 
     for (int ch = 0; ch < 4; ch++) p[(ch + 4 * half) ^ rot] = v[ch];
 }
 
-// Asks for the 128-byte row at `row` to be brought into L1/L2: issued a chunk ahead by the lone
-// warps that will read token rows from global memory, which have nothing to hide that latency behind.
+// Asks for the 128-byte row at `row` to be brought into L2: issued two chunks ahead by the lone warps
+// that will read token rows from global memory (a miss costs them ~3000 cycles, and they have
+// nothing to hide it behind).
 __device__ __forceinline__ void prefetch_row(const void* row) {
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(row));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(row));
 }
 
 // Step 1 for one token row: the dO tile row becomes dnum = dO / den in place, dden = -(dO . O) / den

@@ -137,7 +137,7 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             float den = 1.f;
             if (MODE == 1 && !second && ok) {
                 den = p.den[row];
-                prefetch_row(p.O + row * DE);
+                if (tok + 2 * CH < p.S) prefetch_row(p.O + (row + 2 * CH) * DE);
             }
             mbar_wait(&full[st], (c / NSTAGE) & 1, guard, 1021);
             if (MODE == 1) {
