@@ -185,7 +185,7 @@ int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_
 
 /* Softmax MHA forward + backward on HOST tensors in the reference layout (what kernel_test.cpp
  * does around fused_mha_fwd / fused_mha_bwd with fromTensor / toTensor, kernel_test.cpp:225-249):
- * the plan owns device buffers for up to three chunks of `batch_per_chunk` batch items
+ * the plan owns device buffers for up to four chunks of `batch_per_chunk` batch items
  * (allocated by _create, freed by _destroy) and pipelines copy-in, kernels and copy-out across
  * chunks.  cxxattn_mha_fwd_bwd_host returns after all results are in the host buffers. */
 typedef struct cxxattn_host_plan cxxattn_host_plan;
