@@ -146,3 +146,21 @@ def test_persistent_schedule_many_ragged_items(pkg, dev, orc):
             got = a[rows, cols].float().cpu().numpy()
             assert np.all(np.isfinite(got)), name
             assert rel_err(got, ref) < TOL_BF16, (name, rel_err(got, ref))
+
+
+def test_backward_beyond_32_tiles_takes_one_cta_per_item(pkg, dev, orc):
+    """33 query tiles: the backward leaves its persistent schedule (one CTA per (key tile, batch*head)
+    item instead); same parity bar."""
+    B, S, H, Dh = 1, 4224, 2, 64
+    Q, K, V, dO = bf16_inputs(29, B, S, H, Dh)
+    O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+    cols = slice(Dh, 2 * Dh)
+    f = [x[:, cols].float().numpy() for x in (Q, K, V, dO)]
+    got_O = O[:, cols].float().cpu().numpy()
+    rO = orc.mha_fwd(f[0], f[1], f[2], 1, S, 1, Dh, f64=True)
+    assert rel_err(got_O, rO) < TOL_BF16
+    rdQ, rdK, rdV = orc.mha_bwd(f[0], f[1], f[2], got_O, f[3], 1, S, 1, Dh, f64=True)
+    for name, a, ref in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        got = a[:, cols].float().cpu().numpy()
+        assert np.all(np.isfinite(got)), name
+        assert rel_err(got, ref) < TOL_BF16, (name, rel_err(got, ref))
