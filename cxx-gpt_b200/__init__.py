@@ -23,7 +23,8 @@ SYMBOLS = [
     "cxxattn_linattn_workspace_bytes", "cxxattn_linattn_fwd", "cxxattn_linattn_bwd_step1",
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
-    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_cast", "cxxattn_selftest_umma",
+    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_cast", "cxxattn_rope_cast",
+    "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
 ]
@@ -77,6 +78,8 @@ def lib():
         L.cxxattn_phi_elu_bwd.argtypes = [vp, vp, vp, sz, sz, sz, vp]
         L.cxxattn_rope.argtypes = [vp, vp, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
+        L.cxxattn_cast.argtypes = [vp, i32, vp, i32, sz, vp]
+        L.cxxattn_rope_cast.argtypes = [vp, i32, vp, i32, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_sync_status.argtypes = [vp]
         L.cxxattn_set_timing_events.argtypes = [vp, vp]
         L.cxxattn_set_timing_events.restype = None
@@ -251,6 +254,20 @@ def sync_status():
     rc = lib().cxxattn_sync_status(_stream())
     if rc != 0:
         raise CxxAttnError(rc, "cxxattn_sync_status (wait site %d)" % lib().cxxattn_last_timeout_site())
+
+
+def cast(src, dst):
+    """dst = src converted between float32 and bfloat16 (dense tensors of equal element count)."""
+    check(lib().cxxattn_cast(_ptr(src), _dtype_code(src), _ptr(dst), _dtype_code(dst), src.numel(), _stream()),
+          "cxxattn_cast")
+
+
+def rope_cast(src, dst, B, S, D, head_dim, sign=1.0):
+    """dst = rotary embedding of src ([B*S, D], sign=+1 forward, -1 backward), converting between
+    float32 and bfloat16 in the same pass (two_stage_gpt.hpp:102,113,160,174 with the conversion
+    that the tensor-core kernels need)."""
+    check(lib().cxxattn_rope_cast(_ptr(src), _dtype_code(src), _ptr(dst), _dtype_code(dst), B, S, D, head_dim,
+                                  float(sign), _stream()), "cxxattn_rope_cast")
 
 
 def selftest_umma(mode, A, B, D):

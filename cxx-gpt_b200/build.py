@@ -51,5 +51,25 @@ def build(force=False, verbose=False):
     return LIB
 
 
+COMPAT_CHECK = os.path.join(HERE, "build", "rope_fused_check")
+
+
+def build_compat_check(force=False):
+    """Compiles compat/rope_fused_check.cpp with the adapter against libcxxattn.so: the program that
+    compares the adapter's rope-folded attention pair with the reference's sequence of calls."""
+    compat = os.path.join(HERE, "compat")
+    srcs = [os.path.join(compat, "rope_fused_check.cpp"), os.path.join(compat, "cxxgpt_kernels.cpp")]
+    deps = srcs + [os.path.join(compat, "cxxgpt_kernels.hpp"), os.path.join(compat, "TensorN.hpp"),
+                   os.path.join(ROOT, "include", "cxxattn.h"), LIB]
+    if force or not os.path.exists(COMPAT_CHECK) or \
+            any(os.path.getmtime(d) > os.path.getmtime(COMPAT_CHECK) for d in deps):
+        os.makedirs(os.path.dirname(COMPAT_CHECK), exist_ok=True)
+        subprocess.check_call(["nvcc", "-std=c++17", "-O2", "-Wno-deprecated-gpu-targets", "-I", compat,
+                               "-I", os.path.join(ROOT, "include"), "-o", COMPAT_CHECK] + srcs +
+                              ["-L", HERE, "-lcxxattn", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."])
+    return COMPAT_CHECK
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_compat_check(force="--force" in sys.argv))

@@ -95,6 +95,76 @@ void* to_bf16(const float* src, char*& cursor, size_t n) {
 
 namespace cxxattn_compat {
 void set_tensorcore(bool on) { g_tensorcore = on ? 1 : 0; }
+
+typedef const TensorN::CudaTensor<float>& In;
+typedef TensorN::CudaTensor<float>& Out;
+
+// rotated copy of an fp32 tensor inside the scratch block, in the type the attention kernel takes
+static void* rotated(const float* src, char*& cursor, int dtype, size_t B, size_t S, size_t D, size_t Dh) {
+    void* dst = cursor;
+    cursor += (B * S * D * (dtype == CXXATTN_BF16 ? 2 : 4) + 255) / 256 * 256;
+    ok(cxxattn_rope_cast(src, CXXATTN_F32, dst, dtype, B, S, D, Dh, 1.0f, nullptr), "cxxattn_rope_cast");
+    return dst;
+}
+
+void rope_fused_mha_fwd(In Q, In K, In V, Out O, size_t B, size_t S, size_t H, size_t Dh) {
+    cxxattn_mha_desc d = mha(B, S, H, Dh);
+    const size_t n = B * S * H * Dh, D = H * Dh;
+    if (tensorcore(Dh)) {
+        d.dtype = CXXATTN_BF16;
+        const size_t blk = (n * 2 + 255) / 256 * 256;
+        char* cur = static_cast<char*>(scratch(4 * blk));
+        void* q = rotated(Q.device_ptr(), cur, CXXATTN_BF16, B, S, D, Dh);
+        void* k = rotated(K.device_ptr(), cur, CXXATTN_BF16, B, S, D, Dh);
+        void* v = to_bf16(V.device_ptr(), cur, n);
+        void* o = cur;
+        ok(cxxattn_mha_fwd(&d, q, k, v, o, nullptr, nullptr), "cxxattn_mha_fwd");
+        ok(cxxattn_cast(o, CXXATTN_BF16, O.device_ptr(), CXXATTN_F32, n, nullptr), "cxxattn_cast");
+        return;
+    }
+    const size_t blk = (n * 4 + 255) / 256 * 256;
+    char* cur = static_cast<char*>(scratch(2 * blk));
+    void* q = rotated(Q.device_ptr(), cur, CXXATTN_F32, B, S, D, Dh);
+    void* k = rotated(K.device_ptr(), cur, CXXATTN_F32, B, S, D, Dh);
+    ok(cxxattn_mha_fwd(&d, q, k, V.device_ptr(), O.device_ptr(), nullptr, nullptr), "cxxattn_mha_fwd");
+}
+
+void rope_fused_mha_bwd(In Q, In K, In V, In O, In dO, Out dQ, Out dK, Out dV, size_t B, size_t S, size_t H,
+                        size_t Dh) {
+    cxxattn_mha_desc d = mha(B, S, H, Dh);
+    const size_t n = B * S * H * Dh, D = H * Dh;
+    if (tensorcore(Dh)) {
+        d.dtype = CXXATTN_BF16;
+        const size_t blk = (n * 2 + 255) / 256 * 256;
+        const size_t ws = (cxxattn_mha_bwd_workspace_bytes(&d, 0) + 255) / 256 * 256;
+        char* cur = static_cast<char*>(scratch(8 * blk + ws));
+        void* q = rotated(Q.device_ptr(), cur, CXXATTN_BF16, B, S, D, Dh);
+        void* k = rotated(K.device_ptr(), cur, CXXATTN_BF16, B, S, D, Dh);
+        void* v = to_bf16(V.device_ptr(), cur, n);
+        void* o = to_bf16(O.device_ptr(), cur, n);
+        void* g = to_bf16(dO.device_ptr(), cur, n);
+        char* dq = cur;
+        char* dk = dq + blk;
+        char* dv = dk + blk;
+        char* w = dv + blk;
+        ok(cxxattn_mha_bwd(&d, q, k, v, o, g, nullptr, dq, dk, dv, w, ws, nullptr), "cxxattn_mha_bwd");
+        ok(cxxattn_rope_cast(dq, CXXATTN_BF16, dQ.device_ptr(), CXXATTN_F32, B, S, D, Dh, -1.0f, nullptr),
+           "cxxattn_rope_cast");
+        ok(cxxattn_rope_cast(dk, CXXATTN_BF16, dK.device_ptr(), CXXATTN_F32, B, S, D, Dh, -1.0f, nullptr),
+           "cxxattn_rope_cast");
+        ok(cxxattn_cast(dv, CXXATTN_BF16, dV.device_ptr(), CXXATTN_F32, n, nullptr), "cxxattn_cast");
+        return;
+    }
+    const size_t blk = (n * 4 + 255) / 256 * 256;
+    const size_t ws = (cxxattn_mha_bwd_workspace_bytes(&d, 0) + 255) / 256 * 256;
+    char* cur = static_cast<char*>(scratch(2 * blk + ws));
+    void* q = rotated(Q.device_ptr(), cur, CXXATTN_F32, B, S, D, Dh);
+    void* k = rotated(K.device_ptr(), cur, CXXATTN_F32, B, S, D, Dh);
+    ok(cxxattn_mha_bwd(&d, q, k, V.device_ptr(), O.device_ptr(), dO.device_ptr(), nullptr, dQ.device_ptr(),
+                       dK.device_ptr(), dV.device_ptr(), cur, ws, nullptr),
+       "cxxattn_mha_bwd");
+    ok(cxxattn_rope(dQ.device_ptr(), dK.device_ptr(), B, S, D, Dh, -1.0f, nullptr), "cxxattn_rope");
+}
 }  // namespace cxxattn_compat
 
 namespace two_stage_cuda {

@@ -10,6 +10,20 @@
 // (head dimension 64; tolerance 2e-2 instead of 1e-5).  Default: off, or CXXATTN_COMPAT_PRECISION=tensorcore.
 namespace cxxattn_compat {
 void set_tensorcore(bool on);
+// Stage-1 attention of TwoStageGPT with its rotary embedding folded in: what
+//   rope_fwd(Q, K, ..., Dh); fused_mha_fwd(Q, K, V, O, ...)            (two_stage_gpt.hpp:102-106)
+//   fused_mha_bwd(Q, K, V, O, dO, dQ, dK, dV, ...); rope_bwd(dQ, dK, ..., Dh)   (two_stage_gpt.hpp:171-174)
+// compute, but Q and K are the projections BEFORE the rotation and are left untouched: the rotation
+// runs in the same pass as the conversion the attention kernels need anyway, and the gradients come
+// back already un-rotated.  Follows the precision switch above.
+void rope_fused_mha_fwd(const TensorN::CudaTensor<float>& Q, const TensorN::CudaTensor<float>& K,
+                        const TensorN::CudaTensor<float>& V, TensorN::CudaTensor<float>& O, size_t B, size_t S,
+                        size_t H, size_t Dh);
+void rope_fused_mha_bwd(const TensorN::CudaTensor<float>& Q, const TensorN::CudaTensor<float>& K,
+                        const TensorN::CudaTensor<float>& V, const TensorN::CudaTensor<float>& O,
+                        const TensorN::CudaTensor<float>& dO, TensorN::CudaTensor<float>& dQ,
+                        TensorN::CudaTensor<float>& dK, TensorN::CudaTensor<float>& dV, size_t B, size_t S, size_t H,
+                        size_t Dh);
 }
 
 namespace two_stage_cuda {

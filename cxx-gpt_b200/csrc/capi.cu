@@ -187,6 +187,13 @@ int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_
     return cast(src, src_dtype, dst, dst_dtype, n, static_cast<cudaStream_t>(stream));
 }
 
+int cxxattn_rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D,
+                      size_t head_dim, float sign, cxxattn_stream_t stream) {
+    if (!src || !dst || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 4 || D % head_dim)
+        return CXXATTN_ERR_INVALID;
+    return rope_cast(src, src_dtype, dst, dst_dtype, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
+}
+
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {
     if (!A || !C || n == 0) return CXXATTN_ERR_INVALID;
     return gelu_exact(A, C, n, deriv != 0, static_cast<cudaStream_t>(stream));

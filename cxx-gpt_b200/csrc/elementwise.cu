@@ -151,6 +151,70 @@ int cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cud
     return check_launch();
 }
 
+// Rotary embedding out of place with a type conversion in the same pass: dst = rope(src), where
+// src and dst are fp32 or bf16.  This replaces "rotate fp32 in place, then convert" (three passes
+// over the tensor) by one read and one write when fp32 activations feed the bf16 tensor-core
+// kernels, and the reverse (bf16 gradients -> inverse rotation -> fp32) on the way back.  The
+// angle depends on the position and the pair only, so one thread owns four columns of one
+// position, forms its two sine/cosine pairs once and walks over the batch.  Same angle formula
+// as rope_kernel (ts.cu:1820-1857).
+template <typename TI, typename TO>
+__global__ void rope_cast_kernel(const TI* __restrict__ src, TO* __restrict__ dst, size_t B, size_t S, size_t D,
+                                 size_t hd, float sign) {
+    const size_t qpr = D / 4;  // quads per row
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= S * qpr) return;
+    const size_t pos = idx / qpr, col = (idx % qpr) * 4;
+    const size_t i0 = (col % hd) / 2;  // first pair index inside its head (hd % 4 == 0: i0 + 1 is in it too)
+    float s0, c0, s1, c1;
+    sincosf(sign * (float)pos * expf(-2.0f * (float)i0 / (float)hd * 9.210340371976184f), &s0, &c0);
+    sincosf(sign * (float)pos * expf(-2.0f * (float)(i0 + 1) / (float)hd * 9.210340371976184f), &s1, &c1);
+    for (size_t b = 0; b < B; b++) {
+        const size_t off = (b * S + pos) * D + col;
+        float x0, x1, x2, x3;
+        if constexpr (sizeof(TI) == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + off);
+            x0 = v.x, x1 = v.y, x2 = v.z, x3 = v.w;
+        } else {
+            const uint2 v = *reinterpret_cast<const uint2*>(src + off);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            x0 = lo.x, x1 = lo.y, x2 = hi.x, x3 = hi.y;
+        }
+        const float y0 = x0 * c0 - x1 * s0, y1 = x0 * s0 + x1 * c0;
+        const float y2 = x2 * c1 - x3 * s1, y3 = x2 * s1 + x3 * c1;
+        if constexpr (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(dst + off) = make_float4(y0, y1, y2, y3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+            *reinterpret_cast<uint2*>(dst + off) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+    }
+}
+
+int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
+              float sign, cudaStream_t st) {
+    if (reinterpret_cast<uintptr_t>(src) % 16 || reinterpret_cast<uintptr_t>(dst) % 16) return CXXATTN_ERR_ALIGNMENT;
+    const size_t threads = S * (D / 4);
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    const bool si = src_dtype == CXXATTN_F32, so = dst_dtype == CXXATTN_F32;
+    if ((!si && src_dtype != CXXATTN_BF16) || (!so && dst_dtype != CXXATTN_BF16)) return CXXATTN_ERR_UNSUPPORTED;
+    if (si && so)
+        rope_cast_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), static_cast<float*>(dst),
+                                                            B, S, D, hd, sign);
+    else if (si)
+        rope_cast_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>(
+            static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), B, S, D, hd, sign);
+    else if (so)
+        rope_cast_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(src), static_cast<float*>(dst), B, S, D, hd, sign);
+    else
+        rope_cast_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), B, S, D, hd, sign);
+    return check_launch();
+}
+
 int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st) {
     gelu_kernel<<<flat_grid(n), 256, 0, st>>>(A, C, n, deriv);
     return check_launch();

@@ -80,5 +80,7 @@ int phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, size_t D
 int rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t hd, float sign, cudaStream_t st);
 int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st);
 int cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cudaStream_t st);
+int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
+              float sign, cudaStream_t st);
 
 }  // namespace cxxattn

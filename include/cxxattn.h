@@ -173,6 +173,14 @@ int cxxattn_phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, 
  * sign=-1: rope_bwd (ts.cuh:72-76, ts.cu:1820-1880). */
 int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_dim, float sign,
                  cxxattn_stream_t stream);
+/* Rotary embedding fused with the type conversion either side of the tensor-core kernels:
+ * dst = rope(src, sign) out of place, src and dst each CXXATTN_F32 or CXXATTN_BF16, one tensor
+ * [B*S, D] per call.  Stands for two_stage_cuda::rope_fwd followed by the fp32 -> bf16 conversion
+ * of Q or K (sign=+1; two_stage_gpt.hpp:102,113), and for the bf16 -> fp32 conversion of dQ or dK
+ * followed by rope_bwd (sign=-1; two_stage_gpt.hpp:160,174).  head_dim must be a multiple of 4
+ * and divide D; 16-byte aligned pointers; src and dst must not overlap. */
+int cxxattn_rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D,
+                      size_t head_dim, float sign, cxxattn_stream_t stream);
 /* erf-GELU (deriv=0) and its derivative (deriv=1).  two_stage_cuda::gelu_exact /
  * gelu_exact_deriv (ts.cuh:84-85, ts.cu:1888-1924). */
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream);

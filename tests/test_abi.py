@@ -52,6 +52,9 @@ def test_bad_arguments_are_rejected_without_a_device(pkg):
     assert lib.cxxattn_linattn_fwd(C.byref(badmap), one, one, one, one, one, None, one, 1 << 20, None) == -1
     assert lib.cxxattn_rope(None, None, 1, 1, 8, 8, 1.0, None) == -1
     assert lib.cxxattn_rope(one, one, 1, 1, 8, 3, 1.0, None) == -1
+    assert lib.cxxattn_rope_cast(None, 0, one, 1, 1, 1, 8, 8, 1.0, None) == -1
+    assert lib.cxxattn_rope_cast(one, 0, one, 1, 1, 1, 8, 6, 1.0, None) == -1   # head_dim % 4
+    assert lib.cxxattn_rope_cast(one, 0, one, 1, 1, 1, 12, 8, 1.0, None) == -1  # D % head_dim
     assert lib.cxxattn_phi_elu_fwd(one, one, 4, 2, 4, None) == -1   # E > D
     assert lib.cxxattn_gelu_exact(one, one, 0, 0, None) == -1
 

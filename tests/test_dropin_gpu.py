@@ -64,3 +64,40 @@ def test_reference_kernel_test_program_in_tensorcore_mode():
         v = float(val)
         limit = 1e-2 if name.split()[-1] == "den" else 2e-5
         assert v == v and v < limit, (name, val)
+
+
+def _rope_fused_lines(env=None, args=()):
+    exe = os.path.join(ROOT, "cxx-gpt_b200", "build", "rope_fused_check")
+    if not os.path.exists(exe):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("cxx_gpt_b200_build", os.path.join(ROOT, "cxx-gpt_b200", "build.py"))
+        b = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(b)
+        b.build_compat_check()
+    out = subprocess.run([exe, *map(str, args)], capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, **(env or {})))
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip().endswith("done")
+    return {n: float(v) for n, v in
+            re.findall(r"^(.*\S)\s+maxdiff\s*=\s*([-+0-9.eE]+|nan|inf)\s*$", out.stdout, flags=re.M)}
+
+
+@pytest.mark.parametrize("shape", [(2, 300, 3, 64), (1, 129, 2, 32)])
+def test_rope_folded_attention_pair_equals_the_reference_call_sequence(shape):
+    """cxxattn_compat::rope_fused_mha_fwd / _bwd against rope_fwd; fused_mha_fwd; fused_mha_bwd; rope_bwd
+    (two_stage_gpt.hpp:102-106, 171-174) on the exact path: same arithmetic, inputs left un-rotated."""
+    d = _rope_fused_lines(args=shape)
+    assert len(d) == 6, d
+    for k in ("rope+mha O", "rope+mha dQ", "rope+mha dK", "rope+mha dV"):
+        assert d[k] < 1e-6, d
+    assert d["inputs untouched"] == 0.0
+    assert d["rotation applied"] > 0.1
+
+
+def test_rope_folded_attention_pair_in_tensorcore_mode():
+    """Both sides on the bf16 tensor-core kernels: the folded pair rounds the rotated fp32 values to
+    bf16 exactly as the separate rotation + conversion does, so the results still agree closely."""
+    d = _rope_fused_lines(env={"CXXATTN_COMPAT_PRECISION": "tensorcore"}, args=(2, 300, 3, 64))
+    for k in ("rope+mha O", "rope+mha dQ", "rope+mha dK", "rope+mha dV"):
+        assert d[k] < 1e-6, d
+    assert d["inputs untouched"] == 0.0

@@ -40,6 +40,52 @@ def test_rope_whole_vector_and_long_positions(pkg, dev, orc):
     assert rel_err(t.cpu().numpy(), orc.rope(X, S, D, 1.0)) < 1e-4   # fp32 angle at p ~ 255
 
 
+def _bf16_round(a):
+    return torch.from_numpy(a).bfloat16().float().numpy()
+
+
+@pytest.mark.parametrize("B,S,D,hd", [(2, 6, 16, 8), (3, 130, 768, 64), (1, 33, 64, 64)])
+def test_rope_cast_all_type_pairs(pkg, dev, orc, B, S, D, hd):
+    """The one-pass rotary + conversion gives what rope followed by the conversion gives: equal to
+    the in-place kernel bit for bit in fp32, and to the bf16 rounding of the oracle's rotation up to
+    the rounding of a value that sits on a bf16 tie (one bf16 ulp = 2^-8 relative)."""
+    X, = seeded_normal(63 + S, [(B * S, D)])
+    want_f = orc.rope(X, S, hd, 1.0)
+    src = torch.from_numpy(X.copy()).to(dev)
+    # fp32 -> fp32: the same arithmetic as the in-place kernel
+    out = torch.empty_like(src)
+    pkg.rope_cast(src, out, B, S, D, hd, 1.0)
+    inplace = src.clone()
+    pkg.two_stage_cuda.rope_fwd(inplace, None, B, S, D, hd)
+    assert torch.equal(out, inplace)
+    assert rel_err(out.cpu().numpy(), want_f) < 1e-5
+    # fp32 -> bf16 (forward side of the tensor-core kernels)
+    outb = torch.empty(B * S, D, dtype=torch.bfloat16, device=dev)
+    pkg.rope_cast(src, outb, B, S, D, hd, 1.0)
+    assert torch.equal(outb, inplace.bfloat16())
+    assert np.abs(outb.float().cpu().numpy() - _bf16_round(want_f)).max() <= 2.0 ** -8 * np.abs(want_f).max()
+    # bf16 -> fp32 with the inverse rotation (gradient side): exact on the bf16 input values
+    g = outb.clone()
+    back = torch.empty_like(src)
+    pkg.rope_cast(g, back, B, S, D, hd, -1.0)
+    want_b = orc.rope(g.float().cpu().numpy(), S, hd, -1.0)
+    assert rel_err(back.cpu().numpy(), want_b) < 1e-5
+    assert rel_err(back.cpu().numpy(), X) < 2.0 ** -7   # the round trip loses only the bf16 rounding
+    # bf16 -> bf16
+    bb = torch.empty_like(g)
+    pkg.rope_cast(g, bb, B, S, D, hd, -1.0)
+    assert torch.equal(bb, back.bfloat16())
+
+
+def test_rope_cast_rejects_unaligned_and_unknown_types(pkg, dev):
+    src = torch.zeros(64, 64, device=dev)
+    dst = torch.zeros(64, 64, device=dev)
+    with pytest.raises(pkg.CxxAttnError):
+        pkg.rope_cast(src.view(-1)[1:65], dst, 1, 1, 64, 64, 1.0)
+    lib = pkg.lib()
+    assert lib.cxxattn_rope_cast(src.data_ptr(), 5, dst.data_ptr(), 0, 1, 64, 64, 64, 1.0, None) == -2
+
+
 def test_gelu_exact_and_derivative(pkg, dev, orc):
     X, = seeded_normal(62, [(1000, 37)])
     X *= 3
