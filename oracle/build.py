@@ -91,6 +91,48 @@ def build_reference_cuda(reference=DEFAULT_REFERENCE, force=False):
                                "-I", compat, "-I", os.path.join(reference, "src"), "-o", out, wrap] + srcs)
     return out
 
+def build_model_checks(reference=DEFAULT_REFERENCE, force=False):
+    """Compiles the reference's UNMODIFIED model headers (src/TwoStage/two_stage_gpt.hpp,
+    src/LinearAttention/linear_gpt.hpp, src/GPT/gpt_gpt.hpp) and its src/GPT/gpt_cuda_kernels.cu, with
+    the wider TensorN stand-in of cxx-gpt_b200/compat/full, into four programs under oracle/_ref/:
+      two_stage_check_dropin, linear_gpt_check_dropin   attention kernels = this repository
+                                                        (compat adapter + libcxxattn.so)
+      two_stage_check_ref, linear_gpt_check_ref         attention kernels = the reference's
+                                                        two_stage_cuda_kernels.cu / linear_cuda_kernels.cu
+    Returns the dict name -> path, or None when neither the reference tree nor earlier builds are there."""
+    root = os.path.dirname(HERE)
+    pkg = os.path.join(root, "cxx-gpt_b200")
+    full = os.path.join(pkg, "compat", "full")
+    out_dir = os.path.join(HERE, "_ref")
+    src = os.path.join(reference, "src")
+    models = {"two_stage_check": (os.path.join(src, "TwoStage", "two_stage_gpt.hpp"),
+                                  os.path.join(src, "TwoStage", "two_stage_cuda_kernels.cu")),
+              "linear_gpt_check": (os.path.join(src, "LinearAttention", "linear_gpt.hpp"),
+                                   os.path.join(src, "LinearAttention", "linear_cuda_kernels.cu"))}
+    outs = {f"{m}_{v}": os.path.join(out_dir, f"{m}_{v}") for m in models for v in ("dropin", "ref")}
+    if not all(os.path.exists(h) for h, _ in models.values()):
+        return outs if all(os.path.exists(o) for o in outs.values()) else None
+    gpt_cu = os.path.join(src, "GPT", "gpt_cuda_kernels.cu")
+    ops = os.path.join(full, "tensorn_ops.cu")
+    adapter = os.path.join(pkg, "compat", "cxxgpt_kernels.cpp")
+    flags = ["nvcc", "-std=c++17", "-O2", "-gencode", "arch=compute_100,code=sm_100", "-Wno-deprecated-gpu-targets",
+             "-I", full, "-I", src, "-I", os.path.join(src, "GPT")]
+    os.makedirs(out_dir, exist_ok=True)
+    for m, (header, kernels_cu) in models.items():
+        main = os.path.join(full, m + ".cpp")
+        common = [main, ops, gpt_cu, header, os.path.join(src, "GPT", "gpt_gpt.hpp"),
+                  os.path.join(full, "model_check.hpp"), os.path.join(full, "TensorN.hpp"),
+                  os.path.join(full, "tokenizer.hpp"), os.path.join(pkg, "compat", "TensorN.hpp")]
+        dropin, ref = outs[m + "_dropin"], outs[m + "_ref"]
+        if force or _stale(dropin, common + [adapter, os.path.join(pkg, "libcxxattn.so"),
+                                             os.path.join(root, "include", "cxxattn.h")]):
+            subprocess.check_call(flags + ["-I", os.path.join(root, "include"), "-o", dropin, main, ops, gpt_cu,
+                                           adapter, "-L", pkg, "-lcxxattn", "-lcublas", "-Xlinker", "-rpath",
+                                           "-Xlinker", "$ORIGIN/../../cxx-gpt_b200"])
+        if force or _stale(ref, common + [kernels_cu]):
+            subprocess.check_call(flags + ["-o", ref, main, ops, gpt_cu, kernels_cu, "-lcublas"])
+    return outs
+
 
 if __name__ == "__main__":
     ref = DEFAULT_REFERENCE
@@ -100,3 +142,4 @@ if __name__ == "__main__":
     print(build_reference(ref, force="--force" in sys.argv))
     print(build_dropin_kernel_test(ref, force="--force" in sys.argv))
     print(build_reference_cuda(ref, force="--force" in sys.argv))
+    print(build_model_checks(ref, force="--force" in sys.argv))
