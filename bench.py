@@ -262,6 +262,31 @@ def run_ours(args):
     # the end-to-end results must be the same numbers as the device-resident path
     assert torch.equal(hO, O.cpu()), "host entry point and device path disagree"
 
+    # the reference's own fp32 CUDA kernels on the same tensors (when they were built), one forward +
+    # backward over the whole batch: its grid is one block per (batch, head), so a smaller sample
+    # would leave the GPU idle and overstate its time.  S <= 4096 only: its backward takes
+    # (2 S^2 + S) floats of scratch per (batch, head), 26 GB at S = 4096, and seconds per call.
+    ref_ms, ref_err = None, None
+    try:
+        import oracle
+        if rank == 0 and world == 1 and S <= 4096 and not args.no_reference_cuda and oracle.ReferenceCuda.available():
+            rc = oracle.ReferenceCuda()
+            Qf, Kf, Vf, dOf = (t_.float() for t_ in (Q, K, V, dO))
+            rO, rdQ, rdK, rdV = (torch.empty_like(Qf) for _ in range(4))
+            rc.mha_fwd(Qf, Kf, Vf, rO, B, S, H, DH)
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
+            rc.mha_fwd(Qf, Kf, Vf, rO, B, S, H, DH)
+            rc.mha_bwd(Qf, Kf, Vf, rO, dOf, rdQ, rdK, rdV, B, S, H, DH)
+            r1.record()
+            torch.cuda.synchronize()
+            ref_ms = r0.elapsed_time(r1)
+            ref_err = float((rO - O.float()).abs().max() / rO.abs().max())
+            del Qf, Kf, Vf, dOf, rO, rdQ, rdK, rdV
+    except Exception as e:  # the companion figure is optional; say why it is missing
+        ref_ms, ref_err = None, repr(e)
+
     t = torch.tensor([ms, e2e_ms, fwd_ms, bwd_ms, bwd_main_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -293,6 +318,11 @@ def run_ours(args):
                              # dram__bytes_read + write of mha_tc_bwd_kernel from the ncu capture summarised in
                              # profiles/mha_tc_bwd_kernel_softmax_s4096_b4.md (398.6 MB at B=4), scaled by B/4
                              "traffic": 385.0e6 * B / 4 if S == 4096 else None}}
+        if world == 1:
+            line["reference_cuda"] = {"ms_per_step": ref_ms, "speedup": (ref_ms / ms) if ref_ms else None,
+                                      "max_rel_diff_O": ref_err,
+                                      "what": "reference two_stage_cuda fused_mha_fwd + fused_mha_bwd, unmodified, sm_100, "
+                                              "fp32, the same batch, one call"}
         if world == 1 and not args.no_cpu_baseline:
             tf, cores, dt, desc = cpu_sample(B, min(S, 4096))
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",
