@@ -459,7 +459,10 @@ def run_ours_linattn(args):
                              "kernel": ("linattn_tc_fwd + linattn_tc_bwd_dq + linattn_tc_bwd_dkdv" if w == 2 else
                                         "chunk_state + chunk_scan + chunk_apply (fwd + bwd call)"),
                              "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s", "frac": gbs / hbm,
-                             "traffic": None},
+                             # dram__bytes_read + write summed over the six kernels of one step, from the ncu
+                             # capture summarised in profiles/linattn_tc_kernels_linattn_s4096.md (2064 MB at
+                             # 192 units: the state pre-passes and the two backward passes re-read Q, K, V)
+                             "traffic": 2.064e9 * B / 192 if (w == 2 and S == 4096 and D == 64 and E == 64) else None},
                 "reference_cuda": {"ms_per_step": ref_ms, "speedup": (ref_ms / ms) if ref_ms else None,
                                    "max_rel_diff_O": ref_err if ref_ms else None,
                                    "what": "reference two_stage_cuda kernel_attn fwd+step1+dQ+dKdV, unmodified, sm_100"}}
