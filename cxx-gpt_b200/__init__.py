@@ -24,6 +24,7 @@ SYMBOLS = [
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
     "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_cast", "cxxattn_rope_cast",
+    "cxxattn_linattn_decode_step", "cxxattn_mha_decode_workspace_bytes", "cxxattn_mha_decode_step",
     "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
@@ -80,6 +81,10 @@ def lib():
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
         L.cxxattn_cast.argtypes = [vp, i32, vp, i32, sz, vp]
         L.cxxattn_rope_cast.argtypes = [vp, i32, vp, i32, sz, sz, sz, sz, C.c_float, vp]
+        L.cxxattn_linattn_decode_step.argtypes = [C.POINTER(LinDesc)] + [vp] * 7 + [vp]
+        L.cxxattn_mha_decode_workspace_bytes.restype = sz
+        L.cxxattn_mha_decode_workspace_bytes.argtypes = [C.POINTER(MhaDesc)]
+        L.cxxattn_mha_decode_step.argtypes = [C.POINTER(MhaDesc)] + [vp] * 5 + [C.c_int64, vp, vp, sz, vp]
         L.cxxattn_sync_status.argtypes = [vp]
         L.cxxattn_set_timing_events.argtypes = [vp, vp]
         L.cxxattn_set_timing_events.restype = None
@@ -268,6 +273,24 @@ def rope_cast(src, dst, B, S, D, head_dim, sign=1.0):
     that the tensor-core kernels need)."""
     check(lib().cxxattn_rope_cast(_ptr(src), _dtype_code(src), _ptr(dst), _dtype_code(dst), B, S, D, head_dim,
                                   float(sign), _stream()), "cxxattn_rope_cast")
+
+
+def linattn_decode_step(q, k, v, state_S, state_z, o, den, B, D, E, feature_map=MAP_ELU1, eps_in_den=0):
+    """One new token per unit through the linear stage; state_S [B, D, E] and state_z [B, D] are
+    updated in place (zero before the first token)."""
+    d = lin_desc(B, 1, D, E, F32, feature_map, eps_in_den)
+    check(lib().cxxattn_linattn_decode_step(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(state_S), _ptr(state_z),
+                                            _ptr(o), _ptr(den), _stream()), "cxxattn_linattn_decode_step")
+
+
+def mha_decode_step(q, k, v, K_cache, V_cache, pos, o, B, capacity, H, Dh):
+    """One new token per batch item through the softmax stage; k, v are appended to the caches
+    [B, capacity, H*Dh] at row pos."""
+    d = mha_desc(B, capacity, H, Dh, F32)
+    n = lib().cxxattn_mha_decode_workspace_bytes(C.byref(d))
+    ws = workspace(n, q.device) if n else None
+    check(lib().cxxattn_mha_decode_step(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(K_cache), _ptr(V_cache), int(pos),
+                                        _ptr(o), _ptr(ws), n, _stream()), "cxxattn_mha_decode_step")
 
 
 def selftest_umma(mode, A, B, D):

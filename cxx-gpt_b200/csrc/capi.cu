@@ -187,6 +187,35 @@ int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_
     return cast(src, src_dtype, dst, dst_dtype, n, static_cast<cudaStream_t>(stream));
 }
 
+int cxxattn_linattn_decode_step(const cxxattn_lin_desc* desc, const float* q, const float* k, const float* v,
+                                float* state_S, float* state_z, float* o, float* den, cxxattn_stream_t stream) {
+    if (!desc || desc->B <= 0 || desc->D <= 0 || desc->E <= 0 || desc->reserved != 0 || !q || !k || !v || !state_S ||
+        !state_z || !o)
+        return CXXATTN_ERR_INVALID;
+    if (desc->feature_map != CXXATTN_MAP_NONE && desc->feature_map != CXXATTN_MAP_ELU1) return CXXATTN_ERR_INVALID;
+    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
+    return linattn_decode_step(*desc, q, k, v, state_S, state_z, o, den, static_cast<cudaStream_t>(stream));
+}
+
+static bool decode_ok(const cxxattn_mha_desc* d) {
+    return d && d->B > 0 && d->S > 0 && d->H > 0 && d->Dh > 0 && d->reserved == 0 && d->stride_b == 0 &&
+           d->stride_s == 0 && d->stride_h == 0;
+}
+
+size_t cxxattn_mha_decode_workspace_bytes(const cxxattn_mha_desc* desc) {
+    return decode_ok(desc) ? mha_decode_workspace(*desc) : 0;
+}
+
+int cxxattn_mha_decode_step(const cxxattn_mha_desc* desc, const float* q, const float* k, const float* v,
+                            float* K_cache, float* V_cache, int64_t pos, float* o, void* workspace,
+                            size_t workspace_bytes, cxxattn_stream_t stream) {
+    if (!decode_ok(desc) || !q || !k || !v || !K_cache || !V_cache || !o || pos < 0 || pos >= desc->S)
+        return CXXATTN_ERR_INVALID;
+    if (desc->dtype != CXXATTN_F32 || desc->Dh > 256) return CXXATTN_ERR_UNSUPPORTED;
+    return mha_decode_step(*desc, q, k, v, K_cache, V_cache, pos, o, workspace, workspace_bytes,
+                           static_cast<cudaStream_t>(stream));
+}
+
 int cxxattn_rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D,
                       size_t head_dim, float sign, cxxattn_stream_t stream) {
     if (!src || !dst || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 4 || D % head_dim)

@@ -80,6 +80,11 @@ int phi_elu_bwd(const float* dphi, const float* x, float* dx, size_t N, size_t D
 int rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t hd, float sign, cudaStream_t st);
 int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st);
 int cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cudaStream_t st);
+int linattn_decode_step(const cxxattn_lin_desc& d, const float* q, const float* k, const float* v, float* S, float* z,
+                        float* o, float* den, cudaStream_t st);
+size_t mha_decode_workspace(const cxxattn_mha_desc& d);
+int mha_decode_step(const cxxattn_mha_desc& d, const float* q, const float* k, const float* v, float* Kc, float* Vc,
+                    int64_t pos, float* o, void* ws, size_t ws_bytes, cudaStream_t st);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
 

@@ -158,6 +158,30 @@ int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void*
                         void* dQ, void* dK, void* dV,
                         void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
 
+/* ---- decoding with carried state ----------------------------------------------------------- */
+/* Not in the reference, whose generate() re-runs the whole context through both attention stages
+ * for every new token (two_stage_gpt.hpp:458-474).  One call = one new token per batch unit; the
+ * results equal the last row of the corresponding forward call on the whole prefix. */
+
+/* Linear stage.  q, k [B, D], v [B, E] are the new token's rows; state_S [B, D, E] and state_z
+ * [B, D] (fp32, zero before the first token) are updated in place: z += phi(k), S += phi(k) (x) v;
+ * o [B, E] = phi(q)^T S / (phi(q).z + 1e-8); den [B] (may be NULL) as cxxattn_linattn_fwd stores
+ * it (desc->eps_in_den).  desc->S is not used; dtype must be CXXATTN_F32.  Row t of
+ * kernel_attn_fwd (ts.cu:889-976) / causal_linear_attention_fwd (lin.cu:10-79). */
+int cxxattn_linattn_decode_step(const cxxattn_lin_desc* desc, const float* q, const float* k, const float* v,
+                                float* state_S, float* state_z, float* o, float* den, cxxattn_stream_t stream);
+
+/* Softmax stage with a key/value cache.  desc->S is the cache capacity; K_cache, V_cache
+ * [B, S, H*Dh] fp32 in the reference layout (strides must be 0), rows 0..pos-1 filled by earlier
+ * steps.  q, k, v [B, H*Dh] are the new token's rows: k, v are appended at row pos, then
+ * o [B, H*Dh] = softmax(q.K[0..pos] / sqrt(Dh)) V[0..pos].  Row pos of fused_mha_fwd
+ * (ts.cu:54-125).  Few (batch, head) units are cut along the keys through `workspace`
+ * (cxxattn_mha_decode_workspace_bytes, sized for the capacity; 0 when never needed). */
+size_t cxxattn_mha_decode_workspace_bytes(const cxxattn_mha_desc* desc);
+int cxxattn_mha_decode_step(const cxxattn_mha_desc* desc, const float* q, const float* k, const float* v,
+                            float* K_cache, float* V_cache, int64_t pos, float* o, void* workspace,
+                            size_t workspace_bytes, cxxattn_stream_t stream);
+
 /* ---- elementwise neighbours that share the reference headers ------------------------------ */
 
 /* phi[n,d] = ELU(x[n,d])+1 for d<E, 0 for E<=d<D.  linear_cuda::phi_elu_forward (lin.cuh:39-42,

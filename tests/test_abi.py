@@ -56,6 +56,14 @@ def test_bad_arguments_are_rejected_without_a_device(pkg):
     assert lib.cxxattn_rope_cast(one, 0, one, 1, 1, 1, 8, 6, 1.0, None) == -1   # head_dim % 4
     assert lib.cxxattn_rope_cast(one, 0, one, 1, 1, 1, 12, 8, 1.0, None) == -1  # D % head_dim
     assert lib.cxxattn_phi_elu_fwd(one, one, 4, 2, 4, None) == -1   # E > D
+    dec = pkg.mha_desc(2, 16, 2, 8)
+    assert lib.cxxattn_mha_decode_step(C.byref(dec), one, one, one, one, one, 16, one, None, 0, None) == -1  # pos >= S
+    assert lib.cxxattn_mha_decode_step(C.byref(dec), one, one, one, None, one, 0, one, None, 0, None) == -1
+    assert lib.cxxattn_mha_decode_workspace_bytes(C.byref(dec)) == 0   # 16 keys never need a split
+    long = pkg.mha_desc(1, 8192, 2, 64)
+    assert lib.cxxattn_mha_decode_workspace_bytes(C.byref(long)) > 0
+    assert lib.cxxattn_mha_decode_step(C.byref(long), one, one, one, one, one, 8000, one, None, 0, None) == -3
+    assert lib.cxxattn_linattn_decode_step(C.byref(ld), one, one, one, None, one, one, None, None) == -1
     assert lib.cxxattn_gelu_exact(one, one, 0, 0, None) == -1
 
 
