@@ -1,6 +1,6 @@
 // CXX-GPT's LinearGPT (src/LinearAttention/linear_gpt.hpp, included unmodified) on synthetic token
 // ids, with its numerical gradient check (linear_gpt.hpp:554-610); see model_check.hpp.
-//   linear_gpt_check [B] [S] [n_embd] [n_layer] [vocab] [steps]
+//   linear_gpt_check [B] [S] [n_embd] [n_layer] [vocab] [steps] [learning rate]
 #include <cstdlib>
 
 #include "LinearAttention/linear_gpt.hpp"
@@ -17,7 +17,8 @@ int main(int argc, char** argv) {
     try {
         RNG rng(4321);
         LinearGPT model(cfg, rng);
-        return run_model_check(model, linear_numerical_grad_check, rng, B, S, cfg.vocab_size, arg(6, 8));
+        return run_model_check(model, linear_numerical_grad_check, rng, B, S, cfg.vocab_size, arg(6, 8),
+                               argc > 7 ? std::strtof(argv[7], nullptr) : 3e-3f);
     } catch (const std::exception& e) {
         std::fprintf(stderr, "error: %s\n", e.what());
         return 1;

@@ -11,7 +11,8 @@
 #include <vector>
 
 template <class Model, class GradCheck>
-int run_model_check(Model& model, GradCheck grad_check, RNG& rng, size_t B, size_t S, size_t vocab, size_t steps) {
+int run_model_check(Model& model, GradCheck grad_check, RNG& rng, size_t B, size_t S, size_t vocab, size_t steps,
+                    float lr) {
     std::vector<int> x(B * S), y(B * S);
     for (size_t i = 0; i < B * S; i++) {
         x[i] = rng.randint(0, (int)vocab - 1);
@@ -32,7 +33,7 @@ int run_model_check(Model& model, GradCheck grad_check, RNG& rng, size_t B, size
     for (auto& [name, p] : model.named_parameters())
         std::printf("digest gradnorm %s = %.7g\n", name.c_str(), std::sqrt(gpt_cuda::grad_norm_squared(p->grad)));
 
-    AdamW opt(model.parameters(), 3e-3f);
+    AdamW opt(model.parameters(), lr);
     for (size_t s = 0; s < steps; s++) {
         auto lgs = model.forward(x, B, S);
         auto [l, dl] = cross_entropy_loss(lgs, y);

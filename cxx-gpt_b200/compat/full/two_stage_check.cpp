@@ -1,6 +1,6 @@
 // CXX-GPT's TwoStageGPT (src/TwoStage/two_stage_gpt.hpp, included unmodified) on synthetic token
 // ids, with its numerical gradient check (two_stage_gpt.hpp:547-604); see model_check.hpp.
-//   two_stage_check [B] [S] [n_embd] [n_head] [N] [vocab] [steps]
+//   two_stage_check [B] [S] [n_embd] [n_head] [N] [vocab] [steps] [learning rate]
 #include <cstdlib>
 
 #include "TwoStage/two_stage_gpt.hpp"
@@ -18,7 +18,8 @@ int main(int argc, char** argv) {
     try {
         RNG rng(1234);
         TwoStageGPT model(cfg, rng);
-        return run_model_check(model, two_stage_numerical_grad_check, rng, B, S, cfg.vocab_size, arg(7, 8));
+        return run_model_check(model, two_stage_numerical_grad_check, rng, B, S, cfg.vocab_size, arg(7, 8),
+                               argc > 8 ? std::strtof(argv[8], nullptr) : 3e-3f);
     } catch (const std::exception& e) {
         std::fprintf(stderr, "error: %s\n", e.what());
         return 1;

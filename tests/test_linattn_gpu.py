@@ -103,6 +103,18 @@ def test_ragged_shapes(pkg, dev, orc, B, S, D, E):
     check_two_stage(pkg, dev, orc, Q, K, V, dO, B, S, D, E)
 
 
+@pytest.mark.parametrize("B,S,E", [(2, 64, 768), (2, 64, 384), (2, 100, 320), (8, 256, 768)])
+def test_model_width_single_head(pkg, dev, orc, B, S, E):
+    """Stage 2 of TwoStageGPT is one head over the whole embedding (two_stage_gpt.hpp:113-122): D = E =
+    n_embd, 768 in the full-size configuration.  Only the CPU functions can pin these widths: the
+    reference's own CUDA kernels return O, dQ and dK that are off by their own magnitude from its CPU
+    functions for E = 320, 384 and 768 (same tensors, same GPU), while den and dV agree."""
+    Q, K, V, dO = seeded_normal(90 + E, [(B * S, E), (B * S, E), (B * S, E), (B * S, E)])
+    Q *= 0.5
+    K *= 0.5
+    check_two_stage(pkg, dev, orc, Q, K, V, dO, B, S, E, E)
+
+
 def run_linear_gpt(pkg, dev, xq, xk, V, dO, B, S, D, E):
     """LinearBlock::forward / backward call sequence (linear_gpt.hpp:100-112, 154-172): phi outside,
     scan on the mapped features, phi backward outside."""
