@@ -37,6 +37,13 @@ WORKLOADS = {  # name -> (B, S): B*S = 65536 tokens
     "linattn_s4096": (16, 4096),
     "linattn_s16384": (4, 16384),
 }
+# HBM-bound neighbours of the path (single GPU, one kernel per step, L2 flushed between steps)
+NEIGHBOURS = {
+    "rope_cast": "rotary + fp32 -> bf16 of one [65536, 768] tensor, head width 64",
+    "decode_linear": "linear-stage decoding step, 8192 units, D = E = 64 (state 16 KB per unit)",
+    "decode_linear_wide": "linear-stage decoding step, 64 units, D = E = 768 (state 2.4 MB per unit)",
+    "decode_softmax": "softmax-stage decoding step, 64 x 12 heads of 64, 4096 keys in the cache",
+}
 LIN_METRIC = "causal_linear_attn_fwd_bwd_algorithmic_gbps_per_job"
 METRIC = "causal_softmax_attn_fwd_bwd_tflops_per_job"
 UNIT = "TFLOP/s"
@@ -487,13 +494,76 @@ def run_ours_linattn(args):
         dist.destroy_process_group()
 
 
+def run_neighbours(args):
+    """One HBM-bound kernel per step on one GPU; value = algorithmic bytes / CUDA-event time."""
+    import torch
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    w = args.workload
+    if w == "rope_cast":
+        B, S, D, hd = 16, 4096, 768, 64
+        X = torch.randn(B * S, D, device=dev)
+        Y = torch.empty(B * S, D, device=dev, dtype=torch.bfloat16)
+        nbytes = X.numel() * 6
+        step, kernel = (lambda: pkg.rope_cast(X, Y, B, S, D, hd, 1.0)), "rope_cast_kernel<float, bf16>"
+    elif w in ("decode_linear", "decode_linear_wide"):
+        B, D = (8192, 64) if w == "decode_linear" else (64, 768)
+        E = D
+        q, k, v = (torch.randn(B, D, device=dev) for _ in range(3))
+        S_, z = torch.zeros(B, D, E, device=dev), torch.zeros(B, D, device=dev)
+        o, dn = torch.empty(B, E, device=dev), torch.empty(B, device=dev)
+        nbytes = B * (2 * D * (E + 1) * 4 + (2 * D + 2 * E + 1) * 4)
+        step, kernel = (lambda: pkg.linattn_decode_step(q, k, v, S_, z, o, dn, B, D, E)), "lin_decode_kernel"
+    else:
+        B, cap = 64, 4096
+        q, k, v = (torch.randn(B, H * DH, device=dev) for _ in range(3))
+        Kc, Vc = (torch.randn(B, cap, H * DH, device=dev) for _ in range(2))
+        o = torch.empty(B, H * DH, device=dev)
+        nbytes = 2 * B * cap * H * DH * 4
+        step, kernel = (lambda: pkg.mha_decode_step(q, k, v, Kc, Vc, cap - 1, o, B, cap, H, DH)), "mha_decode_kernel<2>"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    total = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    sampler.stop_flag = True
+    sampler.join()
+    ms = total / args.steps
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm, how = float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        hbm, how = 6650.0, "fallback"
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": w + "_algorithmic_gbps", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": w, "what": NEIGHBOURS[w], "bytes_per_step": nbytes,
+                                 "l2": "256 MB written between steps"},
+                      "gpu_launches": args.steps, "clocks": sampler.result(),
+                      "roofline": {"bound": "hbm", "kernel": kernel, "achieved": gbs, "peak": hbm, "peak_source": how,
+                                   "unit": "GB/s", "frac": gbs / hbm, "traffic": None}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS) + sorted(NEIGHBOURS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-cuda", action="store_true",
                     help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
@@ -501,8 +571,12 @@ def main():
                     help="element type of the linattn_* workloads (bf16: tensor-core kernels, f32: exact kernels)")
     args = ap.parse_args()
     if args.impl == "reference":
+        if args.workload in NEIGHBOURS:
+            ap.error("--impl reference covers the attention workloads only")
         args.steps = min(args.steps, 3)
         run_reference(args)
+    elif args.workload in NEIGHBOURS:
+        run_neighbours(args)
     elif args.workload.startswith("linattn"):
         run_ours_linattn(args)
     else:

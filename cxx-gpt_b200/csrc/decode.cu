@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstdint>
 
 #include "internal.cuh"
 
@@ -124,7 +125,40 @@ struct DecParams {
     float scale;
 };
 
-template <int NV>
+// NV floats of one row for this lane.  VEC (Dh == 32*NV): lane owns columns lane*NV .. lane*NV+NV-1
+// and fetches them with one 4/8/16-byte load (two for NV = 8); otherwise columns lane + 32*i.
+template <int NV, bool VEC>
+__device__ __forceinline__ void load_row(const float* __restrict__ row, int lane, int Dh, bool live, float (&x)[NV]) {
+    if constexpr (VEC) {
+        if (!live) {
+#pragma unroll
+            for (int i = 0; i < NV; i++) x[i] = 0.f;
+        } else if constexpr (NV == 1) {
+            x[0] = row[lane];
+        } else if constexpr (NV == 2) {
+            const float2 v = reinterpret_cast<const float2*>(row)[lane];
+            x[0] = v.x, x[1] = v.y;
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV / 4; j++) {
+                const float4 v = reinterpret_cast<const float4*>(row)[lane * (NV / 4) + j];
+                x[4 * j] = v.x, x[4 * j + 1] = v.y, x[4 * j + 2] = v.z, x[4 * j + 3] = v.w;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int d = lane + 32 * i;
+            x[i] = live && d < Dh ? row[d] : 0.f;
+        }
+    }
+}
+template <int NV, bool VEC>
+__device__ __forceinline__ int col_of(int lane, int i) {
+    return VEC ? lane * NV + i : lane + 32 * i;
+}
+
+template <int NV, bool VEC>
 __global__ void __launch_bounds__(DEC_WARPS * 32) mha_decode_kernel(DecParams p) {
     const int bh = blockIdx.x, split = blockIdx.y, b = bh / p.H, h = bh % p.H;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,10 +174,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) mha_decode_kernel(DecParams p)
     const int per = (nkeys + p.nsplit - 1) / p.nsplit;
     const int t0 = split * per, t1 = min(nkeys, t0 + per);
     float qv[NV], acc[NV];
+    load_row<NV, VEC>(p.q + (size_t)b * HD + h * p.Dh, lane, p.Dh, true, qv);
 #pragma unroll
     for (int i = 0; i < NV; i++) {
-        const int d = lane + 32 * i;
-        qv[i] = d < p.Dh ? p.q[(size_t)b * HD + h * p.Dh + d] * p.scale : 0.f;
+        qv[i] *= p.scale;
         acc[i] = 0.f;
     }
     float m = -INFINITY, l = 0.f;
@@ -155,13 +189,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) mha_decode_kernel(DecParams p)
             const bool fresh = t == p.pos;
             const float* kr = fresh ? knew : Krow + (size_t)t * HD;
             const float* vr = fresh ? vnew : Vrow + (size_t)t * HD;
-#pragma unroll
-            for (int i = 0; i < NV; i++) {
-                const int d = lane + 32 * i;
-                const bool in = t < t1 && d < p.Dh;
-                kv[u][i] = in ? kr[d] : 0.f;
-                vv[u][i] = in ? vr[d] : 0.f;
-            }
+            load_row<NV, VEC>(kr, lane, p.Dh, t < t1, kv[u]);
+            load_row<NV, VEC>(vr, lane, p.Dh, t < t1, vv[u]);
         }
         if (tb <= p.pos && p.pos < tb + DEC_KEYS && p.pos < t1) {  // append the new token's rows to the cache
             const int u = p.pos - tb;
@@ -170,7 +199,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) mha_decode_kernel(DecParams p)
                 if (uu != u) continue;
 #pragma unroll
                 for (int i = 0; i < NV; i++) {
-                    const int d = lane + 32 * i;
+                    const int d = col_of<NV, VEC>(lane, i);
                     if (d < p.Dh) {
                         Krow[(size_t)p.pos * HD + d] = kv[uu][i];
                         Vrow[(size_t)p.pos * HD + d] = vv[uu][i];
@@ -213,7 +242,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) mha_decode_kernel(DecParams p)
         sm_l[warp] = l;
     }
 #pragma unroll
-    for (int i = 0; i < NV; i++) sm_o[warp][lane + 32 * i] = acc[i];
+    for (int i = 0; i < NV; i++) sm_o[warp][col_of<NV, VEC>(lane, i)] = acc[i];
     __syncthreads();
     float M = -INFINITY;
     for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, sm_m[w]);
@@ -254,6 +283,83 @@ __global__ void mha_decode_merge_kernel(DecParams p) {
 
 }  // namespace
 
+// The same step with 16-byte accesses, for E % 4 == 0: the CTA's columns [e_begin, e_end) are nq
+// quads; thread (ty, tq) owns quad tq of rows d = ty, ty + R, ... (R = 256 / nq row lanes), four rows
+// in flight, and the R partial numerators of a quad meet in shared memory.
+template <bool Z_DONE>
+__global__ void __launch_bounds__(256)
+lin_decode_vec_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                      float* __restrict__ S, float* __restrict__ z, float* __restrict__ o, float* __restrict__ den,
+                      int D, int E, int map, int eps_in_den, int cols_per_cta) {
+    extern __shared__ float sm[];
+    float* pq = sm;            // phi(q) [D]
+    float* pk = sm + D;        // phi(k) [D]
+    float* part = sm + 2 * D;  // [R][nq * 4] partial numerators (at most 256 * 4 floats)
+    const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const float* qb = q + (size_t)b * D;
+    const float* kb = k + (size_t)b * D;
+    float* zb = z + (size_t)b * D;
+    float dpart = 0.f;
+    for (int d = t; d < D; d += 256) {
+        const float a = map ? phi_f(qb[d]) : qb[d], c = map ? phi_f(kb[d]) : kb[d];
+        pq[d] = a;
+        pk[d] = c;
+        float zn = zb[d];
+        if (!Z_DONE) {
+            zn += c;
+            zb[d] = zn;
+        }
+        dpart += a * zn;
+    }
+    for (int off = 16; off; off >>= 1) dpart += __shfl_xor_sync(0xffffffffu, dpart, off);
+    __shared__ float dsum[8];
+    if (lane == 0) dsum[warp] = dpart;
+    __syncthreads();
+    float dn = 0.f;
+    for (int i = 0; i < 8; i++) dn += dsum[i];
+    if (t == 0 && blockIdx.y == 0 && den != nullptr) den[b] = eps_in_den ? dn + 1e-8f : dn;
+    const float inv = 1.0f / (dn + 1e-8f);
+
+    const int e_begin = blockIdx.y * cols_per_cta;
+    const int e_end = min(E, e_begin + cols_per_cta);
+    const int nq = (e_end - e_begin) / 4;  // <= 256
+    const int R = 256 / nq;
+    const int tq = t % nq, ty = t / nq;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ty < R) {
+        float4* Sq = reinterpret_cast<float4*>(S + (size_t)b * D * E + e_begin) + tq;  // row stride E/4 quads
+        const size_t rs = (size_t)E / 4;
+        const float4 ve = reinterpret_cast<const float4*>(v + (size_t)b * E + e_begin)[tq];
+        int d = ty;
+        for (; d + 3 * R < D; d += 4 * R) {
+            float4 sv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) sv[u] = Sq[(size_t)(d + u * R) * rs];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float c = pk[d + u * R], a = pq[d + u * R];
+                sv[u].x += c * ve.x, sv[u].y += c * ve.y, sv[u].z += c * ve.z, sv[u].w += c * ve.w;
+                Sq[(size_t)(d + u * R) * rs] = sv[u];
+                acc.x += a * sv[u].x, acc.y += a * sv[u].y, acc.z += a * sv[u].z, acc.w += a * sv[u].w;
+            }
+        }
+        for (; d < D; d += R) {
+            float4 x = Sq[(size_t)d * rs];
+            const float c = pk[d], a = pq[d];
+            x.x += c * ve.x, x.y += c * ve.y, x.z += c * ve.z, x.w += c * ve.w;
+            Sq[(size_t)d * rs] = x;
+            acc.x += a * x.x, acc.y += a * x.y, acc.z += a * x.z, acc.w += a * x.w;
+        }
+        reinterpret_cast<float4*>(part)[ty * nq + tq] = acc;
+    }
+    __syncthreads();
+    for (int c = t; c < nq * 4; c += 256) {
+        float n = 0.f;
+        for (int r = 0; r < R; r++) n += part[r * nq * 4 + c];
+        o[(size_t)b * E + e_begin + c] = n * inv;
+    }
+}
+
 int linattn_decode_step(const cxxattn_lin_desc& d, const float* q, const float* k, const float* v, float* S, float* z,
                         float* o, float* den, cudaStream_t st) {
     const size_t smem = (2 * (size_t)d.D + 8 * 32) * sizeof(float);
@@ -265,23 +371,38 @@ int linattn_decode_step(const cxxattn_lin_desc& d, const float* q, const float* 
     int64_t groups = (4 * 148 + d.B - 1) / d.B;
     if (groups > tiles) groups = tiles;
     if (d.D * d.E <= 64 * 64 || groups < 1) groups = 1;
-    const int per = (int)((tiles + groups - 1) / groups);
+    int per = (int)((tiles + groups - 1) / groups);
+    // 16-byte accesses when the rows allow it; a CTA then takes at most 1024 columns (256 quads)
+    const uintptr_t all = reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(S);
+    const bool vec = d.E % 4 == 0 && all % 16 == 0;
+    if (vec && per > 32) per = 32;
     groups = (tiles + per - 1) / per;
-    if (groups == 1) {
-        lin_decode_kernel<false><<<dim3((unsigned)d.B, 1), 256, smem, st>>>(q, k, v, S, z, o, den, (int)d.D, (int)d.E, map,
-                                                                          d.eps_in_den, per);
-    } else {
+    const dim3 grid((unsigned)d.B, (unsigned)groups);
+    if (groups > 1) {
         const size_t n = (size_t)d.B * d.D;
         lin_decode_z_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(k, z, n, map);
-        lin_decode_kernel<true><<<dim3((unsigned)d.B, (unsigned)groups), 256, smem, st>>>(
-            q, k, v, S, z, o, den, (int)d.D, (int)d.E, map, d.eps_in_den, per);
+    }
+    if (vec) {
+        const size_t smem_v = (2 * (size_t)d.D + 256 * 4) * sizeof(float);
+        if (smem_v > 48 * 1024) return CXXATTN_ERR_TOO_LARGE;
+        if (groups == 1)
+            lin_decode_vec_kernel<false><<<grid, 256, smem_v, st>>>(q, k, v, S, z, o, den, (int)d.D, (int)d.E, map,
+                                                                  d.eps_in_den, per * 32);
+        else
+            lin_decode_vec_kernel<true><<<grid, 256, smem_v, st>>>(q, k, v, S, z, o, den, (int)d.D, (int)d.E, map,
+                                                                 d.eps_in_den, per * 32);
+    } else if (groups == 1) {
+        lin_decode_kernel<false><<<grid, 256, smem, st>>>(q, k, v, S, z, o, den, (int)d.D, (int)d.E, map, d.eps_in_den, per);
+    } else {
+        lin_decode_kernel<true><<<grid, 256, smem, st>>>(q, k, v, S, z, o, den, (int)d.D, (int)d.E, map, d.eps_in_den, per);
     }
     return check_launch();
 }
 
-// Key splits: enough CTAs for about four per SM, at least 256 keys per split.
+// Key splits: enough CTAs (of four warps) for about sixteen per SM, which is what keeps enough rows
+// in flight to cover the DRAM latency; at least 256 keys per split.
 int mha_decode_splits(int64_t BH, int64_t nkeys) {
-    int64_t want = (4 * 148 + BH - 1) / BH, most = (nkeys + 255) / 256;
+    int64_t want = (16 * 148 + BH - 1) / BH, most = (nkeys + 255) / 256;
     int64_t n = want < most ? want : most;
     return (int)(n < 1 ? 1 : n > 64 ? 64 : n);
 }
@@ -303,10 +424,19 @@ int mha_decode_step(const cxxattn_mha_desc& d, const float* q, const float* k, c
     if (p.nsplit > 1 && (!ws || ws_bytes < (size_t)d.B * d.H * p.nsplit * (d.Dh + 2) * sizeof(float)))
         return CXXATTN_ERR_WORKSPACE;
     const dim3 grid((unsigned)(d.B * d.H), (unsigned)p.nsplit);
-    if (d.Dh <= 32) mha_decode_kernel<1><<<grid, DEC_WARPS * 32, 0, st>>>(p);
-    else if (d.Dh <= 64) mha_decode_kernel<2><<<grid, DEC_WARPS * 32, 0, st>>>(p);
-    else if (d.Dh <= 128) mha_decode_kernel<4><<<grid, DEC_WARPS * 32, 0, st>>>(p);
-    else mha_decode_kernel<8><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+    // vector loads: whole rows of 32*NV floats, and every tensor on a 16-byte boundary
+    const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                          reinterpret_cast<uintptr_t>(Kc) | reinterpret_cast<uintptr_t>(Vc);
+    const bool vec = (d.Dh == 32 || d.Dh == 64 || d.Dh == 128 || d.Dh == 256) && all % 16 == 0;
+    if (vec) {
+        if (d.Dh == 32) mha_decode_kernel<1, true><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+        else if (d.Dh == 64) mha_decode_kernel<2, true><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+        else if (d.Dh == 128) mha_decode_kernel<4, true><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+        else mha_decode_kernel<8, true><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+    } else if (d.Dh <= 32) mha_decode_kernel<1, false><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+    else if (d.Dh <= 64) mha_decode_kernel<2, false><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+    else if (d.Dh <= 128) mha_decode_kernel<4, false><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+    else mha_decode_kernel<8, false><<<grid, DEC_WARPS * 32, 0, st>>>(p);
     if (p.nsplit > 1) mha_decode_merge_kernel<<<(unsigned)(d.B * d.H), 64, 0, st>>>(p);
     return check_launch();
 }

@@ -73,3 +73,21 @@ def test_softmax_stage_long_cache_takes_key_splits(pkg, dev, orc):
         pkg.mha_decode_step(tq[:, t].contiguous(), tk[:, t].contiguous(), tv[:, t].contiguous(), Kc, Vc, t, o,
                             B, T, H, Dh)
         assert rel_err(o.cpu().numpy(), O.reshape(B, T, H * Dh)[:, t]) < 1e-5
+
+
+def test_softmax_stage_unaligned_rows_take_the_scalar_loads(pkg, dev, orc):
+    """Head dimension 64 normally uses 8-byte loads; a query that does not start on a 16-byte
+    boundary must give the same numbers through the scalar path."""
+    B, T, H, Dh = 2, 21, 2, 64
+    Q, K, V = seeded_normal(91, [(B * T, H * Dh)] * 3)
+    O = orc.mha_fwd(Q, K, V, B, T, H, Dh).reshape(B, T, H * Dh)
+    tq, tk, tv = (torch.from_numpy(x.reshape(B, T, H * Dh)).to(dev) for x in (Q, K, V))
+    Kc, Vc = torch.zeros(B, T, H * Dh, device=dev), torch.zeros(B, T, H * Dh, device=dev)
+    Kc[:, :T - 1], Vc[:, :T - 1] = tk[:, :T - 1], tv[:, :T - 1]
+    pad = torch.zeros(B * H * Dh + 1, device=dev)
+    q_off = pad[1:]                      # 4 bytes past a 16-byte boundary
+    q_off.copy_(tq[:, T - 1].reshape(-1))
+    assert q_off.data_ptr() % 16 == 4
+    o = torch.empty(B, H * Dh, device=dev)
+    pkg.mha_decode_step(q_off, tk[:, T - 1].contiguous(), tv[:, T - 1].contiguous(), Kc, Vc, T - 1, o, B, T, H, Dh)
+    assert rel_err(o.cpu().numpy(), O[:, T - 1]) < 1e-5
