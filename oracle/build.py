@@ -134,6 +134,33 @@ def build_model_checks(reference=DEFAULT_REFERENCE, force=False):
     return outs
 
 
+def build_gpt_block_check(reference=DEFAULT_REFERENCE, force=False):
+    """Compiles cxx-gpt_b200/compat/full/gpt_block_attention_check.cpp with the reference's
+    src/GPT/gpt_cuda_kernels.cu (its mask and softmax-backward kernels, unmodified, where it lies), the
+    TensorN stand-in and this repository's adapter into oracle/_ref/gpt_block_attention_check."""
+    root = os.path.dirname(HERE)
+    pkg = os.path.join(root, "cxx-gpt_b200")
+    full = os.path.join(pkg, "compat", "full")
+    out = os.path.join(HERE, "_ref", "gpt_block_attention_check")
+    src = os.path.join(reference, "src")
+    gpt_cu = os.path.join(src, "GPT", "gpt_cuda_kernels.cu")
+    if not os.path.exists(gpt_cu):
+        return out if os.path.exists(out) else None
+    main = os.path.join(full, "gpt_block_attention_check.cpp")
+    ops = os.path.join(full, "tensorn_ops.cu")
+    adapter = os.path.join(pkg, "compat", "cxxgpt_kernels.cpp")
+    deps = [main, ops, gpt_cu, adapter, os.path.join(full, "TensorN.hpp"), os.path.join(pkg, "compat", "TensorN.hpp"),
+            os.path.join(pkg, "libcxxattn.so"), os.path.join(root, "include", "cxxattn.h")]
+    if force or _stale(out, deps):
+        os.makedirs(os.path.dirname(out), exist_ok=True)
+        subprocess.check_call(["nvcc", "-std=c++17", "-O2", "-gencode", "arch=compute_100,code=sm_100",
+                               "-Wno-deprecated-gpu-targets", "-I", full, "-I", src, "-I", os.path.join(src, "GPT"),
+                               "-I", os.path.join(root, "include"), "-o", out, main, ops, gpt_cu, adapter,
+                               "-L", pkg, "-lcxxattn", "-lcublas", "-Xlinker", "-rpath", "-Xlinker",
+                               "$ORIGIN/../../cxx-gpt_b200"])
+    return out
+
+
 if __name__ == "__main__":
     ref = DEFAULT_REFERENCE
     if "--reference" in sys.argv:
@@ -143,3 +170,4 @@ if __name__ == "__main__":
     print(build_dropin_kernel_test(ref, force="--force" in sys.argv))
     print(build_reference_cuda(ref, force="--force" in sys.argv))
     print(build_model_checks(ref, force="--force" in sys.argv))
+    print(build_gpt_block_check(ref, force="--force" in sys.argv))
