@@ -198,6 +198,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     B, S = WORKLOADS[args.workload]
+    if args.strong:  # fixed total work: the batch items are dealt out over the ranks
+        if B % world:
+            raise SystemExit(f"--strong needs the batch ({B}) to divide over {world} ranks")
+        B //= world
     N = B * S
     gen = torch.Generator(device="cpu").manual_seed(3 + rank)
     hQ, hK, hV, hdO = (torch.randn(N, H * DH, generator=gen).bfloat16().pin_memory() for _ in range(4))
@@ -206,9 +210,20 @@ def run_ours(args):
     O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
     lse = torch.empty(B * H * S, device=dev)
 
+    # A per-rank working set below twice the L2 (only with --strong on many ranks) is rotated over
+    # copies, so that no step finds the tensors of the step before in the 126 MB L2.
+    set_bytes = 8 * N * H * DH * 2
+    nset = max(1, -(-(2 * 126 << 20) // set_bytes))
+    sets = [(Q, K, V, dO, O, dQ, dK, dV, lse)]
+    for _ in range(nset - 1):
+        sets.append(tuple(torch.empty_like(t).copy_(t) for t in sets[0]))
+    turn = [0]
+
     def step():
-        pkg.mha_fwd(Q, K, V, O, B, S, H, DH, lse=lse)
-        pkg.mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, DH, lse=lse)
+        q_, k_, v_, g_, o_, dq_, dk_, dv_, l_ = sets[turn[0] % nset]
+        turn[0] += 1
+        pkg.mha_fwd(q_, k_, v_, o_, B, S, H, DH, lse=l_)
+        pkg.mha_bwd(q_, k_, v_, o_, g_, dq_, dk_, dv_, B, S, H, DH, lse=l_)
 
     def barrier():
         torch.cuda.synchronize()
@@ -307,10 +322,11 @@ def run_ours(args):
         nbytes = 4 * N * H * DH * 2
         line = {"metric": METRIC, "value": world * fl / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "scaling": "strong" if args.strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": args.workload, "B_per_gpu": B, "S": S, "H": H, "Dh": DH,
                            "tokens_per_gpu": N, "sharding": "(batch, head) units per rank, no collective",
-                           "l2": "inputs+outputs 8 x %.0f MB per step exceed the 126 MB L2" % (N * H * DH * 2 / 1e6)},
+                           "l2": ("inputs+outputs 8 x %.0f MB per step exceed the 126 MB L2" % (N * H * DH * 2 / 1e6)) if nset == 1
+                           else "steps rotate over %d copies of the 8 x %.0f MB working set" % (nset, N * H * DH * 2 / 1e6)},
                 "tokens_per_s": world * N / (ms * 1e-3),
                 "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                 "fwd_tflops": fl / 3.5 / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": bwd_tf,
@@ -565,6 +581,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS) + sorted(NEIGHBOURS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--strong", action="store_true",
+                    help="softmax workloads: keep the total batch fixed and give each rank B / N items (default: "
+                         "every rank runs the whole per-GPU workload, weak scaling)")
     ap.add_argument("--no-reference-cuda", action="store_true",
                     help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
     ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
