@@ -26,6 +26,7 @@
 // are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
 // when it grows by more than 8 (in log2 units), so the rescaling of O in TMEM is rare.
 #include <algorithm>
+#include <cstdlib>
 
 #include "internal.cuh"
 #include "tc_common.cuh"
@@ -42,6 +43,7 @@ constexpr int STAGES = 3;
 constexpr int TILE_BYTES = BM * DH * 2;  // 16 KB: one 128 x 64 bf16 tile
 constexpr int NTHREADS = 384;  // 12 warps: 8 softmax, producer, MMA issuer, 2 idle (they only give up registers)
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int LATE_FROM = 96;  // key tiles per row from which the softmax warps wait late for PV
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 constexpr size_t SMEM_BYTES = (4 + 2 * STAGES) * TILE_BYTES + 1024;  // Q x2 (2 tiles each), K/V ring, alignment slack
 
@@ -76,6 +78,9 @@ __device__ __forceinline__ bool get_item(int round, int npairs, int nbh, int S, 
     return true;
 }
 
+// LATE_WAIT: the softmax warps form the first half of a step's exponentials before they wait for
+// the PV product of the step before (faster on long rows, slower on short ones; the host picks).
+template <bool LATE_WAIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -294,23 +299,24 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
                 const float m_use = raise ? m_new : m;
                 const float alpha = raise ? ex2(m - m_new) : 1.0f;
-                if (j > 0) {
-                    mbar_wait(&pv_done[t], (cj - 1) & 1, guard, 305 + t);  // O_t stable, P_t free
+                // O_t must be stable and P_t free before this step's P is stored (and before a rescaling
+                // of O_t): wait for the PV product of the step before, here or after half the exponentials
+                auto settle = [&]() {
+                    mbar_wait(&pv_done[t], (cj - 1) & 1, guard, 305 + t);
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, raise)) {
-                        uint32_t o0[32], o1[32];
-                        tmem_ld32(tO, o0);
-                        tmem_ld32(tO + 32, o1);
-                        tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-                            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+                        for (int h = 0; h < 2; h++) {
+                            uint32_t o[32];
+                            tmem_ld32(tO + 32 * h, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(tO + 32 * h, o);
                         }
-                        tmem_st32(tO, o0);
-                        tmem_st32(tO + 32, o1);
                     }
-                }
+                };
+                if (!LATE_WAIT && j > 0) settle();
                 // (j == 0: P_t is free since the epilogue of the item before waited for its last PV)
                 m = m_use;
                 // pass 2: P = exp2(c*S - m) as bf16 pairs (masked scores are -inf and give 0); the
@@ -334,6 +340,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         pk[i / 2] = pack_bf16(a0, a1);
                         pk[16 + i / 2] = pack_bf16(b0, b1);
                     }
+                    if (LATE_WAIT && c == 0 && j > 0) settle();
                     tmem_st32(tP + 32 * c, pk);
                 }
                 float rs, rs_hi;
@@ -414,8 +421,10 @@ int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, v
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(mha_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(mha_tc_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(mha_tc_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SMEM_BYTES) != cudaSuccess)
             return CXXATTN_ERR_CUDA;
         attr_set[dev] = true;
     }
@@ -427,7 +436,11 @@ int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, v
     const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
     const int64_t items = (int64_t)npairs * p.B * p.H;
     const int64_t grid = std::min<int64_t>(items, (dev >= 0 && dev < 64 && nsm[dev] > 0) ? nsm[dev] : 148);
-    mha_tc_fwd_kernel<<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
+    // measured on B200: waiting late wins from about LATE_FROM key tiles per row on (CXXATTN_FWD_LATE_WAIT=0/1 forces)
+    bool late = (p.S + BN - 1) / BN >= LATE_FROM;
+    if (const char* e = std::getenv("CXXATTN_FWD_LATE_WAIT")) late = e[0] == '1';
+    if (late) mha_tc_fwd_kernel<true><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
+    else mha_tc_fwd_kernel<false><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
     return check_launch();
 }
 
