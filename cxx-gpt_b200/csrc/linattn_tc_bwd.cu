@@ -21,6 +21,8 @@
 // As in the forward, the states stay in TMEM (fp32) for the whole sequence and are copied as bf16
 // into shared memory once per chunk to serve as matrix operands.
 #include "linattn_tc_common.cuh"
+#include <cstdlib>
+#include <mutex>
 
 namespace cxxattn {
 namespace {
@@ -563,6 +565,34 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 
 }  // namespace
 
+namespace {
+// A side stream per device for the suffix-state pre-pass.  Only the dK/dV pass needs that state, so
+// the pre-pass runs beside the prefix pre-pass and the dQ pass, in the SMs their last waves leave
+// idle.  Fork and join are events on the caller's stream: its order is kept and the call stays
+// capturable.  The events are shared by all calls on a device, so enqueueing is serialised.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    int state = 0;  // 0 not tried, 1 usable, -1 unavailable
+};
+std::mutex g_side_mutex;
+SideStream* side_stream(int dev) {
+    static SideStream tab[64];
+    if (dev < 0 || dev >= 64) return nullptr;
+    SideStream& s = tab[dev];
+    if (s.state == 0) {
+        const char* e = std::getenv("CXXATTN_LIN_SIDE_STREAM");
+        const bool on = !(e && e[0] == '0');
+        s.state = on && cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
+                          cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess &&
+                          cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess
+                      ? 1
+                      : -1;
+    }
+    return s.state == 1 ? &s : nullptr;
+}
+}  // namespace
+
 int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O,
                    const void* dO, const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes,
                    cudaStream_t st) {
@@ -597,14 +627,23 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
     float* gss = plan.G > 1 ? reinterpret_cast<float*>(static_cast<char*>(ws) + plan.state_bytes) : nullptr;
     p.sgp = SeqGroups{gsp, plan.G, plan.gc};
     p.sgs = SeqGroups{gss, plan.G, plan.gc};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::unique_lock<std::mutex> side_lock(g_side_mutex, std::defer_lock);
+    SideStream* side = nullptr;
     if (plan.G > 1) {
+        side_lock.lock();
+        side = side_stream(dev);
+        if (side && (cudaEventRecord(side->fork, st) != cudaSuccess ||
+                     cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess))
+            side = nullptr;
         int rc = linattn_tc_group_states(0, plan, B, S, p.map_elu, K, V, nullptr, nullptr, gsp, st);
-        if (rc == CXXATTN_OK) rc = linattn_tc_group_states(1, plan, B, S, p.map_elu, Q, dO, O, den, gss, st);
+        if (rc == CXXATTN_OK)
+            rc = linattn_tc_group_states(1, plan, B, S, p.map_elu, Q, dO, O, den, gss, side ? side->stream : st);
+        if (side && cudaEventRecord(side->join, side->stream) != cudaSuccess) rc = CXXATTN_ERR_CUDA;
         if (rc != CXXATTN_OK) return rc;
     }
     static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(linattn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM1_BYTES) != cudaSuccess ||
@@ -615,6 +654,7 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
     }
     linattn_tc_bwd_dq_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM1_BYTES, st>>>(tmK, tmV, tmG, p);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+    if (side && cudaStreamWaitEvent(st, side->join, 0) != cudaSuccess) return CXXATTN_ERR_CUDA;
     linattn_tc_bwd_dkdv_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM2_BYTES, st>>>(tmQ, tmK, tmV, tmG, p);
     return check_launch();
 }
