@@ -4,9 +4,10 @@
 
 A step is one forward + backward pass of causal softmax attention over one batch of synthetic
 bf16 inputs (the long-sequence configuration: 12 heads x 64, B*S = 65536 tokens, S = 4096 by
-default).  With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the
-same per-GPU workload on its own shard of (batch, head) units; nothing is exchanged between
-ranks (weak scaling), the timed region is bracketed by barriers and the slowest rank counts.
+default).  With N > 1 (launched by torch.distributed.run, one rank per GPU) the workload's
+(batch, head) units are dealt over the ranks (cxx-gpt_b200/sharding.py; fixed total work, "strong"
+scaling; --weak gives every rank the whole workload instead); nothing is exchanged between ranks,
+the timed region is bracketed by barriers and the slowest rank counts.
 
 One JSON line is printed by rank 0.  `value` is device-resident throughput (CUDA events),
 `e2e` the same metric through the host-buffer entry point with the copies inside the timed
@@ -116,77 +117,97 @@ def host_threads():
         return max(1, os.cpu_count() or 1)
 
 
-def cpu_sample(B, S, threads=None, units=None):
-    """Times the CPU oracle (fp32, the reference's operation order) on `units` (batch, head) units
-    of the workload, one per host thread by default.  Returns (TFLOP/s, cores, description)."""
+def load_traffic(kernel):
+    """DRAM bytes per unit of work of `kernel`, from the table that is written next to the profiler
+    summaries whenever a capture is refreshed (profiles/traffic.json: bytes of one captured launch
+    and the units that launch processed).  None when the table has no entry for the kernel."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            e = json.load(f)[kernel]
+        return float(e["dram_bytes_per_launch"]) / float(e["units_per_launch"])
+    except Exception:
+        return None
+
+
+def job_config(workload, world, weak):
+    """The `config` object of the JSON line; a function of the command line alone, so that the GPU arm
+    and the reference arm of one (workload, N) print the same object."""
+    B, S = WORKLOADS[workload]
+    mult = world if weak else 1
+    per_rank_mb = 8 * B * S * H * DH * 2 / (1 if weak else world) / 1e6
+    l2 = ("inputs+outputs of a step (%.0f MB per rank) exceed the 126 MB L2" % per_rank_mb) if per_rank_mb > 252 else \
+        ("steps rotate over copies of the %.0f MB per-rank working set, so no step starts from a warm L2" % per_rank_mb)
+    if workload.startswith("linattn"):
+        return {"workload": workload, "units": B * H * mult, "S": S, "D": DH, "E": DH, "tokens": B * S * mult,
+                "feature_map": "elu+1", "n_ranks": world,
+                "sharding": "contiguous ranges of units per rank, no collective", "l2": l2}
+    return {"workload": workload, "B": B * mult, "S": S, "H": H, "Dh": DH, "tokens": B * S * mult, "n_ranks": world,
+            "sharding": "(batch, head) units dealt over the ranks in contiguous ranges (whole batch items, or head "
+                        "ranges of one addressed in place through strides), no collective", "l2": l2}
+
+
+def cpu_sample(workload, S, seed=3):
+    """Times the CPU oracle (fp32, the reference's operation order) forward + backward on one unit
+    per host thread of `workload` (sequences cut to S), all host threads.  Returns
+    (metric value, cores, seconds, description)."""
     import numpy as np
     import oracle
     orc = oracle.Oracle()
-    cores = threads or host_threads()
+    cores = host_threads()
     orc.set_threads(cores)
-    units = units or cores
-    rng = np.random.default_rng(3)
+    units = cores
+    B = WORKLOADS[workload][0]
+    rng = np.random.default_rng(seed)
     Q, K, V, dO = (rng.standard_normal((units * S, DH)).astype(np.float32) for _ in range(4))
+    if workload.startswith("linattn"):
+        t0 = time.perf_counter()
+        O, den, _ = orc.linattn_fwd(Q, K, V, units, S, DH, DH)
+        orc.kernel_attn_bwd(Q, K, V, O, dO, den, units, S, DH, DH)
+        dt = time.perf_counter() - t0
+        return (lin_bytes_fwd_bwd(units, S, DH, DH) / dt / 1e9, cores, dt,
+                f"{units} of {B * H} units of S={S}, D=E={DH}, fp32 oracle, fwd+bwd")
     t0 = time.perf_counter()
     O = orc.mha_fwd(Q, K, V, units, S, 1, DH)
     orc.mha_bwd(Q, K, V, O, dO, units, S, 1, DH)
     dt = time.perf_counter() - t0
-    tf = 7.0 * units * S * S * DH / dt / 1e12
-    return tf, cores, dt, f"{units} of {B * H} (batch, head) units of S={S}, Dh={DH}, fp32 oracle, fwd+bwd"
+    return (7.0 * units * S * S * DH / dt / 1e12, cores, dt,
+            f"{units} of {B * H} (batch, head) units of S={S}, Dh={DH}, fp32 oracle, fwd+bwd")
 
 
 def run_reference(args):
+    """The reference arm: the CPU oracle port of the reference math on the host cores, rank 0 only.
+    Every step is the same bounded sample of the workload (one unit per host thread, sequences cut
+    at 4096 so that a step stays within seconds); `value` is the median over the steps."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
     B, S = WORKLOADS[args.workload]
-    # bounded sample: one unit per core and step; S=16384 units are cut to keep a step in seconds
-    s_eff = min(S, 4096)
     lin = args.workload.startswith("linattn")
-
-    def sample(s_len):
-        if not lin:
-            return cpu_sample(B, s_len)
-        import numpy as np
-        import oracle
-        orc = oracle.Oracle()
-        units = host_threads()
-        orc.set_threads(units)
-        rng = np.random.default_rng(3)
-        q, k, v, g_ = (rng.standard_normal((units * s_len, DH)).astype(np.float32) for _ in range(4))
-        t0 = time.perf_counter()
-        o, dn, _ = orc.linattn_fwd(q, k, v, units, s_len, DH, DH)
-        orc.kernel_attn_bwd(q, k, v, o, g_, dn, units, s_len, DH, DH)
-        dt = time.perf_counter() - t0
-        return (lin_bytes_fwd_bwd(units, s_len, DH, DH) / dt / 1e9, units, dt,
-                f"{units} of {B * H} units of S={s_len}, D=E={DH}, fp32 oracle, fwd+bwd")
-    for _ in range(min(args.warmup, 1)):
-        sample(min(S, 512))
+    for _ in range(args.warmup):
+        cpu_sample(args.workload, min(S, 512))
     vals, times = [], []
     desc, cores = "", 1
     for _ in range(args.steps):
-        tf, cores, dt, desc = sample(s_eff)
-        vals.append(tf)
+        v, cores, dt, desc = cpu_sample(args.workload, min(S, 4096))
+        vals.append(v)
         times.append(dt)
-    value = sum(vals) / len(vals)
-    METRIC, UNIT = (LIN_METRIC, "GB/s") if lin else (globals()["METRIC"], globals()["UNIT"])
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+    value = sorted(vals)[len(vals) // 2]
+    metric, unit = (LIN_METRIC, "GB/s") if lin else (METRIC, UNIT)
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sorted(times)[len(times) // 2],
+            "higher_is_better": True, "scaling": "weak" if args.weak else "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "gpu_launches": 0,
-            "config": {"workload": args.workload, "B": B, "S": S, "H": H, "Dh": DH,
-                       "note": "CPU oracle port of the reference math on host cores; each step is a bounded sample"},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "config": job_config(args.workload, world, args.weak),
+            "note": "CPU oracle port of the reference math on host cores (rank 0 only); each step is a bounded sample",
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args):
+def init_ranks():
     import torch
     import torch.distributed as dist
-    import __graft_entry__ as g
-    pkg = g.load_package()
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -196,34 +217,64 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    return world, rank, local, dev
 
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    from cxx_gpt_b200 import sharding
+
+    world, rank, local, dev = init_ranks()
     B, S = WORKLOADS[args.workload]
-    if args.strong:  # fixed total work: the batch items are dealt out over the ranks
-        if B % world:
-            raise SystemExit(f"--strong needs the batch ({B}) to divide over {world} ranks")
-        B //= world
-    N = B * S
+    # Fixed total (default): the B*H (batch, head) units of the workload are dealt over the ranks.
+    # --weak: every rank runs the whole workload on data of its own.
+    calls = [(0, B, 0, H)] if args.weak else sharding.calls(B, H, world, rank)
     gen = torch.Generator(device="cpu").manual_seed(3 + rank)
-    hQ, hK, hV, hdO = (torch.randn(N, H * DH, generator=gen).bfloat16().pin_memory() for _ in range(4))
-    hO, hdQ, hdK, hdV = (torch.empty(N, H * DH, dtype=torch.bfloat16).pin_memory() for _ in range(4))
-    Q, K, V, dO = (t.to(dev) for t in (hQ, hK, hV, hdO))
-    O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
-    lse = torch.empty(B * H * S, device=dev)
 
-    # A per-rank working set below twice the L2 (only with --strong on many ranks) is rotated over
-    # copies, so that no step finds the tensors of the step before in the 126 MB L2.
-    set_bytes = 8 * N * H * DH * 2
-    nset = max(1, -(-(2 * 126 << 20) // set_bytes))
-    sets = [(Q, K, V, dO, O, dQ, dK, dV, lse)]
-    for _ in range(nset - 1):
-        sets.append(tuple(torch.empty_like(t).copy_(t) for t in sets[0]))
+    # One record per kernel call of a step.  A call over whole batch items has dense tensors; a head
+    # range of one batch item lives inside full-width rows [S, H*Dh] and is addressed through strides.
+    class Call:
+        pass
+    work = []
+    for b0, nb, h0, nh in calls:
+        c = Call()
+        c.nb, c.nh, c.h0 = nb, nh, h0
+        c.host_in = [torch.randn(nb * S, nh * DH, generator=gen).bfloat16().pin_memory() for _ in range(4)]
+        c.host_out = [torch.empty(nb * S, nh * DH, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+        c.strides = None if nh == H else (S * H * DH, H * DH, DH)
+        work.append(c)
+    units_rank = sum(c.nb * c.nh for c in work)
+    set_bytes = 8 * units_rank * S * DH * 2
+    # A per-rank working set below twice the L2 (fixed total on many ranks) is rotated over copies,
+    # so that no step finds the tensors of the step before in the 126 MB L2.
+    nset = max(1, -(-(2 * 126 << 20) // max(set_bytes, 1)))
+
+    def device_set(c):
+        full = [torch.zeros(c.nb * S, H * DH, dtype=torch.bfloat16, device=dev) for _ in range(8)] if c.strides else None
+        if c.strides:
+            t = [f[:, c.h0 * DH:(c.h0 + c.nh) * DH] for f in full]
+            for v, h in zip(t[:4], c.host_in):
+                v.copy_(h)
+        else:
+            t = [h.to(dev) for h in c.host_in] + [torch.empty(c.nb * S, H * DH, dtype=torch.bfloat16, device=dev)
+                                                  for _ in range(4)]
+        return t + [torch.empty(c.nb * c.nh * S, device=dev)]  # Q K V dO O dQ dK dV lse
+    for c in work:
+        c.sets = [device_set(c) for _ in range(nset)]
     turn = [0]
 
+    def run_call(c, t):
+        q_, k_, v_, g_, o_, dq_, dk_, dv_, l_ = t
+        pkg.mha_fwd(q_, k_, v_, o_, c.nb, S, c.nh, DH, lse=l_, strides=c.strides)
+        pkg.mha_bwd(q_, k_, v_, o_, g_, dq_, dk_, dv_, c.nb, S, c.nh, DH, lse=l_, strides=c.strides)
+
     def step():
-        q_, k_, v_, g_, o_, dq_, dk_, dv_, l_ = sets[turn[0] % nset]
+        for c in work:
+            run_call(c, c.sets[turn[0] % nset])
         turn[0] += 1
-        pkg.mha_fwd(q_, k_, v_, o_, B, S, H, DH, lse=l_)
-        pkg.mha_bwd(q_, k_, v_, o_, g_, dq_, dk_, dv_, B, S, H, DH, lse=l_)
 
     def barrier():
         torch.cuda.synchronize()
@@ -249,40 +300,50 @@ def run_ours(args):
     ms = e0.elapsed_time(e1) / args.steps
     pkg.sync_status()
 
-    # ---- per-kernel split (forward call, backward call) for the roofline ----
+    # ---- per-kernel split (forward call, backward call, backward main kernel) on the first call ----
     ef = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
     for e in ef:
         e.record()  # creates the underlying CUDA events
     fwd_ms = bwd_ms = bwd_main_ms = 0.0
     reps = max(3, min(args.steps, 10))
+    c0 = work[0]
     pkg.set_timing_events(ef[3], ef[4])  # recorded by the library around the main backward kernel
-    for _ in range(reps):
+    for i in range(reps):
+        q_, k_, v_, g_, o_, dq_, dk_, dv_, l_ = c0.sets[i % nset]
         ef[0].record()
-        pkg.mha_fwd(Q, K, V, O, B, S, H, DH, lse=lse)
+        pkg.mha_fwd(q_, k_, v_, o_, c0.nb, S, c0.nh, DH, lse=l_, strides=c0.strides)
         ef[1].record()
-        pkg.mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, DH, lse=lse)
+        pkg.mha_bwd(q_, k_, v_, o_, g_, dq_, dk_, dv_, c0.nb, S, c0.nh, DH, lse=l_, strides=c0.strides)
         ef[2].record()
         torch.cuda.synchronize()
         fwd_ms += ef[0].elapsed_time(ef[1]) / reps
         bwd_ms += ef[1].elapsed_time(ef[2]) / reps
         bwd_main_ms += ef[3].elapsed_time(ef[4]) / reps
     pkg.set_timing_events(None, None)
+    units_c0 = c0.nb * c0.nh
 
     # ---- end to end: host buffers in, host buffers out, through the C-ABI host entry point ----
-    plan = pkg.HostPlan(B, S, H, DH, pkg.BF16, max(1, B // 16))  # 16 chunks: short pipeline fill and drain
+    plans = [pkg.HostPlan(c.nb, S, c.nh, DH, pkg.BF16, max(1, c.nb // 16)) for c in work]
+
+    def e2e_step():
+        for c, plan in zip(work, plans):
+            plan.fwd_bwd(*c.host_in, *c.host_out)
     for _ in range(2):
-        plan.fwd_bwd(hQ, hK, hV, hdO, hO, hdQ, hdK, hdV)
+        e2e_step()
     barrier()
     t0 = time.perf_counter()
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(e2e_steps):
-        plan.fwd_bwd(hQ, hK, hV, hdO, hO, hdQ, hdK, hdV)
+        e2e_step()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    plan.close()
+    for plan in plans:
+        plan.close()
     pkg.sync_status()
     # the end-to-end results must be the same numbers as the device-resident path
-    assert torch.equal(hO, O.cpu()), "host entry point and device path disagree"
+    run_call(c0, c0.sets[0])
+    torch.cuda.synchronize()
+    assert torch.equal(c0.host_out[0], c0.sets[0][4].cpu()), "host entry point and device path disagree"
 
     # the reference's own fp32 CUDA kernels on the same tensors (when they were built), one forward +
     # backward over the whole batch: its grid is one block per (batch, head), so a smaller sample
@@ -293,6 +354,7 @@ def run_ours(args):
         import oracle
         if rank == 0 and world == 1 and S <= 4096 and not args.no_reference_cuda and oracle.ReferenceCuda.available():
             rc = oracle.ReferenceCuda()
+            Q, K, V, dO, O = c0.sets[0][:5]
             Qf, Kf, Vf, dOf = (t_.float() for t_ in (Q, K, V, dO))
             rO, rdQ, rdK, rdV = (torch.empty_like(Qf) for _ in range(4))
             rc.mha_fwd(Qf, Kf, Vf, rO, B, S, H, DH)
@@ -315,39 +377,40 @@ def run_ours(args):
     ms, e2e_ms, fwd_ms, bwd_ms, bwd_main_ms = t.tolist()
 
     if rank == 0:
-        fl = flops_fwd_bwd(B, S)
+        mult = world if args.weak else 1
+        fl = flops_fwd_bwd(B, S) * mult          # whole job
+        fl_c0 = 7.0 * units_c0 * S * S * DH      # rank 0's first call, the one the split timings cover
         peak, peak_sustained, how = measured_peaks()
-        bwd_tf = fl * (2.5 / 3.5) / (bwd_ms * 1e-3) / 1e12
-        main_tf = fl * (2.5 / 3.5) / (bwd_main_ms * 1e-3) / 1e12
-        nbytes = 4 * N * H * DH * 2
-        line = {"metric": METRIC, "value": world * fl / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+        main_tf = fl_c0 * (2.5 / 3.5) / (bwd_main_ms * 1e-3) / 1e12
+        nbytes = 4 * B * S * H * DH * 2 * mult // world  # per rank and direction
+        per_unit = load_traffic("mha_tc_bwd_kernel")
+        line = {"metric": METRIC, "value": fl / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "strong" if args.strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": args.workload, "B_per_gpu": B, "S": S, "H": H, "Dh": DH,
-                           "tokens_per_gpu": N, "sharding": "(batch, head) units per rank, no collective",
-                           "l2": ("inputs+outputs 8 x %.0f MB per step exceed the 126 MB L2" % (N * H * DH * 2 / 1e6)) if nset == 1
-                           else "steps rotate over %d copies of the 8 x %.0f MB working set" % (nset, N * H * DH * 2 / 1e6)},
-                "tokens_per_s": world * N / (ms * 1e-3),
+                "scaling": "weak" if args.weak else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": job_config(args.workload, world, args.weak),
+                "per_rank": {"units": units_rank, "calls_per_step": len(work), "working_sets": nset},
+                "tokens_per_s": B * S * mult / (ms * 1e-3),
                 "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
-                "fwd_tflops": fl / 3.5 / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": bwd_tf,
-                "frac_of_peak_fwd_bwd": fl / (ms * 1e-3) / 1e12 / peak,
-                "gpu_launches": args.steps * 4,
+                "fwd_tflops": fl_c0 / 3.5 / (fwd_ms * 1e-3) / 1e12,
+                "bwd_tflops": fl_c0 * (2.5 / 3.5) / (bwd_ms * 1e-3) / 1e12,
+                "frac_of_peak_fwd_bwd": fl / (ms * 1e-3) / 1e12 / (peak * world),
+                "gpu_launches": args.steps * 4 * len(work) * world,
                 "clocks": sampler.result(),
-                "e2e": {"value": world * fl / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+                "e2e": {"value": fl / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world},
                 "roofline": {"bound": "tensor", "kernel": "mha_tc_bwd_kernel", "launch_ms": bwd_main_ms,
                              "achieved": main_tf, "peak": peak, "peak_sustained": peak_sustained,
                              "peak_source": how, "unit": UNIT, "frac": main_tf / peak,
-                             # dram__bytes_read + write of mha_tc_bwd_kernel from the ncu capture summarised in
-                             # profiles/mha_tc_bwd_kernel_softmax_s4096_b4.md (398.6 MB at B=4), scaled by B/4
-                             "traffic": 385.0e6 * B / 4 if S == 4096 else None}}
+                             # DRAM bytes of one launch: the profiler's figure per (batch, head) unit of a
+                             # captured smaller launch of the same sequence length, times this launch's units
+                             "traffic": per_unit * units_c0 if (per_unit and S == 4096) else None}}
         if world == 1:
             line["reference_cuda"] = {"ms_per_step": ref_ms, "speedup": (ref_ms / ms) if ref_ms else None,
                                       "max_rel_diff_O": ref_err,
                                       "what": "reference two_stage_cuda fused_mha_fwd + fused_mha_bwd, unmodified, sm_100, "
                                               "fp32, the same batch, one call"}
         if world == 1 and not args.no_cpu_baseline:
-            tf, cores, dt, desc = cpu_sample(B, min(S, 4096))
+            tf, cores, dt, desc = cpu_sample(args.workload, min(S, 4096))
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": desc + " (%.1f s)" % dt}
         print(json.dumps(line), flush=True)
@@ -369,27 +432,32 @@ def run_ours_linattn(args):
     import torch.distributed as dist
     import __graft_entry__ as g
     pkg = g.load_package()
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path in the product")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    from cxx_gpt_b200 import sharding
+    world, rank, local, dev = init_ranks()
     B0, S = WORKLOADS[args.workload]
-    B, D, E = B0 * H, DH, DH
+    D = E = DH
+    units_job = B0 * H * (world if args.weak else 1)
+    if args.weak:
+        B = B0 * H
+    else:  # fixed total: a contiguous range of the folded (batch, head) units per rank
+        lo, hi = sharding.unit_range(B0 * H, world, rank)
+        B = hi - lo
     N = B * S
     gen = torch.Generator(device="cpu").manual_seed(3 + rank)
     tdt = torch.bfloat16 if args.lin_dtype == "bf16" else torch.float32
     w = 2 if args.lin_dtype == "bf16" else 4
     hQ, hK, hV, hdO = (torch.randn(N, D, generator=gen).to(tdt).pin_memory() for _ in range(4))
-    Q, K, V, dO = (t.to(dev) for t in (hQ, hK, hV, hdO))
-    O, dQ, dK, dV = (torch.empty_like(Q) for _ in range(4))
-    den = torch.empty(N, device=dev)
+    set_bytes = 9 * N * D * w
+    nset = max(1, -(-(2 * 126 << 20) // max(set_bytes, 1)))
+    sets = []
+    for _ in range(nset):
+        sets.append([t.to(dev) for t in (hQ, hK, hV, hdO)] + [torch.empty(N, D, dtype=tdt, device=dev) for _ in range(4)] +
+                    [torch.empty(N, device=dev)])
+    turn = [0]
 
     def step():
+        Q, K, V, dO, O, dQ, dK, dV, den = sets[turn[0] % nset]
+        turn[0] += 1
         pkg.linattn_fwd(Q, K, V, O, den, None, B, S, D, E, pkg.MAP_ELU1, 0)
         pkg.linattn_bwd(Q, K, V, O, dO, den, dQ, dK, dV, B, S, D, E, pkg.MAP_ELU1, 0)
 
@@ -401,6 +469,7 @@ def run_ours_linattn(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
+    pkg.sync_status()
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
@@ -412,32 +481,28 @@ def run_ours_linattn(args):
     barrier()
     sampler.stop_flag = True
     ms = e0.elapsed_time(e1) / args.steps
+    pkg.sync_status()
 
-    # end to end: pinned host tensors in, host tensors out (plain copies around the same two calls)
+    # end to end: pinned host tensors in, host tensors out, through the C-ABI host entry point
     hO, hdQ, hdK, hdV = (torch.empty(N, D, dtype=tdt).pin_memory() for _ in range(4))
     hden = torch.empty(N).pin_memory()
-
-    def e2e_step():
-        for d_, h_ in ((Q, hQ), (K, hK), (V, hV), (dO, hdO)):
-            d_.copy_(h_, non_blocking=True)
-        step()
-        for h_, d_ in ((hO, O), (hden, den), (hdQ, dQ), (hdK, dK), (hdV, dV)):
-            h_.copy_(d_, non_blocking=True)
-        torch.cuda.synchronize()
-    e2e_step()
+    plan = pkg.LinHostPlan(B, S, D, E, pkg.BF16 if w == 2 else pkg.F32, max(1, B // 16))
+    plan.fwd_bwd(hQ, hK, hV, hdO, hO, hden, hdQ, hdK, hdV)
     barrier()
     t0 = time.perf_counter()
     n_e2e = max(3, min(args.steps, 10))
     for _ in range(n_e2e):
-        e2e_step()
+        plan.fwd_bwd(hQ, hK, hV, hdO, hO, hden, hdQ, hdK, hdV)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
+    plan.close()
+    Q, K, V, dO, O = sets[0][:5]
 
     # the reference's own serial-scan CUDA kernels on the same tensors (when they were built)
     ref_ms = None
     try:
         import oracle
-        if rank == 0 and not args.no_reference_cuda and oracle.ReferenceCuda.available():
+        if rank == 0 and world == 1 and not args.no_reference_cuda and oracle.ReferenceCuda.available():
             rc = oracle.ReferenceCuda()
             buf = rc.scan_buffers(B, S, D, E, dev)
             Qf, Kf, Vf, dOf = (t.float() for t in (Q, K, V, dO))  # the same values, as the reference's fp32
@@ -450,7 +515,9 @@ def run_ours_linattn(args):
             r1.record()
             torch.cuda.synchronize()
             ref_ms = r0.elapsed_time(r1) / 2
-            ref_err = float((buf["O"] - O.float()).abs().max() / buf["O"].abs().max())
+            step()
+            torch.cuda.synchronize()
+            ref_err = float((buf["O"] - sets[(turn[0] - 1) % nset][4].float()).abs().max() / buf["O"].abs().max())
             del Qf, Kf, Vf, dOf
     except Exception as e:  # the baseline is optional; say why it is missing
         ref_ms, ref_err = None, repr(e)
@@ -460,51 +527,41 @@ def run_ours_linattn(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
     if rank == 0:
-        nbytes = lin_bytes_fwd_bwd(B, S, D, E, w)
+        nbytes = lin_bytes_fwd_bwd(units_job, S, D, E, w)  # whole job
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
                 hbm, how = float(json.load(f)["hbm_gbs"]), "measured"
         except Exception:
             hbm, how = 6650.0, "fallback"
         gbs = nbytes / (ms * 1e-3) / 1e9
-        line = {"metric": LIN_METRIC, "value": world * gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        kernels = ("linattn_tc_fwd + linattn_tc_bwd_dq + linattn_tc_bwd_dkdv (+ group-state pre-passes)" if w == 2 else
+                   "chunk_state + chunk_scan + chunk_apply (fwd + bwd call)")
+        per_unit = load_traffic("linattn_tc_step" if w == 2 else "linattn_f32_step")
+        line = {"metric": LIN_METRIC, "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak" if args.weak else "strong",
                 "vs_baseline": None, "dtype": args.lin_dtype, "data": "synthetic",
-                "config": {"workload": args.workload, "units_per_gpu": B, "S": S, "D": D, "E": E,
-                           "tokens_per_gpu": B0 * S, "feature_map": "elu+1",
-                           "l2": "9 tensors x %.0f MB per step exceed the 126 MB L2" % (N * D * w / 1e6)},
-                "tokens_per_s": world * B0 * S / (ms * 1e-3),
-                "gpu_launches": args.steps * (3 if args.lin_dtype == "bf16" else 12),
+                "config": job_config(args.workload, world, args.weak),
+                "per_rank": {"units": B, "working_sets": nset},
+                "tokens_per_s": units_job // H * S / (ms * 1e-3),
+                "gpu_launches": args.steps * (3 if args.lin_dtype == "bf16" else 12) * world,
                 "clocks": sampler.result(),
-                "e2e": {"value": world * nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": 4 * N * D * w, "d2h_bytes_per_step": 4 * N * D * w + N * 4},
-                "roofline": {"bound": "hbm",
-                             "kernel": ("linattn_tc_fwd + linattn_tc_bwd_dq + linattn_tc_bwd_dkdv" if w == 2 else
-                                        "chunk_state + chunk_scan + chunk_apply (fwd + bwd call)"),
-                             "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s", "frac": gbs / hbm,
-                             # dram__bytes_read + write summed over the six kernels of one step, from the ncu
-                             # capture summarised in profiles/linattn_tc_kernels_linattn_s4096.md (2064 MB at
-                             # 192 units: the state pre-passes and the two backward passes re-read Q, K, V)
-                             "traffic": 2.064e9 * B / 192 if (w == 2 and S == 4096 and D == 64 and E == 64) else None},
+                "e2e": {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": 4 * units_job * S * D * w,
+                        "d2h_bytes_per_step": 4 * units_job * S * D * w + units_job * S * 4},
+                "roofline": {"bound": "hbm", "kernel": kernels,
+                             "achieved": gbs / world, "peak": hbm, "peak_source": how, "unit": "GB/s",
+                             "frac": gbs / world / hbm,
+                             # DRAM bytes of all launches of one step: the profiler's figure per unit of a
+                             # captured step at this sequence length, times this rank's units
+                             "traffic": per_unit * B if (per_unit and S == 4096 and D == 64 and E == 64) else None},
                 "reference_cuda": {"ms_per_step": ref_ms, "speedup": (ref_ms / ms) if ref_ms else None,
                                    "max_rel_diff_O": ref_err if ref_ms else None,
                                    "what": "reference two_stage_cuda kernel_attn fwd+step1+dQ+dKdV, unmodified, sm_100"}}
         if world == 1 and not args.no_cpu_baseline:
-            import numpy as np
-            import oracle
-            orc = oracle.Oracle()
-            units = host_threads()
-            orc.set_threads(units)
-            s_eff = min(S, 4096)
-            rng = np.random.default_rng(3)
-            q, k, v, g_ = (rng.standard_normal((units * s_eff, D)).astype(np.float32) for _ in range(4))
-            t0 = time.perf_counter()
-            o, dn, _ = orc.linattn_fwd(q, k, v, units, s_eff, D, E)
-            orc.kernel_attn_bwd(q, k, v, o, g_, dn, units, s_eff, D, E)
-            dt = time.perf_counter() - t0
-            line["cpu_baseline"] = {"value": lin_bytes_fwd_bwd(units, s_eff, D, E, w) / dt / 1e9, "unit": "GB/s",
-                                    "cores": units, "kind": "port",
-                                    "sample": f"{units} of {B} units of S={s_eff}, fp32 oracle, fwd+bwd ({dt:.1f} s)"}
+            v, cores, dt, desc = cpu_sample(args.workload, min(S, 4096))
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": desc + " (%.1f s)" % dt}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -581,9 +638,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS) + sorted(NEIGHBOURS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--strong", action="store_true",
-                    help="softmax workloads: keep the total batch fixed and give each rank B / N items (default: "
-                         "every rank runs the whole per-GPU workload, weak scaling)")
+    ap.add_argument("--weak", action="store_true",
+                    help="every rank runs the whole workload on data of its own (default: the workload's 65,536 "
+                         "tokens are a fixed total whose (batch, head) units are dealt over the ranks)")
     ap.add_argument("--no-reference-cuda", action="store_true",
                     help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
     ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
@@ -592,7 +649,6 @@ def main():
     if args.impl == "reference":
         if args.workload in NEIGHBOURS:
             ap.error("--impl reference covers the attention workloads only")
-        args.steps = min(args.steps, 3)
         run_reference(args)
     elif args.workload in NEIGHBOURS:
         run_neighbours(args)

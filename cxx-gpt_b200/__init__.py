@@ -28,7 +28,12 @@ SYMBOLS = [
     "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
+    "cxxattn_lin_host_plan_create", "cxxattn_lin_host_plan_destroy", "cxxattn_linattn_fwd_bwd_host",
+    "cxxattn_set_option", "cxxattn_get_option", "cxxattn_selftest_wait_limit",
 ]
+
+# cxxattn_set_option keys (include/cxxattn.h)
+OPT_FWD_LATE_WAIT, OPT_BWD_PERSISTENT, OPT_LIN_GROUPS, OPT_LIN_SIDE_STREAM = 0, 1, 2, 3
 
 
 class MhaDesc(C.Structure):
@@ -96,6 +101,13 @@ def lib():
         L.cxxattn_host_plan_destroy.restype = None
         L.cxxattn_mha_fwd_bwd_host.argtypes = [vp] * 9
         L.cxxattn_selftest_umma.argtypes = [i32, vp, vp, vp, vp]
+        L.cxxattn_lin_host_plan_create.argtypes = [C.POINTER(vp), C.POINTER(LinDesc), i32]
+        L.cxxattn_lin_host_plan_destroy.argtypes = [vp]
+        L.cxxattn_lin_host_plan_destroy.restype = None
+        L.cxxattn_linattn_fwd_bwd_host.argtypes = [vp] * 10
+        L.cxxattn_set_option.argtypes = [i32, i32]
+        L.cxxattn_get_option.argtypes = [i32, C.POINTER(i32)]
+        L.cxxattn_selftest_wait_limit.argtypes = [C.c_uint64, vp]
         _lib = L
     return _lib
 
@@ -113,12 +125,14 @@ def check(code, what):
 # torch plumbing: device pointers, the current stream, cached workspaces
 # ---------------------------------------------------------------------------------------------
 
-def _ptr(t):
+def _ptr(t, strided=False):
+    """Device address of a tensor.  `strided`: the caller describes the layout through the
+    descriptor's strides (a view into a larger tensor), so the view need not be contiguous."""
     if t is None:
         return None
     if not t.is_cuda:
         raise ValueError("cxxattn kernels take CUDA tensors; there is no CPU path")
-    if not t.is_contiguous():
+    if not strided and not t.is_contiguous():
         raise ValueError("tensor must be contiguous")
     return t.data_ptr()
 
@@ -166,7 +180,8 @@ def lin_desc(B, S, D, E, dtype=F32, feature_map=MAP_ELU1, eps_in_den=0):
 
 def mha_fwd(Q, K, V, O, B, S, H, Dh, lse=None, strides=None):
     d = mha_desc(B, S, H, Dh, _dtype_code(Q), strides)
-    check(lib().cxxattn_mha_fwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(lse), _stream()),
+    v = strides is not None
+    check(lib().cxxattn_mha_fwd(C.byref(d), _ptr(Q, v), _ptr(K, v), _ptr(V, v), _ptr(O, v), _ptr(lse), _stream()),
           "cxxattn_mha_fwd")
 
 
@@ -174,8 +189,9 @@ def mha_bwd(Q, K, V, O, dO, dQ, dK, dV, B, S, H, Dh, lse=None, strides=None):
     d = mha_desc(B, S, H, Dh, _dtype_code(Q), strides)
     n = lib().cxxattn_mha_bwd_workspace_bytes(C.byref(d), int(lse is not None))
     ws = workspace(n, Q.device)
-    check(lib().cxxattn_mha_bwd(C.byref(d), _ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(lse),
-                                _ptr(dQ), _ptr(dK), _ptr(dV), ws.data_ptr(), ws.numel(), _stream()),
+    v = strides is not None
+    check(lib().cxxattn_mha_bwd(C.byref(d), _ptr(Q, v), _ptr(K, v), _ptr(V, v), _ptr(O, v), _ptr(dO, v), _ptr(lse),
+                                _ptr(dQ, v), _ptr(dK, v), _ptr(dV, v), ws.data_ptr(), ws.numel(), _stream()),
           "cxxattn_mha_bwd")
 
 
@@ -245,6 +261,61 @@ class HostPlan:
             self.close()
         except Exception:
             pass
+
+
+class LinHostPlan:
+    """Owner of the device staging buffers behind cxxattn_linattn_fwd_bwd_host (host tensors in,
+    host tensors out; heads folded into the B units)."""
+
+    def __init__(self, B, S, D, E, dtype, units_per_chunk, feature_map=MAP_ELU1, eps_in_den=0):
+        self.handle = C.c_void_p()
+        d = lin_desc(B, S, D, E, dtype, feature_map, eps_in_den)
+        check(lib().cxxattn_lin_host_plan_create(C.byref(self.handle), C.byref(d), units_per_chunk),
+              "cxxattn_lin_host_plan_create")
+
+    def fwd_bwd(self, Q, K, V, dO, O, den, dQ, dK, dV):
+        ptrs = [t.data_ptr() for t in (Q, K, V, dO, O, den, dQ, dK, dV)]
+        check(lib().cxxattn_linattn_fwd_bwd_host(self.handle, *ptrs), "cxxattn_linattn_fwd_bwd_host")
+
+    def close(self):
+        if self.handle:
+            lib().cxxattn_lin_host_plan_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def set_option(option, value):
+    """Process-wide schedule switch (OPT_*); see cxxattn_set_option."""
+    check(lib().cxxattn_set_option(int(option), int(value)), "cxxattn_set_option")
+
+
+def get_option(option):
+    v = C.c_int(0)
+    check(lib().cxxattn_get_option(int(option), C.byref(v)), "cxxattn_get_option")
+    return v.value
+
+
+class forced_option:
+    """with forced_option(OPT_x, v): ... sets the option and puts the old value back."""
+
+    def __init__(self, option, value):
+        self.option, self.value = option, value
+
+    def __enter__(self):
+        self.old = get_option(self.option)
+        set_option(self.option, self.value)
+
+    def __exit__(self, *exc):
+        set_option(self.option, self.old)
+
+
+def selftest_wait_limit(limit_ns):
+    check(lib().cxxattn_selftest_wait_limit(int(limit_ns), _stream()), "cxxattn_selftest_wait_limit")
 
 
 def set_timing_events(start, stop):

@@ -6,6 +6,30 @@
 
 using namespace cxxattn;
 
+namespace cxxattn {
+
+namespace {
+// defaults: choose by size, choose by size, cost model, side stream on
+std::atomic<int> g_options[CXXATTN_OPT_COUNT_] = {{-1}, {-1}, {0}, {1}};
+}  // namespace
+
+int option(int which) {
+    return which >= 0 && which < CXXATTN_OPT_COUNT_ ? g_options[which].load(std::memory_order_relaxed) : 0;
+}
+
+int sm_count() {
+    static std::atomic<int> cache[kMaxDevices];
+    const int dev = current_device();
+    int n = dev >= 0 ? cache[dev].load(std::memory_order_relaxed) : 0;
+    if (n <= 0) {
+        if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        if (dev >= 0) cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
+}  // namespace cxxattn
+
 namespace {
 
 bool resolve(const cxxattn_mha_desc* d, MhaShape* p) {
@@ -170,6 +194,36 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
     return rope(Q, K, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
 }
 
+int cxxattn_set_option(int option, int value) {
+    switch (option) {
+        case CXXATTN_OPT_FWD_LATE_WAIT:
+        case CXXATTN_OPT_BWD_PERSISTENT:
+            if (value < -1 || value > 1) return CXXATTN_ERR_INVALID;
+            break;
+        case CXXATTN_OPT_LIN_GROUPS:
+            if (value < 0 || value > 1024) return CXXATTN_ERR_INVALID;
+            break;
+        case CXXATTN_OPT_LIN_SIDE_STREAM:
+            if (value < 0 || value > 1) return CXXATTN_ERR_INVALID;
+            break;
+        default:
+            return CXXATTN_ERR_INVALID;
+    }
+    g_options[option].store(value, std::memory_order_relaxed);
+    return CXXATTN_OK;
+}
+
+int cxxattn_get_option(int option, int* value) {
+    if (option < 0 || option >= CXXATTN_OPT_COUNT_ || value == nullptr) return CXXATTN_ERR_INVALID;
+    *value = cxxattn::option(option);
+    return CXXATTN_OK;
+}
+
+int cxxattn_selftest_wait_limit(uint64_t limit_ns, cxxattn_stream_t stream) {
+    if (limit_ns < 1000 || limit_ns > 2000000000ull) return CXXATTN_ERR_INVALID;
+    return wait_selftest(limit_ns, static_cast<cudaStream_t>(stream));
+}
+
 void cxxattn_set_timing_events(void* start_event, void* stop_event) {
     mha_tc_bwd_set_timing_events(start_event, stop_event);
 }
@@ -189,17 +243,20 @@ int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_
 
 int cxxattn_linattn_decode_step(const cxxattn_lin_desc* desc, const float* q, const float* k, const float* v,
                                 float* state_S, float* state_z, float* o, float* den, cxxattn_stream_t stream) {
-    if (!desc || desc->B <= 0 || desc->D <= 0 || desc->E <= 0 || desc->reserved != 0 || !q || !k || !v || !state_S ||
-        !state_z || !o)
-        return CXXATTN_ERR_INVALID;
-    if (desc->feature_map != CXXATTN_MAP_NONE && desc->feature_map != CXXATTN_MAP_ELU1) return CXXATTN_ERR_INVALID;
+    // desc->S is not used by a decoding step; every other field is held to the bounds of lin_ok()
+    if (!desc || !q || !k || !v || !state_S || !state_z || !o) return CXXATTN_ERR_INVALID;
+    cxxattn_lin_desc one = *desc;
+    one.S = 1;
+    if (!lin_ok(&one)) return CXXATTN_ERR_INVALID;
     if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
     return linattn_decode_step(*desc, q, k, v, state_S, state_z, o, den, static_cast<cudaStream_t>(stream));
 }
 
 static bool decode_ok(const cxxattn_mha_desc* d) {
+    // the kernels index with 32-bit grid dimensions: B*H is one of them
     return d && d->B > 0 && d->S > 0 && d->H > 0 && d->Dh > 0 && d->reserved == 0 && d->stride_b == 0 &&
-           d->stride_s == 0 && d->stride_h == 0;
+           d->stride_s == 0 && d->stride_h == 0 && d->B <= INT32_MAX && d->S <= INT32_MAX && d->H <= INT32_MAX &&
+           d->Dh <= INT32_MAX && d->B * d->H <= INT32_MAX;
 }
 
 size_t cxxattn_mha_decode_workspace_bytes(const cxxattn_mha_desc* desc) {

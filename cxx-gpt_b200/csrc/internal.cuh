@@ -2,9 +2,11 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include "cxxattn.h"
+#include "cxxattn_diag.h"
 
 namespace cxxattn {
 
@@ -20,6 +22,28 @@ inline int check_launch() {
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- per-device state shared by the launch paths ----
+// Host calls may come from several threads at once.  Everything a launch path caches per device
+// (function attributes set, SM count, symbol addresses) is a value that every thread would compute
+// identically, kept in relaxed atomics: a race only repeats the look-up.
+constexpr int kMaxDevices = 64;
+// The current device, or -1 when it cannot be read or lies beyond kMaxDevices.
+inline int current_device() {
+    int d = -1;
+    return cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < kMaxDevices ? d : -1;
+}
+// Streaming multiprocessors of the current device (148 when the attribute cannot be read).
+int sm_count();
+// One flag per device: `claim()` is true when `done()` has not yet been called for the current device.
+struct OncePerDevice {
+    std::atomic<bool> set[kMaxDevices];
+    bool pending(int dev) const { return dev < 0 || !set[dev].load(std::memory_order_relaxed); }
+    void done(int dev) { if (dev >= 0) set[dev].store(true, std::memory_order_relaxed); }
+};
+
+// ---- run-time options (cxxattn_set_option) ----
+int option(int which);
 
 // ---- exact fp32 SIMT softmax MHA (mha_f32.cu) ----
 int mha_f32_fwd(const MhaShape& p, const float* Q, const float* K, const float* V, float* O,
@@ -52,6 +76,7 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
 
 // ---- diagnostics (umma_selftest.cu) ----
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);
+int wait_selftest(uint64_t limit_ns, cudaStream_t st);
 int sync_status(cudaStream_t st);
 int last_timeout_site();
 

@@ -420,18 +420,18 @@ size_t linattn_f32_static_capacity() { return kStaticScratchBytes; }
 int linattn_f32_fwd_static(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V,
                            float* O, float* den, float* z_cache, cudaStream_t st) {
     if (static_fwd_bytes(d) > kStaticScratchBytes) return CXXATTN_ERR_TOO_LARGE;
-    static void* addr[64] = {};
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CXXATTN_ERR_CUDA;
-    if (addr[dev] == nullptr) {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return CXXATTN_ERR_CUDA;
-        addr[dev] = p;
+    static std::atomic<void*> addr[kMaxDevices];  // filled with the same value by whichever thread comes first
+    const int dev = current_device();
+    if (dev < 0) return CXXATTN_ERR_CUDA;
+    void* scratch = addr[dev].load(std::memory_order_relaxed);
+    if (scratch == nullptr) {
+        if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess || scratch == nullptr) return CXXATTN_ERR_CUDA;
+        addr[dev].store(scratch, std::memory_order_relaxed);
     }
     // carve() lays out states | z states | (dnum | dden); the forward touches the first two only,
     // and static_fwd_bytes() bounds exactly those.  Every chunk state is fully rewritten by
     // chunk_state_kernel before it is read, so stale contents of an earlier call do not matter.
-    const Ws w = carve(d, addr[dev]);
+    const Ws w = carve(d, scratch);
     const bool map = d.feature_map == CXXATTN_MAP_ELU1;
     int rc = build_states(d, w, K, V, nullptr, map, false, st);
     if (rc != CXXATTN_OK) return rc;

@@ -21,7 +21,6 @@
 // As in the forward, the states stay in TMEM (fp32) for the whole sequence and are copied as bf16
 // into shared memory once per chunk to serve as matrix operands.
 #include "linattn_tc_common.cuh"
-#include <cstdlib>
 #include <mutex>
 
 namespace cxxattn {
@@ -568,27 +567,28 @@ linattn_tc_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 namespace {
 // A side stream per device for the suffix-state pre-pass.  Only the dK/dV pass needs that state, so
 // the pre-pass runs beside the prefix pre-pass and the dQ pass, in the SMs their last waves leave
-// idle.  Fork and join are events on the caller's stream: its order is kept and the call stays
-// capturable.  The events are shared by all calls on a device, so enqueueing is serialised.
+// idle.  Fork and join are events on the caller's stream, so its order is kept.  Stream and events
+// are shared by all calls on a device: enqueueing is serialised by g_side_mutex, and a call whose
+// stream is being captured does not use them at all (work of another thread's uncaptured call must
+// not land in that capture), it runs the pre-pass in line.  Callers of side_stream() hold the mutex.
 struct SideStream {
     cudaStream_t stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
     int state = 0;  // 0 not tried, 1 usable, -1 unavailable
 };
 std::mutex g_side_mutex;
-SideStream* side_stream(int dev) {
-    static SideStream tab[64];
-    if (dev < 0 || dev >= 64) return nullptr;
+SideStream* side_stream(int dev, cudaStream_t caller) {
+    static SideStream tab[kMaxDevices];
+    if (dev < 0 || option(CXXATTN_OPT_LIN_SIDE_STREAM) == 0) return nullptr;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(caller, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
     SideStream& s = tab[dev];
-    if (s.state == 0) {
-        const char* e = std::getenv("CXXATTN_LIN_SIDE_STREAM");
-        const bool on = !(e && e[0] == '0');
-        s.state = on && cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
+    if (s.state == 0)
+        s.state = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
                           cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess &&
                           cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess
                       ? 1
                       : -1;
-    }
     return s.state == 1 ? &s : nullptr;
 }
 }  // namespace
@@ -627,34 +627,42 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
     float* gss = plan.G > 1 ? reinterpret_cast<float*>(static_cast<char*>(ws) + plan.state_bytes) : nullptr;
     p.sgp = SeqGroups{gsp, plan.G, plan.gc};
     p.sgs = SeqGroups{gss, plan.G, plan.gc};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    std::unique_lock<std::mutex> side_lock(g_side_mutex, std::defer_lock);
-    SideStream* side = nullptr;
-    if (plan.G > 1) {
-        side_lock.lock();
-        side = side_stream(dev);
-        if (side && (cudaEventRecord(side->fork, st) != cudaSuccess ||
-                     cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess))
-            side = nullptr;
-        int rc = linattn_tc_group_states(0, plan, B, S, p.map_elu, K, V, nullptr, nullptr, gsp, st);
-        if (rc == CXXATTN_OK)
-            rc = linattn_tc_group_states(1, plan, B, S, p.map_elu, Q, dO, O, den, gss, side ? side->stream : st);
-        if (side && cudaEventRecord(side->join, side->stream) != cudaSuccess) rc = CXXATTN_ERR_CUDA;
-        if (rc != CXXATTN_OK) return rc;
-    }
-    static bool attr_set[64] = {};
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    const int dev = current_device();
+    static OncePerDevice attr;
+    if (attr.pending(dev)) {
         if (cudaFuncSetAttribute(linattn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM1_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(linattn_tc_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM2_BYTES) != cudaSuccess)
             return CXXATTN_ERR_CUDA;
-        attr_set[dev] = true;
+        attr.done(dev);
     }
-    linattn_tc_bwd_dq_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM1_BYTES, st>>>(tmK, tmV, tmG, p);
-    if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
-    if (side && cudaStreamWaitEvent(st, side->join, 0) != cudaSuccess) return CXXATTN_ERR_CUDA;
+    std::unique_lock<std::mutex> side_lock(g_side_mutex, std::defer_lock);
+    SideStream* side = nullptr;
+    int rc = CXXATTN_OK;
+    if (plan.G > 1) {
+        side_lock.lock();
+        side = side_stream(dev, st);
+        if (side && (cudaEventRecord(side->fork, st) != cudaSuccess ||
+                     cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess))
+            side = nullptr;
+        rc = linattn_tc_group_states(0, plan, B, S, p.map_elu, K, V, nullptr, nullptr, gsp, st);
+        if (rc == CXXATTN_OK)
+            rc = linattn_tc_group_states(1, plan, B, S, p.map_elu, Q, dO, O, den, gss, side ? side->stream : st);
+        if (side && cudaEventRecord(side->join, side->stream) != cudaSuccess) {
+            // nothing can be joined through the event: drain the side stream instead, once
+            cudaStreamSynchronize(side->stream);
+            side = nullptr;
+            if (rc == CXXATTN_OK) rc = CXXATTN_ERR_CUDA;
+        }
+    }
+    if (rc == CXXATTN_OK) {
+        linattn_tc_bwd_dq_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM1_BYTES, st>>>(tmK, tmV, tmG, p);
+        rc = check_launch();
+    }
+    // once forked, the side stream is joined on every path out of this function, failures included
+    if (side && cudaStreamWaitEvent(st, side->join, 0) != cudaSuccess && rc == CXXATTN_OK) rc = CXXATTN_ERR_CUDA;
+    if (rc != CXXATTN_OK) return rc;
     linattn_tc_bwd_dkdv_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM2_BYTES, st>>>(tmQ, tmK, tmV, tmG, p);
     return check_launch();
 }

@@ -314,14 +314,13 @@ int linattn_tc_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
         const int rc = linattn_tc_group_states(0, plan, B, S, p.map_elu, K, V, nullptr, nullptr, static_cast<float*>(ws), st);
         if (rc != CXXATTN_OK) return rc;
     }
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static OncePerDevice attr;
+    const int dev = current_device();
+    if (attr.pending(dev)) {
         if (cudaFuncSetAttribute(linattn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
             cudaSuccess)
             return CXXATTN_ERR_CUDA;
-        attr_set[dev] = true;
+        attr.done(dev);
     }
     linattn_tc_fwd_kernel<<<(unsigned)(B * plan.G), NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, p);
     return check_launch();

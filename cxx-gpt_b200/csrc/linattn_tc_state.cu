@@ -15,7 +15,6 @@
 // the 65th column is z), accumulated in TMEM over the group and written as fp32 to global memory.
 // The main kernels start a group from the sum of the states of the groups before (after) it.
 #include <algorithm>
-#include <cstdlib>
 
 #include "linattn_tc_common.cuh"
 
@@ -188,21 +187,13 @@ linattn_tc_state_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 // CTA costs its chunks plus a fixed fill/drain of about two, a pre-pass CTA about a quarter of that
 // per chunk; CTAs run in waves of one per SM.
 LinGroupPlan linattn_tc_plan(int B, int S) {
-    static int sms[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    int nsm = 148;
-    if (dev >= 0 && dev < 64) {
-        if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            sms[dev] = 148;
-        nsm = sms[dev] > 0 ? sms[dev] : 148;
-    }
+    const int nsm = sm_count();
     const int nc = (S + lintc::CH - 1) / lintc::CH;
     auto waves = [&](int64_t ctas) { return (double)((ctas + nsm - 1) / nsm); };
     LinGroupPlan best{1, nc, 0};
     double best_cost = waves(B) * (nc + 2.0);
-    // tuning knob: CXXATTN_LIN_GROUPS=<G> forces the number of groups (rounded to one without empty groups)
-    static const int forced = [] { const char* e = std::getenv("CXXATTN_LIN_GROUPS"); return e ? std::atoi(e) : 0; }();
+    // CXXATTN_OPT_LIN_GROUPS = G > 0 forces the number of groups (rounded to one without empty groups)
+    const int forced = option(CXXATTN_OPT_LIN_GROUPS);
     if (forced > 0) {
         const int gc = (nc + std::min(forced, nc) - 1) / std::min(forced, nc);
         const int G = (nc + gc - 1) / gc;
@@ -237,16 +228,15 @@ int linattn_tc_group_states(int mode, const LinGroupPlan& plan, int B, int S, in
     if (p.status == nullptr) return CXXATTN_ERR_CUDA;
     p.B = B; p.S = S; p.G = plan.G; p.gc = plan.gc;
     p.map_elu = map_elu;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static OncePerDevice attr;
+    const int dev = current_device();
+    if (attr.pending(dev)) {
         if (cudaFuncSetAttribute(linattn_tc_state_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(linattn_tc_state_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM_BYTES) != cudaSuccess)
             return CXXATTN_ERR_CUDA;
-        attr_set[dev] = true;
+        attr.done(dev);
     }
     const unsigned grid = (unsigned)(B * (plan.G - 1));
     if (mode == 0) linattn_tc_state_kernel<0><<<grid, NTHREADS, SMEM_BYTES, st>>>(tmA, tmB, p);

@@ -30,7 +30,6 @@
 // accumulator cleared), the main kernel, and a pass turning the accumulator into bf16 dQ.
 // dQ is summed with atomics, so its low bits depend on the order in which CTAs arrive.
 #include <algorithm>
-#include <cstdlib>
 
 #include "internal.cuh"
 #include "tc_common.cuh"
@@ -683,28 +682,23 @@ int mha_tc_bwd(const MhaShape& p, const void* Q, const void* K, const void* V, c
     bp.sb = p.sb; bp.ss = p.ss; bp.sh = p.sh;
     bp.scale = p.scale;
     bp.scale_log2 = p.scale * 1.4426950408889634f;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static OncePerDevice attr;
+    const int dev = current_device();
+    if (attr.pending(dev)) {
         if (cudaFuncSetAttribute(mha_tc_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(mha_tc_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM_BYTES) != cudaSuccess)
             return CXXATTN_ERR_CUDA;
-        attr_set[dev] = true;
+        attr.done(dev);
     }
-    // persistent CTAs, one per SM, each walking its share of the (key tile, batch*head) items
-    static int nsm[64] = {};
-    if (dev >= 0 && dev < 64 && nsm[dev] == 0 &&
-        cudaDeviceGetAttribute(&nsm[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        nsm[dev] = 148;
     const int64_t items = (int64_t)(Spad / BT) * p.B * p.H;
-    // Short sequences (few query tiles per item): persistent CTAs; long ones: one CTA per item, whose
-    // tile loop compiles a little tighter.  Tuning knob: CXXATTN_BWD_PERSIST=0/1 forces the choice.
-    static const int forced = [] { const char* e = std::getenv("CXXATTN_BWD_PERSIST"); return e ? std::atoi(e) : -1; }();
+    // Short sequences (few query tiles per item): persistent CTAs, one per SM, each walking its share of
+    // the (key tile, batch*head) items; long ones: one CTA per item, whose tile loop compiles a little
+    // tighter.  CXXATTN_OPT_BWD_PERSISTENT = 0 / 1 forces the choice.
+    const int forced = option(CXXATTN_OPT_BWD_PERSISTENT);
     const bool persist = forced >= 0 ? forced != 0 : Spad / BT <= 32;
-    const int64_t grid = persist ? std::min<int64_t>(items, (dev >= 0 && dev < 64 && nsm[dev] > 0) ? nsm[dev] : 148) : items;
+    const int64_t grid = persist ? std::min<int64_t>(items, sm_count()) : items;
     if (g_ev_start) cudaEventRecord(g_ev_start, st);
     if (persist) mha_tc_bwd_kernel<true><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);
     else mha_tc_bwd_kernel<false><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmG, bp);

@@ -26,7 +26,6 @@
 // are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
 // when it grows by more than 8 (in log2 units), so the rescaling of O in TMEM is rare.
 #include <algorithm>
-#include <cstdlib>
 
 #include "internal.cuh"
 #include "tc_common.cuh"
@@ -417,28 +416,24 @@ int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, v
     fp.B = p.B; fp.S = p.S; fp.H = p.H;
     fp.sb = p.sb; fp.ss = p.ss; fp.sh = p.sh;
     fp.scale_log2 = p.scale * 1.4426950408889634f;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static OncePerDevice attr;
+    const int dev = current_device();
+    if (attr.pending(dev)) {
         if (cudaFuncSetAttribute(mha_tc_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(mha_tc_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)SMEM_BYTES) != cudaSuccess)
             return CXXATTN_ERR_CUDA;
-        attr_set[dev] = true;
+        attr.done(dev);
     }
     // persistent CTAs, one per SM, each walking its share of the (query-tile pair, batch*head) items
-    static int nsm[64] = {};
-    if (dev >= 0 && dev < 64 && nsm[dev] == 0 &&
-        cudaDeviceGetAttribute(&nsm[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        nsm[dev] = 148;
     const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
     const int64_t items = (int64_t)npairs * p.B * p.H;
-    const int64_t grid = std::min<int64_t>(items, (dev >= 0 && dev < 64 && nsm[dev] > 0) ? nsm[dev] : 148);
-    // measured on B200: waiting late wins from about LATE_FROM key tiles per row on (CXXATTN_FWD_LATE_WAIT=0/1 forces)
-    bool late = (p.S + BN - 1) / BN >= LATE_FROM;
-    if (const char* e = std::getenv("CXXATTN_FWD_LATE_WAIT")) late = e[0] == '1';
+    const int64_t grid = std::min<int64_t>(items, sm_count());
+    // measured on B200: waiting late wins from about LATE_FROM key tiles per row on
+    // (CXXATTN_OPT_FWD_LATE_WAIT = 0 / 1 forces the choice)
+    const int forced = option(CXXATTN_OPT_FWD_LATE_WAIT);
+    const bool late = forced >= 0 ? forced != 0 : (p.S + BN - 1) / BN >= LATE_FROM;
     if (late) mha_tc_fwd_kernel<true><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
     else mha_tc_fwd_kernel<false><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
     return check_launch();

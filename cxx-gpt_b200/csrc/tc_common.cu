@@ -15,30 +15,31 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // The driver entry point is looked up at run time so that the library has no link-time
 // dependency on libcuda (it must load on machines without a driver).
 EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    // looked up once, thread-safely (function-local static initialisation)
+    static const EncodeTiledFn fn = [] {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
+            return reinterpret_cast<EncodeTiledFn>(p);
+        return static_cast<EncodeTiledFn>(nullptr);
+    }();
     return fn;
 }
 }  // namespace
 
 int* status_word() {
-    static int* cache[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (cache[dev] == nullptr) {
+    static std::atomic<int*> cache[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0) return nullptr;
+    int* w = cache[dev].load(std::memory_order_relaxed);
+    if (w == nullptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
-        cache[dev] = static_cast<int*>(p);
+        w = static_cast<int*>(p);
+        cache[dev].store(w, std::memory_order_relaxed);
     }
-    return cache[dev];
+    return w;
 }
 
 bool make_tmap_bhsd(CUtensorMap* out, const void* base, int B, int S, int H, int Dh, int64_t sb, int64_t ss,

@@ -63,7 +63,8 @@ __device__ __forceinline__ uint64_t global_ns() {
 // Bounded wait; `code` identifies the wait site in the status word.  Gives up after kWaitNs of
 // wall time, or at once when this CTA has aborted or any CTA of the device has recorded a
 // failure (so a fault costs one timeout for the whole grid, not one per CTA).
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const Guard& g, int code) {
+__device__ __forceinline__ void mbar_wait_limit(uint64_t* bar, uint32_t parity, const Guard& g, int code,
+                                                uint64_t limit_ns) {
     if (mbar_try(bar, parity)) return;
     const uint64_t t0 = global_ns();
     for (uint32_t i = 1;; i++) {
@@ -71,11 +72,14 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
         if ((i & 63u) == 0u) {
             if (*g.abort_flag) return;
             if (*reinterpret_cast<volatile int*>(g.status) != 0) break;
-            if (global_ns() - t0 > kWaitNs) break;
+            if (global_ns() - t0 > limit_ns) break;
         }
     }
     *g.abort_flag = 1;
     atomicCAS(g.status, 0, code);
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const Guard& g, int code) {
+    mbar_wait_limit(bar, parity, g, code, kWaitNs);
 }
 
 // The same bounded wait for a role that is a single thread (the MMA issuer).  It polls without

@@ -110,7 +110,45 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
 }
 
+// One CTA of 128 threads with tensor memory allocated, as the attention kernels have: every thread
+// waits for a barrier phase that no one completes.  The wait (the routine the attention kernels
+// use, with `limit_ns` in place of their two seconds) gives up, records site 990, raises the CTA's
+// abort flag, and all warps fall through to the common teardown.
+__global__ void __launch_bounds__(128, 1) wait_selftest_kernel(uint64_t limit_ns, int* status) {
+    __shared__ uint64_t never;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x / 32;
+    const Guard guard{&abort_flag, status};
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&never, 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 32);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    mbar_wait_limit(&never, 0, guard, 990, limit_ns);  // no thread ever arrives on `never`
+    // a second wait after the abort returns at once (what keeps a kernel with many waits short)
+    mbar_wait_limit(&never, 0, guard, 991, limit_ns);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 32);
+    }
+}
+
 }  // namespace
+
+int wait_selftest(uint64_t limit_ns, cudaStream_t st) {
+    int* status = status_word();
+    if (status == nullptr) return CXXATTN_ERR_CUDA;
+    wait_selftest_kernel<<<1, 128, 0, st>>>(limit_ns, status);
+    return check_launch();
+}
 
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st) {
     if (mode < 0 || mode > 2) return CXXATTN_ERR_INVALID;
@@ -129,8 +167,8 @@ int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t
     return check_launch();
 }
 
-static int g_last_site = 0;
-int last_timeout_site() { return g_last_site; }
+static std::atomic<int> g_last_site{0};
+int last_timeout_site() { return g_last_site.load(std::memory_order_relaxed); }
 
 int sync_status(cudaStream_t st) {
     int* status = status_word();
@@ -139,7 +177,7 @@ int sync_status(cudaStream_t st) {
     if (cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return CXXATTN_ERR_CUDA;
     if (cudaStreamSynchronize(st) != cudaSuccess) return CXXATTN_ERR_CUDA;
     if (host != 0) {
-        g_last_site = host;
+        g_last_site.store(host, std::memory_order_relaxed);
         cudaMemsetAsync(status, 0, sizeof(int), st);
         cudaStreamSynchronize(st);
         return CXXATTN_ERR_TIMEOUT;

@@ -31,6 +31,21 @@ def slabs(B, H, world, rank):
     return out
 
 
+def calls(B, H, world, rank):
+    """This rank's share as kernel calls (b0, nb, h0, nh): batch items b0..b0+nb-1, heads h0..h0+nh-1
+    of each.  Consecutive slabs that cover whole batch items merge into one call; a partial slab is a
+    call of its own, addressed in place through the descriptor's strides (stride_b = S*H*Dh,
+    stride_s = H*Dh, stride_h = Dh of the unsplit tensor, base pointer moved by h0*Dh elements)."""
+    out = []
+    for b, h0, h1 in slabs(B, H, world, rank):
+        whole = h0 == 0 and h1 == H
+        if whole and out and out[-1][2] == 0 and out[-1][3] == H and out[-1][0] + out[-1][1] == b:
+            out[-1] = (out[-1][0], out[-1][1] + 1, 0, H)
+        else:
+            out.append((b, 1, h0, h1 - h0))
+    return out
+
+
 def max_over_ranks(values, group=None):
     """Element-wise maximum of a list of floats over all ranks (the slowest rank counts)."""
     import torch

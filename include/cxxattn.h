@@ -226,6 +226,18 @@ void cxxattn_host_plan_destroy(cxxattn_host_plan* plan);
 int cxxattn_mha_fwd_bwd_host(cxxattn_host_plan* plan, const void* hQ, const void* hK, const void* hV,
                              const void* hdO, void* hO, void* hdQ, void* hdK, void* hdV);
 
+/* The same for causal linear attention: forward + fused backward on HOST tensors (what
+ * kernel_test.cpp does around kernel_attn_fwd / _bwd_step1 / _bwd_dQ / _bwd_dKdV,
+ * kernel_test.cpp:266-292), chunked over the units of desc->B.  hQ, hK, hdQ, hdK are (B*S, D),
+ * hV, hdO, hO, hdV (B*S, E) of desc->dtype, hden (B*S) float.  Both *_host calls return
+ * CXXATTN_ERR_TIMEOUT when a device-side wait gave up during the call, and refuse a plan made on
+ * another device than the current one. */
+typedef struct cxxattn_lin_host_plan cxxattn_lin_host_plan;
+int cxxattn_lin_host_plan_create(cxxattn_lin_host_plan** out, const cxxattn_lin_desc* desc, int units_per_chunk);
+void cxxattn_lin_host_plan_destroy(cxxattn_lin_host_plan* plan);
+int cxxattn_linattn_fwd_bwd_host(cxxattn_lin_host_plan* plan, const void* hQ, const void* hK, const void* hV,
+                                 const void* hdO, void* hO, float* hden, void* hdQ, void* hdK, void* hdV);
+
 /* ---- status and diagnostics (no reference counterpart) ------------------------------------- */
 
 /* Synchronises `stream`, then reports whether any tensor-core kernel launched so far on the
@@ -237,15 +249,35 @@ int cxxattn_sync_status(cxxattn_stream_t stream);
  * cxxattn_sync_status reported in this process; 0 if none. */
 int cxxattn_last_timeout_site(void);
 
-/* Measurement hook: two cudaEvent_t handles that later cxxattn_mha_bwd calls (dtype BF16) of the
- * calling thread record on their stream right before and right after the main backward kernel,
- * so that its duration can be read without the pre- and post-pass.  NULL, NULL switches it off. */
-void cxxattn_set_timing_events(void* start_event, void* stop_event);
+/* ---- run-time options (no reference counterpart) --------------------------------------------- */
 
-/* One-tile check of the tcgen05 operand conventions (bf16 device buffers, float result):
- *   mode 0: D[128x128] = A[128x64] B[128x64]^T;  mode 1: D[128x64] = A[128x128] B[128x64];
- *   mode 2: D[128x64]  = A[128x128]^T B[128x64]. */
-int cxxattn_selftest_umma(int mode, const void* A, const void* B, float* D, cxxattn_stream_t stream);
+/* Process-wide switches that override a choice the launch paths otherwise make from the problem
+ * size.  They are read at every call (no environment variable is consulted anywhere in the
+ * library) and may be set from any thread; results are the same under every setting, only the
+ * schedule changes. */
+enum {
+    CXXATTN_OPT_FWD_LATE_WAIT = 0,  /* bf16 softmax forward: where a softmax warp waits for the PV product
+                                       of the step before.  -1 by sequence length (default), 0 before
+                                       the exponentials, 1 after half of them                          */
+    CXXATTN_OPT_BWD_PERSISTENT = 1, /* bf16 softmax backward: -1 by sequence length (default), 1 one
+                                       persistent CTA per SM drawing (key tile, batch*head) items,
+                                       0 one CTA per item                                               */
+    CXXATTN_OPT_LIN_GROUPS = 2,     /* bf16 linear attention: sequence groups per unit; 0 cost model
+                                       (default), G > 0 forces G (rounded so that no group is empty)    */
+    CXXATTN_OPT_LIN_SIDE_STREAM = 3,/* bf16 linear backward: 1 (default) the suffix-state pre-pass runs on
+                                       a library-owned side stream beside the dQ pass, 0 in line        */
+    CXXATTN_OPT_COUNT_ = 4
+};
+/* CXXATTN_ERR_INVALID for an unknown option or a value outside the option's range. */
+int cxxattn_set_option(int option, int value);
+int cxxattn_get_option(int option, int* value);
+
+/* ---- threads ---------------------------------------------------------------------------------- */
+/* Host calls may be made from several threads, also for the same device: what the library caches
+ * per device (kernel attributes, SM count, symbol addresses) is kept in atomics and is the same
+ * whichever thread fills it.  Work on the GPU is ordered by the streams the caller passes, with
+ * three exceptions that the caller must serialise per device: calls that share one workspace,
+ * cxxattn_linattn_fwd_noalloc (one scratch array), and cxxattn_sync_status (one status word). */
 
 #ifdef __cplusplus
 }

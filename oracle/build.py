@@ -3,13 +3,18 @@ own CPU test functions (ref_wrap.cpp, which includes src/TwoStage/kernel_test.cp
 lies) into oracle/_ref/.  Test infrastructure only; building the checker is not using it.
 
     python oracle/build.py [--reference /path/to/CXX-GPT]
+
+The CXX-GPT source tree is taken from --reference, else from the environment variable
+CXXGPT_REFERENCE, else from a checkout named `reference` beside this repository; without one the
+previously built files under oracle/_ref/ are used as they are.
 """
 import os
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = os.environ.get("CXXGPT_REFERENCE", "/root/reference")
+DEFAULT_REFERENCE = os.environ.get("CXXGPT_REFERENCE") or \
+    os.path.normpath(os.path.join(HERE, os.pardir, os.pardir, "reference"))
 
 
 def _stale(target, sources):

@@ -1,6 +1,7 @@
-"""CPU checks of the drop-in boundary: the shared library loads, exports every symbol that
-include/cxxattn.h declares, and rejects bad arguments with error codes before touching a device."""
+"""CPU checks of the drop-in boundary: the shared library loads, exports every symbol that the
+headers under include/ declare, and rejects bad arguments with error codes before touching a device."""
 import ctypes as C
+import glob
 import os
 import re
 
@@ -8,9 +9,11 @@ from conftest import ROOT
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "cxxattn.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(cxxattn_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for path in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
+        text = re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
+        names |= set(re.findall(r"\b(cxxattn_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol(pkg):
@@ -18,7 +21,7 @@ def test_library_exports_every_declared_symbol(pkg):
     names = declared_symbols()
     assert len(names) >= 15
     for n in names:
-        assert hasattr(lib, n), f"{n} declared in include/cxxattn.h but not exported"
+        assert hasattr(lib, n), f"{n} declared under include/ but not exported"
     assert set(pkg.SYMBOLS) <= set(names)
 
 
@@ -65,6 +68,34 @@ def test_bad_arguments_are_rejected_without_a_device(pkg):
     assert lib.cxxattn_mha_decode_step(C.byref(long), one, one, one, one, one, 8000, one, None, 0, None) == -3
     assert lib.cxxattn_linattn_decode_step(C.byref(ld), one, one, one, None, one, one, None, None) == -1
     assert lib.cxxattn_gelu_exact(one, one, 0, 0, None) == -1
+    # decoding steps hold their descriptors to the same bounds as the other entry points
+    huge = pkg.lin_desc(1 << 40, 8, 4, 4)
+    assert lib.cxxattn_linattn_decode_step(C.byref(huge), one, one, one, one, one, one, None, None) == -1
+    badeps = pkg.lin_desc(2, 8, 4, 4, eps_in_den=5)
+    assert lib.cxxattn_linattn_decode_step(C.byref(badeps), one, one, one, one, one, one, None, None) == -1
+    wide = pkg.mha_desc(1 << 20, 16, 1 << 20, 8)   # B*H beyond a 32-bit grid dimension
+    assert lib.cxxattn_mha_decode_step(C.byref(wide), one, one, one, one, one, 0, one, None, 0, None) == -1
+    # host plans: bad descriptors are refused before any allocation
+    plan = C.c_void_p()
+    assert lib.cxxattn_host_plan_create(C.byref(plan), C.byref(bad), 1) == -1
+    assert lib.cxxattn_lin_host_plan_create(C.byref(plan), C.byref(pkg.lin_desc(0, 8, 4, 4)), 1) == -1
+    assert lib.cxxattn_linattn_fwd_bwd_host(None, one, one, one, one, one, one, one, one, one) == -1
+    assert lib.cxxattn_selftest_wait_limit(10, None) == -1            # below the smallest limit
+
+
+def test_options_are_validated_and_readable(pkg):
+    lib = pkg.lib()
+    defaults = {pkg.OPT_FWD_LATE_WAIT: -1, pkg.OPT_BWD_PERSISTENT: -1, pkg.OPT_LIN_GROUPS: 0,
+                pkg.OPT_LIN_SIDE_STREAM: 1}
+    for opt, want in defaults.items():
+        assert pkg.get_option(opt) == want
+    assert lib.cxxattn_set_option(99, 0) == -1
+    assert lib.cxxattn_set_option(pkg.OPT_FWD_LATE_WAIT, 2) == -1
+    assert lib.cxxattn_set_option(pkg.OPT_LIN_GROUPS, -1) == -1
+    assert lib.cxxattn_get_option(pkg.OPT_LIN_GROUPS, None) == -1
+    with pkg.forced_option(pkg.OPT_LIN_GROUPS, 3):
+        assert pkg.get_option(pkg.OPT_LIN_GROUPS) == 3
+    assert pkg.get_option(pkg.OPT_LIN_GROUPS) == 0
 
 
 def test_python_front_end_mirrors_reference_names(pkg):

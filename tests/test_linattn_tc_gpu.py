@@ -180,3 +180,87 @@ def test_many_units_take_one_group(pkg, dev, orc):
     rO, rden, _ = orc.linattn_fwd(Q[:n].float().numpy(), K[:n].float().numpy(), V[:n].float().numpy(), 4, S, 64, 64,
                                   elu=True, f64=True)
     assert rel_err(O[:n], rO) < TOL_BF16 and rel_err(den[:n], rden) < TOL_BF16
+
+
+def check_units(orc, Q, K, V, dO, res, S, units):
+    O, den, dQ, dK, dV = res
+    for u in units:
+        r = slice(u * S, (u + 1) * S)
+        f = [x[r].float().numpy() for x in (Q, K, V, dO)]
+        rO, rden, _ = orc.linattn_fwd(f[0], f[1], f[2], 1, S, 64, 64, elu=True, f64=True)
+        assert rel_err(O[r], rO) < TOL_BF16, ("O", u, rel_err(O[r], rO))
+        assert rel_err(den[r], rden) < TOL_BF16, ("den", u)
+        rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O[r], f[3], den[r], 1, S, 64, 64, f64=True)
+        for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+            assert rel_err(a[r], b) < TOL_BF16, (name, u, rel_err(a[r], b))
+
+
+def test_long_sequence_sweep_shape_s16384(pkg, dev, orc):
+    """48 units x S=16384 (B=4 x 12 heads folded) — the longest point of the sequence sweep at full
+    size: fewer units than SMs, so every unit is cut into sequence groups seeded by the state
+    pre-passes (the backward's suffix pre-pass on the side stream).  Parity on the first and last unit."""
+    import ctypes as C
+    B, S = 48, 16384
+    d = pkg.lin_desc(B, S, 64, 64, pkg.BF16, pkg.MAP_ELU1, 0)
+    assert pkg.lib().cxxattn_linattn_workspace_bytes(C.byref(d)) > 0  # groups are planned
+    Q, K, V = inputs(71, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(11)).bfloat16()
+    res = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+    for a in res:
+        assert np.all(np.isfinite(a))
+    check_units(orc, Q, K, V, dO, res, S, [0, 47])
+
+
+def test_long_sequence_sweep_shape_s1024(pkg, dev, orc):
+    """768 units x S=1024 (B=64 x 12 heads folded): more units than SMs, one group, several waves."""
+    B, S = 768, 1024
+    Q, K, V = inputs(73, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(13)).bfloat16()
+    res = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+    for a in res:
+        assert np.all(np.isfinite(a))
+    check_units(orc, Q, K, V, dO, res, S, [0, 400, 767])
+
+
+@pytest.mark.parametrize("groups", [1, 2, 5])
+def test_group_count_option(pkg, dev, orc, groups):
+    """CXXATTN_OPT_LIN_GROUPS forces the number of sequence groups; every setting meets the oracle."""
+    B, S = 3, 1300
+    Q, K, V = inputs(81, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(5)).bfloat16()
+    with pkg.forced_option(pkg.OPT_LIN_GROUPS, groups):
+        res = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+    check_units(orc, Q, K, V, dO, res, S, [0, 2])
+
+
+def test_side_stream_option_both_settings(pkg, dev):
+    """The suffix-state pre-pass of the backward runs on the library's side stream or in line
+    (CXXATTN_OPT_LIN_SIDE_STREAM); the results are the same bits either way."""
+    B, S = 3, 1300
+    Q, K, V = inputs(83, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(7)).bfloat16()
+    out = []
+    for setting in (1, 0):
+        with pkg.forced_option(pkg.OPT_LIN_SIDE_STREAM, setting):
+            out.append(run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0))
+    for a, b in zip(*out):
+        assert np.array_equal(a, b)
+
+
+def test_host_entry_point_matches_device_entry_points(pkg, dev):
+    """cxxattn_linattn_fwd_bwd_host (host tensors in and out, chunked over the units) gives the bits of
+    the device-pointer entry points on the same chunks."""
+    B, S = 12, 512
+    Q, K, V = inputs(91, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(17)).bfloat16()
+    hO, hdQ, hdK, hdV = (torch.empty(B * S, 64, dtype=torch.bfloat16) for _ in range(4))
+    hden = torch.empty(B * S)
+    plan = pkg.LinHostPlan(B, S, 64, 64, pkg.BF16, 5)  # chunks of 5, 5, 2 units
+    plan.fwd_bwd(Q, K, V, dO, hO, hden, hdQ, hdK, hdV)
+    plan.close()
+    for lo, hi in ((0, 5), (5, 10), (10, 12)):
+        r = slice(lo * S, hi * S)
+        want = run_fwd_bwd(pkg, dev, Q[r], K[r], V[r], dO[r], hi - lo, S, pkg.MAP_ELU1, 0)
+        got = [t[r].float().numpy() for t in (hO, hden, hdQ, hdK, hdV)]
+        for name, a, b in zip(("O", "den", "dQ", "dK", "dV"), got, want):
+            assert np.array_equal(a, b), (name, lo)

@@ -164,3 +164,102 @@ def test_backward_beyond_32_tiles_takes_one_cta_per_item(pkg, dev, orc):
         got = a[:, cols].float().cpu().numpy()
         assert np.all(np.isfinite(got)), name
         assert rel_err(got, ref) < TOL_BF16, (name, rel_err(got, ref))
+
+
+def check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, slices):
+    """Parity of chosen (batch, head) slices against the fp64 oracle; O of the kernel under test is
+    what the oracle's backward consumes, as in the reference."""
+    for b, h in slices:
+        rows = slice(b * S, (b + 1) * S)
+        cols = slice(h * Dh, (h + 1) * Dh)
+        f = [x[rows, cols].float().numpy() for x in (Q, K, V, dO)]
+        got_O = O[rows, cols].float().cpu().numpy()
+        rO = orc.mha_fwd(f[0], f[1], f[2], 1, S, 1, Dh, f64=True)
+        assert np.all(np.isfinite(got_O))
+        assert rel_err(got_O, rO) < TOL_BF16, ("O", b, h, rel_err(got_O, rO))
+        rdQ, rdK, rdV = orc.mha_bwd(f[0], f[1], f[2], got_O, f[3], 1, S, 1, Dh, f64=True)
+        for name, a, ref in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+            got = a[rows, cols].float().cpu().numpy()
+            assert np.all(np.isfinite(got)), (name, b, h)
+            assert rel_err(got, ref) < TOL_BF16, (name, b, h, rel_err(got, ref))
+
+
+def test_long_sequence_sweep_shape_s16384(pkg, dev, orc):
+    """B=4, S=16384, 12 heads x 64 — the longest point of the sequence sweep, at full size.  128 key
+    tiles per row: the forward takes its late-wait instantiation and the backward one CTA per
+    (key tile, batch*head) item with 128 query tiles.  Parity on the last (batch, head) slice, the
+    one whose items are scheduled last."""
+    B, S, H, Dh = 4, 16384, 12, 64
+    assert pkg.get_option(pkg.OPT_FWD_LATE_WAIT) == -1 and pkg.get_option(pkg.OPT_BWD_PERSISTENT) == -1
+    Q, K, V, dO = bf16_inputs(31, B, S, H, Dh)
+    O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+    for t in (O, dQ, dK, dV):
+        assert bool(torch.isfinite(t.float()).all())
+    check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, [(3, 11)])
+
+
+def test_long_sequence_sweep_shape_s1024(pkg, dev, orc):
+    """B=64, S=1024, 12 heads x 64 — the shortest point of the sweep at full size: 768 (batch, head)
+    units of 8 tiles, every persistent CTA walks dozens of items.  Parity on three slices."""
+    B, S, H, Dh = 64, 1024, 12, 64
+    Q, K, V, dO = bf16_inputs(37, B, S, H, Dh)
+    O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+    for t in (O, dQ, dK, dV):
+        assert bool(torch.isfinite(t.float()).all())
+    check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, [(0, 0), (31, 5), (63, 11)])
+
+
+@pytest.mark.parametrize("S", [77, 200, 640, 1024])
+def test_forward_wait_placement_option_both_settings(pkg, dev, orc, S):
+    """CXXATTN_OPT_FWD_LATE_WAIT forces either instantiation of the forward kernel (where a softmax
+    warp waits for the previous PV product); both must meet the oracle on ragged last tile pairs and
+    with several items per CTA, and give the same O and lse bit for bit (the arithmetic is the
+    same, only the order of waits differs)."""
+    B, H, Dh = 3, 2, 64
+    Q, K, V = bf16_inputs(41 + S, B, S, H, Dh, n=3)
+    rO, rl = orc.mha_fwd(Q.float().numpy(), K.float().numpy(), V.float().numpy(), B, S, H, Dh, f64=True, want_lse=True)
+    out = []
+    for setting in (0, 1):
+        with pkg.forced_option(pkg.OPT_FWD_LATE_WAIT, setting):
+            O, lse = run_fwd(pkg, dev, Q, K, V, B, S, H, Dh)
+        assert rel_err(O.float().cpu().numpy(), rO) < TOL_BF16, setting
+        assert np.abs(lse.cpu().numpy() - rl).max() < 2e-2, setting
+        out.append((O, lse))
+    assert pkg.get_option(pkg.OPT_FWD_LATE_WAIT) == -1
+    assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
+
+
+def test_backward_schedule_option_both_settings(pkg, dev, orc):
+    """CXXATTN_OPT_BWD_PERSISTENT forces the persistent or the CTA-per-item schedule of the backward;
+    both meet the oracle, dK and dV agree bit for bit (each key tile is summed in the same order by
+    one CTA either way; dQ is summed in arrival order)."""
+    B, S, H, Dh = 2, 640, 2, 64
+    Q, K, V, dO = bf16_inputs(43, B, S, H, Dh)
+    res = []
+    for setting in (0, 1):
+        with pkg.forced_option(pkg.OPT_BWD_PERSISTENT, setting):
+            O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+        check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, [(0, 0), (1, 1)])
+        res.append((dQ, dK, dV))
+    assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2])
+    assert rel_err(res[0][0].float().cpu().numpy(), res[1][0].float().cpu().numpy()) < 1e-2
+
+
+def test_bounded_wait_gives_up_and_reports(pkg, dev):
+    """A device-side wait that can never be satisfied (one CTA waiting on a barrier nothing arrives
+    on, limit 1 ms) returns by itself: the status call reports the timeout and the wait site, the
+    flag is cleared, and a normal launch right after it is correct."""
+    import ctypes as C
+    pkg.sync_status()  # clean slate
+    pkg.selftest_wait_limit(1_000_000)
+    rc = pkg.lib().cxxattn_sync_status(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == -5 and "timed out" in pkg.strerror(rc)
+    assert pkg.lib().cxxattn_last_timeout_site() == 990
+    pkg.sync_status()  # cleared: no exception
+    g = torch.Generator().manual_seed(1)
+    A = torch.randn(128, 64, generator=g).bfloat16()
+    Bm = torch.randn(128, 64, generator=g).bfloat16()
+    D = torch.full((128, 128), float("nan"), device=dev)
+    pkg.selftest_umma(0, A.to(dev), Bm.to(dev), D)
+    pkg.sync_status()
+    assert rel_err(D.cpu().numpy(), (A.float() @ Bm.float().T).numpy()) < 1e-5

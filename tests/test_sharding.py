@@ -38,6 +38,23 @@ def test_slabs_partition_all_units(B, H, world):
     assert max(sizes) - min(sizes) <= 1
 
 
+@pytest.mark.parametrize("B,H,world", [(16, 12, 8), (4, 12, 8), (1, 12, 8), (3, 5, 4), (2, 3, 7), (64, 12, 1)])
+def test_calls_cover_the_slabs_with_merged_whole_batch_items(B, H, world):
+    sh = load_sharding()
+    seen = np.zeros((B, H), int)
+    for r in range(world):
+        cs = sh.calls(B, H, world, r)
+        for b0, nb, h0, nh in cs:
+            assert nb >= 1 and nh >= 1 and (nb == 1 or (h0 == 0 and nh == H))
+            seen[b0:b0 + nb, h0:h0 + nh] += 1
+        assert len(cs) <= 3 or H > 12   # at most a partial head range either side of whole batch items
+    assert np.all(seen == 1)
+    sh16 = sh.calls(16, 12, 8, 3)
+    assert sh16 == [(6, 2, 0, 12)]                       # 65,536 tokens at S=4096 on 8 ranks: two batch items each
+    assert sh.calls(4, 12, 8, 5) == [(2, 1, 6, 6)]        # S=16384: rank g gets batch g/2, heads 6*(g%2)..+5
+    assert sh.calls(64, 12, 1, 0) == [(0, 64, 0, 12)]
+
+
 def _worker(rank, world, port, tmp):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     sys.path.insert(0, ROOT)

@@ -8,8 +8,10 @@ still passes inputs and outputs; the chunk states go to a fixed 8 MiB array insi
 
 The test calls the entry point through the C-ABI twice in a row with different inputs and shapes
 (the array is shared between calls and keeps the previous contents) and compares each result with
-the workspace-taking entry point cxxattn_linattn_fwd at the fp32 tolerance of this suite (1e-5 as
-max|a-b|/max|b|); it also checks the size limit.  The file name keeps it last in collection order,
+the workspace-taking entry point cxxattn_linattn_fwd — the same kernels on the same inputs, so the
+results must be the same bits — and with the CPU oracle at the fp32 tolerance of this suite (1e-5
+as max|a-b|/max|b|), so that the library is not only compared with itself; it also checks the size
+limit.  The file name keeps it last in collection order,
 so a run that stops at the first failure has already run every other test.
 """
 import ctypes as C
@@ -24,7 +26,7 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-5
 
 
-def call_both(pkg, dev, seed, B, S, D, E, feature_map, eps_in_den):
+def call_both(pkg, dev, orc, seed, B, S, D, E, feature_map, eps_in_den):
     lib = pkg.lib()
     Q, K, V = seeded_normal(seed, [(B * S, D), (B * S, D), (B * S, E)])
     if feature_map == pkg.MAP_NONE:  # pre-mapped features are positive
@@ -48,17 +50,21 @@ def call_both(pkg, dev, seed, B, S, D, E, feature_map, eps_in_den):
                                  den2.data_ptr(), zc2.data_ptr(), ws.data_ptr(), n, stream)
     assert rc == 0, pkg.strerror(rc)
     torch.cuda.synchronize()
-    for name, a, b in (("O", O1, O2), ("den", den1, den2), ("z_cache", zc1, zc2)):
+    # elu=False is the LinearGPT flavour of the oracle: pre-mapped features, den stored with its 1e-8
+    assert (feature_map == pkg.MAP_ELU1) == (eps_in_den == 0)
+    want = orc.linattn_fwd(Q, K, V, B, S, D, E, elu=feature_map == pkg.MAP_ELU1)
+    for name, a, b, w in (("O", O1, O2, want[0]), ("den", den1, den2, want[1]), ("z_cache", zc1, zc2, want[2])):
         a, b = a.cpu().numpy(), b.cpu().numpy()
         assert np.all(np.isfinite(a)), name
-        assert rel_err(a, b) < TOL, (name, rel_err(a, b))
+        assert np.array_equal(a, b), (name, rel_err(a, b))
+        assert rel_err(a, np.asarray(w).reshape(a.shape)) < TOL, (name, rel_err(a, np.asarray(w).reshape(a.shape)))
 
 
-def test_noalloc_forward_matches_workspace_forward_on_two_calls_in_a_row(pkg, dev):
+def test_noalloc_forward_matches_workspace_forward_on_two_calls_in_a_row(pkg, dev, orc):
     # first call: ELU+1 flavour, five chunks per sequence with a ragged tail (2 MB of the scratch)
-    call_both(pkg, dev, 71, B=24, S=300, D=64, E=64, feature_map=pkg.MAP_ELU1, eps_in_den=0)
+    call_both(pkg, dev, orc, 71, B=24, S=300, D=64, E=64, feature_map=pkg.MAP_ELU1, eps_in_den=0)
     # second call right after it: other shape and flavour, on top of the first call's leftovers
-    call_both(pkg, dev, 72, B=5, S=130, D=48, E=20, feature_map=pkg.MAP_NONE, eps_in_den=1)
+    call_both(pkg, dev, orc, 72, B=5, S=130, D=48, E=20, feature_map=pkg.MAP_NONE, eps_in_den=1)
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch(pkg, dev):
