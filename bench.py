@@ -645,7 +645,16 @@ def main():
                     help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
     ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
                     help="element type of the linattn_* workloads (bf16: tensor-core kernels, f32: exact kernels)")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library schedule switch for this run, e.g. FWD_LATE_WAIT=1 (cxxattn_set_option; names as the "
+                         "CXXATTN_OPT_* constants without the prefix)")
     args = ap.parse_args()
+    if args.option and args.impl == "ours":
+        import __graft_entry__ as g
+        pkg = g.load_package()
+        for item in args.option:
+            name, _, value = item.partition("=")
+            pkg.set_option(getattr(pkg, "OPT_" + name.upper()), int(value))
     if args.impl == "reference":
         if args.workload in NEIGHBOURS:
             ap.error("--impl reference covers the attention workloads only")

@@ -6,13 +6,17 @@
 // time with shuffle reductions, this kernel is a FlashAttention pipeline:
 //
 //   CTA  = persistent, one per SM; a work item = 2 query tiles of 128 rows (rows q0 .. q0+255 of one
-//          (batch, head)); 12 warps:
-//          warps 0-3  softmax group of tile 0  (thread i <-> query row i <-> TMEM lane i)
-//          warps 4-7  softmax group of tile 1
-//          warp  8    TMA producer: Q of the item (two buffers, so the next item's Q is already
-//                     there), then K/V tiles of 128 keys through a 3-stage ring
-//          warp  9    MMA issuer (the warp runs uniformly, one elected lane issues) and TMEM owner
-//          warps 10-11 idle; with warps 8-9 they release registers to the softmax warps (setmaxnreg)
+//          (batch, head)); 18 warps:
+//          warps 0-7   softmax group of tile 0: warp w holds the 32 rows of TMEM lane quarter w % 4 and
+//                      the half w / 4 of the 128 key columns, so a query row is shared by two threads
+//                      of two warps (they exchange the row maximum through shared memory each step)
+//          warps 8-15  softmax group of tile 1, likewise
+//          warp  16    TMA producer: Q of the item (two buffers, so the next item's Q is already
+//                      there), then K/V tiles of 128 keys through a 3-stage ring
+//          warp  17    MMA issuer (the warp runs uniformly, one elected lane issues) and TMEM owner
+//          Four softmax warps per scheduler: with a whole row per thread (two warps per scheduler) the
+//          exponent unit was 64 % busy and every instruction waited 2.2 cycles on average for a
+//          fixed-latency result that no other warp could cover.
 //   TMEM = S0 | S1 (128 fp32 columns each) | O0 | O1 (64 columns each) | P0 | P1 (128 bf16 = 64
 //          columns each): all 512 columns.  P feeds the PV product directly from TMEM.
 //
@@ -20,7 +24,7 @@
 //                    P_t = exp2(c*S_t - m_t), l_t += rowsum      -> TMEM (bf16)
 //                    O_t += P_t V_j    (TS MMA, 128x64x128)
 //
-// A softmax thread pulls its whole row of scores (128 values) into registers and releases the score
+// A softmax thread pulls its half row of scores (64 values) into registers and releases the score
 // columns at once; since P has columns of its own, the MMA warp can then issue S_t(j+1) while the
 // exponentials of step j are still running, and a softmax group never waits for its next scores.  KV tiles above the causal diagonal
 // are never loaded; only the diagonal tile is masked.  A row's running maximum is only raised
@@ -40,9 +44,9 @@ constexpr int BN = 128;       // keys per KV tile
 constexpr int DH = 64;        // head dimension
 constexpr int STAGES = 3;
 constexpr int TILE_BYTES = BM * DH * 2;  // 16 KB: one 128 x 64 bf16 tile
-constexpr int NTHREADS = 384;  // 12 warps: 8 softmax, producer, MMA issuer, 2 idle (they only give up registers)
+constexpr int NTHREADS = 576;  // 18 warps: 16 softmax, producer, MMA issuer; 112 registers each fill the register file
+constexpr int W_PROD = 16, W_MMA = 17;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int LATE_FROM = 96;  // key tiles per row from which the softmax warps wait late for PV
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 constexpr size_t SMEM_BYTES = (4 + 2 * STAGES) * TILE_BYTES + 1024;  // Q x2 (2 tiles each), K/V ring, alignment slack
 
@@ -78,7 +82,8 @@ __device__ __forceinline__ bool get_item(int round, int npairs, int nbh, int S, 
 }
 
 // LATE_WAIT: the softmax warps form the first half of a step's exponentials before they wait for
-// the PV product of the step before (faster on long rows, slower on short ones; the host picks).
+// the PV product of the step before (the default: 4 to 11 % faster than waiting first at every
+// sequence length measured, 1024 to 16384; CXXATTN_OPT_FWD_LATE_WAIT = 0 selects the other form).
 template <bool LATE_WAIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -88,6 +93,9 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         p_full[2], pv_done[2], o_free[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    // what the two threads of a row tell each other: the maximum of their half of the scores (two slots,
+    // by step parity) and, at the end of an item, their half of the row sum
+    __shared__ float xmax[2][2][2][BM], xsum[2][2][BM];
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                                // 2 buffers x 2 tiles
@@ -112,26 +120,20 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&s_free[t], 4);  // one arrival per softmax warp
-            mbar_init(&p_full[t], 4);
+            mbar_init(&s_free[t], 8);  // one arrival per softmax warp
+            mbar_init(&p_full[t], 8);
             mbar_init(&pv_done[t], 1);
-            mbar_init(&o_free[t], 4);  // the output accumulator has been read out (once per item)
+            mbar_init(&o_free[t], 8);  // the output accumulator has been read out (once per item)
         }
         fence_barrier_init();
     }
-    if (warp == 9) tmem_alloc(&tmem_slot, TMEM_COLS);
+    if (warp == W_MMA) tmem_alloc(&tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    // Register budget: the softmax warps keep a whole row of scores (128 values) in registers, so
-    // the other warp group hands most of its registers over.
-    if (warp >= 8) {
-        // Warps 8-11 form one warp group; all four execute this one instruction together.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    }
-    if (warp == 8) {
+    if (warp == W_PROD) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             prefetch_tmap(&tmQ);
@@ -156,7 +158,7 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == W_MMA) {
         // ---------------- MMA issuer ----------------
         // the whole warp runs the loop (uniform control flow and operands); one elected lane issues
         const uint32_t el = elect_one();
@@ -244,56 +246,56 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 i1++;
             }
         }
-    } else if (warp >= 10) {
-        // idle warps: they only take part in the register hand-over above
     } else {
         // ---------------- softmax groups ----------------
-        // served from what warps 8-11 gave back: 8 warps x 32 x (224 - 168) <= 4 x 32 x (168 - 40); a larger
-        // request would block forever
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-        const int t = warp / 4;
-        const int r = (warp % 4) * 32 + lane;  // row inside the tile == TMEM lane
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp % 4) * 32) << 16);
-        const uint32_t tS = lane_base + COL_S + t * BN;
-        const uint32_t tO = lane_base + COL_O + t * DH;
-        const uint32_t tP = lane_base + COL_P + t * 64;
+        const int t = warp / 8;        // query tile of the item
+        const int hf = (warp / 4) & 1;  // half of the key columns: 64*hf .. 64*hf + 63
+        const int q4 = warp % 4;        // TMEM lane quarter
+        const int r = q4 * 32 + lane;   // row inside the tile == TMEM lane
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+        const uint32_t tS = lane_base + COL_S + t * BN + 64 * hf;
+        const uint32_t tO = lane_base + COL_O + t * DH + 32 * hf;  // this thread's half of the output row
+        const uint32_t tP = lane_base + COL_P + t * 64 + 32 * hf;
+        const int pair_bar = 1 + t * 4 + q4;  // named barrier of the two warps that share these 32 rows
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
         int ct = 0;  // steps so far of this group's query tile, over all items (phases of its barriers)
         Item w;
         for (int k = 0; get_item(k, npairs, nbh, p.S, w); k++) {
             if (t == 1 && !w.has_t1) continue;  // a ragged last pair has no second tile
             const int jlast = w.n0 + t;
-            float m = -INFINITY, l = 0.f;
+            float m = -INFINITY, l = 0.f;  // l: this thread's half of the row sum
             for (int j = 0; j <= jlast; j++) {
                 const int cj = ct + j;
                 mbar_wait(&s_full[t], cj & 1, guard, 301 + t);
                 tc_fence_after();
                 const bool diag = j == jlast;
-                // The whole row of scores goes to registers at once, and the score columns are handed
+                // The half row of scores goes to registers at once, and the score columns are handed
                 // back right away: S_t(j+1) is computed while this step's exponentials run.
-                uint32_t sv[4][32];
-#pragma unroll
-                for (int c = 0; c < 4; c++) tmem_ld32(tS + 32 * c, sv[c]);
+                uint32_t sv[2][32];
+                tmem_ld32(tS, sv[0]);
+                tmem_ld32(tS + 32, sv[1]);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_free[t]);
-                // pass 1: row maximum; on the diagonal tile key column c is visible iff c <= r
-                float mx = -INFINITY;
+                // pass 1: maximum of the half row (two chains); on the diagonal tile key column c is visible iff c <= r
+                float mx0 = -INFINITY, mx1 = -INFINITY;
                 if (diag) {
 #pragma unroll
-                    for (int c = 0; c < 4; c++)
+                    for (int c = 0; c < 2; c++)
 #pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            if (32 * c + i > r) sv[c][i] = 0xff800000u;  // -inf
-                            mx = fmaxf(mx, __uint_as_float(sv[c][i]));
-                        }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            mx = max3(mx, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+                        for (int i = 0; i < 32; i++)
+                            if (64 * hf + 32 * c + i > r) sv[c][i] = 0xff800000u;  // -inf
                 }
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    mx0 = max3(mx0, __uint_as_float(sv[0][i]), __uint_as_float(sv[0][i + 1]));
+                    mx1 = max3(mx1, __uint_as_float(sv[1][i]), __uint_as_float(sv[1][i + 1]));
+                }
+                // the other half's maximum: both threads of a row must scale by the same reference
+                xmax[t][cj & 1][hf][r] = fmaxf(mx0, mx1);
+                pair_sync();
+                const float mx = fmaxf(fmaxf(mx0, mx1), xmax[t][cj & 1][hf ^ 1][r]);
                 const float m_new = fmaxf(m, mx * p.scale_log2);
                 const bool raise = m_new - m > 8.0f;  // also true on the first tile (m = -inf)
                 const float m_use = raise ? m_new : m;
@@ -303,15 +305,15 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 auto settle = [&]() {
                     mbar_wait(&pv_done[t], (cj - 1) & 1, guard, 305 + t);
                     tc_fence_after();
-                    if (__any_sync(0xffffffffu, raise)) {
+                    if (__any_sync(0xffffffffu, raise)) {  // the partner warp sees the same flags row by row
 #pragma unroll
-                        for (int h = 0; h < 2; h++) {
-                            uint32_t o[32];
-                            tmem_ld32(tO + 32 * h, o);
+                        for (int h2 = 0; h2 < 2; h2++) {  // 16 columns at a time: the score row fills the registers
+                            uint32_t o[16];
+                            tmem_ld16(tO + 16 * h2, o);
                             tmem_ld_wait();
 #pragma unroll
-                            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            tmem_st32(tO + 32 * h, o);
+                            for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st16(tO + 16 * h2, o);
                         }
                     }
                 };
@@ -324,23 +326,22 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 uint64_t rs2 = pack2(0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    uint32_t pk[32];
+                    // the bf16 pairs are packed into the front of the score registers they come from
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
+                    for (int i = 0; i < 32; i += 4) {
                         float a0, a1, b0, b1;
-                        unpack2(fma2(pack2(__uint_as_float(sv[2 * c][i]), __uint_as_float(sv[2 * c][i + 1])), c2, m2), a0, a1);
-                        unpack2(fma2(pack2(__uint_as_float(sv[2 * c + 1][i]), __uint_as_float(sv[2 * c + 1][i + 1])), c2, m2),
-                                b0, b1);
+                        unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), c2, m2), a0, a1);
+                        unpack2(fma2(pack2(__uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3])), c2, m2), b0, b1);
                         a0 = ex2(a0);
                         a1 = ex2(a1);
                         b0 = ex2(b0);
                         b1 = ex2(b1);
                         rs2 = add2(rs2, add2(pack2(a0, a1), pack2(b0, b1)));
-                        pk[i / 2] = pack_bf16(a0, a1);
-                        pk[16 + i / 2] = pack_bf16(b0, b1);
+                        sv[c][i / 2] = pack_bf16(a0, a1);
+                        sv[c][i / 2 + 1] = pack_bf16(b0, b1);
                     }
-                    if (LATE_WAIT && c == 0 && j > 0) settle();
-                    tmem_st32(tP + 32 * c, pk);
+                    if (c == 0 && LATE_WAIT && j > 0) settle();
+                    tmem_st16(tP + 16 * c, sv[c]);
                 }
                 float rs, rs_hi;
                 unpack2(rs2, rs, rs_hi);
@@ -356,37 +357,39 @@ mha_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_wait(&pv_done[t], (ct + jlast) & 1, guard, 311 + t);
             tc_fence_after();
             ct += jlast + 1;
-            const int qr = w.q0 + t * BM + r;
-            const float inv = 1.0f / l;
-            uint32_t o[2][32];
-            tmem_ld32(tO, o[0]);
-            tmem_ld32(tO + 32, o[1]);
+            uint32_t o[32];
+            tmem_ld32(tO, o);
+            xsum[t][hf][r] = l;
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&o_free[t]);
+            pair_sync();
+            l += xsum[t][hf ^ 1][r];
+            const int qr = w.q0 + t * BM + r;
+            const float inv = 1.0f / l;
             const int b = w.bh / p.H, h = w.bh % p.H;
             if (qr < p.S && p.O != nullptr) {
-                uint4* dst = reinterpret_cast<uint4*>(p.O + (int64_t)b * p.sb + (int64_t)qr * p.ss + (int64_t)h * p.sh);
+                uint4* dst = reinterpret_cast<uint4*>(p.O + (int64_t)b * p.sb + (int64_t)qr * p.ss + (int64_t)h * p.sh + 32 * hf);
 #pragma unroll
-                for (int c = 0; c < 2; c++)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 v;
-                        v.x = pack_bf16(__uint_as_float(o[c][i + 0]) * inv, __uint_as_float(o[c][i + 1]) * inv);
-                        v.y = pack_bf16(__uint_as_float(o[c][i + 2]) * inv, __uint_as_float(o[c][i + 3]) * inv);
-                        v.z = pack_bf16(__uint_as_float(o[c][i + 4]) * inv, __uint_as_float(o[c][i + 5]) * inv);
-                        v.w = pack_bf16(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
-                        dst[(c * 32 + i) / 8] = v;
-                    }
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v;
+                    v.x = pack_bf16(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+                    v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                    v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                    v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                    dst[i / 8] = v;
+                }
             }
-            if (qr < p.S && p.lse != nullptr) p.lse[(int64_t)w.bh * p.S + qr] = (m + log2f(l)) * 0.6931471805599453f;
+            if (hf == 0 && qr < p.S && p.lse != nullptr) p.lse[(int64_t)w.bh * p.S + qr] = (m + log2f(l)) * 0.6931471805599453f;
+            // the partner must have read this item's row sum before the next item's is written
+            pair_sync();
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == W_MMA) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
@@ -430,10 +433,7 @@ int mha_tc_fwd(const MhaShape& p, const void* Q, const void* K, const void* V, v
     const int npairs = (p.S + 2 * BM - 1) / (2 * BM);
     const int64_t items = (int64_t)npairs * p.B * p.H;
     const int64_t grid = std::min<int64_t>(items, sm_count());
-    // measured on B200: waiting late wins from about LATE_FROM key tiles per row on
-    // (CXXATTN_OPT_FWD_LATE_WAIT = 0 / 1 forces the choice)
-    const int forced = option(CXXATTN_OPT_FWD_LATE_WAIT);
-    const bool late = forced >= 0 ? forced != 0 : (p.S + BN - 1) / BN >= LATE_FROM;
+    const bool late = option(CXXATTN_OPT_FWD_LATE_WAIT) != 0;  // -1 (default) and 1: wait late
     if (late) mha_tc_fwd_kernel<true><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
     else mha_tc_fwd_kernel<false><<<(unsigned)grid, NTHREADS, SMEM_BYTES, st>>>(tmQ, tmK, tmV, fp);
     return check_launch();

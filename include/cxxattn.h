@@ -257,8 +257,8 @@ int cxxattn_last_timeout_site(void);
  * schedule changes. */
 enum {
     CXXATTN_OPT_FWD_LATE_WAIT = 0,  /* bf16 softmax forward: where a softmax warp waits for the PV product
-                                       of the step before.  -1 by sequence length (default), 0 before
-                                       the exponentials, 1 after half of them                          */
+                                       of the step before.  -1 the library's choice (default; today 1),
+                                       0 before the exponentials, 1 after half of them                 */
     CXXATTN_OPT_BWD_PERSISTENT = 1, /* bf16 softmax backward: -1 by sequence length (default), 1 one
                                        persistent CTA per SM drawing (key tile, batch*head) items,
                                        0 one CTA per item                                               */

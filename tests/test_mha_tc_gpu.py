@@ -186,8 +186,8 @@ def check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, slices):
 
 def test_long_sequence_sweep_shape_s16384(pkg, dev, orc):
     """B=4, S=16384, 12 heads x 64 — the longest point of the sequence sweep, at full size.  128 key
-    tiles per row: the forward takes its late-wait instantiation and the backward one CTA per
-    (key tile, batch*head) item with 128 query tiles.  Parity on the last (batch, head) slice, the
+    tiles per row: the forward in its default (late-wait) instantiation and the backward with one CTA
+    per (key tile, batch*head) item of 128 query tiles.  Parity on the last (batch, head) slice, the
     one whose items are scheduled last."""
     B, S, H, Dh = 4, 16384, 12, 64
     assert pkg.get_option(pkg.OPT_FWD_LATE_WAIT) == -1 and pkg.get_option(pkg.OPT_BWD_PERSISTENT) == -1
