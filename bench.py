@@ -45,6 +45,9 @@ NEIGHBOURS = {
     "decode_linear_wide": "linear-stage decoding step, 64 units, D = E = 768 (state 2.4 MB per unit)",
     "decode_softmax": "softmax-stage decoding step, 64 x 12 heads of 64, 4096 keys in the cache",
 }
+# The full-model data-parallel training step (vocab 6400, block 256, n_embd 768, 12 heads, 12 blocks, batch 8 per GPU)
+DP_WORKLOAD = "dp_step"
+DP_METRIC = "hybrid_gpt_train_tokens_per_s_per_job"
 LIN_METRIC = "causal_linear_attn_fwd_bwd_algorithmic_gbps_per_job"
 METRIC = "causal_softmax_attn_fwd_bwd_tflops_per_job"
 UNIT = "TFLOP/s"
@@ -567,6 +570,121 @@ def run_ours_linattn(args):
         dist.destroy_process_group()
 
 
+def run_dp_step(args):
+    """One step = forward + backward + gradient all-reduce + fused AdamW of the hybrid model on 8
+    sequences of 256 tokens per GPU (weak scaling: the global batch grows with the ranks, as in
+    data-parallel training).  Token ids come from pinned host memory and the loss is read back every
+    step, in the device-timed loop and in the end-to-end loop alike."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    from cxx_gpt_b200 import hybrid_gpt as hy
+    world, rank, local, dev = init_ranks()
+    cfg = hy.HybridConfig()
+    B, S = 8, cfg.block_size
+    model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=4)
+    stepper = hy.DataParallelStep(model, lr=1e-3, cuda_graph=not args.no_cuda_graph)
+    gen = torch.Generator(device="cpu").manual_seed(4 + rank)
+    nbatch = 8
+    # token ids uniform in [0, vocab); the target of a position is a fixed function of its token, so
+    # that the loss can fall and the line shows it
+    host = []
+    for _ in range(nbatch):
+        idx = torch.randint(0, cfg.vocab_size, (B, S), generator=gen)
+        host.append((idx.pin_memory(), ((idx * 7 + 3) % cfg.vocab_size).pin_memory()))
+    hloss = torch.zeros(1).pin_memory()
+    turn = [0]
+
+    def step():
+        idx, tgt = host[turn[0] % nbatch]
+        turn[0] += 1
+        loss, nsq = stepper.step(idx.to(dev, non_blocking=True), tgt.to(dev, non_blocking=True))
+        hloss.copy_(loss.reshape(1), non_blocking=True)
+        return loss
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    first = None
+    for _ in range(max(args.warmup, 3)):
+        step()
+        torch.cuda.synchronize()
+        first = first if first is not None else float(hloss)
+    pkg.sync_status()
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    sampler.stop_flag = True
+    ms = e0.elapsed_time(e1) / args.steps
+    last = float(hloss)
+    # end to end: wall clock around the same call, each step's loss read on the host before the next
+    barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(3, min(args.steps, 10))
+    for _ in range(n_e2e):
+        step()
+        torch.cuda.synchronize()
+        float(hloss)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
+    # the optimiser kernel alone (the kernel that follows the collective): HBM-bound, 28 bytes per parameter
+    oe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    opt_ms = 0.0
+    for _ in range(5):
+        flush.zero_()
+        oe[0].record()
+        pkg.adamw_step(model.flat_param, model.flat_grad, stepper.m, stepper.v, stepper.t + 1, 0.0, grad_scale=1.0)
+        oe[1].record()
+        torch.cuda.synchronize()
+        opt_ms += oe[0].elapsed_time(oe[1]) / 5
+    t = torch.tensor([ms, e2e_ms, opt_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, opt_ms = t.tolist()
+    if rank == 0:
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                hbm, how = float(json.load(f)["hbm_gbs"]), "measured"
+        except Exception:
+            hbm, how = 6650.0, "fallback"
+        tokens = world * B * S
+        gbs = 28.0 * model.numel / (opt_ms * 1e-3) / 1e9
+        line = {"metric": DP_METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": dp_config(world),
+                "parameters": model.numel, "loss_first": first, "loss_last": last,
+                "cuda_graph": stepper.graph is not None,
+                "gpu_launches": args.steps * world * (cfg.n_layer * (4 + 2 + 4 + 12) + 1),
+                "clocks": sampler.result(),
+                "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": world * 2 * B * S * 8, "d2h_bytes_per_step": world * 4},
+                "roofline": {"bound": "hbm", "kernel": "adamw_fused_kernel (the kernel after the gradient all-reduce)",
+                             "launch_ms": opt_ms, "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s",
+                             "frac": gbs / hbm, "traffic": None}}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def dp_config(world):
+    return {"workload": DP_WORKLOAD, "model": "hybrid GPT: 12 pre-LN blocks, softmax MHA then ELU+1 linear attention",
+            "vocab": 6400, "block_size": 256, "n_embd": 768, "n_head": 12, "n_layer": 12, "batch_per_gpu": 8,
+            "global_batch": 8 * world, "seq_len": 256, "optimizer": "AdamW lr 1e-3", "parallelism": "dp%d" % world,
+            "n_ranks": world}
+
+
 def run_neighbours(args):
     """One HBM-bound kernel per step on one GPU; value = algorithmic bytes / CUDA-event time."""
     import torch
@@ -636,7 +754,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS) + sorted(NEIGHBOURS))
+    ap.add_argument("--workload", default="softmax_s4096", choices=sorted(WORKLOADS) + sorted(NEIGHBOURS) + [DP_WORKLOAD])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weak", action="store_true",
                     help="every rank runs the whole workload on data of its own (default: the workload's 65,536 "
@@ -645,6 +763,8 @@ def main():
                     help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
     ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
                     help="element type of the linattn_* workloads (bf16: tensor-core kernels, f32: exact kernels)")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="dp_step: launch every kernel of forward + backward from Python instead of replaying a CUDA graph")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="library schedule switch for this run, e.g. FWD_LATE_WAIT=1 (cxxattn_set_option; names as the "
                          "CXXATTN_OPT_* constants without the prefix)")
@@ -656,9 +776,11 @@ def main():
             name, _, value = item.partition("=")
             pkg.set_option(getattr(pkg, "OPT_" + name.upper()), int(value))
     if args.impl == "reference":
-        if args.workload in NEIGHBOURS:
+        if args.workload in NEIGHBOURS or args.workload == DP_WORKLOAD:
             ap.error("--impl reference covers the attention workloads only")
         run_reference(args)
+    elif args.workload == DP_WORKLOAD:
+        run_dp_step(args)
     elif args.workload in NEIGHBOURS:
         run_neighbours(args)
     elif args.workload.startswith("linattn"):

@@ -110,7 +110,8 @@ int cxxattn_mha_bwd(const cxxattn_mha_desc* desc, const void* Q, const void* K, 
 size_t cxxattn_linattn_workspace_bytes(const cxxattn_lin_desc* desc) {
     if (!lin_ok(desc)) return 0;
     if (desc->dtype == CXXATTN_F32) return linattn_f32_workspace(*desc);
-    if (desc->dtype == CXXATTN_BF16) return linattn_tc_workspace(*desc);
+    if (desc->dtype == CXXATTN_BF16)
+        return linattn_tc_supported(*desc) ? linattn_tc_workspace(*desc) : linattn_wide_workspace(*desc);
     return 0;
 }
 
@@ -123,8 +124,9 @@ int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void*
         return linattn_f32_fwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (float*)O, den,
                                z_cache, workspace, workspace_bytes, st);
     if (desc->dtype == CXXATTN_BF16) {
-        if (z_cache != nullptr) return CXXATTN_ERR_UNSUPPORTED;  // the bf16 path keeps z on chip
-        return linattn_tc_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
+        if (z_cache != nullptr) return CXXATTN_ERR_UNSUPPORTED;  // the bf16 paths keep z on chip or need none
+        if (linattn_tc_supported(*desc)) return linattn_tc_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
+        return linattn_wide_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
     }
     return CXXATTN_ERR_INVALID;
 }
@@ -171,8 +173,11 @@ int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void*
         return linattn_f32_bwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (const float*)O,
                                (const float*)dO, den, (float*)dQ, (float*)dK, (float*)dV,
                                workspace, workspace_bytes, st);
-    if (desc->dtype == CXXATTN_BF16)
-        return linattn_tc_bwd(*desc, Q, K, V, O, dO, den, dQ, dK, dV, workspace, workspace_bytes, st);
+    if (desc->dtype == CXXATTN_BF16) {
+        if (linattn_tc_supported(*desc))
+            return linattn_tc_bwd(*desc, Q, K, V, O, dO, den, dQ, dK, dV, workspace, workspace_bytes, st);
+        return linattn_wide_bwd(*desc, Q, K, V, O, dO, den, dQ, dK, dV, workspace, workspace_bytes, st);
+    }
     return CXXATTN_ERR_INVALID;
 }
 
@@ -278,6 +283,16 @@ int cxxattn_rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, 
     if (!src || !dst || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 4 || D % head_dim)
         return CXXATTN_ERR_INVALID;
     return rope_cast(src, src_dtype, dst, dst_dtype, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_adamw_step(float* param, const float* grad, float* m, float* v, size_t n, float grad_scale, float lr,
+                       float beta1, float beta2, float weight_decay, float eps, int step, float* grad_norm_sq,
+                       cxxattn_stream_t stream) {
+    if (!param || !grad || !m || !v || n == 0 || step < 1 || !(beta1 >= 0.f && beta1 < 1.f) ||
+        !(beta2 >= 0.f && beta2 < 1.f) || !(eps > 0.f))
+        return CXXATTN_ERR_INVALID;
+    return adamw_fused(param, grad, m, v, n, grad_scale, lr, beta1, beta2, weight_decay, eps, step, grad_norm_sq,
+                       static_cast<cudaStream_t>(stream));
 }
 
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {

@@ -172,7 +172,7 @@ int cxxattn_lin_host_plan_create(cxxattn_lin_host_plan** out, const cxxattn_lin_
     // a descriptor the device-pointer entry points would refuse is refused here too
     const size_t ws = cxxattn_linattn_workspace_bytes(&cd);
     if (ws == 0 && desc->dtype == CXXATTN_F32) return CXXATTN_ERR_INVALID;
-    if (desc->dtype == CXXATTN_BF16 && !linattn_tc_supported(cd)) return CXXATTN_ERR_UNSUPPORTED;
+    if (desc->dtype == CXXATTN_BF16 && !linattn_tc_supported(cd) && !linattn_wide_supported(cd)) return CXXATTN_ERR_UNSUPPORTED;
     const int dev = current_device();
     if (dev < 0) return CXXATTN_ERR_CUDA;
     cxxattn_lin_host_plan* p = new (std::nothrow) cxxattn_lin_host_plan();

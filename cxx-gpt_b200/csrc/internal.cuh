@@ -74,6 +74,15 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
                    const void* dO, const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes,
                    cudaStream_t st);
 
+// ---- tcgen05 bf16 linear attention with one wide head, D and E multiples of 64 (linattn_wide.cu) ----
+bool linattn_wide_supported(const cxxattn_lin_desc& d);
+size_t linattn_wide_workspace(const cxxattn_lin_desc& d);
+int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
+                     void* ws, size_t ws_bytes, cudaStream_t st);
+int linattn_wide_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O,
+                     const void* dO, const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes,
+                     cudaStream_t st);
+
 // ---- diagnostics (umma_selftest.cu) ----
 int umma_selftest(int mode, const void* A, const void* B, float* D, cudaStream_t st);
 int wait_selftest(uint64_t limit_ns, cudaStream_t st);
@@ -110,6 +119,8 @@ int linattn_decode_step(const cxxattn_lin_desc& d, const float* q, const float* 
 size_t mha_decode_workspace(const cxxattn_mha_desc& d);
 int mha_decode_step(const cxxattn_mha_desc& d, const float* q, const float* k, const float* v, float* Kc, float* Vc,
                     int64_t pos, float* o, void* ws, size_t ws_bytes, cudaStream_t st);
+int adamw_fused(float* param, const float* grad, float* m, float* v, size_t n, float grad_scale, float lr, float beta1,
+                float beta2, float wd, float eps, int step, float* norm_sq, cudaStream_t st);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
 

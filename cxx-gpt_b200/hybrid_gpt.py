@@ -1,0 +1,313 @@
+"""The data-parallel training step around the attention kernels (full-model configuration of the
+baseline: vocab 6400, block 256, n_embd 768, 12 heads x 64, 12 pre-LN blocks, batch 8 per GPU,
+AdamW lr 1e-3).
+
+No single reference file implements this model; it is the reference's GPT skeleton
+(src/GPT/gpt_gpt.hpp:333-399 block, :480-511 model: token + position embedding, pre-LN blocks with
+residuals, GELU MLP, final LayerNorm) whose attention is TwoStageGPT's pair of stages
+(src/TwoStage/two_stage_gpt.hpp:101-122 forward, :149-174 backward): q/k/v projections -> rotary
+embedding per head -> fused causal softmax MHA -> lq/lk/lv projections (bias-free) -> rotary
+embedding over the whole width -> ELU+1 linear attention with ONE head of width n_embd -> output
+projection; and TwoStageGPT's weight-tied lm_head (two_stage_gpt.hpp:272-276, 304-313).  With these
+layers the model has 111.4 M parameters (111,401,472) at the full size (the baseline's "~95 M" is the plain GPT).
+
+What runs where:
+  * the two attention stages, the rotary embedding fused with the type conversion, and the
+    optimiser step are this library's kernels, called through its C-ABI (`CudaKernels`);
+  * the dense glue (linear layers, LayerNorm, GELU, embedding, cross-entropy) is plain torch, i.e.
+    cuBLAS and library kernels: it is outside the attention path and is not tuned here;
+  * gradients live in ONE flat fp32 buffer that the autograd engine accumulates into in place; after
+    the backward pass of a bucket of it, `torch.distributed.all_reduce` (NCCL, sum) is started on
+    that bucket while the rest of the backward pass runs; the kernel after the collective,
+    cxxattn_adamw_step, turns the sum into the mean, applies AdamW as the reference's optimiser
+    does (src/GPT/gpt_cuda_kernels.cu:488-501) and accumulates the gradient norm, in one pass.
+
+There is no CPU path in the product: `CudaKernels` refuses to run without a CUDA device.  The model
+code takes the kernel set as an argument so that the multi-rank host logic (bucketing, the
+all-reduce, the step) can be tested on CPU ranks with a stand-in that the tests supply.
+"""
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+
+class HybridConfig:
+    def __init__(self, vocab_size=6400, block_size=256, n_embd=768, n_head=12, n_layer=12, ln_eps=1e-5,
+                 compute_dtype=torch.bfloat16):
+        assert n_embd % n_head == 0
+        self.vocab_size, self.block_size, self.n_embd = vocab_size, block_size, n_embd
+        self.n_head, self.n_layer, self.ln_eps = n_head, n_layer, ln_eps
+        self.head_dim = n_embd // n_head
+        self.compute_dtype = compute_dtype
+
+
+class CudaKernels:
+    """The library's kernels behind the interface the model uses.  Tensors are CUDA tensors; outputs
+    are allocated with torch (plumbing), everything else happens inside libcxxattn.so."""
+
+    def __init__(self, pkg):
+        if not torch.cuda.is_available():
+            raise RuntimeError("the training step needs a CUDA device: there is no CPU path in the product")
+        self.pkg = pkg
+
+    def rope_cast(self, x, B, S, D, head_dim, sign, out_dtype):
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        self.pkg.rope_cast(x.contiguous(), out, B, S, D, head_dim, sign)
+        return out
+
+    def mha_fwd(self, q, k, v, B, S, H, Dh):
+        o = torch.empty_like(q)
+        lse = torch.empty(B * H * S, dtype=torch.float32, device=q.device)
+        self.pkg.mha_fwd(q, k, v, o, B, S, H, Dh, lse=lse)
+        return o, lse
+
+    def mha_bwd(self, q, k, v, o, do, lse, B, S, H, Dh):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        self.pkg.mha_bwd(q, k, v, o, do.contiguous(), dq, dk, dv, B, S, H, Dh, lse=lse)
+        return dq, dk, dv
+
+    def lin_fwd(self, q, k, v, B, S, D, E):
+        o = torch.empty_like(v)
+        den = torch.empty(B * S, dtype=torch.float32, device=q.device)
+        self.pkg.linattn_fwd(q, k, v, o, den, None, B, S, D, E, self.pkg.MAP_ELU1, 0)
+        return o, den
+
+    def lin_bwd(self, q, k, v, o, do, den, B, S, D, E):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        self.pkg.linattn_bwd(q, k, v, o, do.contiguous(), den, dq, dk, dv, B, S, D, E, self.pkg.MAP_ELU1, 0)
+        return dq, dk, dv
+
+    def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq):
+        self.pkg.adamw_step(param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq)
+
+
+class _RopeCast(torch.autograd.Function):
+    """y = rope(x) in `out_dtype` (two_stage_cuda::rope_fwd + the conversion the next kernel wants);
+    backward = rope with the opposite sign back to x's type (rope_bwd, two_stage_gpt.hpp:160,174)."""
+
+    @staticmethod
+    def forward(ctx, x, kernels, B, S, D, head_dim, out_dtype):
+        ctx.kernels, ctx.dims, ctx.in_dtype = kernels, (B, S, D, head_dim), x.dtype
+        return kernels.rope_cast(x, B, S, D, head_dim, 1.0, out_dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        B, S, D, hd = ctx.dims
+        return ctx.kernels.rope_cast(g, B, S, D, hd, -1.0, ctx.in_dtype), None, None, None, None, None, None
+
+
+class _SoftmaxStage(torch.autograd.Function):
+    """Stage 1: fused causal softmax MHA (fused_mha_fwd / fused_mha_bwd, two_stage_gpt.hpp:106,171)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, kernels, B, S, H, Dh):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = kernels.mha_fwd(q, k, v, B, S, H, Dh)
+        ctx.kernels, ctx.dims = kernels, (B, S, H, Dh)
+        ctx.save_for_backward(q, k, v, o, lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ctx.kernels.mha_bwd(q, k, v, o, do, lse, *ctx.dims)
+        return dq, dk, dv, None, None, None, None, None
+
+
+class _LinearStage(torch.autograd.Function):
+    """Stage 2: ELU+1 causal linear attention, one head of width D = E (kernel_attn_fwd and the
+    step1 / dQ / dKdV backward, two_stage_gpt.hpp:121,149-156)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, kernels, B, S, D, E):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, den = kernels.lin_fwd(q, k, v, B, S, D, E)
+        ctx.kernels, ctx.dims = kernels, (B, S, D, E)
+        ctx.save_for_backward(q, k, v, o, den)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, den = ctx.saved_tensors
+        dq, dk, dv = ctx.kernels.lin_bwd(q, k, v, o, do, den, *ctx.dims)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def parameter_table(cfg):
+    """(name, shape, init std or None for ones / 0.0 for zeros) in the order the forward pass uses them,
+    which is the reverse of the order in which the backward pass finishes their gradients."""
+    E, V = cfg.n_embd, cfg.vocab_size
+    t = [("wte", (V, E), 0.02), ("wpe", (cfg.block_size, E), 0.02)]
+    for i in range(cfg.n_layer):
+        p = f"h{i}."
+        t += [(p + "ln_1.g", (E,), None), (p + "ln_1.b", (E,), 0.0)]
+        for n in ("attn_q", "attn_k", "attn_v"):
+            t += [(p + n + ".w", (E, E), 0.02), (p + n + ".b", (E,), 0.0)]
+        for n in ("lq_proj", "lk_proj", "lv_proj"):
+            t += [(p + n + ".w", (E, E), 0.02)]
+        t += [(p + "attn_proj.w", (E, E), 0.02), (p + "attn_proj.b", (E,), 0.0),
+              (p + "ln_2.g", (E,), None), (p + "ln_2.b", (E,), 0.0),
+              (p + "mlp_fc.w", (4 * E, E), 0.02), (p + "mlp_fc.b", (4 * E,), 0.0),
+              (p + "mlp_proj.w", (E, 4 * E), 0.02), (p + "mlp_proj.b", (E,), 0.0)]
+    t += [("ln_f.g", (E,), None), ("ln_f.b", (E,), 0.0)]
+    return t
+
+
+class HybridGPT:
+    """Parameters, gradients and AdamW moments in four flat fp32 buffers; `p[name]` are views."""
+
+    def __init__(self, cfg, kernels, device, seed=0):
+        self.cfg, self.kernels, self.device = cfg, kernels, device
+        table = parameter_table(cfg)
+        self.offsets, off = {}, 0
+        for name, shape, _ in table:
+            n = math.prod(shape)
+            self.offsets[name] = (off, n, shape)
+            off += (n + 3) // 4 * 4  # every view starts on a 16-byte boundary
+        self.numel = off
+        self.flat_param = torch.zeros(off, dtype=torch.float32, device=device)
+        self.flat_grad = torch.zeros_like(self.flat_param)
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.p = {}
+        for name, shape, std in table:
+            o, n, _ = self.offsets[name]
+            view = self.flat_param[o:o + n].view(shape)
+            if std is None:
+                view.fill_(1.0)
+            elif std > 0:
+                view.copy_((torch.randn(shape, generator=g) * std).to(device))
+            view.requires_grad_(True)
+            view.grad = self.flat_grad[o:o + n].view(shape)  # autograd accumulates into the flat buffer in place
+            self.p[name] = view
+        self.order = [name for name, _, _ in table]
+
+    def _linear(self, x, name, bias=True):
+        dt = x.dtype
+        w = self.p[name + ".w"].to(dt)
+        return F.linear(x, w, self.p[name + ".b"].to(dt) if bias else None)
+
+    def _ln(self, x, name):
+        E = self.cfg.n_embd
+        return F.layer_norm(x.float(), (E,), self.p[name + ".g"], self.p[name + ".b"], self.cfg.ln_eps).to(x.dtype)
+
+    def loss(self, idx, targets):
+        """Mean next-token cross-entropy of logits = model(idx); idx, targets [B, S] int64."""
+        cfg, K = self.cfg, self.kernels
+        B, S = idx.shape
+        E, H, Dh, dt = cfg.n_embd, cfg.n_head, cfg.head_dim, cfg.compute_dtype
+        pos = torch.arange(S, device=idx.device)
+        h = (F.embedding(idx, self.p["wte"]) + F.embedding(pos, self.p["wpe"])[None]).reshape(B * S, E).to(dt)
+        for i in range(cfg.n_layer):
+            p = f"h{i}."
+            a = self._ln(h, p + "ln_1")
+            q, k, v = (self._linear(a, p + n) for n in ("attn_q", "attn_k", "attn_v"))
+            q = _RopeCast.apply(q, K, B, S, E, Dh, dt)
+            k = _RopeCast.apply(k, K, B, S, E, Dh, dt)
+            ra = _SoftmaxStage.apply(q, k, v, K, B, S, H, Dh)
+            lq, lk, lv = (self._linear(ra, p + n, bias=False) for n in ("lq_proj", "lk_proj", "lv_proj"))
+            # stage 2, one head of width n_embd: the tensor-core kernels in bf16 when the width is a multiple
+            # of 64, the exact fp32 kernels otherwise
+            dt2 = dt if (dt == torch.bfloat16 and E % 64 == 0) else torch.float32
+            lq = _RopeCast.apply(lq, K, B, S, E, E, dt2)
+            lk = _RopeCast.apply(lk, K, B, S, E, E, dt2)
+            ac = _LinearStage.apply(lq, lk, lv.to(dt2), K, B, S, E, E).to(dt)
+            h = h + self._linear(ac, p + "attn_proj")
+            m = self._linear(F.gelu(self._linear(self._ln(h, p + "ln_2"), p + "mlp_fc")), p + "mlp_proj")
+            h = h + m
+        h = self._ln(h, "ln_f")
+        logits = F.linear(h, self.p["wte"].to(dt))  # weight-tied lm_head
+        return F.cross_entropy(logits.float(), targets.reshape(-1))
+
+
+class DataParallelStep:
+    """One optimiser step per call: forward, backward with the bucketed gradient all-reduce started from
+    autograd hooks, then the fused mean + AdamW + gradient-norm kernel.  `group` None = the default
+    process group when torch.distributed is initialised, else a single rank."""
+
+    def __init__(self, model, lr=1e-3, beta1=0.9, beta2=0.999, weight_decay=0.01, eps=1e-8, n_buckets=4, group=None,
+                 cuda_graph=False):
+        self.model, self.group = model, group
+        # cuda_graph: after three eager steps, forward + backward (+ the all-reduces) of a fixed batch
+        # shape are captured once and replayed; the step is a few thousand short launches, and issuing
+        # them from Python costs more time than the GPU needs to run them
+        self.cuda_graph, self.graph, self.eager_steps = cuda_graph, None, 0
+        self.hp = (lr, beta1, beta2, weight_decay, eps)
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.m = torch.zeros_like(model.flat_param)
+        self.v = torch.zeros_like(model.flat_param)
+        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=model.device)
+        self.t = 0
+        # Buckets are contiguous ranges of the flat buffer, cut at parameter borders into roughly equal
+        # parts.  The backward pass finishes gradients from the end of the buffer towards its start, so
+        # the last bucket is ready first.
+        names = model.order
+        target = model.numel / max(1, n_buckets)
+        self.buckets, lo, count = [], 0, 0
+        for j, name in enumerate(names):
+            o, n, _ = model.offsets[name]
+            count += 1
+            end = (o + n + 3) // 4 * 4
+            if end - lo >= target or j == len(names) - 1:
+                self.buckets.append({"lo": lo, "hi": end, "params": count, "ready": 0})
+                lo, count = end, 0
+        self.bucket_of = {}
+        for b in self.buckets:
+            for name in names:
+                o, _, _ = model.offsets[name]
+                if b["lo"] <= o < b["hi"]:
+                    self.bucket_of[name] = b
+        self.pending = []
+        if self.world > 1:
+            for name in names:
+                model.p[name].register_post_accumulate_grad_hook(self._make_hook(name))
+
+    def _make_hook(self, name):
+        b = self.bucket_of[name]
+
+        def hook(_param):
+            b["ready"] += 1
+            if b["ready"] == b["params"]:  # the whole bucket is final: reduce it while backward goes on
+                b["ready"] = 0
+                self.pending.append(dist.all_reduce(self.model.flat_grad[b["lo"]:b["hi"]], op=dist.ReduceOp.SUM,
+                                                    group=self.group, async_op=True))
+        return hook
+
+    def _forward_backward(self, idx, targets):
+        model = self.model
+        model.flat_grad.zero_()
+        loss = model.loss(idx, targets)
+        loss.backward()
+        for w in self.pending:
+            w.wait()
+        self.pending.clear()
+        return loss.detach()
+
+    def _capture(self, idx, targets):
+        self.static_idx, self.static_tgt = idx.clone(), targets.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.static_loss = self._forward_backward(self.static_idx, self.static_tgt)
+        self.graph = graph
+
+    def step(self, idx, targets):
+        """Returns (loss of this rank's batch, squared norm of the mean gradient), both device tensors."""
+        model = self.model
+        if self.graph is not None:
+            self.static_idx.copy_(idx, non_blocking=True)
+            self.static_tgt.copy_(targets, non_blocking=True)
+            self.graph.replay()
+            loss = self.static_loss
+        else:
+            loss = self._forward_backward(idx, targets)
+            self.eager_steps += 1
+            if self.cuda_graph and self.eager_steps == 3:
+                self._capture(idx, targets)  # the captured pass only records; this step's gradients stand
+        self.t += 1
+        self.norm_sq.zero_()
+        lr, b1, b2, wd, eps = self.hp
+        with torch.no_grad():
+            model.kernels.adamw(model.flat_param, model.flat_grad, self.m, self.v, self.t, lr, b1, b2, wd, eps,
+                                1.0 / self.world, self.norm_sq)
+        return loss, self.norm_sq

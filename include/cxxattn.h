@@ -213,6 +213,21 @@ int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_st
  * pointers. */
 int cxxattn_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cxxattn_stream_t stream);
 
+/* ---- the optimiser step of the data-parallel training step ----------------------------------- */
+
+/* One fused pass over flat fp32 buffers of n elements (16-byte aligned): g = grad * grad_scale (1/world
+ * after an all-reduce that summed the ranks' gradients; grad itself is not modified), then AdamW as
+ * the reference's optimiser applies it, gpt_cuda::adamw_step with the factors AdamW::step() passes
+ * (gpt_cuda_kernels.cu:488-512, gpt_gpt.hpp:273-286):
+ *   m = beta1 m + (1-beta1) g;  v = beta2 v + (1-beta2) g^2;
+ *   param -= lr sqrt(1-beta2^step)/(1-beta1^step) * m / (sqrt(v) + eps sqrt(1-beta2^step)) + lr weight_decay param
+ * step counts from 1.  If grad_norm_sq is not NULL, the sum of g^2 is ADDED to that device float
+ * (clear it first); the reference computes it per parameter in a kernel of its own with an
+ * allocation and a blocking copy (gpt_cuda::grad_norm_squared, gpt_cuda_kernels.cu:517-547). */
+int cxxattn_adamw_step(float* param, const float* grad, float* m, float* v, size_t n, float grad_scale, float lr,
+                       float beta1, float beta2, float weight_decay, float eps, int step, float* grad_norm_sq,
+                       cxxattn_stream_t stream);
+
 /* ---- host-buffer entry points ------------------------------------------------------------- */
 
 /* Softmax MHA forward + backward on HOST tensors in the reference layout (what kernel_test.cpp

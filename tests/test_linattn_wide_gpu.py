@@ -1,0 +1,97 @@
+"""GPU parity of the tcgen05 (bf16) linear attention with one wide head — the widths the models call
+(TwoStageGPT stage 2: D = E = n_embd; LinearGPT: D = next_pow2(n_embd), E = n_embd, pre-mapped
+features) — against the CPU oracle, through the C-ABI.  Inputs are rounded to bf16 first and the same
+rounded values go to the oracle (double accumulation).  Tolerance of the bf16 path: 2e-2."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL_BF16 = 2e-2
+
+
+def inputs(seed, B, S, D, E, positive, scale):
+    g = torch.Generator().manual_seed(seed)
+    Q, K = (torch.randn(B * S, D, generator=g) * scale for _ in range(2))
+    V, dO = (torch.randn(B * S, E, generator=g) for _ in range(2))
+    if positive:  # pre-mapped features of the LinearGPT flavour are positive
+        Q, K = Q.abs() + 0.1, K.abs() + 0.1
+    return [t.bfloat16() for t in (Q, K, V, dO)]
+
+
+def run(pkg, dev, Q, K, V, dO, B, S, D, E, fmap, eps):
+    tq, tk, tv, tg = (x.to(dev) for x in (Q, K, V, dO))
+    O = torch.full_like(tv, float("nan"))
+    den = torch.full((B * S,), float("nan"), device=dev)
+    pkg.linattn_fwd(tq, tk, tv, O, den, None, B, S, D, E, fmap, eps)
+    dQ, dK = torch.full_like(tq, float("nan")), torch.full_like(tq, float("nan"))
+    dV = torch.full_like(tv, float("nan"))
+    pkg.linattn_bwd(tq, tk, tv, O, tg, den, dQ, dK, dV, B, S, D, E, fmap, eps)
+    pkg.sync_status()
+    return [t.float().cpu().numpy() for t in (O, den, dQ, dK, dV)]
+
+
+@pytest.mark.parametrize("B,S,D,E", [(2, 256, 128, 128), (3, 200, 256, 256), (1, 256, 768, 768), (2, 77, 128, 320),
+                                     (1, 600, 192, 128), (8, 256, 768, 768)])
+def test_elu_flavour_matches_oracle(pkg, dev, orc, B, S, D, E):
+    """two_stage_cuda::kernel_attn_* semantics (ELU+1 fused, den stored without the 1e-8), one head of
+    width D -> E; ragged last tiles, result widths that are not a multiple of the column group, several
+    row tiles per unit."""
+    Q, K, V, dO = inputs(5 + S + D, B, S, D, E, False, 0.5)
+    O, den, dQ, dK, dV = run(pkg, dev, Q, K, V, dO, B, S, D, E, pkg.MAP_ELU1, 0)
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    rO, rden, _ = orc.linattn_fwd(f[0], f[1], f[2], B, S, D, E, elu=True, f64=True)
+    assert np.all(np.isfinite(O)) and np.all(np.isfinite(den))
+    assert rel_err(O, rO) < TOL_BF16, rel_err(O, rO)
+    assert rel_err(den, rden) < TOL_BF16, rel_err(den, rden)
+    # the reference backward consumes the stored O and den of the forward under test
+    rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O, f[3], den, B, S, D, E, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert np.all(np.isfinite(a)), name
+        assert rel_err(a, b) < TOL_BF16, (name, rel_err(a, b))
+
+
+@pytest.mark.parametrize("B,S,D,E", [(2, 256, 1024, 768), (2, 130, 256, 128)])
+def test_premapped_flavour_matches_oracle(pkg, dev, orc, B, S, D, E):
+    """linear_cuda::causal_linear_attention_* semantics: features already mapped, den stored with the
+    1e-8, gradients with respect to the mapped features; D = 1024, E = 768 is LinearGPT at n_embd 768."""
+    Q, K, V, dO = inputs(7 + S, B, S, D, E, True, 1.0)
+    O, den, dQ, dK, dV = run(pkg, dev, Q, K, V, dO, B, S, D, E, pkg.MAP_NONE, 1)
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    rO, rden, _ = orc.linattn_fwd(f[0], f[1], f[2], B, S, D, E, elu=False, f64=True)
+    assert rel_err(O, rO) < TOL_BF16 and rel_err(den, rden) < TOL_BF16
+    dnum, dden = orc.linattn_step1(O, f[3], den, f64=True)
+    rdQ, rdK, rdV = orc.linattn_bwd(f[0], f[1], f[2], dnum, dden, B, S, D, E, elu=False, f64=True)
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert rel_err(a, b) < TOL_BF16, (name, rel_err(a, b))
+
+
+def test_zero_padded_feature_columns_give_the_unpadded_result(pkg, dev):
+    """LinearGPT pads its mapped features with zero columns from E to D (phi_elu_forward,
+    linear_cuda_kernels.cu:316-323).  The padded call and the call on the first E columns alone agree
+    bit for bit in O, den and dV, and the padded gradient columns are exactly zero."""
+    B, S, D, E = 2, 256, 256, 192
+    Q, K, V, dO = inputs(11, B, S, E, E, True, 1.0)
+    pad = torch.zeros(B * S, D - E, dtype=torch.bfloat16)
+    Qp, Kp = torch.cat([Q, pad], 1).contiguous(), torch.cat([K, pad], 1).contiguous()
+    a = run(pkg, dev, Q, K, V, dO, B, S, E, E, pkg.MAP_NONE, 1)
+    b = run(pkg, dev, Qp, Kp, V, dO, B, S, D, E, pkg.MAP_NONE, 1)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]) and np.array_equal(a[4], b[4])
+    assert np.array_equal(a[2], b[2][:, :E]) and np.array_equal(a[3], b[3][:, :E])
+    assert not b[2][:, E:].any() and not b[3][:, E:].any()
+
+
+def test_workspace_is_required_and_widths_off_the_grid_are_refused(pkg, dev):
+    lib = pkg.lib()
+    t = torch.zeros(256 * 128, dtype=torch.bfloat16, device=dev)
+    f = torch.zeros(256, device=dev)
+    d = pkg.lin_desc(1, 256, 128, 128, pkg.BF16, pkg.MAP_ELU1, 0)
+    assert lib.cxxattn_linattn_workspace_bytes(C.byref(d)) > 0
+    p = t.data_ptr()
+    assert lib.cxxattn_linattn_fwd(C.byref(d), p, p, p, p, f.data_ptr(), None, None, 0, None) == -3
+    odd = pkg.lin_desc(1, 256, 96, 96, pkg.BF16, pkg.MAP_ELU1, 0)  # not a multiple of 64: no bf16 kernel
+    assert lib.cxxattn_linattn_fwd(C.byref(odd), p, p, p, p, f.data_ptr(), None, p, 1 << 20, None) == -2
