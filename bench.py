@@ -44,6 +44,9 @@ NEIGHBOURS = {
     "decode_linear": "linear-stage decoding step, 8192 units, D = E = 64 (state 16 KB per unit)",
     "decode_linear_wide": "linear-stage decoding step, 64 units, D = E = 768 (state 2.4 MB per unit)",
     "decode_softmax": "softmax-stage decoding step, 64 x 12 heads of 64, 4096 keys in the cache",
+    "adamw_step": "fused mean + AdamW + gradient norm over the 111.4 M parameters of the hybrid model (28 B each)",
+    "stage2_wide": "ELU+1 linear attention forward + backward, one head of width 768, B = 8, S = 256, bf16 "
+                   "(stage 2 of the full-size model); value in TFLOP/s",
 }
 # The full-model data-parallel training step (vocab 6400, block 256, n_embd 768, 12 heads, 12 blocks, batch 8 per GPU)
 DP_WORKLOAD = "dp_step"
@@ -707,6 +710,25 @@ def run_neighbours(args):
         o, dn = torch.empty(B, E, device=dev), torch.empty(B, device=dev)
         nbytes = B * (2 * D * (E + 1) * 4 + (2 * D + 2 * E + 1) * 4)
         step, kernel = (lambda: pkg.linattn_decode_step(q, k, v, S_, z, o, dn, B, D, E)), "lin_decode_kernel"
+    elif w == "adamw_step":
+        n = 111_401_472
+        prm, grd, m1, m2 = (torch.randn(n, device=dev) * 0.01 for _ in range(4))
+        m2.abs_()
+        nsq = torch.zeros(1, device=dev)
+        nbytes = 28 * n
+        step, kernel = (lambda: pkg.adamw_step(prm, grd, m1, m2, 10, 1e-3, grad_scale=0.125, grad_norm_sq=nsq)), \
+            "adamw_fused_kernel"
+    elif w == "stage2_wide":
+        B, S, D = 8, 256, 768
+        q, k, v, g_ = (torch.randn(B * S, D, device=dev).bfloat16() for _ in range(4))
+        o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        dn = torch.empty(B * S, device=dev)
+
+        def step():
+            pkg.linattn_fwd(q, k, v, o, dn, None, B, S, D, D, pkg.MAP_ELU1, 0)
+            pkg.linattn_bwd(q, k, v, o, g_, dn, dq, dk, dv, B, S, D, D, pkg.MAP_ELU1, 0)
+        nbytes = 0
+        kernel = "linattn_wide_kernel<FWD, DQ, DV, DK> + element-wise passes"
     else:
         B, cap = 64, 4096
         q, k, v = (torch.randn(B, H * DH, device=dev) for _ in range(3))
@@ -737,6 +759,21 @@ def run_neighbours(args):
             hbm, how = float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         hbm, how = 6650.0, "fallback"
+    if w == "stage2_wide":
+        # causal-half convention: every one of the four modes forms S^2/2 x (D + E) multiply-adds per unit
+        fl = 4.0 * 8 * 256 * 256 * (768 + 768)
+        peak, _, how = measured_peaks()
+        tf = fl / (ms * 1e-3) / 1e12
+        print(json.dumps({"metric": w + "_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": w, "what": NEIGHBOURS[w], "flop_per_step": fl,
+                                     "l2": "256 MB written between steps"},
+                          "gpu_launches": args.steps * 11, "clocks": sampler.result(),
+                          "roofline": {"bound": "tensor", "kernel": kernel, "achieved": tf, "peak": peak,
+                                       "peak_source": how, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None}}),
+              flush=True)
+        return
     gbs = nbytes / (ms * 1e-3) / 1e9
     print(json.dumps({"metric": w + "_algorithmic_gbps", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",

@@ -259,7 +259,12 @@ class DataParallelStep:
                 if b["lo"] <= o < b["hi"]:
                     self.bucket_of[name] = b
         self.pending = []
-        if self.world > 1:
+        # Eager steps start each bucket's all-reduce from an autograd hook, as soon as the backward pass
+        # has finished the bucket.  With CUDA-graph replay the collectives stay outside the graph (a
+        # captured NCCL call did not complete on this platform): the buckets are reduced after the
+        # replay, last bucket first, and the optimiser kernel follows.
+        self.reduce_in_hooks = self.world > 1 and not cuda_graph
+        if self.reduce_in_hooks:
             for name in names:
                 model.p[name].register_post_accumulate_grad_hook(self._make_hook(name))
 
@@ -304,6 +309,11 @@ class DataParallelStep:
             self.eager_steps += 1
             if self.cuda_graph and self.eager_steps == 3:
                 self._capture(idx, targets)  # the captured pass only records; this step's gradients stand
+        if self.world > 1 and not self.reduce_in_hooks:
+            works = [dist.all_reduce(model.flat_grad[b["lo"]:b["hi"]], op=dist.ReduceOp.SUM, group=self.group,
+                                     async_op=True) for b in reversed(self.buckets)]
+            for w in works:
+                w.wait()
         self.t += 1
         self.norm_sq.zero_()
         lr, b1, b2, wd, eps = self.hp
