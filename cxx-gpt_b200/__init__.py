@@ -78,6 +78,7 @@ def lib():
         L.cxxattn_linattn_fwd.argtypes = [C.POINTER(LinDesc)] + [vp] * 6 + [vp, sz, vp]
         L.cxxattn_linattn_bwd_step1.argtypes = [vp] * 5 + [sz, sz, vp]
         L.cxxattn_linattn_bwd_dq.argtypes = [C.POINTER(LinDesc)] + [vp] * 7 + [vp, sz, vp]
+        L.cxxattn_linattn_fwd.restype = L.cxxattn_linattn_bwd_dq.restype = L.cxxattn_linattn_bwd_dkdv.restype = i32
         L.cxxattn_linattn_bwd_dkdv.argtypes = [C.POINTER(LinDesc)] + [vp] * 7 + [vp, sz, vp]
         L.cxxattn_linattn_bwd.argtypes = [C.POINTER(LinDesc)] + [vp] * 9 + [vp, sz, vp]
         L.cxxattn_phi_elu_fwd.argtypes = [vp, vp, sz, sz, sz, vp]

@@ -54,42 +54,95 @@ cxxattn_lin_desc lin(size_t B, size_t S, size_t D, size_t E, int map, int eps_in
     return d;
 }
 
-void lin_fwd(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V, float* O, float* den,
-             float* zc) {
-    const size_t n = cxxattn_linattn_workspace_bytes(&d);
-    ok(cxxattn_linattn_fwd(&d, Q, K, V, O, den, zc, scratch(n), n, nullptr), "cxxattn_linattn_fwd");
-}
-void lin_dq(const cxxattn_lin_desc& d, const float* K, const float* V, const float* dnum, const float* dden,
-            const float* zc, const float* Q, float* dQ) {
-    const size_t n = cxxattn_linattn_workspace_bytes(&d);
-    ok(cxxattn_linattn_bwd_dq(&d, K, V, dnum, dden, zc, Q, dQ, scratch(n), n, nullptr), "cxxattn_linattn_bwd_dq");
-}
-void lin_dkdv(const cxxattn_lin_desc& d, const float* Q, const float* K, const float* V, const float* dnum,
-              const float* dden, float* dK, float* dV) {
-    const size_t n = cxxattn_linattn_workspace_bytes(&d);
-    ok(cxxattn_linattn_bwd_dkdv(&d, Q, K, V, dnum, dden, dK, dV, scratch(n), n, nullptr), "cxxattn_linattn_bwd_dkdv");
-}
-
 }  // namespace
 
-// Opt-in: the kept fp32 signatures of the softmax attention run on the bf16 tensor-core kernels
-// (inputs rounded to bf16 on the way in, results widened on the way out; 2e-2 instead of 1e-5).
-// Environment CXXATTN_COMPAT_PRECISION=tensorcore, or cxxattn_compat::set_tensorcore(true).
+// Opt-in: the kept fp32 signatures run on the bf16 tensor-core kernels (inputs rounded to bf16 on the
+// way in, results widened on the way out; 2e-2 instead of 1e-5): the softmax attention for head
+// dimension 64, the linear attention for one wide head (D and E multiples of 64 other than 64/64, the
+// widths of TwoStageGPT's stage 2 and of LinearGPT).  Everything else stays on the exact fp32 kernels.
+// Environment CXXATTN_COMPAT_PRECISION=tensorcore (read by this adapter, not by the library), or
+// cxxattn_compat::set_tensorcore(true).
 namespace {
 int g_tensorcore = -1;
-bool tensorcore(size_t Dh) {
+bool tensorcore_on() {
     if (g_tensorcore < 0) {
         const char* e = std::getenv("CXXATTN_COMPAT_PRECISION");
         g_tensorcore = (e != nullptr && std::string(e) == "tensorcore") ? 1 : 0;
     }
-    return g_tensorcore == 1 && Dh == 64;
+    return g_tensorcore == 1;
 }
+bool tensorcore(size_t Dh) { return tensorcore_on() && Dh == 64; }
+bool tensorcore_lin(int64_t D, int64_t E) { return tensorcore_on() && D % 64 == 0 && E % 64 == 0 && !(D == 64 && E == 64); }
+size_t blk256(size_t bytes) { return (bytes + 255) / 256 * 256; }
 // bf16 copy of an fp32 tensor inside the scratch block
 void* to_bf16(const float* src, char*& cursor, size_t n) {
     void* dst = cursor;
-    cursor += (n * 2 + 255) / 256 * 256;
+    cursor += blk256(n * 2);
     ok(cxxattn_cast(src, CXXATTN_F32, dst, CXXATTN_BF16, n, nullptr), "cxxattn_cast");
     return dst;
+}
+void* take(char*& cursor, size_t bytes) {
+    void* p = cursor;
+    cursor += blk256(bytes);
+    return p;
+}
+
+void lin_fwd(cxxattn_lin_desc d, const float* Q, const float* K, const float* V, float* O, float* den, float* zc) {
+    if (tensorcore_lin(d.D, d.E)) {
+        d.dtype = CXXATTN_BF16;
+        const size_t nD = (size_t)(d.B * d.S * d.D), nE = (size_t)(d.B * d.S * d.E);
+        const size_t ws = blk256(cxxattn_linattn_workspace_bytes(&d));
+        char* cur = static_cast<char*>(scratch(2 * blk256(nD * 2) + 2 * blk256(nE * 2) + ws));
+        void* q = to_bf16(Q, cur, nD);
+        void* k = to_bf16(K, cur, nD);
+        void* v = to_bf16(V, cur, nE);
+        void* o = take(cur, nE * 2);
+        ok(cxxattn_linattn_fwd(&d, q, k, v, o, den, zc, cur, ws, nullptr), "cxxattn_linattn_fwd");
+        ok(cxxattn_cast(o, CXXATTN_BF16, O, CXXATTN_F32, nE, nullptr), "cxxattn_cast");
+        return;
+    }
+    const size_t n = cxxattn_linattn_workspace_bytes(&d);
+    ok(cxxattn_linattn_fwd(&d, Q, K, V, O, den, zc, scratch(n), n, nullptr), "cxxattn_linattn_fwd");
+}
+void lin_dq(cxxattn_lin_desc d, const float* K, const float* V, const float* dnum, const float* dden,
+            const float* zc, const float* Q, float* dQ) {
+    if (tensorcore_lin(d.D, d.E)) {
+        d.dtype = CXXATTN_BF16;
+        const size_t nD = (size_t)(d.B * d.S * d.D), nE = (size_t)(d.B * d.S * d.E);
+        const size_t ws = blk256(cxxattn_linattn_workspace_bytes(&d));
+        char* cur = static_cast<char*>(scratch(3 * blk256(nD * 2) + 2 * blk256(nE * 2) + ws));
+        void* k = to_bf16(K, cur, nD);
+        void* v = to_bf16(V, cur, nE);
+        void* g = to_bf16(dnum, cur, nE);
+        void* q = Q ? to_bf16(Q, cur, nD) : nullptr;
+        void* dq = take(cur, nD * 2);
+        ok(cxxattn_linattn_bwd_dq(&d, k, v, g, dden, nullptr, q, dq, cur, ws, nullptr), "cxxattn_linattn_bwd_dq");
+        ok(cxxattn_cast(dq, CXXATTN_BF16, dQ, CXXATTN_F32, nD, nullptr), "cxxattn_cast");
+        return;
+    }
+    const size_t n = cxxattn_linattn_workspace_bytes(&d);
+    ok(cxxattn_linattn_bwd_dq(&d, K, V, dnum, dden, zc, Q, dQ, scratch(n), n, nullptr), "cxxattn_linattn_bwd_dq");
+}
+void lin_dkdv(cxxattn_lin_desc d, const float* Q, const float* K, const float* V, const float* dnum,
+              const float* dden, float* dK, float* dV) {
+    if (tensorcore_lin(d.D, d.E)) {
+        d.dtype = CXXATTN_BF16;
+        const size_t nD = (size_t)(d.B * d.S * d.D), nE = (size_t)(d.B * d.S * d.E);
+        const size_t ws = blk256(cxxattn_linattn_workspace_bytes(&d));
+        char* cur = static_cast<char*>(scratch(3 * blk256(nD * 2) + 3 * blk256(nE * 2) + ws));
+        void* q = to_bf16(Q, cur, nD);
+        void* k = to_bf16(K, cur, nD);
+        void* v = to_bf16(V, cur, nE);
+        void* g = to_bf16(dnum, cur, nE);
+        void* dk = take(cur, nD * 2);
+        void* dv = take(cur, nE * 2);
+        ok(cxxattn_linattn_bwd_dkdv(&d, q, k, v, g, dden, dk, dv, cur, ws, nullptr), "cxxattn_linattn_bwd_dkdv");
+        ok(cxxattn_cast(dk, CXXATTN_BF16, dK, CXXATTN_F32, nD, nullptr), "cxxattn_cast");
+        ok(cxxattn_cast(dv, CXXATTN_BF16, dV, CXXATTN_F32, nE, nullptr), "cxxattn_cast");
+        return;
+    }
+    const size_t n = cxxattn_linattn_workspace_bytes(&d);
+    ok(cxxattn_linattn_bwd_dkdv(&d, Q, K, V, dnum, dden, dK, dV, scratch(n), n, nullptr), "cxxattn_linattn_bwd_dkdv");
 }
 }  // namespace
 

@@ -124,9 +124,11 @@ int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void*
         return linattn_f32_fwd(*desc, (const float*)Q, (const float*)K, (const float*)V, (float*)O, den,
                                z_cache, workspace, workspace_bytes, st);
     if (desc->dtype == CXXATTN_BF16) {
-        if (z_cache != nullptr) return CXXATTN_ERR_UNSUPPORTED;  // the bf16 paths keep z on chip or need none
-        if (linattn_tc_supported(*desc)) return linattn_tc_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
-        return linattn_wide_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
+        if (linattn_tc_supported(*desc)) {
+            if (z_cache != nullptr) return CXXATTN_ERR_UNSUPPORTED;  // D = E = 64 keeps z on chip
+            return linattn_tc_fwd(*desc, Q, K, V, O, den, workspace, workspace_bytes, st);
+        }
+        return linattn_wide_fwd(*desc, Q, K, V, O, den, z_cache, workspace, workspace_bytes, st);
     }
     return CXXATTN_ERR_INVALID;
 }
@@ -146,22 +148,28 @@ int cxxattn_linattn_bwd_step1(const float* O, const float* dO, const float* den,
     return step1_f32(O, dO, den, dnum, dden, N, E, static_cast<cudaStream_t>(stream));
 }
 
-int cxxattn_linattn_bwd_dq(const cxxattn_lin_desc* desc, const float* K, const float* V,
-                           const float* dnum, const float* dden, const float* z_cache, const float* Q,
-                           float* dQ, void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
+int cxxattn_linattn_bwd_dq(const cxxattn_lin_desc* desc, const void* K, const void* V,
+                           const void* dnum, const float* dden, const float* z_cache, const void* Q,
+                           void* dQ, void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
     if (!lin_ok(desc) || !K || !V || !dnum || !dden || !dQ) return CXXATTN_ERR_INVALID;
-    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
-    return linattn_f32_bwd_dq(*desc, K, V, dnum, dden, z_cache, Q, dQ, workspace, workspace_bytes,
-                              static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == CXXATTN_BF16)  // one wide head; z_cache is not needed
+        return linattn_wide_bwd_dq(*desc, K, V, dnum, dden, Q, dQ, workspace, workspace_bytes, st);
+    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_INVALID;
+    return linattn_f32_bwd_dq(*desc, (const float*)K, (const float*)V, (const float*)dnum, dden, z_cache,
+                              (const float*)Q, (float*)dQ, workspace, workspace_bytes, st);
 }
 
-int cxxattn_linattn_bwd_dkdv(const cxxattn_lin_desc* desc, const float* Q, const float* K,
-                             const float* V, const float* dnum, const float* dden, float* dK, float* dV,
+int cxxattn_linattn_bwd_dkdv(const cxxattn_lin_desc* desc, const void* Q, const void* K,
+                             const void* V, const void* dnum, const float* dden, void* dK, void* dV,
                              void* workspace, size_t workspace_bytes, cxxattn_stream_t stream) {
     if (!lin_ok(desc) || !Q || !K || !V || !dnum || !dden || !dK || !dV) return CXXATTN_ERR_INVALID;
-    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_UNSUPPORTED;
-    return linattn_f32_bwd_dkdv(*desc, Q, K, V, dnum, dden, dK, dV, workspace, workspace_bytes,
-                                static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == CXXATTN_BF16)
+        return linattn_wide_bwd_dkdv(*desc, Q, K, V, dnum, dden, dK, dV, workspace, workspace_bytes, st);
+    if (desc->dtype != CXXATTN_F32) return CXXATTN_ERR_INVALID;
+    return linattn_f32_bwd_dkdv(*desc, (const float*)Q, (const float*)K, (const float*)V, (const float*)dnum, dden,
+                                (float*)dK, (float*)dV, workspace, workspace_bytes, st);
 }
 
 int cxxattn_linattn_bwd(const cxxattn_lin_desc* desc, const void* Q, const void* K, const void* V,

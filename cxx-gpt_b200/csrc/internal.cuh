@@ -78,7 +78,11 @@ int linattn_tc_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, cons
 bool linattn_wide_supported(const cxxattn_lin_desc& d);
 size_t linattn_wide_workspace(const cxxattn_lin_desc& d);
 int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
-                     void* ws, size_t ws_bytes, cudaStream_t st);
+                     float* z_cache, void* ws, size_t ws_bytes, cudaStream_t st);
+int linattn_wide_bwd_dq(const cxxattn_lin_desc& d, const void* K, const void* V, const void* dnum, const float* dden,
+                        const void* Q, void* dQ, void* ws, size_t ws_bytes, cudaStream_t st);
+int linattn_wide_bwd_dkdv(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* dnum,
+                          const float* dden, void* dK, void* dV, void* ws, size_t ws_bytes, cudaStream_t st);
 int linattn_wide_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O,
                      const void* dO, const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes,
                      cudaStream_t st);

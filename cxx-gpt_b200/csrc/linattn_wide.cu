@@ -303,6 +303,21 @@ __global__ void wide_step1_kernel(const uint4* __restrict__ O, const uint4* __re
     if (lane == 0) dden[row] = -dot * inv;
 }
 
+// z_cache[t][d] = sum over s <= t of phiK[s][d] (float), one thread per (unit, d) walking the sequence; the
+// threads of a warp read consecutive d.  Only for callers of the kept reference signature, which hands
+// z_cache to its backward; this library's wide backward does not read it.
+__global__ void wide_zcache_kernel(const __nv_bfloat16* __restrict__ pk, float* __restrict__ zc, int B, int S, int D) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)B * D) return;
+    const int b = (int)(i / D), d = (int)(i % D);
+    float run = 0.f;
+    for (int t = 0; t < S; t++) {
+        const int64_t o = ((int64_t)b * S + t) * D + d;
+        run += __bfloat162float(pk[o]);
+        zc[o] = run;
+    }
+}
+
 unsigned flat_grid8(size_t n8) { return (unsigned)std::max<size_t>(1, std::min<size_t>((n8 + 255) / 256, (size_t)sm_count() * 8)); }
 
 // Carves the workspace: phiQ | phiK | dnum | dden | dphiQ | dphiK
@@ -370,8 +385,8 @@ bool linattn_wide_supported(const cxxattn_lin_desc& d) {
 
 size_t linattn_wide_workspace(const cxxattn_lin_desc& d) { return linattn_wide_supported(d) ? carve(d, nullptr).bytes : 0; }
 
-int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den, void* ws,
-                     size_t ws_bytes, cudaStream_t st) {
+int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
+                     float* z_cache, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!linattn_wide_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
     for (const void* q : {Q, K, V, (const void*)O})
         if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
@@ -387,44 +402,84 @@ int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, co
         q = w.pq;
         k = w.pk;
     }
+    if (z_cache != nullptr) {
+        const int64_t n = d.B * d.D;
+        wide_zcache_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(k), z_cache, (int)d.B,
+                                                                      (int)d.S, (int)d.D);
+        if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+    }
     return launch<FWD>(d, q, k, V, (int)d.D, (int)d.E, O, den, nullptr, st);
 }
 
+// The two halves of the backward as the reference's interface cuts it (kernel_attn_bwd_dQ / _dKdV,
+// causal_linear_attention_bwd_dQ / _dKdV): dnum (bf16) and dden (float) come from step 1.
+int linattn_wide_bwd_dq(const cxxattn_lin_desc& d, const void* K, const void* V, const void* dnum, const float* dden,
+                        const void* Q, void* dQ, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (!linattn_wide_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
+    const bool map = d.feature_map == CXXATTN_MAP_ELU1;
+    if (map && Q == nullptr) return CXXATTN_ERR_INVALID;
+    for (const void* q : {K, V, dnum, Q, (const void*)dQ})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    if (ws == nullptr || ws_bytes < carve(d, nullptr).bytes) return CXXATTN_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(ws) % 256) return CXXATTN_ERR_ALIGNMENT;
+    const WideWs w = carve(d, ws);
+    const size_t n8 = (size_t)d.B * d.S * d.D / 8;
+    const void* k = K;
+    if (map) {  // the mapped copies are rebuilt: the workspace need not survive from an earlier call
+        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
+        if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+        k = w.pk;
+    }
+    int rc = launch<DQ>(d, dnum, V, k, (int)d.E, (int)d.D, map ? (void*)w.dpq : dQ, nullptr, dden, st);
+    if (rc != CXXATTN_OK || !map) return rc;
+    wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpq), static_cast<const uint4*>(Q),
+                                                    static_cast<uint4*>(dQ), n8);
+    return check_launch();
+}
+
+int linattn_wide_bwd_dkdv(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* dnum,
+                          const float* dden, void* dK, void* dV, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (!linattn_wide_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
+    for (const void* q : {Q, K, V, dnum, (const void*)dK, (const void*)dV})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    if (ws == nullptr || ws_bytes < carve(d, nullptr).bytes) return CXXATTN_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(ws) % 256) return CXXATTN_ERR_ALIGNMENT;
+    const WideWs w = carve(d, ws);
+    const bool map = d.feature_map == CXXATTN_MAP_ELU1;
+    const size_t n8 = (size_t)d.B * d.S * d.D / 8;
+    const void *q = Q, *k = K;
+    if (map) {
+        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(Q), reinterpret_cast<uint4*>(w.pq), n8);
+        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
+        if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+        q = w.pq;
+        k = w.pk;
+    }
+    int rc = launch<DV>(d, k, q, dnum, (int)d.D, (int)d.E, dV, nullptr, nullptr, st);
+    if (rc != CXXATTN_OK) return rc;
+    rc = launch<DK>(d, V, dnum, q, (int)d.E, (int)d.D, map ? (void*)w.dpk : dK, nullptr, dden, st);
+    if (rc != CXXATTN_OK || !map) return rc;
+    wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpk), static_cast<const uint4*>(K),
+                                                    static_cast<uint4*>(dK), n8);
+    return check_launch();
+}
+
+// The whole backward: step 1, then the two halves.
 int linattn_wide_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* O, const void* dO,
                      const float* den, void* dQ, void* dK, void* dV, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!linattn_wide_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
-    for (const void* q : {Q, K, V, O, dO, (const void*)dQ, (const void*)dK, (const void*)dV})
+    for (const void* q : {O, dO})
         if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
     if (ws == nullptr || ws_bytes < carve(d, nullptr).bytes) return CXXATTN_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(ws) % 256) return CXXATTN_ERR_ALIGNMENT;
     const WideWs w = carve(d, ws);
     const size_t N = (size_t)d.B * d.S;
-    const bool map = d.feature_map == CXXATTN_MAP_ELU1;
-    const size_t n8 = N * d.D / 8;
-    const void *q = Q, *k = K;
-    if (map) {  // the mapped copies are rebuilt: the workspace need not survive from the forward call
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(Q), reinterpret_cast<uint4*>(w.pq), n8);
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
-        q = w.pq;
-        k = w.pk;
-    }
     wide_step1_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO), den,
                                                               reinterpret_cast<uint4*>(w.dnum), w.dden, N, (int)(d.E / 8));
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
-    int rc = launch<DQ>(d, w.dnum, V, k, (int)d.E, (int)d.D, map ? (void*)w.dpq : dQ, nullptr, w.dden, st);
+    int rc = linattn_wide_bwd_dq(d, K, V, w.dnum, w.dden, Q, dQ, ws, ws_bytes, st);
     if (rc != CXXATTN_OK) return rc;
-    rc = launch<DV>(d, k, q, w.dnum, (int)d.D, (int)d.E, dV, nullptr, nullptr, st);
-    if (rc != CXXATTN_OK) return rc;
-    rc = launch<DK>(d, V, w.dnum, q, (int)d.E, (int)d.D, map ? (void*)w.dpk : dK, nullptr, w.dden, st);
-    if (rc != CXXATTN_OK) return rc;
-    if (map) {
-        wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpq), static_cast<const uint4*>(Q),
-                                                        static_cast<uint4*>(dQ), n8);
-        wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpk), static_cast<const uint4*>(K),
-                                                        static_cast<uint4*>(dK), n8);
-        return check_launch();
-    }
-    return CXXATTN_OK;
+    return linattn_wide_bwd_dkdv(d, Q, K, V, w.dnum, w.dden, dK, dV, ws, ws_bytes, st);
 }
 
 }  // namespace cxxattn

@@ -99,7 +99,8 @@ size_t cxxattn_linattn_workspace_bytes(const cxxattn_lin_desc* desc);
 
 /* Forward.  Replaces two_stage_cuda::kernel_attn_fwd (ts.cuh:39-44, ts.cu:1133-1185) with
  * feature_map=ELU1, eps_in_den=0 and linear_cuda::causal_linear_attention_fwd (lin.cuh:11-17,
- * lin.cu:81-99) with feature_map=NONE, eps_in_den=1.  z_cache may be NULL (then not written).
+ * lin.cu:81-99) with feature_map=NONE, eps_in_den=1.  z_cache may be NULL (then not written); the
+ * bf16 kernels for D = E = 64 do not take one.
  * The reference's S_buf / z_buf scratch arguments have no counterpart: the sequence is cut into
  * chunks whose states live in `workspace`. */
 int cxxattn_linattn_fwd(const cxxattn_lin_desc* desc, const void* Q, const void* K, const void* V,
@@ -137,18 +138,19 @@ int cxxattn_linattn_bwd_step1(const float* O, const float* dO, const float* den,
 /* dQ from (dnum, dden).  Replaces two_stage_cuda::kernel_attn_bwd_dQ (ts.cuh:51-55,
  * ts.cu:1408-1453; Q needed for phi') and linear_cuda::causal_linear_attention_bwd_dQ
  * (lin.cuh:25-30, lin.cu:199-215; Q may be NULL).  z_cache may be NULL: the z term is then
- * rebuilt from K.  float tensors only. */
-int cxxattn_linattn_bwd_dq(const cxxattn_lin_desc* desc, const float* K, const float* V,
-                           const float* dnum, const float* dden, const float* z_cache,
-                           const float* Q, float* dQ,
+ * rebuilt from K.  K, V, dnum, Q, dQ are of desc->dtype: float, or bf16 for one wide head (D and E
+ * multiples of 64 other than 64/64; z_cache is then not read); dden and z_cache are float. */
+int cxxattn_linattn_bwd_dq(const cxxattn_lin_desc* desc, const void* K, const void* V,
+                           const void* dnum, const float* dden, const float* z_cache,
+                           const void* Q, void* dQ,
                            void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
 
 /* dK, dV from (dnum, dden).  Replaces two_stage_cuda::kernel_attn_bwd_dKdV (ts.cuh:57-61,
  * ts.cu:1743-1809) and linear_cuda::causal_linear_attention_bwd_dKdV (lin.cuh:32-37,
- * lin.cu:275-298).  float tensors only. */
-int cxxattn_linattn_bwd_dkdv(const cxxattn_lin_desc* desc, const float* Q, const float* K,
-                             const float* V, const float* dnum, const float* dden,
-                             float* dK, float* dV,
+ * lin.cu:275-298).  Tensor types as for cxxattn_linattn_bwd_dq. */
+int cxxattn_linattn_bwd_dkdv(const cxxattn_lin_desc* desc, const void* Q, const void* K,
+                             const void* V, const void* dnum, const float* dden,
+                             void* dK, void* dV,
                              void* workspace, size_t workspace_bytes, cxxattn_stream_t stream);
 
 /* Whole backward in one call (step1 + dQ + dK/dV without the dnum/dden/z_cache round trips).

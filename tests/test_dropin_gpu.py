@@ -39,10 +39,12 @@ def test_reference_kernel_test_program_passes_on_this_library():
 
 
 def test_reference_kernel_test_program_in_tensorcore_mode():
-    """The same unmodified program with the adapter's opt-in switch: the fp32 signatures of the softmax
-    attention run on the bf16 tensor-core kernels where the head dimension is 64 (the "big S=256"
-    block); everything else stays on the exact path.  Inputs there are uniform in [-1, 1] (outputs and
-    gradients of order one), so 2e-2 absolute is the bf16 bar."""
+    """The same unmodified program with the adapter's opt-in switch: the fp32 signatures run on the bf16
+    tensor-core kernels where those exist — the softmax attention with head dimension 64 (the "big
+    S=256" block) and the linear attention with one wide head (the "chunk" block, D = E = 256);
+    everything else stays on the exact path.  Inputs are uniform in [-1, 1] (outputs and gradients of
+    order one), so 2e-2 absolute is the bf16 bar; the denominators of the chunk block are sums of up to
+    32 x 256 products of order one, so theirs is 2e-2 of 1e4."""
     exe = os.path.join(ROOT, "oracle", "_ref", "kernel_test_dropin")
     if not os.path.exists(exe):
         import oracle
@@ -58,8 +60,13 @@ def test_reference_kernel_test_program_in_tensorcore_mode():
     for name, v in big:
         # above the fp32 path's error (so the tensor-core kernels really ran), below the bf16 bar
         assert 2e-5 < v < 2e-2, (name, v)
+    chunk = [(n, float(v)) for n, v in lines if n.startswith("chunk")]
+    assert len(chunk) == 5, lines
+    for name, v in chunk:
+        assert v == v and v < (2e2 if name.split()[-1] == "den" else 2e-2), (name, v)
+    assert max(v for n, v in chunk if n.split()[-1] != "den") > 2e-6  # the tensor-core kernels really ran
     for name, val in lines:
-        if name.startswith("big S=256"):
+        if name.startswith("big S=256") or name.startswith("chunk"):
             continue
         v = float(val)
         limit = 1e-2 if name.split()[-1] == "den" else 2e-5

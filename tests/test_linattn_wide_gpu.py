@@ -95,3 +95,38 @@ def test_workspace_is_required_and_widths_off_the_grid_are_refused(pkg, dev):
     assert lib.cxxattn_linattn_fwd(C.byref(d), p, p, p, p, f.data_ptr(), None, None, 0, None) == -3
     odd = pkg.lin_desc(1, 256, 96, 96, pkg.BF16, pkg.MAP_ELU1, 0)  # not a multiple of 64: no bf16 kernel
     assert lib.cxxattn_linattn_fwd(C.byref(odd), p, p, p, p, f.data_ptr(), None, p, 1 << 20, None) == -2
+
+
+def test_split_backward_entry_points_and_z_cache(pkg, dev, orc):
+    """The reference cuts the backward into step 1, dQ and dK/dV calls and hands a z_cache from the
+    forward to the dQ call.  In bf16 the same cut (cxxattn_linattn_bwd_dq / _bwd_dkdv with dnum in bf16)
+    gives the bits of the fused call, and the forward fills z_cache = running sum of phi(K)."""
+    lib = pkg.lib()
+    B, S, D, E = 2, 200, 128, 192
+    Q, K, V, dO = inputs(23, B, S, D, E, False, 0.5)
+    fused = run(pkg, dev, Q, K, V, dO, B, S, D, E, pkg.MAP_ELU1, 0)
+    tq, tk, tv, tg = (x.to(dev) for x in (Q, K, V, dO))
+    d = pkg.lin_desc(B, S, D, E, pkg.BF16, pkg.MAP_ELU1, 0)
+    n = lib.cxxattn_linattn_workspace_bytes(C.byref(d))
+    ws = torch.empty(n, dtype=torch.uint8, device=dev)
+    O = torch.empty_like(tv)
+    den = torch.empty(B * S, device=dev)
+    zc = torch.full((B * S, D), float("nan"), device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.cxxattn_linattn_fwd(C.byref(d), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), O.data_ptr(), den.data_ptr(),
+                                   zc.data_ptr(), ws.data_ptr(), n, st) == 0
+    # step 1 on the stored (bf16-rounded) O, as the fused call does, with dnum rounded to bf16
+    inv = 1.0 / den
+    dnum = (tg.float() * inv[:, None]).bfloat16()
+    dden = -(tg.float() * O.float()).sum(1) * inv
+    dQ, dK, dV = torch.empty_like(tq), torch.empty_like(tq), torch.empty_like(tv)
+    assert lib.cxxattn_linattn_bwd_dq(C.byref(d), tk.data_ptr(), tv.data_ptr(), dnum.data_ptr(), dden.data_ptr(), None,
+                                      tq.data_ptr(), dQ.data_ptr(), ws.data_ptr(), n, st) == 0
+    assert lib.cxxattn_linattn_bwd_dkdv(C.byref(d), tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), dnum.data_ptr(),
+                                        dden.data_ptr(), dK.data_ptr(), dV.data_ptr(), ws.data_ptr(), n, st) == 0
+    pkg.sync_status()
+    for name, a, b in (("dQ", dQ, fused[2]), ("dK", dK, fused[3]), ("dV", dV, fused[4])):
+        assert rel_err(a.float().cpu().numpy(), b) < 5e-3, name  # dden summed in another order, dnum the same bits
+    f = [x.float().numpy() for x in (Q, K, V)]
+    _, _, rzc = orc.linattn_fwd(f[0], f[1], f[2], B, S, D, E, elu=True, f64=True)
+    assert rel_err(zc.cpu().numpy(), rzc) < TOL_BF16

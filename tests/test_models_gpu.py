@@ -79,13 +79,43 @@ def test_reference_model_gives_the_same_numbers_on_this_library(model, args):
 
 
 def test_two_stage_model_on_the_tensor_core_kernels():
-    """Same model with the adapter's opt-in precision switch: stage 1 (head dimension 64) runs on the
-    bf16 tcgen05 kernels; loss and training curve stay within the bf16 bar of the fp32 reference."""
+    """Same model with the adapter's opt-in precision switch: stage 1 (4 heads of 64) runs on the bf16
+    tcgen05 softmax kernels and stage 2 (one head of width 256) on the bf16 wide-head linear-attention
+    kernel; loss and training curve stay within the bf16 bar of the fp32 reference build."""
     dropin, ref = _programs("two_stage_check")
     args = (2, 256, 256, 4, 2, 512, 5)
     d_tc, _ = _run(dropin, args, env={"CXXATTN_COMPAT_PRECISION": "tensorcore"})
+    d_fp32, _ = _run(dropin, args)
     d_ref, _ = _run(ref, args)
     for (n, a), (_, b) in zip(d_tc, d_ref):
+        if n.startswith("train") or n == "digest loss":
+            assert _close(a, b, 2e-2, 1e-6), (n, a, b)
+    # the switch changed the numbers (both stages left the exact path) without leaving the bf16 bar
+    assert any(a != b for (_, a), (_, b) in zip(d_tc, d_fp32))
+
+
+def test_linear_gpt_model_on_the_tensor_core_kernels():
+    """LinearGPT (D = E = 256 here: pre-mapped features, den stored with its 1e-8) with the adapter's
+    switch on: the scan, dQ and dK/dV calls run on the bf16 wide-head kernel."""
+    dropin, ref = _programs("linear_gpt_check")
+    args = (2, 256, 256, 2, 512, 5)
+    d_tc, _ = _run(dropin, args, env={"CXXATTN_COMPAT_PRECISION": "tensorcore"})
+    d_ref, _ = _run(ref, args)
+    for (n, a), (_, b) in zip(d_tc, d_ref):
+        if n.startswith("train") or n == "digest loss":
+            assert _close(a, b, 2e-2, 1e-6), (n, a, b)
+
+
+def test_two_stage_model_at_full_width_on_the_tensor_core_kernels():
+    """n_embd = 768, 12 heads of 64, both stages on the tensor cores: finite numbers and a falling loss,
+    close to the same run on the exact kernels."""
+    dropin, _ = _programs("two_stage_check")
+    args = (2, 128, 768, 12, 1, 512, 4, "3e-4")
+    d_tc, _ = _run(dropin, args, env={"CXXATTN_COMPAT_PRECISION": "tensorcore"})
+    d_fp32, _ = _run(dropin, args)
+    losses = [v for n, v in d_tc if n.startswith("train")]
+    assert len(losses) == 4 and all(v == v for v in losses) and losses[-1] < losses[0]
+    for (n, a), (_, b) in zip(d_tc, d_fp32):
         if n.startswith("train") or n == "digest loss":
             assert _close(a, b, 2e-2, 1e-6), (n, a, b)
 
