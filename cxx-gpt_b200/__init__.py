@@ -45,7 +45,7 @@ class MhaDesc(C.Structure):
 class LinDesc(C.Structure):
     _fields_ = [("B", C.c_int64), ("S", C.c_int64), ("D", C.c_int64), ("E", C.c_int64),
                 ("dtype", C.c_int32), ("feature_map", C.c_int32), ("eps_in_den", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("ld_qk", C.c_int32)]
 
 
 class CxxAttnError(RuntimeError):
@@ -173,8 +173,8 @@ def mha_desc(B, S, H, Dh, dtype=F32, strides=None):
     return MhaDesc(B, S, H, Dh, sb, ss, sh, dtype, 0)
 
 
-def lin_desc(B, S, D, E, dtype=F32, feature_map=MAP_ELU1, eps_in_den=0):
-    return LinDesc(B, S, D, E, dtype, feature_map, eps_in_den, 0)
+def lin_desc(B, S, D, E, dtype=F32, feature_map=MAP_ELU1, eps_in_den=0, ld_qk=0):
+    return LinDesc(B, S, D, E, dtype, feature_map, eps_in_den, ld_qk)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -10,7 +10,9 @@
 #include "cxxgpt_kernels.hpp"
 
 #include <cstdlib>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 
 #include "cxxattn.h"
 
@@ -87,8 +89,10 @@ void* take(char*& cursor, size_t bytes) {
     return p;
 }
 
+// (The tensor-core detour converts dense fp32 tensors; descriptors that address padded rows in place stay
+// on the exact kernels.)
 void lin_fwd(cxxattn_lin_desc d, const float* Q, const float* K, const float* V, float* O, float* den, float* zc) {
-    if (tensorcore_lin(d.D, d.E)) {
+    if (d.ld_qk == 0 && tensorcore_lin(d.D, d.E)) {
         d.dtype = CXXATTN_BF16;
         const size_t nD = (size_t)(d.B * d.S * d.D), nE = (size_t)(d.B * d.S * d.E);
         const size_t ws = blk256(cxxattn_linattn_workspace_bytes(&d));
@@ -106,7 +110,7 @@ void lin_fwd(cxxattn_lin_desc d, const float* Q, const float* K, const float* V,
 }
 void lin_dq(cxxattn_lin_desc d, const float* K, const float* V, const float* dnum, const float* dden,
             const float* zc, const float* Q, float* dQ) {
-    if (tensorcore_lin(d.D, d.E)) {
+    if (d.ld_qk == 0 && tensorcore_lin(d.D, d.E)) {
         d.dtype = CXXATTN_BF16;
         const size_t nD = (size_t)(d.B * d.S * d.D), nE = (size_t)(d.B * d.S * d.E);
         const size_t ws = blk256(cxxattn_linattn_workspace_bytes(&d));
@@ -125,7 +129,7 @@ void lin_dq(cxxattn_lin_desc d, const float* K, const float* V, const float* dnu
 }
 void lin_dkdv(cxxattn_lin_desc d, const float* Q, const float* K, const float* V, const float* dnum,
               const float* dden, float* dK, float* dV) {
-    if (tensorcore_lin(d.D, d.E)) {
+    if (d.ld_qk == 0 && tensorcore_lin(d.D, d.E)) {
         d.dtype = CXXATTN_BF16;
         const size_t nD = (size_t)(d.B * d.S * d.D), nE = (size_t)(d.B * d.S * d.E);
         const size_t ws = blk256(cxxattn_linattn_workspace_bytes(&d));
@@ -305,12 +309,66 @@ void gelu_exact_deriv(In A, Out C) { ok(cxxattn_gelu_exact(A.device_ptr(), C.dev
 
 }  // namespace two_stage_cuda
 
+// Zero padding of LinearGPT's mapped features.  phi_elu_forward writes phi(x) into the first E columns of
+// rows of D = next_pow2(E) and zeros into the rest (linear_cuda_kernels.cu:316-323), and the scan then
+// multiplies those zeros: a quarter of the state work at n_embd = 768.  The adapter remembers which
+// device tensors its own phi_elu_forward produced; when the scan entry points are handed such tensors
+// they run on the first E columns only (row stride D) and the padded columns of the outputs are set to
+// the zeros the full computation would give.  For the forward and dQ it is K_phi that decides (a zero
+// K column makes the state row, the z entry and the dQ column zero whatever Q holds); dK's padded
+// columns also need Q_phi's to be zero.  On by default; CXXATTN_COMPAT_SKIP_PADDING=0 in the environment or
+// cxxattn_compat::set_skip_padding(false) turns it off.
+namespace {
+std::mutex g_pad_mutex;
+std::unordered_map<const void*, std::pair<size_t, size_t>> g_padded;  // device pointer -> (D, E) of phi_elu_forward
+int g_skip_padding = -1;  // -1: not read yet; CXXATTN_COMPAT_SKIP_PADDING=0 in the environment turns it off
+bool skip_padding() {
+    if (g_skip_padding < 0) {
+        const char* e = std::getenv("CXXATTN_COMPAT_SKIP_PADDING");
+        g_skip_padding = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return g_skip_padding == 1;
+}
+
+void remember_padded(const void* ptr, size_t D, size_t E) {
+    std::lock_guard<std::mutex> lock(g_pad_mutex);
+    if (g_padded.size() > 4096) g_padded.clear();
+    if (E < D) g_padded[ptr] = {D, E};
+    else g_padded.erase(ptr);
+}
+// The number of leading columns that can be non-zero in a D-wide tensor at ptr: E if this adapter's
+// phi_elu_forward wrote it with that D, else D.
+size_t live_columns(const void* ptr, size_t D, size_t E) {
+    // in tensor-core mode the dense tensors are converted as they are; the zero columns cost little there
+    if (!skip_padding() || tensorcore_lin((int64_t)D, (int64_t)E)) return D;
+    std::lock_guard<std::mutex> lock(g_pad_mutex);
+    auto it = g_padded.find(ptr);
+    return (it != g_padded.end() && it->second.first == D) ? it->second.second : D;
+}
+// columns live..D-1 of N rows := 0
+void zero_pad(float* base, size_t N, size_t D, size_t live) {
+    if (live < D)
+        CHECK_CUDA_ERROR(cudaMemset2DAsync(base + live, D * sizeof(float), 0, (D - live) * sizeof(float), N, nullptr));
+}
+cxxattn_lin_desc lin_padded(size_t B, size_t S, size_t D, size_t live, size_t E) {
+    cxxattn_lin_desc d = lin(B, S, live, E, CXXATTN_MAP_NONE, 1);
+    d.ld_qk = live < D ? (int32_t)D : 0;
+    return d;
+}
+}  // namespace
+
+namespace cxxattn_compat {
+void set_skip_padding(bool on) { g_skip_padding = on ? 1 : 0; }
+}  // namespace cxxattn_compat
+
 namespace linear_cuda {
 
 void causal_linear_attention_fwd(In Q_phi, In K_phi, In V, Out O, Out den_cache, Out z_cache, Out, Out, size_t B,
                                  size_t S, size_t D, size_t E) {
-    lin_fwd(lin(B, S, D, E, CXXATTN_MAP_NONE, 1), Q_phi.device_ptr(), K_phi.device_ptr(), V.device_ptr(),
+    const size_t live = live_columns(K_phi.device_ptr(), D, E);
+    lin_fwd(lin_padded(B, S, D, live, E), Q_phi.device_ptr(), K_phi.device_ptr(), V.device_ptr(),
             O.device_ptr(), den_cache.device_ptr(), z_cache.device_ptr());
+    zero_pad(z_cache.device_ptr(), B * S, D, live);
 }
 void causal_linear_attention_bwd_step1(In O, In dO, In den_cache, Out dnum, Out dden, size_t N, size_t E) {
     ok(cxxattn_linattn_bwd_step1(O.device_ptr(), dO.device_ptr(), den_cache.device_ptr(), dnum.device_ptr(),
@@ -319,16 +377,23 @@ void causal_linear_attention_bwd_step1(In O, In dO, In den_cache, Out dnum, Out 
 }
 void causal_linear_attention_bwd_dQ(In K_phi, In V, In dnum, In dden, In z_cache, Out dQ_phi, Out, size_t B, size_t S,
                                     size_t D, size_t E) {
-    lin_dq(lin(B, S, D, E, CXXATTN_MAP_NONE, 1), K_phi.device_ptr(), V.device_ptr(), dnum.device_ptr(),
+    const size_t live = live_columns(K_phi.device_ptr(), D, E);
+    lin_dq(lin_padded(B, S, D, live, E), K_phi.device_ptr(), V.device_ptr(), dnum.device_ptr(),
            dden.device_ptr(), z_cache.device_ptr(), nullptr, dQ_phi.device_ptr());
+    zero_pad(dQ_phi.device_ptr(), B * S, D, live);
 }
 void causal_linear_attention_bwd_dKdV(In Q_phi, In K_phi, In V, In dnum, In dden, Out dK_phi, Out dV, size_t B,
                                       size_t S, size_t D, size_t E) {
-    lin_dkdv(lin(B, S, D, E, CXXATTN_MAP_NONE, 1), Q_phi.device_ptr(), K_phi.device_ptr(), V.device_ptr(),
+    // both must be padded the same way: dK's padded columns are zero only if Q_phi's are
+    const size_t lk = live_columns(K_phi.device_ptr(), D, E), lq = live_columns(Q_phi.device_ptr(), D, E);
+    const size_t live = lk == lq ? lk : D;
+    lin_dkdv(lin_padded(B, S, D, live, E), Q_phi.device_ptr(), K_phi.device_ptr(), V.device_ptr(),
              dnum.device_ptr(), dden.device_ptr(), dK_phi.device_ptr(), dV.device_ptr());
+    zero_pad(dK_phi.device_ptr(), B * S, D, live);
 }
 void phi_elu_forward(In x, Out phi, size_t D, size_t E) {
     ok(cxxattn_phi_elu_fwd(x.device_ptr(), phi.device_ptr(), x.shape()[0], D, E, nullptr), "cxxattn_phi_elu_fwd");
+    remember_padded(phi.device_ptr(), D, E);
 }
 void phi_elu_backward(In dphi, In x, Out dx, size_t D, size_t E) {
     ok(cxxattn_phi_elu_bwd(dphi.device_ptr(), x.device_ptr(), dx.device_ptr(), dphi.shape()[0], D, E, nullptr),

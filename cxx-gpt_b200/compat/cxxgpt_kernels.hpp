@@ -10,6 +10,11 @@
 // (head dimension 64; tolerance 2e-2 instead of 1e-5).  Default: off, or CXXATTN_COMPAT_PRECISION=tensorcore.
 namespace cxxattn_compat {
 void set_tensorcore(bool on);
+// LinearGPT's mapped features carry zero columns from n_embd to the next power of two
+// (linear_cuda_kernels.cu:316-323).  On (the default; CXXATTN_COMPAT_SKIP_PADDING=0 turns it off): the scan
+// entry points skip those columns for tensors that this adapter's phi_elu_forward produced, with the
+// same results.
+void set_skip_padding(bool on);
 // Stage-1 attention of TwoStageGPT with its rotary embedding folded in: what
 //   rope_fwd(Q, K, ..., Dh); fused_mha_fwd(Q, K, V, O, ...)            (two_stage_gpt.hpp:102-106)
 //   fused_mha_bwd(Q, K, V, O, dO, dQ, dK, dV, ...); rope_bwd(dQ, dK, ..., Dh)   (two_stage_gpt.hpp:171-174)

@@ -47,7 +47,7 @@ bool resolve(const cxxattn_mha_desc* d, MhaShape* p) {
 }
 
 bool lin_ok(const cxxattn_lin_desc* d) {
-    return d != nullptr && d->B > 0 && d->S > 0 && d->D > 0 && d->E > 0 && d->reserved == 0 &&
+    return d != nullptr && d->B > 0 && d->S > 0 && d->D > 0 && d->E > 0 && (d->ld_qk == 0 || d->ld_qk >= d->D) &&
            d->B <= INT32_MAX && d->S <= INT32_MAX && d->D <= INT32_MAX && d->E <= INT32_MAX &&
            (d->feature_map == CXXATTN_MAP_NONE || d->feature_map == CXXATTN_MAP_ELU1) &&
            (d->eps_in_den == 0 || d->eps_in_den == 1);

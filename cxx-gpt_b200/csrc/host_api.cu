@@ -167,6 +167,7 @@ int cxxattn_lin_host_plan_create(cxxattn_lin_host_plan** out, const cxxattn_lin_
     if (desc->dtype != CXXATTN_F32 && desc->dtype != CXXATTN_BF16) return CXXATTN_ERR_INVALID;
     cxxattn_lin_desc cd = *desc;
     if (cd.B <= 0) return CXXATTN_ERR_INVALID;
+    if (cd.ld_qk != 0 && cd.ld_qk != cd.D) return CXXATTN_ERR_UNSUPPORTED;  // host tensors are dense
     const int chunk_b = units_per_chunk > cd.B ? (int)cd.B : units_per_chunk;
     cd.B = chunk_b;
     // a descriptor the device-pointer entry points would refuse is refused here too

@@ -52,6 +52,7 @@ struct ApplyArgs {
     float* den;          // [N]    (FWD)
     float* zc_out;       // [N][D] (FWD, optional)
     int S, D, E, nc;
+    int ldd;             // row stride (elements) of the D-wide tensors: Q, K, dQ, dK, z_cache; >= D
     int map;             // CXXATTN_MAP_*
     int eps_in_den;
 };
@@ -79,6 +80,8 @@ __global__ void __launch_bounds__(NT) chunk_apply_kernel(ApplyArgs g) {
     constexpr bool STATE_T = (MODE == DQ || MODE == DK);  // state read as [j][i] instead of [i][j]
     const int I = (MODE == FWD || MODE == DV) ? g.D : g.E;
     const int J = (MODE == FWD || MODE == DV) ? g.E : g.D;
+    const int ldI = (MODE == FWD || MODE == DV) ? g.ldd : g.E;  // a, b are the D-wide tensors in FWD and DV
+    const int ldJ = (MODE == FWD || MODE == DV) ? g.E : g.ldd;  // c, X and the output are in DQ and DK
 
     // As | Bs | St are live during the loop over the contracted dimension; Cs reuses their space
     // afterwards (2*CH*LDI + TI*LDJ >= CH*LDJ), which keeps the CTA under 48 KB of static smem.
@@ -116,8 +119,8 @@ __global__ void __launch_bounds__(NT) chunk_apply_kernel(ApplyArgs g) {
 
     for (int i0 = 0; i0 < I; i0 += TI) {
         __syncthreads();
-        load_slice<TI, LDI>(As, g.a, row0, nrows, I, i0, I, map_a);
-        load_slice<TI, LDI>(Bs, g.b, row0, nrows, I, i0, I, map_b);
+        load_slice<TI, LDI>(As, g.a, row0, nrows, ldI, i0, I, map_a);
+        load_slice<TI, LDI>(Bs, g.b, row0, nrows, ldI, i0, I, map_b);
         for (int k = threadIdx.x; k < TI * TJ; k += NT) {
             const int ii = STATE_T ? k % TI : k / TJ, jj = STATE_T ? k / TI : k % TJ;  // coalesced either way
             float v = 0.f;
@@ -167,7 +170,7 @@ __global__ void __launch_bounds__(NT) chunk_apply_kernel(ApplyArgs g) {
             float run = zs[threadIdx.x];
             for (int r = 0; r < nrows; r++) {
                 run += Bs[r * LDI + threadIdx.x];
-                g.zc_out[(row0 + r) * g.D + i0 + threadIdx.x] = run;
+                g.zc_out[(row0 + r) * g.ldd + i0 + threadIdx.x] = run;
             }
         }
     }
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(NT) chunk_apply_kernel(ApplyArgs g) {
         }
     }
     __syncthreads();  // every reader of As/Bs/St is done before Cs overwrites them
-    load_slice<TJ, LDJ>(Cs, g.c, row0, nrows, J, j0, J, map_c);
+    load_slice<TJ, LDJ>(Cs, g.c, row0, nrows, ldJ, j0, J, map_c);
     __syncthreads();
 
     // intra-chunk part: out[t][j] += sum_s w[t][s] c_s[j]
@@ -230,10 +233,10 @@ __global__ void __launch_bounds__(NT) chunk_apply_kernel(ApplyArgs g) {
             if (col >= J) continue;
             float v = out[i][j];
             if (MODE == FWD) v = v / (rowx[i] + 1e-8f);
-            if (MODE == DQ) v += g.zcache ? g.zcache[row * g.D + col] * g.dden[row] : g.dden[row] * zstate[col];
+            if (MODE == DQ) v += g.zcache ? g.zcache[row * g.ldd + col] * g.dden[row] : g.dden[row] * zstate[col];
             if (MODE == DK) v += zstate[col];
-            if ((MODE == DQ || MODE == DK) && g.X != nullptr) v *= phi_der(g.X[row * J + col]);
-            g.out[row * J + col] = v;
+            if ((MODE == DQ || MODE == DK) && g.X != nullptr) v *= phi_der(g.X[row * ldJ + col]);
+            g.out[row * ldJ + col] = v;
         }
     }
 }
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(NT) chunk_apply_kernel(ApplyArgs g) {
 __global__ void __launch_bounds__(NT) chunk_state_kernel(const float* __restrict__ X, const float* __restrict__ Y,
                                                          const float* __restrict__ wgt, float* __restrict__ state,
                                                          float* __restrict__ zstate, int S, int D, int E, int nc,
-                                                         bool map_x) {
+                                                         int ldx, bool map_x) {
     __shared__ __align__(16) float Xs[CH * LDJ];
     __shared__ __align__(16) float Ys[CH * LDJ];
     const int ndt = (D + TJ - 1) / TJ, net = (E + TJ - 1) / TJ;
@@ -256,7 +259,7 @@ __global__ void __launch_bounds__(NT) chunk_state_kernel(const float* __restrict
     const int64_t row0 = (int64_t)b * S + t0;
     const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
 
-    load_slice<TJ, LDJ>(Xs, X, row0, nrows, D, dt * TJ, D, map_x);
+    load_slice<TJ, LDJ>(Xs, X, row0, nrows, ldx, dt * TJ, D, map_x);
     load_slice<TJ, LDJ>(Ys, Y, row0, nrows, E, et * TJ, E, false);
     __syncthreads();
 
@@ -343,7 +346,7 @@ int build_states(const cxxattn_lin_desc& d, const Ws& w, const float* X, const f
     const int ndt = (int)((d.D + TJ - 1) / TJ), net = (int)((d.E + TJ - 1) / TJ);
     const int64_t grid = (int64_t)d.B * w.nc * ndt * net;
     chunk_state_kernel<<<(unsigned)grid, NT, 0, st>>>(X, Y, wgt, w.state, w.zstate, (int)d.S, (int)d.D,
-                                                      (int)d.E, w.nc, map_x);
+                                                      (int)d.E, w.nc, (int)(d.ld_qk ? d.ld_qk : d.D), map_x);
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
     int64_t width = d.D * d.E, total = d.B * width;
     chunk_scan_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(w.state, width, w.nc, total, rev);
@@ -369,6 +372,7 @@ ApplyArgs base_args(const cxxattn_lin_desc& d, const Ws& w) {
     g.D = (int)d.D;
     g.E = (int)d.E;
     g.nc = w.nc;
+    g.ldd = (int)(d.ld_qk ? d.ld_qk : d.D);
     g.map = d.feature_map;
     g.eps_in_den = d.eps_in_den;
     return g;

@@ -278,7 +278,7 @@ linattn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 }  // namespace
 
-bool linattn_tc_supported(const cxxattn_lin_desc& d) { return d.D == DE && d.E == DE; }
+bool linattn_tc_supported(const cxxattn_lin_desc& d) { return d.D == DE && d.E == DE && (d.ld_qk == 0 || d.ld_qk == DE); }
 
 size_t linattn_tc_workspace(const cxxattn_lin_desc& d) {
     if (!linattn_tc_supported(d)) return 0;

@@ -53,6 +53,7 @@ struct WideParams {
     const float* dden;   // DQ: per row, DK: per column
     int* status;
     int B, S, WL, WO;    // WL = width of L and R (the K-loop), WO = width of Z and of the result
+    int ldo;             // row stride of the result (>= WO)
     int eps_in_den;
 };
 
@@ -237,7 +238,7 @@ linattn_wide_kernel(const __grid_constant__ CUtensorMap tmL, const __grid_consta
             tmem_ld32(tO + 32 * cb, o);
             tmem_ld_wait();
             if (grow < p.S) {
-                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)b * p.S + grow) * p.WO + g * GW + 32 * cb);
+                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)b * p.S + grow) * p.ldo + g * GW + 32 * cb);
 #pragma unroll
                 for (int i = 0; i < 32; i += 8)
                     dst[i / 8] = make_uint4(
@@ -306,15 +307,16 @@ __global__ void wide_step1_kernel(const uint4* __restrict__ O, const uint4* __re
 // z_cache[t][d] = sum over s <= t of phiK[s][d] (float), one thread per (unit, d) walking the sequence; the
 // threads of a warp read consecutive d.  Only for callers of the kept reference signature, which hands
 // z_cache to its backward; this library's wide backward does not read it.
-__global__ void wide_zcache_kernel(const __nv_bfloat16* __restrict__ pk, float* __restrict__ zc, int B, int S, int D) {
+__global__ void wide_zcache_kernel(const __nv_bfloat16* __restrict__ pk, float* __restrict__ zc, int B, int S, int D,
+                                   int ldk, int ldz) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)B * D) return;
     const int b = (int)(i / D), d = (int)(i % D);
     float run = 0.f;
     for (int t = 0; t < S; t++) {
-        const int64_t o = ((int64_t)b * S + t) * D + d;
-        run += __bfloat162float(pk[o]);
-        zc[o] = run;
+        const int64_t row = (int64_t)b * S + t;
+        run += __bfloat162float(pk[row * ldk + d]);
+        zc[row * ldz + d] = run;
     }
 }
 
@@ -342,14 +344,17 @@ WideWs carve(const cxxattn_lin_desc& d, void* base) {
     return w;
 }
 
+// ldw: row stride of the D-wide tensors among L, R, Z and the result (the E-wide ones are dense)
 template <int MODE>
 int launch(const cxxattn_lin_desc& d, const void* L, const void* R, const void* Z, int WL, int WO, void* out, float* den,
-           const float* dden, cudaStream_t st) {
+           const float* dden, int ldw, cudaStream_t st) {
     const int B = (int)d.B, S = (int)d.S;
+    constexpr bool LR_WIDE = MODE == FWD || MODE == DV;  // L and R are Q/K-like; otherwise Z and the result are
+    const int ldL = LR_WIDE ? ldw : WL, ldZ = LR_WIDE ? WO : ldw;
     CUtensorMap tmL, tmR, tmZ;
-    if (!make_tmap_bhsd(&tmL, L, B, S, WL / KB, KB, (int64_t)S * WL, WL, KB, BT) ||
-        !make_tmap_bhsd(&tmR, R, B, S, WL / KB, KB, (int64_t)S * WL, WL, KB, BT) ||
-        !make_tmap_bhsd(&tmZ, Z, B, S, WO / KB, KB, (int64_t)S * WO, WO, KB, BT))
+    if (!make_tmap_bhsd(&tmL, L, B, S, WL / KB, KB, (int64_t)S * ldL, ldL, KB, BT) ||
+        !make_tmap_bhsd(&tmR, R, B, S, WL / KB, KB, (int64_t)S * ldL, ldL, KB, BT) ||
+        !make_tmap_bhsd(&tmZ, Z, B, S, WO / KB, KB, (int64_t)S * ldZ, ldZ, KB, BT))
         return CXXATTN_ERR_CUDA;
     WideParams p;
     p.out = static_cast<__nv_bfloat16*>(out);
@@ -358,6 +363,7 @@ int launch(const cxxattn_lin_desc& d, const void* L, const void* R, const void* 
     p.status = status_word();
     if (p.status == nullptr) return CXXATTN_ERR_CUDA;
     p.B = B; p.S = S; p.WL = WL; p.WO = WO;
+    p.ldo = ldZ;
     p.eps_in_den = d.eps_in_den;
     static OncePerDevice attr;
     const int dev = current_device();
@@ -375,12 +381,18 @@ int launch(const cxxattn_lin_desc& d, const void* L, const void* R, const void* 
     return check_launch();
 }
 
+// Row stride of the D-wide operands of a launch: the mapped copies in the workspace are dense
+int ldw(const cxxattn_lin_desc& d, bool map) { return (map || d.ld_qk == 0) ? (int)d.D : (int)d.ld_qk; }
+
 }  // namespace
 
 // bf16, widths that are multiples of the 64-wide K block; D = E = 64 has kernels of its own
 bool linattn_wide_supported(const cxxattn_lin_desc& d) {
+    const bool dense = d.ld_qk == 0 || d.ld_qk == d.D;
+    // rows wider than D (the first D columns of padded features) only without the fused feature map, and
+    // on a stride TMA can take (a multiple of 16 bytes)
     return d.dtype == CXXATTN_BF16 && d.D % KB == 0 && d.E % KB == 0 && d.D <= 8192 && d.E <= 8192 &&
-           !(d.D == 64 && d.E == 64);
+           (dense ? !(d.D == 64 && d.E == 64) : (d.feature_map == CXXATTN_MAP_NONE && d.ld_qk % 8 == 0));
 }
 
 size_t linattn_wide_workspace(const cxxattn_lin_desc& d) { return linattn_wide_supported(d) ? carve(d, nullptr).bytes : 0; }
@@ -394,7 +406,8 @@ int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, co
     if (reinterpret_cast<uintptr_t>(ws) % 256) return CXXATTN_ERR_ALIGNMENT;
     const WideWs w = carve(d, ws);
     const void *q = Q, *k = K;
-    if (d.feature_map == CXXATTN_MAP_ELU1) {
+    const bool map = d.feature_map == CXXATTN_MAP_ELU1;
+    if (map) {
         const size_t n8 = (size_t)d.B * d.S * d.D / 8;
         wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(Q), reinterpret_cast<uint4*>(w.pq), n8);
         wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
@@ -405,10 +418,10 @@ int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, co
     if (z_cache != nullptr) {
         const int64_t n = d.B * d.D;
         wide_zcache_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(k), z_cache, (int)d.B,
-                                                                      (int)d.S, (int)d.D);
+                                                                      (int)d.S, (int)d.D, ldw(d, map), ldw(d, false));
         if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
     }
-    return launch<FWD>(d, q, k, V, (int)d.D, (int)d.E, O, den, nullptr, st);
+    return launch<FWD>(d, q, k, V, (int)d.D, (int)d.E, O, den, nullptr, ldw(d, map), st);
 }
 
 // The two halves of the backward as the reference's interface cuts it (kernel_attn_bwd_dQ / _dKdV,
@@ -430,7 +443,7 @@ int linattn_wide_bwd_dq(const cxxattn_lin_desc& d, const void* K, const void* V,
         if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
         k = w.pk;
     }
-    int rc = launch<DQ>(d, dnum, V, k, (int)d.E, (int)d.D, map ? (void*)w.dpq : dQ, nullptr, dden, st);
+    int rc = launch<DQ>(d, dnum, V, k, (int)d.E, (int)d.D, map ? (void*)w.dpq : dQ, nullptr, dden, ldw(d, map), st);
     if (rc != CXXATTN_OK || !map) return rc;
     wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpq), static_cast<const uint4*>(Q),
                                                     static_cast<uint4*>(dQ), n8);
@@ -455,9 +468,9 @@ int linattn_wide_bwd_dkdv(const cxxattn_lin_desc& d, const void* Q, const void* 
         q = w.pq;
         k = w.pk;
     }
-    int rc = launch<DV>(d, k, q, dnum, (int)d.D, (int)d.E, dV, nullptr, nullptr, st);
+    int rc = launch<DV>(d, k, q, dnum, (int)d.D, (int)d.E, dV, nullptr, nullptr, ldw(d, map), st);
     if (rc != CXXATTN_OK) return rc;
-    rc = launch<DK>(d, V, dnum, q, (int)d.E, (int)d.D, map ? (void*)w.dpk : dK, nullptr, dden, st);
+    rc = launch<DK>(d, V, dnum, q, (int)d.E, (int)d.D, map ? (void*)w.dpk : dK, nullptr, dden, ldw(d, map), st);
     if (rc != CXXATTN_OK || !map) return rc;
     wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpk), static_cast<const uint4*>(K),
                                                     static_cast<uint4*>(dK), n8);

@@ -66,7 +66,13 @@ typedef struct cxxattn_lin_desc {
     int32_t feature_map; /* CXXATTN_MAP_*                                                        */
     int32_t eps_in_den;  /* 0: den = phi(q).z stored, O = num/(den+1e-8)   (ts.cu:971-972)
                             1: den = q.z + 1e-8 stored, O = num/den        (lin.cu:66-75)        */
-    int32_t reserved;    /* must be 0                                                            */
+    int32_t ld_qk;       /* row stride, in elements, of the D-wide tensors (Q, K, dQ, dK, z_cache): 0 = D
+                            (dense).  A larger stride addresses the first D columns of wider rows in
+                            place: LinearGPT pads its mapped features with zero columns from n_embd to
+                            the next power of two (lin.cu:316-323), and a caller that knows it passes
+                            D = n_embd, ld_qk = the padded width instead of scanning the zeros.  The
+                            columns beyond D are neither read nor written.  fp32, and bf16 with one wide
+                            head and feature_map NONE; other kernels want 0 or D.                       */
 } cxxattn_lin_desc;
 
 const char* cxxattn_strerror(int code);

@@ -219,3 +219,55 @@ def test_long_sequence_properties(pkg, dev, orc):
     rO, rden, _ = orc.linattn_fwd(Q[:sub * S], K[:sub * S], V[:sub * S], sub, S, D, E, elu=True, f64=True)
     assert rel_err(O[:sub * S].cpu().numpy(), rO) < TOL
     assert rel_err(den[:sub * S].cpu().numpy(), rden) < TOL
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_padded_rows_addressed_in_place_give_the_dense_result(pkg, dev, dtype):
+    """ld_qk: the first D columns of wider rows (LinearGPT's zero-padded mapped features) addressed in
+    place give the results of the same call on compact copies; the columns beyond D are not touched."""
+    import ctypes as C
+    lib = pkg.lib()
+    B, S, D, E, LD = 2, 200, 128, 192, 256
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    code = pkg.F32 if dtype == "f32" else pkg.BF16
+    g = torch.Generator().manual_seed(77)
+    Q, K = (torch.rand(B * S, D, generator=g) + 0.1 for _ in range(2))
+    V, dO = (torch.randn(B * S, E, generator=g) for _ in range(2))
+    Q, K, V, dO = (t.to(tdt).to(dev) for t in (Q, K, V, dO))
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run(ld):
+        wide = ld != 0
+        def padded(t):
+            if not wide:
+                return t.contiguous()
+            p = torch.full((B * S, LD), 7.0, dtype=tdt, device=dev)  # the tail must be neither read nor written
+            p[:, :D] = t
+            return p
+        q, k = padded(Q), padded(K)
+        d = pkg.lin_desc(B, S, D, E, code, pkg.MAP_NONE, 1, ld_qk=ld)
+        n = lib.cxxattn_linattn_workspace_bytes(C.byref(d))
+        assert n > 0
+        ws = torch.empty(n, dtype=torch.uint8, device=dev)
+        O = torch.empty_like(V)
+        den = torch.empty(B * S, device=dev)
+        zc = padded(torch.zeros(B * S, D, device=dev)).float() if dtype == "f32" else None
+        if zc is not None and wide:
+            zc[:, D:] = 7.0
+        assert lib.cxxattn_linattn_fwd(C.byref(d), q.data_ptr(), k.data_ptr(), V.data_ptr(), O.data_ptr(), den.data_ptr(),
+                                       zc.data_ptr() if zc is not None else None, ws.data_ptr(), n, st) == 0
+        dQ, dK = padded(torch.zeros_like(Q)), padded(torch.zeros_like(Q))
+        dV = torch.empty_like(V)
+        assert lib.cxxattn_linattn_bwd(C.byref(d), q.data_ptr(), k.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(),
+                                       den.data_ptr(), dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), ws.data_ptr(), n, st) == 0
+        pkg.sync_status()
+        out = [O, den, dQ[:, :D], dK[:, :D], dV] + ([zc[:, :D]] if zc is not None else [])
+        tails = [t[:, D:] for t in (dQ, dK) + ((zc,) if zc is not None else ())] if wide else []
+        return [t.float().cpu().numpy() for t in out], tails
+
+    dense, _ = run(0)
+    strided, tails = run(LD)
+    for a, b in zip(strided, dense):
+        assert np.array_equal(a, b)
+    for t in tails:
+        assert bool((t == 7.0).all())

@@ -154,3 +154,20 @@ def test_fused_entry_points_reproduce_the_gpt_block_attention(args):
     assert set(d) == {"O", "dQ", "dK", "dV"}, out.stdout
     for k, v in d.items():
         assert v == v and v < 2e-5, (k, v)
+
+
+def test_linear_gpt_skips_its_zero_padding_with_the_same_numbers():
+    """n_embd = 96: LinearGPT maps its features into rows of 128 columns, 32 of them zeros
+    (linear_cuda_kernels.cu:316-323).  The adapter runs the scan on the 96 live columns of the tensors its
+    own phi_elu_forward produced; with that switched off it scans all 128.  Same printout either way
+    (the reference build is no pin at this width: its step-1 kernel drops terms unless the width is a
+    power of two)."""
+    dropin, _ = _programs("linear_gpt_check")
+    args = (2, 48, 96, 2, 96, 6)
+    d_skip, c_skip = _run(dropin, args)
+    d_full, c_full = _run(dropin, args, env={"CXXATTN_COMPAT_SKIP_PADDING": "0"})
+    assert [n for n, _ in d_skip] == [n for n, _ in d_full] and len(d_full) >= 10
+    bad = [(n, a, b) for (n, a), (_, b) in zip(d_skip, d_full) if not _close(a, b, 1e-5, 1e-7)]
+    assert not bad, bad
+    losses = [v for n, v in d_skip if n.startswith("train")]
+    assert losses[-1] < losses[0]
