@@ -647,7 +647,8 @@ def run_dp_step(args):
     for _ in range(5):
         flush.zero_()
         oe[0].record()
-        pkg.adamw_step(model.flat_param, model.flat_grad, stepper.m, stepper.v, stepper.t + 1, 0.0, grad_scale=1.0)
+        pkg.adamw_step(model.flat_param, model.flat_grad, stepper.m, stepper.v, stepper.t + 1, 0.0, grad_scale=1.0,
+                       param_copy=model.flat_work if model.mixed else None)
         oe[1].record()
         torch.cuda.synchronize()
         opt_ms += oe[0].elapsed_time(oe[1]) / 5

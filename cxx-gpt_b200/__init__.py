@@ -30,6 +30,7 @@ SYMBOLS = [
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
     "cxxattn_lin_host_plan_create", "cxxattn_lin_host_plan_destroy", "cxxattn_linattn_fwd_bwd_host",
     "cxxattn_set_option", "cxxattn_get_option", "cxxattn_selftest_wait_limit", "cxxattn_adamw_step",
+    "cxxattn_adamw_step_mixed",
 ]
 
 # cxxattn_set_option keys (include/cxxattn.h)
@@ -111,6 +112,7 @@ def lib():
         L.cxxattn_selftest_wait_limit.argtypes = [C.c_uint64, vp]
         f32 = C.c_float
         L.cxxattn_adamw_step.argtypes = [vp, vp, vp, vp, sz, f32, f32, f32, f32, f32, f32, i32, vp, vp]
+        L.cxxattn_adamw_step_mixed.argtypes = [vp, vp, vp, vp, vp, sz, f32, f32, f32, f32, f32, f32, i32, vp, vp]
         _lib = L
     return _lib
 
@@ -318,8 +320,17 @@ class forced_option:
 
 
 def adamw_step(param, grad, m, v, step, lr, beta1=0.9, beta2=0.999, weight_decay=0.01, eps=1e-8, grad_scale=1.0,
-               grad_norm_sq=None):
-    """Fused mean-of-ranks + AdamW + squared gradient norm over flat fp32 buffers (cxxattn_adamw_step)."""
+               grad_norm_sq=None, param_copy=None):
+    """Fused mean-of-ranks + AdamW + squared gradient norm over flat buffers: fp32 gradient
+    (cxxattn_adamw_step), or bf16 gradient with a bf16 copy of the parameters written in the same pass
+    (cxxattn_adamw_step_mixed; param_copy required)."""
+    import torch
+    if grad.dtype == torch.bfloat16:
+        check(lib().cxxattn_adamw_step_mixed(_ptr(param), _ptr(grad), _ptr(m), _ptr(v), _ptr(param_copy), param.numel(),
+                                             float(grad_scale), float(lr), float(beta1), float(beta2),
+                                             float(weight_decay), float(eps), int(step), _ptr(grad_norm_sq), _stream()),
+              "cxxattn_adamw_step_mixed")
+        return
     check(lib().cxxattn_adamw_step(_ptr(param), _ptr(grad), _ptr(m), _ptr(v), param.numel(), float(grad_scale),
                                    float(lr), float(beta1), float(beta2), float(weight_decay), float(eps), int(step),
                                    _ptr(grad_norm_sq), _stream()), "cxxattn_adamw_step")

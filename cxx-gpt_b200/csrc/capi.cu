@@ -299,8 +299,18 @@ int cxxattn_adamw_step(float* param, const float* grad, float* m, float* v, size
     if (!param || !grad || !m || !v || n == 0 || step < 1 || !(beta1 >= 0.f && beta1 < 1.f) ||
         !(beta2 >= 0.f && beta2 < 1.f) || !(eps > 0.f))
         return CXXATTN_ERR_INVALID;
-    return adamw_fused(param, grad, m, v, n, grad_scale, lr, beta1, beta2, weight_decay, eps, step, grad_norm_sq,
-                       static_cast<cudaStream_t>(stream));
+    return adamw_fused(param, grad, CXXATTN_F32, m, v, nullptr, n, grad_scale, lr, beta1, beta2, weight_decay, eps, step,
+                       grad_norm_sq, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_adamw_step_mixed(float* param, const void* grad_bf16, float* m, float* v, void* param_bf16, size_t n,
+                             float grad_scale, float lr, float beta1, float beta2, float weight_decay, float eps,
+                             int step, float* grad_norm_sq, cxxattn_stream_t stream) {
+    if (!param || !grad_bf16 || !m || !v || !param_bf16 || n == 0 || step < 1 || !(beta1 >= 0.f && beta1 < 1.f) ||
+        !(beta2 >= 0.f && beta2 < 1.f) || !(eps > 0.f))
+        return CXXATTN_ERR_INVALID;
+    return adamw_fused(param, grad_bf16, CXXATTN_BF16, m, v, param_bf16, n, grad_scale, lr, beta1, beta2, weight_decay, eps,
+                       step, grad_norm_sq, static_cast<cudaStream_t>(stream));
 }
 
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {

@@ -123,8 +123,9 @@ int linattn_decode_step(const cxxattn_lin_desc& d, const float* q, const float* 
 size_t mha_decode_workspace(const cxxattn_mha_desc& d);
 int mha_decode_step(const cxxattn_mha_desc& d, const float* q, const float* k, const float* v, float* Kc, float* Vc,
                     int64_t pos, float* o, void* ws, size_t ws_bytes, cudaStream_t st);
-int adamw_fused(float* param, const float* grad, float* m, float* v, size_t n, float grad_scale, float lr, float beta1,
-                float beta2, float wd, float eps, int step, float* norm_sq, cudaStream_t st);
+int adamw_fused(float* param, const void* grad, int grad_dtype, float* m, float* v, void* param_copy, size_t n,
+                float grad_scale, float lr, float beta1, float beta2, float wd, float eps, int step, float* norm_sq,
+                cudaStream_t st);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
 

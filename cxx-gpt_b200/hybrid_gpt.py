@@ -16,7 +16,7 @@ What runs where:
     optimiser step are this library's kernels, called through its C-ABI (`CudaKernels`);
   * the dense glue (linear layers, LayerNorm, GELU, embedding, cross-entropy) is plain torch, i.e.
     cuBLAS and library kernels: it is outside the attention path and is not tuned here;
-  * gradients live in ONE flat fp32 buffer that the autograd engine accumulates into in place; after
+  * gradients live in ONE flat buffer (fp32, or bf16 in mixed precision) that the autograd engine accumulates into in place; after
     the backward pass of a bucket of it, `torch.distributed.all_reduce` (NCCL, sum) is started on
     that bucket while the rest of the backward pass runs; the kernel after the collective,
     cxxattn_adamw_step, turns the sum into the mean, applies AdamW as the reference's optimiser
@@ -79,8 +79,9 @@ class CudaKernels:
         self.pkg.linattn_bwd(q, k, v, o, do.contiguous(), den, dq, dk, dv, B, S, D, E, self.pkg.MAP_ELU1, 0)
         return dq, dk, dv
 
-    def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq):
-        self.pkg.adamw_step(param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq)
+    def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq, param_copy=None):
+        self.pkg.adamw_step(param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq,
+                            param_copy=param_copy)
 
 
 class _RopeCast(torch.autograd.Function):
@@ -156,7 +157,13 @@ def parameter_table(cfg):
 
 
 class HybridGPT:
-    """Parameters, gradients and AdamW moments in four flat fp32 buffers; `p[name]` are views."""
+    """Parameters, gradients and AdamW moments in flat buffers; `p[name]` are views.
+
+    fp32 compute: the leaves of the autograd graph are views of the fp32 parameter buffer and their gradients
+    views of an fp32 gradient buffer.  bf16 compute (mixed precision): the fp32 buffer is the optimiser's
+    master copy; the leaves are views of a bf16 working copy that the optimiser kernel rewrites in the pass
+    that updates the master, and the gradient buffer is bf16 too (half the bytes through the all-reduce, no
+    per-layer conversions in either pass)."""
 
     def __init__(self, cfg, kernels, device, seed=0):
         self.cfg, self.kernels, self.device = cfg, kernels, device
@@ -165,12 +172,11 @@ class HybridGPT:
         for name, shape, _ in table:
             n = math.prod(shape)
             self.offsets[name] = (off, n, shape)
-            off += (n + 3) // 4 * 4  # every view starts on a 16-byte boundary
+            off += (n + 7) // 8 * 8  # every view starts on a 16-byte boundary, in bf16 too
         self.numel = off
+        self.mixed = cfg.compute_dtype == torch.bfloat16
         self.flat_param = torch.zeros(off, dtype=torch.float32, device=device)
-        self.flat_grad = torch.zeros_like(self.flat_param)
         g = torch.Generator(device="cpu").manual_seed(seed)
-        self.p = {}
         for name, shape, std in table:
             o, n, _ = self.offsets[name]
             view = self.flat_param[o:o + n].view(shape)
@@ -178,6 +184,12 @@ class HybridGPT:
                 view.fill_(1.0)
             elif std > 0:
                 view.copy_((torch.randn(shape, generator=g) * std).to(device))
+        self.flat_work = self.flat_param.to(torch.bfloat16) if self.mixed else self.flat_param
+        self.flat_grad = torch.zeros_like(self.flat_work)
+        self.p = {}
+        for name, shape, _ in table:
+            o, n, _ = self.offsets[name]
+            view = self.flat_work[o:o + n].view(shape)
             view.requires_grad_(True)
             view.grad = self.flat_grad[o:o + n].view(shape)  # autograd accumulates into the flat buffer in place
             self.p[name] = view
@@ -190,7 +202,8 @@ class HybridGPT:
 
     def _ln(self, x, name):
         E = self.cfg.n_embd
-        return F.layer_norm(x.float(), (E,), self.p[name + ".g"], self.p[name + ".b"], self.cfg.ln_eps).to(x.dtype)
+        return F.layer_norm(x.float(), (E,), self.p[name + ".g"].float(), self.p[name + ".b"].float(),
+                            self.cfg.ln_eps).to(x.dtype)
 
     def loss(self, idx, targets):
         """Mean next-token cross-entropy of logits = model(idx); idx, targets [B, S] int64."""
@@ -198,7 +211,7 @@ class HybridGPT:
         B, S = idx.shape
         E, H, Dh, dt = cfg.n_embd, cfg.n_head, cfg.head_dim, cfg.compute_dtype
         pos = torch.arange(S, device=idx.device)
-        h = (F.embedding(idx, self.p["wte"]) + F.embedding(pos, self.p["wpe"])[None]).reshape(B * S, E).to(dt)
+        h = (F.embedding(idx, self.p["wte"]).float() + F.embedding(pos, self.p["wpe"]).float()[None]).reshape(B * S, E).to(dt)
         for i in range(cfg.n_layer):
             p = f"h{i}."
             a = self._ln(h, p + "ln_1")
@@ -248,7 +261,7 @@ class DataParallelStep:
         for j, name in enumerate(names):
             o, n, _ = model.offsets[name]
             count += 1
-            end = (o + n + 3) // 4 * 4
+            end = (o + n + 7) // 8 * 8
             if end - lo >= target or j == len(names) - 1:
                 self.buckets.append({"lo": lo, "hi": end, "params": count, "ready": 0})
                 lo, count = end, 0
@@ -319,5 +332,5 @@ class DataParallelStep:
         lr, b1, b2, wd, eps = self.hp
         with torch.no_grad():
             model.kernels.adamw(model.flat_param, model.flat_grad, self.m, self.v, self.t, lr, b1, b2, wd, eps,
-                                1.0 / self.world, self.norm_sq)
+                                1.0 / self.world, self.norm_sq, model.flat_work if model.mixed else None)
         return loss, self.norm_sq

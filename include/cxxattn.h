@@ -236,6 +236,13 @@ int cxxattn_adamw_step(float* param, const float* grad, float* m, float* v, size
                        float beta1, float beta2, float weight_decay, float eps, int step, float* grad_norm_sq,
                        cxxattn_stream_t stream);
 
+/* The same step for mixed-precision training: the gradient is bf16 (n elements, 16-byte aligned), the fp32
+ * master parameters and moments are updated as above, and the bf16 working copy param_bf16 (8-byte
+ * aligned) that the forward and backward passes read is rewritten in the same pass. */
+int cxxattn_adamw_step_mixed(float* param, const void* grad_bf16, float* m, float* v, void* param_bf16, size_t n,
+                             float grad_scale, float lr, float beta1, float beta2, float weight_decay, float eps,
+                             int step, float* grad_norm_sq, cxxattn_stream_t stream);
+
 /* ---- host-buffer entry points ------------------------------------------------------------- */
 
 /* Softmax MHA forward + backward on HOST tensors in the reference layout (what kernel_test.cpp

@@ -51,8 +51,10 @@ class OracleKernels:
                      self.orc.kernel_attn_bwd(q.numpy(), k.numpy(), v.numpy(), o.numpy(), do.contiguous().numpy(),
                                               den.numpy(), B, S, D, E))
 
-    def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq):
-        reference_adamw(param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq)
+    def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq, param_copy=None):
+        reference_adamw(param, grad.float(), m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq)
+        if param_copy is not None:
+            param_copy.copy_(param)
 
 
 def reference_adamw(param, grad, m, v, step, lr, beta1, beta2, wd, eps, grad_scale, norm_sq):
@@ -89,7 +91,7 @@ def test_parameter_layout_and_count():
     assert n == V * E + 256 * E + 12 * per_block + 2 * E == 111_401_472
     model = hy.HybridGPT(small_config(hy), OracleKernels(), torch.device("cpu"))
     for name, (off, cnt, shape) in model.offsets.items():
-        assert off % 4 == 0 and model.p[name].data_ptr() == model.flat_param.data_ptr() + 4 * off
+        assert off % 8 == 0 and model.p[name].data_ptr() == model.flat_param.data_ptr() + 4 * off
         assert model.p[name].grad.data_ptr() == model.flat_grad.data_ptr() + 4 * off
     # buckets partition the buffer at parameter borders
     st = hy.DataParallelStep(model, n_buckets=3)

@@ -35,6 +35,27 @@ def test_fused_adamw_matches_the_reference_formula(pkg, dev, n, world):
     assert abs(float(nsq) - float(nsq_want)) < 1e-5 * float(nsq_want)
 
 
+def test_mixed_precision_adamw_matches_the_reference_formula(pkg, dev):
+    """bf16 gradient in, fp32 master and moments updated as by the fp32 kernel on the same (bf16-valued)
+    gradient, bf16 working copy = the rounded master."""
+    n, world = 100_003, 4
+    g = torch.Generator().manual_seed(3)
+    param, grad = torch.randn(n, generator=g), (torch.randn(n, generator=g) * world).bfloat16()
+    m, v = torch.randn(n, generator=g) * 0.1, torch.rand(n, generator=g) * 0.1
+    a = [t.clone().to(dev) for t in (param, grad.float(), m, v)]
+    b = [t.clone().to(dev) for t in (param, grad, m, v)]
+    copy = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    na, nb = torch.zeros(1, device=dev), torch.zeros(1, device=dev)
+    for step in (1, 2):
+        pkg.adamw_step(a[0], a[1], a[2], a[3], step, 1e-3, grad_scale=1.0 / world, grad_norm_sq=na)
+        pkg.adamw_step(b[0], b[1], b[2], b[3], step, 1e-3, grad_scale=1.0 / world, grad_norm_sq=nb, param_copy=copy)
+    torch.cuda.synchronize()
+    for x, y in zip(a[:1] + a[2:], b[:1] + b[2:]):
+        assert torch.equal(x, y)
+    assert torch.equal(copy, b[0].bfloat16())
+    assert abs(float(na) - float(nb)) < 1e-5 * float(na)  # one atomic per CTA: the order of the sum varies
+
+
 def test_model_on_the_exact_kernels_matches_the_oracle_model(pkg, dev):
     """fp32 compute: every custom autograd function runs the library's exact kernels; loss and the
     whole flat gradient agree with the same model computed by the CPU oracle."""
@@ -74,7 +95,7 @@ def test_training_on_the_tensor_core_kernels_learns_and_tracks_fp32(pkg, dev):
         loss, nsq = step.step(idx.to(dev), tgt.to(dev))
         losses.append(float(loss))
         if i == 0:
-            g, r = model.flat_grad.cpu(), ref.flat_grad
+            g, r = model.flat_grad.float().cpu(), ref.flat_grad  # bf16 gradient buffer in mixed precision
             cos = float((g @ r) / (g.norm() * r.norm()))
             assert cos > 0.995 and abs(float(g.norm() / r.norm()) - 1) < 3e-2, (cos, float(g.norm() / r.norm()))
             assert abs(float(nsq) - float(g.norm() ** 2)) < 1e-3 * float(nsq)
