@@ -192,7 +192,9 @@ def check_units(orc, Q, K, V, dO, res, S, units):
         assert rel_err(den[r], rden) < TOL_BF16, ("den", u)
         rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O[r], f[3], den[r], 1, S, 64, 64, f64=True)
         for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
-            assert rel_err(a[r], b) < TOL_BF16, (name, u, rel_err(a[r], b))
+            # the floor matters for a single token only: its dQ and dK are zero by cancellation
+            floor = 0.2 if S == 1 else 1e-30  # absolute bar 4e-3 on terms of order one
+            assert rel_err(a[r], b, floor=floor) < TOL_BF16, (name, u, rel_err(a[r], b, floor=floor))
 
 
 def test_long_sequence_sweep_shape_s16384(pkg, dev, orc):
@@ -264,3 +266,14 @@ def test_host_entry_point_matches_device_entry_points(pkg, dev):
         got = [t[r].float().numpy() for t in (hO, hden, hdQ, hdK, hdV)]
         for name, a, b in zip(("O", "den", "dQ", "dK", "dV"), got, want):
             assert np.array_equal(a, b), (name, lo)
+
+
+@pytest.mark.parametrize("B,S", [(1, 1), (2, 129), (300, 130)])
+def test_edge_shapes(pkg, dev, orc, B, S):
+    """A single token, one row past a chunk border, more units than SMs with a ragged second chunk."""
+    Q, K, V = inputs(95 + S, B, S, 64, 64)
+    dO = torch.randn(B * S, 64, generator=torch.Generator().manual_seed(S)).bfloat16()
+    res = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, pkg.MAP_ELU1, 0)
+    for a in res:
+        assert np.all(np.isfinite(a))
+    check_units(orc, Q, K, V, dO, res, S, [0, B - 1])

@@ -130,3 +130,21 @@ def test_split_backward_entry_points_and_z_cache(pkg, dev, orc):
     f = [x.float().numpy() for x in (Q, K, V)]
     _, _, rzc = orc.linattn_fwd(f[0], f[1], f[2], B, S, D, E, elu=True, f64=True)
     assert rel_err(zc.cpu().numpy(), rzc) < TOL_BF16
+
+
+@pytest.mark.parametrize("B,S,D,E", [(1, 1, 128, 128), (2, 128, 64, 128), (2, 100, 128, 64), (3, 257, 192, 320)])
+def test_edge_shapes(pkg, dev, orc, B, S, D, E):
+    """A single token, exactly one tile, widths where only one of D, E is 64 (these take the wide-head
+    kernel too), one row past a tile border with a result width that is not a multiple of the column group."""
+    Q, K, V, dO = inputs(31 + S + D, B, S, D, E, False, 0.5)
+    O, den, dQ, dK, dV = run(pkg, dev, Q, K, V, dO, B, S, D, E, pkg.MAP_ELU1, 0)
+    f = [x.float().numpy() for x in (Q, K, V, dO)]
+    rO, rden, _ = orc.linattn_fwd(f[0], f[1], f[2], B, S, D, E, elu=True, f64=True)
+    assert rel_err(O, rO) < TOL_BF16 and rel_err(den, rden) < TOL_BF16
+    rdQ, rdK, rdV = orc.kernel_attn_bwd(f[0], f[1], f[2], O, f[3], den, B, S, D, E, f64=True)
+    # A single token: dQ and dK are a difference of two equal terms (O = v), so what is left of them is the
+    # bf16 rounding of O and dnum; they are held to an absolute bar there.
+    floor = 5e-2 if S == 1 else 1e-30
+    for name, a, b in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
+        assert np.all(np.isfinite(a)), name
+        assert rel_err(a, b, floor=floor) < TOL_BF16, (name, rel_err(a, b, floor=floor))

@@ -181,7 +181,8 @@ def check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, slices):
         for name, a, ref in (("dQ", dQ, rdQ), ("dK", dK, rdK), ("dV", dV, rdV)):
             got = a[rows, cols].float().cpu().numpy()
             assert np.all(np.isfinite(got)), (name, b, h)
-            assert rel_err(got, ref) < TOL_BF16, (name, b, h, rel_err(got, ref))
+            # the floor matters for a single token only: its dQ and dK are zero by cancellation
+            assert rel_err(got, ref, floor=1e-3) < TOL_BF16, (name, b, h, rel_err(got, ref, floor=1e-3))
 
 
 def test_long_sequence_sweep_shape_s16384(pkg, dev, orc):
@@ -263,3 +264,45 @@ def test_bounded_wait_gives_up_and_reports(pkg, dev):
     pkg.selftest_umma(0, A.to(dev), Bm.to(dev), D)
     pkg.sync_status()
     assert rel_err(D.cpu().numpy(), (A.float() @ Bm.float().T).numpy()) < 1e-5
+
+
+def test_head_range_inside_full_width_rows_matches_the_dense_call(pkg, dev):
+    """What a rank of the 8-GPU split of the S=16384 point does: heads 6..11 of a batch item are
+    addressed in place inside rows of 12 heads through the descriptor's strides (stride_b = S*H*Dh,
+    stride_s = H*Dh, stride_h = Dh, base pointer moved by 6*Dh elements).  Same bits as the dense call on
+    compact copies for O, lse, dK, dV; dQ within its arrival-order noise; the other heads' columns of the
+    output tensors are not written."""
+    B, S, H, Dh, h0, nh = 2, 640, 12, 64, 6, 6
+    Q, K, V, dO = (t.to(dev) for t in bf16_inputs(53, B, S, H, Dh))
+    cols = slice(h0 * Dh, (h0 + nh) * Dh)
+    strides = (S * H * Dh, H * Dh, Dh)
+
+    def outputs():
+        return [torch.full_like(Q, 9.0) for _ in range(4)]
+    O, dQ, dK, dV = outputs()
+    lse = torch.empty(B * nh * S, device=dev)
+    view = lambda t: t[:, cols]
+    pkg.mha_fwd(view(Q), view(K), view(V), view(O), B, S, nh, Dh, lse=lse, strides=strides)
+    pkg.mha_bwd(view(Q), view(K), view(V), view(O), view(dO), view(dQ), view(dK), view(dV), B, S, nh, Dh, lse=lse,
+                strides=strides)
+    cq, ck, cv, cg = (view(t).contiguous() for t in (Q, K, V, dO))
+    cO, cdQ, cdK, cdV = (torch.empty_like(cq) for _ in range(4))
+    clse = torch.empty_like(lse)
+    pkg.mha_fwd(cq, ck, cv, cO, B, S, nh, Dh, lse=clse)
+    pkg.mha_bwd(cq, ck, cv, cO, cg, cdQ, cdK, cdV, B, S, nh, Dh, lse=clse)
+    pkg.sync_status()
+    assert torch.equal(view(O), cO) and torch.equal(lse, clse)
+    assert torch.equal(view(dK), cdK) and torch.equal(view(dV), cdV)
+    assert rel_err(view(dQ).float().cpu().numpy(), cdQ.float().cpu().numpy()) < 1e-2
+    for t in (O, dQ, dK, dV):  # heads 0..5 untouched
+        assert bool((t[:, :h0 * Dh] == 9.0).all())
+
+
+@pytest.mark.parametrize("B,S,H", [(1, 1, 1), (2, 129, 3), (40, 130, 12)])
+def test_edge_shapes_forward_and_backward(pkg, dev, orc, B, S, H):
+    """A single token, one row past a tile border, and 480 short (batch, head) units (more items than SMs
+    in both kernels, each with a ragged second tile)."""
+    Dh = 64
+    Q, K, V, dO = bf16_inputs(59 + S, B, S, H, Dh)
+    O, dQ, dK, dV = run_fwd_bwd(pkg, dev, Q, K, V, dO, B, S, H, Dh)
+    check_slices(orc, Q, K, V, dO, O, dQ, dK, dV, S, H, Dh, [(0, 0), (B - 1, H - 1)])
