@@ -88,14 +88,17 @@ class ClockSampler(threading.Thread):
 
     def sample(self):
         nv = self.nv
-        names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
-                 nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
-                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
-                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+        # every reason NVML can name, so that a clock below the maximum never goes unexplained
+        names = {getattr(nv, "nvmlClocksThrottleReason" + k, 0): v for k, v in (
+            ("HwSlowdown", "hw_slowdown"), ("HwThermalSlowdown", "hw_thermal_slowdown"),
+            ("SwThermalSlowdown", "sw_thermal_slowdown"), ("SwPowerCap", "sw_power_cap"),
+            ("HwPowerBrakeSlowdown", "hw_power_brake_slowdown"), ("SyncBoost", "sync_boost"),
+            ("ApplicationsClocksSetting", "applications_clocks_setting"),
+            ("DisplayClockSetting", "display_clock_setting"), ("GpuIdle", "gpu_idle"))}
         self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
         r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
         for bit, name in names.items():
-            if r & bit:
+            if bit and r & bit:
                 self.reasons.add(name)
 
     def run(self):
