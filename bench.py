@@ -589,8 +589,10 @@ def run_dp_step(args):
     world, rank, local, dev = init_ranks()
     cfg = hy.HybridConfig()
     B, S = 8, cfg.block_size
-    model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=4)
-    stepper = hy.DataParallelStep(model, lr=1e-3, cuda_graph=not args.no_cuda_graph)
+    # more than one rank: gradient exchange and optimiser as one kernel over peer memory, unless NCCL is asked for
+    exchange = args.dp_exchange if args.dp_exchange != "auto" else ("peer" if world > 1 else "nccl")
+    model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=4, peer=exchange == "peer")
+    stepper = hy.DataParallelStep(model, lr=1e-3, cuda_graph=not args.no_cuda_graph, exchange=exchange)
     gen = torch.Generator(device="cpu").manual_seed(4 + rank)
     nbatch = 8
     # token ids uniform in [0, vocab); the target of a position is a fixed function of its token, so
@@ -643,16 +645,27 @@ def run_dp_step(args):
         float(hloss)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
-    # the optimiser kernel alone (the kernel that follows the collective): HBM-bound, 28 bytes per parameter
+    # the optimiser kernel alone.  After an all-reduce it is HBM-bound, 28 bytes per parameter.  The exchange
+    # kernel is timed between barriers on all ranks at once (its loads and stores cross NVLink while the
+    # other ranks' do): (world-1)/world of the gradient bytes come in and as many parameter bytes go out.
     oe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     opt_ms = 0.0
     for _ in range(5):
         flush.zero_()
-        oe[0].record()
-        pkg.adamw_step(model.flat_param, model.flat_grad, stepper.m, stepper.v, stepper.t + 1, 0.0, grad_scale=1.0,
-                       param_copy=model.flat_work if model.mixed else None)
-        oe[1].record()
+        if exchange == "peer":
+            barrier()
+            oe[0].record()
+            model.kernels.adamw_exchange(stepper.master, stepper.m, stepper.v, stepper.grad_ptrs, stepper.param_ptrs,
+                                         model.flat_work.dtype, stepper.rank, stepper.lo, stepper.t + 1, 0.0, 0.9,
+                                         0.999, 0.0, 1e-8, 1.0 / world, None)
+            oe[1].record()
+            barrier()
+        else:
+            oe[0].record()
+            pkg.adamw_step(model.flat_param, model.flat_grad, stepper.m, stepper.v, stepper.t + 1, 0.0, grad_scale=1.0,
+                           param_copy=model.flat_work if model.mixed else None)
+            oe[1].record()
         torch.cuda.synchronize()
         opt_ms += oe[0].elapsed_time(oe[1]) / 5
     t = torch.tensor([ms, e2e_ms, opt_ms], device=dev, dtype=torch.float64)
@@ -667,6 +680,17 @@ def run_dp_step(args):
             hbm, how = 6650.0, "fallback"
         tokens = world * B * S
         gbs = 28.0 * model.numel / (opt_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": "adamw_fused_kernel (the kernel after the gradient all-reduce)",
+                "launch_ms": opt_ms, "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s",
+                "frac": gbs / hbm, "traffic": None}
+        if exchange == "peer" and world > 1:
+            # bytes that must cross NVLink per GPU and direction / the measured peer-copy bandwidth
+            item = model.flat_work.element_size()
+            link = (world - 1) / world * model.numel * item / (opt_ms * 1e-3) / 1e9
+            roof = {"bound": "nvlink", "kernel": "adamw_exchange_kernel (gradient exchange + AdamW over peer memory)",
+                    "launch_ms": opt_ms, "achieved": link, "peak": 770.0,
+                    "peak_source": "peer copy per direction measured on this pool", "unit": "GB/s",
+                    "frac": link / 770.0, "traffic": None}
         line = {"metric": DP_METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -677,10 +701,10 @@ def run_dp_step(args):
                 "clocks": sampler.result(),
                 "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": world * 2 * B * S * 8, "d2h_bytes_per_step": world * 4},
-                "roofline": {"bound": "hbm", "kernel": "adamw_fused_kernel (the kernel after the gradient all-reduce)",
-                             "launch_ms": opt_ms, "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s",
-                             "frac": gbs / hbm, "traffic": None}}
+                "exchange": exchange, "roofline": roof}
         print(json.dumps(line), flush=True)
+    barrier()  # no rank unmaps or frees a buffer while another may still touch it
+    stepper.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -804,6 +828,9 @@ def main():
                     help="linear-attention workloads: skip timing the reference's own CUDA kernels beside ours")
     ap.add_argument("--lin-dtype", default="bf16", choices=["bf16", "f32"],
                     help="element type of the linattn_* workloads (bf16: tensor-core kernels, f32: exact kernels)")
+    ap.add_argument("--dp-exchange", default="auto", choices=["auto", "nccl", "peer"],
+                    help="dp_step: gradients through an NCCL all-reduce followed by the optimiser kernel, or exchange "
+                         "and optimiser as one kernel over peer memory (auto: peer with more than one rank)")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="dp_step: launch every kernel of forward + backward from Python instead of replaying a CUDA graph")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",

@@ -30,7 +30,8 @@ SYMBOLS = [
     "cxxattn_linattn_fwd_noalloc", "cxxattn_linattn_noalloc_capacity", "cxxattn_set_timing_events",
     "cxxattn_lin_host_plan_create", "cxxattn_lin_host_plan_destroy", "cxxattn_linattn_fwd_bwd_host",
     "cxxattn_set_option", "cxxattn_get_option", "cxxattn_selftest_wait_limit", "cxxattn_adamw_step",
-    "cxxattn_adamw_step_mixed",
+    "cxxattn_adamw_step_mixed", "cxxattn_adamw_step_exchange",
+    "cxxattn_peer_alloc", "cxxattn_peer_free", "cxxattn_peer_export", "cxxattn_peer_open", "cxxattn_peer_close",
 ]
 
 # cxxattn_set_option keys (include/cxxattn.h)
@@ -113,6 +114,13 @@ def lib():
         f32 = C.c_float
         L.cxxattn_adamw_step.argtypes = [vp, vp, vp, vp, sz, f32, f32, f32, f32, f32, f32, i32, vp, vp]
         L.cxxattn_adamw_step_mixed.argtypes = [vp, vp, vp, vp, vp, sz, f32, f32, f32, f32, f32, f32, i32, vp, vp]
+        L.cxxattn_adamw_step_exchange.argtypes = [vp, vp, vp, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, sz, sz,
+                                                  f32, f32, f32, f32, f32, f32, i32, vp, vp]
+        L.cxxattn_peer_alloc.argtypes = [sz, C.POINTER(vp)]
+        L.cxxattn_peer_free.argtypes = [vp]
+        L.cxxattn_peer_export.argtypes = [vp, C.c_char_p]
+        L.cxxattn_peer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+        L.cxxattn_peer_close.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -168,6 +176,15 @@ def _dtype_code(t):
     if t.dtype == torch.bfloat16:
         return BF16
     raise ValueError(f"unsupported dtype {t.dtype}")
+
+
+def _dtype_code_of(dtype):
+    import torch
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise ValueError(f"unsupported dtype {dtype}")
 
 
 def mha_desc(B, S, H, Dh, dtype=F32, strides=None):
@@ -334,6 +351,73 @@ def adamw_step(param, grad, m, v, step, lr, beta1=0.9, beta2=0.999, weight_decay
     check(lib().cxxattn_adamw_step(_ptr(param), _ptr(grad), _ptr(m), _ptr(v), param.numel(), float(grad_scale),
                                    float(lr), float(beta1), float(beta2), float(weight_decay), float(eps), int(step),
                                    _ptr(grad_norm_sq), _stream()), "cxxattn_adamw_step")
+
+
+def adamw_step_exchange(param_shard, m_shard, v_shard, grad_ptrs, param_ptrs, dtype, rank, lo, step, lr, beta1=0.9,
+                        beta2=0.999, weight_decay=0.01, eps=1e-8, grad_scale=1.0, grad_norm_sq=None):
+    """Gradient exchange + AdamW of one data-parallel rank over peer memory (cxxattn_adamw_step_exchange).
+    grad_ptrs / param_ptrs: device addresses (ints), one per rank, of the ranks' whole gradient and
+    parameter buffers of torch dtype `dtype` as this rank's GPU sees them; the rank owns elements
+    [lo, lo + param_shard.numel())."""
+    world = len(grad_ptrs)
+    arr = C.c_void_p * world
+    check(lib().cxxattn_adamw_step_exchange(_ptr(param_shard), _ptr(m_shard), _ptr(v_shard), arr(*grad_ptrs),
+                                            arr(*param_ptrs), _dtype_code_of(dtype), world, int(rank), int(lo),
+                                            param_shard.numel(), float(grad_scale), float(lr), float(beta1),
+                                            float(beta2), float(weight_decay), float(eps), int(step),
+                                            _ptr(grad_norm_sq), _stream()), "cxxattn_adamw_step_exchange")
+
+
+class PeerBuffer:
+    """A device buffer other processes' GPUs of this machine can map (cxxattn_peer_*).  `tensor` is a
+    flat torch view of it; `handle()` is what another process passes to `PeerBuffer.open`."""
+
+    def __init__(self, numel, dtype, device):
+        import torch
+        self.numel, self.dtype, self.device = int(numel), dtype, torch.device(device)
+        self.itemsize = torch.empty(0, dtype=dtype).element_size()
+        self.ptr, self.owned = C.c_void_p(), True
+        with torch.cuda.device(self.device):
+            check(lib().cxxattn_peer_alloc(max(1, self.numel) * self.itemsize, C.byref(self.ptr)), "cxxattn_peer_alloc")
+        self.tensor = self._view()
+        self.tensor.zero_()
+
+    def _view(self):
+        import torch
+        raw = torch.as_tensor(_CudaArray(self.ptr.value, self.numel * self.itemsize, self), device=self.device)
+        return raw.view(self.dtype)
+
+    def handle(self):
+        buf = C.create_string_buffer(64)
+        check(lib().cxxattn_peer_export(self.ptr, buf), "cxxattn_peer_export")
+        return buf.raw
+
+    @classmethod
+    def open(cls, handle, numel, dtype, device):
+        """Maps a buffer another process exported; only the address is used (`ptr.value`)."""
+        import torch
+        self = cls.__new__(cls)
+        self.numel, self.dtype, self.device = int(numel), dtype, torch.device(device)
+        self.itemsize = torch.empty(0, dtype=dtype).element_size()
+        self.ptr, self.owned, self.tensor = C.c_void_p(), False, None
+        with torch.cuda.device(self.device):
+            check(lib().cxxattn_peer_open(C.create_string_buffer(handle, 64), C.byref(self.ptr)), "cxxattn_peer_open")
+        return self
+
+    def close(self):
+        if self.ptr and self.ptr.value:
+            import torch
+            with torch.cuda.device(self.device):
+                (lib().cxxattn_peer_free if self.owned else lib().cxxattn_peer_close)(self.ptr)
+            self.ptr = C.c_void_p()
+
+
+class _CudaArray:
+    """A byte range of device memory for torch.as_tensor (the CUDA array interface); keeps its owner alive."""
+
+    def __init__(self, ptr, nbytes, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
 def selftest_wait_limit(limit_ns):

@@ -313,6 +313,24 @@ int cxxattn_adamw_step_mixed(float* param, const void* grad_bf16, float* m, floa
                        step, grad_norm_sq, static_cast<cudaStream_t>(stream));
 }
 
+int cxxattn_adamw_step_exchange(float* param_shard, float* m_shard, float* v_shard, const void* const* grads,
+                                void* const* params, int dtype, int world, int rank, size_t lo, size_t count,
+                                float grad_scale, float lr, float beta1, float beta2, float weight_decay, float eps,
+                                int step, float* grad_norm_sq, cxxattn_stream_t stream) {
+    if (!grads || !params || (count != 0 && (!param_shard || !m_shard || !v_shard)) || step < 1 ||
+        !(beta1 >= 0.f && beta1 < 1.f) || !(beta2 >= 0.f && beta2 < 1.f) || !(eps > 0.f) ||
+        (dtype != CXXATTN_F32 && dtype != CXXATTN_BF16))
+        return CXXATTN_ERR_INVALID;
+    return adamw_exchange(param_shard, m_shard, v_shard, grads, params, dtype, world, rank, lo, count, grad_scale, lr,
+                          beta1, beta2, weight_decay, eps, step, grad_norm_sq, static_cast<cudaStream_t>(stream));
+}
+
+int cxxattn_peer_alloc(size_t bytes, void** ptr) { return peer_alloc(bytes, ptr); }
+int cxxattn_peer_free(void* ptr) { return ptr ? peer_free(ptr) : CXXATTN_OK; }
+int cxxattn_peer_export(const void* ptr, unsigned char handle[CXXATTN_PEER_HANDLE_BYTES]) { return peer_export(ptr, handle); }
+int cxxattn_peer_open(const unsigned char handle[CXXATTN_PEER_HANDLE_BYTES], void** ptr) { return peer_open(handle, ptr); }
+int cxxattn_peer_close(void* ptr) { return ptr ? peer_close(ptr) : CXXATTN_OK; }
+
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream) {
     if (!A || !C || n == 0) return CXXATTN_ERR_INVALID;
     return gelu_exact(A, C, n, deriv != 0, static_cast<cudaStream_t>(stream));

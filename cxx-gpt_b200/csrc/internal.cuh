@@ -126,6 +126,15 @@ int mha_decode_step(const cxxattn_mha_desc& d, const float* q, const float* k, c
 int adamw_fused(float* param, const void* grad, int grad_dtype, float* m, float* v, void* param_copy, size_t n,
                 float grad_scale, float lr, float beta1, float beta2, float wd, float eps, int step, float* norm_sq,
                 cudaStream_t st);
+// ---- gradient exchange + optimiser step over peer memory (adamw_exchange.cu) ----
+int adamw_exchange(float* param_shard, float* m_shard, float* v_shard, const void* const* grads, void* const* copies,
+                   int dtype, int world, int rank, size_t lo, size_t count, float grad_scale, float lr, float beta1,
+                   float beta2, float wd, float eps, int step, float* norm_sq, cudaStream_t st);
+int peer_alloc(size_t bytes, void** ptr);
+int peer_free(void* ptr);
+int peer_export(const void* ptr, unsigned char* handle);
+int peer_open(const unsigned char* handle, void** ptr);
+int peer_close(void* ptr);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
 

@@ -20,7 +20,12 @@ What runs where:
     the backward pass of a bucket of it, `torch.distributed.all_reduce` (NCCL, sum) is started on
     that bucket while the rest of the backward pass runs; the kernel after the collective,
     cxxattn_adamw_step, turns the sum into the mean, applies AdamW as the reference's optimiser
-    does (src/GPT/gpt_cuda_kernels.cu:488-501) and accumulates the gradient norm, in one pass.
+    does (src/GPT/gpt_cuda_kernels.cu:488-501) and accumulates the gradient norm, in one pass;
+  * or (`exchange="peer"`, one process per GPU of one machine) exchange and optimiser are ONE kernel over
+    peer memory, cxxattn_adamw_step_exchange: every rank owns a contiguous shard of the flat buffers,
+    reads all ranks' gradients of it over NVLink, keeps master parameters and moments for the shard only
+    and writes the updated parameters into every rank's buffer; two one-element all-reduces order it
+    against the backward pass before and the forward pass after.
 
 There is no CPU path in the product: `CudaKernels` refuses to run without a CUDA device.  The model
 code takes the kernel set as an argument so that the multi-rank host logic (bucketing, the
@@ -82,6 +87,18 @@ class CudaKernels:
     def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq, param_copy=None):
         self.pkg.adamw_step(param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq,
                             param_copy=param_copy)
+
+    def peer_buffer(self, numel, dtype, device):
+        """A zeroed flat buffer that the other ranks' GPUs can map."""
+        return self.pkg.PeerBuffer(numel, dtype, device)
+
+    def open_peer(self, handle, numel, dtype, device):
+        return self.pkg.PeerBuffer.open(handle, numel, dtype, device)
+
+    def adamw_exchange(self, param_shard, m_shard, v_shard, grad_ptrs, param_ptrs, dtype, rank, lo, step, lr, beta1,
+                       beta2, weight_decay, eps, grad_scale, norm_sq):
+        self.pkg.adamw_step_exchange(param_shard, m_shard, v_shard, grad_ptrs, param_ptrs, dtype, rank, lo, step, lr,
+                                     beta1, beta2, weight_decay, eps, grad_scale, norm_sq)
 
 
 class _RopeCast(torch.autograd.Function):
@@ -163,9 +180,10 @@ class HybridGPT:
     views of an fp32 gradient buffer.  bf16 compute (mixed precision): the fp32 buffer is the optimiser's
     master copy; the leaves are views of a bf16 working copy that the optimiser kernel rewrites in the pass
     that updates the master, and the gradient buffer is bf16 too (half the bytes through the all-reduce, no
-    per-layer conversions in either pass)."""
+    per-layer conversions in either pass).  `peer`: the buffer the passes read and the gradient buffer are
+    allocated so that the other ranks' GPUs can map them (DataParallelStep with exchange="peer")."""
 
-    def __init__(self, cfg, kernels, device, seed=0):
+    def __init__(self, cfg, kernels, device, seed=0, peer=False):
         self.cfg, self.kernels, self.device = cfg, kernels, device
         table = parameter_table(cfg)
         self.offsets, off = {}, 0
@@ -175,7 +193,13 @@ class HybridGPT:
             off += (n + 7) // 8 * 8  # every view starts on a 16-byte boundary, in bf16 too
         self.numel = off
         self.mixed = cfg.compute_dtype == torch.bfloat16
-        self.flat_param = torch.zeros(off, dtype=torch.float32, device=device)
+        work_dtype = torch.bfloat16 if self.mixed else torch.float32
+        self.peer = None
+        if peer:
+            self.peer = {"work": kernels.peer_buffer(off, work_dtype, device),
+                         "grad": kernels.peer_buffer(off, work_dtype, device)}
+        self.flat_param = self.peer["work"].tensor if peer and not self.mixed else \
+            torch.zeros(off, dtype=torch.float32, device=device)
         g = torch.Generator(device="cpu").manual_seed(seed)
         for name, shape, std in table:
             o, n, _ = self.offsets[name]
@@ -184,8 +208,14 @@ class HybridGPT:
                 view.fill_(1.0)
             elif std > 0:
                 view.copy_((torch.randn(shape, generator=g) * std).to(device))
-        self.flat_work = self.flat_param.to(torch.bfloat16) if self.mixed else self.flat_param
-        self.flat_grad = torch.zeros_like(self.flat_work)
+        if not self.mixed:
+            self.flat_work = self.flat_param
+        elif peer:
+            self.flat_work = self.peer["work"].tensor
+            self.flat_work.copy_(self.flat_param)
+        else:
+            self.flat_work = self.flat_param.to(torch.bfloat16)
+        self.flat_grad = self.peer["grad"].tensor if peer else torch.zeros_like(self.flat_work)
         self.p = {}
         for name, shape, _ in table:
             o, n, _ = self.offsets[name]
@@ -237,21 +267,33 @@ class HybridGPT:
 class DataParallelStep:
     """One optimiser step per call: forward, backward with the bucketed gradient all-reduce started from
     autograd hooks, then the fused mean + AdamW + gradient-norm kernel.  `group` None = the default
-    process group when torch.distributed is initialised, else a single rank."""
+    process group when torch.distributed is initialised, else a single rank.
+
+    exchange="nccl": as above.  exchange="peer" (the model built with peer=True; all ranks on one machine):
+    no all-reduce of gradients; after the backward pass a one-element all-reduce tells every rank that all
+    gradients are final, cxxattn_adamw_step_exchange updates this rank's shard from all ranks' gradients and
+    writes it into all ranks' parameter buffers, and the all-reduce of the partial squared norms tells every
+    rank that its parameters are complete.  Master parameters and moments exist for the shard only
+    (`gather_master()` collects the fp32 master of all shards)."""
 
     def __init__(self, model, lr=1e-3, beta1=0.9, beta2=0.999, weight_decay=0.01, eps=1e-8, n_buckets=4, group=None,
-                 cuda_graph=False):
-        self.model, self.group = model, group
+                 cuda_graph=False, exchange="nccl"):
+        assert exchange in ("nccl", "peer")
+        self.model, self.group, self.exchange = model, group, exchange
         # cuda_graph: after three eager steps, forward + backward (+ the all-reduces) of a fixed batch
         # shape are captured once and replayed; the step is a few thousand short launches, and issuing
         # them from Python costs more time than the GPU needs to run them
         self.cuda_graph, self.graph, self.eager_steps = cuda_graph, None, 0
         self.hp = (lr, beta1, beta2, weight_decay, eps)
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
-        self.m = torch.zeros_like(model.flat_param)
-        self.v = torch.zeros_like(model.flat_param)
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=model.device)
         self.t = 0
+        if exchange == "peer":
+            self._setup_peers()
+        else:
+            self.m = torch.zeros_like(model.flat_param)
+            self.v = torch.zeros_like(model.flat_param)
         # Buckets are contiguous ranges of the flat buffer, cut at parameter borders into roughly equal
         # parts.  The backward pass finishes gradients from the end of the buffer towards its start, so
         # the last bucket is ready first.
@@ -276,10 +318,64 @@ class DataParallelStep:
         # has finished the bucket.  With CUDA-graph replay the collectives stay outside the graph (a
         # captured NCCL call did not complete on this platform): the buckets are reduced after the
         # replay, last bucket first, and the optimiser kernel follows.
-        self.reduce_in_hooks = self.world > 1 and not cuda_graph
+        self.reduce_in_hooks = self.world > 1 and not cuda_graph and exchange == "nccl"
         if self.reduce_in_hooks:
             for name in names:
                 model.p[name].register_post_accumulate_grad_hook(self._make_hook(name))
+
+    def _setup_peers(self):
+        """Shard bounds, shard-sized moments, and the addresses of every rank's gradient and parameter
+        buffers as this rank's GPU sees them (CUDA IPC handles exchanged once through the process group)."""
+        model, world, rank = self.model, self.world, self.rank
+        if model.peer is None:
+            raise ValueError('exchange="peer" needs a model built with peer=True')
+        per = (model.numel // 8 + world - 1) // world * 8  # numel is a multiple of 8 by construction
+        self.lo = min(model.numel, rank * per)
+        self.hi = min(model.numel, self.lo + per)
+        self.shard_len = per
+        n = self.hi - self.lo
+        # the fp32 master of the shard: a view of the parameter buffer in fp32 compute (which the exchange
+        # kernel then also fills for the other shards), a buffer of its own in mixed precision
+        self.master = model.flat_param[self.lo:self.hi] if not model.mixed else model.flat_param[self.lo:self.hi].clone()
+        self.m = torch.zeros(n, dtype=torch.float32, device=model.device)
+        self.v = torch.zeros(n, dtype=torch.float32, device=model.device)
+        self.sync = torch.zeros(1, dtype=torch.float32, device=model.device)
+        mine = (model.peer["work"].handle(), model.peer["grad"].handle())
+        handles = [mine]
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=self.group)
+        dtype = model.flat_work.dtype
+        self.opened, self.param_ptrs, self.grad_ptrs = [], [], []
+        for r in range(world):
+            if r == rank:
+                self.param_ptrs.append(model.peer["work"].ptr.value)
+                self.grad_ptrs.append(model.peer["grad"].ptr.value)
+            else:
+                w = model.kernels.open_peer(handles[r][0], model.numel, dtype, model.device)
+                g = model.kernels.open_peer(handles[r][1], model.numel, dtype, model.device)
+                self.opened += [w, g]
+                self.param_ptrs.append(w.ptr.value)
+                self.grad_ptrs.append(g.ptr.value)
+
+    def close(self):
+        """Unmaps the other ranks' buffers (collective in spirit: call it on every rank before the buffers go)."""
+        for b in getattr(self, "opened", []):
+            b.close()
+        self.opened = []
+
+    def gather_master(self):
+        """The fp32 master parameters of all shards as one flat tensor (every rank gets all of it)."""
+        model = self.model
+        if self.exchange != "peer":
+            return model.flat_param.clone()
+        mine = torch.zeros(self.shard_len, dtype=torch.float32, device=model.device)
+        mine[:self.hi - self.lo] = self.master
+        if self.world == 1:
+            return mine[:model.numel].clone()
+        out = torch.empty(self.shard_len * self.world, dtype=torch.float32, device=model.device)
+        dist.all_gather_into_tensor(out, mine, group=self.group)
+        return out[:model.numel].clone()
 
     def _make_hook(self, name):
         b = self.bucket_of[name]
@@ -322,14 +418,24 @@ class DataParallelStep:
             self.eager_steps += 1
             if self.cuda_graph and self.eager_steps == 3:
                 self._capture(idx, targets)  # the captured pass only records; this step's gradients stand
+        self.t += 1
+        self.norm_sq.zero_()
+        lr, b1, b2, wd, eps = self.hp
+        if self.exchange == "peer":
+            with torch.no_grad():
+                if self.world > 1:
+                    dist.all_reduce(self.sync, group=self.group)  # every rank's gradients are final
+                model.kernels.adamw_exchange(self.master, self.m, self.v, self.grad_ptrs, self.param_ptrs,
+                                             model.flat_work.dtype, self.rank, self.lo, self.t, lr, b1, b2, wd, eps,
+                                             1.0 / self.world, self.norm_sq)
+                if self.world > 1:  # the shards' shares of the norm; and: every rank's parameters are complete
+                    dist.all_reduce(self.norm_sq, group=self.group)
+            return loss, self.norm_sq
         if self.world > 1 and not self.reduce_in_hooks:
             works = [dist.all_reduce(model.flat_grad[b["lo"]:b["hi"]], op=dist.ReduceOp.SUM, group=self.group,
                                      async_op=True) for b in reversed(self.buckets)]
             for w in works:
                 w.wait()
-        self.t += 1
-        self.norm_sq.zero_()
-        lr, b1, b2, wd, eps = self.hp
         with torch.no_grad():
             model.kernels.adamw(model.flat_param, model.flat_grad, self.m, self.v, self.t, lr, b1, b2, wd, eps,
                                 1.0 / self.world, self.norm_sq, model.flat_work if model.mixed else None)

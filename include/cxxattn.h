@@ -243,6 +243,36 @@ int cxxattn_adamw_step_mixed(float* param, const void* grad_bf16, float* m, floa
                              float grad_scale, float lr, float beta1, float beta2, float weight_decay, float eps,
                              int step, float* grad_norm_sq, cxxattn_stream_t stream);
 
+/* The gradient exchange and the optimiser step of `world` data-parallel ranks (one process per GPU) as
+ * one kernel over peer memory, in place of an all-reduce followed by cxxattn_adamw_step[_mixed].  Rank
+ * `rank` owns elements [lo, lo + count) of the flat buffers (multiples of 8 elements for CXXATTN_BF16,
+ * of 4 for CXXATTN_F32; count may be 0).  grads[r] / params[r], r = 0..world-1 (at most 16), are device
+ * addresses, valid on the calling rank's GPU, of rank r's whole gradient buffer and of the whole
+ * parameter buffer its forward pass reads, both of `dtype` (16-byte aligned; the calling rank's own
+ * buffers by their local address, the others' as mapped by cxxattn_peer_open).  The kernel sums the
+ * ranks' gradients of the shard in fp32, applies grad_scale (1/world) and AdamW as above to the fp32
+ * master parameters and moments of the shard (param_shard, m_shard, v_shard: `count` floats each), and
+ * writes the updated values as `dtype` into params[r] of every rank.  grad_norm_sq receives the shard's
+ * share of the squared gradient norm (added).  The caller orders the call between two barriers over the
+ * ranks: after every rank's gradients are final, and before any rank reads its parameters again.  The
+ * kernel itself waits for nothing and uses plain loads and stores.  The reference trains on one GPU and
+ * has no counterpart. */
+int cxxattn_adamw_step_exchange(float* param_shard, float* m_shard, float* v_shard, const void* const* grads,
+                                void* const* params, int dtype, int world, int rank, size_t lo, size_t count,
+                                float grad_scale, float lr, float beta1, float beta2, float weight_decay, float eps,
+                                int step, float* grad_norm_sq, cxxattn_stream_t stream);
+
+/* Device buffers that other processes' GPUs of the same machine can map (CUDA IPC): _alloc / _free own
+ * the memory, _export fills the handle another process passes to _open, which returns the address the
+ * buffer has in the opening process (peer access is enabled as needed); _close unmaps it.  A handle
+ * cannot be opened by the process that exported it. */
+#define CXXATTN_PEER_HANDLE_BYTES 64
+int cxxattn_peer_alloc(size_t bytes, void** ptr);
+int cxxattn_peer_free(void* ptr);
+int cxxattn_peer_export(const void* ptr, unsigned char handle[CXXATTN_PEER_HANDLE_BYTES]);
+int cxxattn_peer_open(const unsigned char handle[CXXATTN_PEER_HANDLE_BYTES], void** ptr);
+int cxxattn_peer_close(void* ptr);
+
 /* ---- host-buffer entry points ------------------------------------------------------------- */
 
 /* Softmax MHA forward + backward on HOST tensors in the reference layout (what kernel_test.cpp

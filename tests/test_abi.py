@@ -81,6 +81,26 @@ def test_bad_arguments_are_rejected_without_a_device(pkg):
     assert lib.cxxattn_lin_host_plan_create(C.byref(plan), C.byref(pkg.lin_desc(0, 8, 4, 4)), 1) == -1
     assert lib.cxxattn_linattn_fwd_bwd_host(None, one, one, one, one, one, one, one, one, one) == -1
     assert lib.cxxattn_selftest_wait_limit(10, None) == -1            # below the smallest limit
+    # exchange + optimiser step: rank set, shard bounds and pointers are checked before any launch
+    two = (C.c_void_p * 2)(16, 32)
+    f = [1.0, 1e-3, 0.9, 0.999, 0.01, 1e-8]
+    ex = lib.cxxattn_adamw_step_exchange
+    assert ex(one, one, one, two, two, pkg.BF16, 0, 0, 0, 8, *f, 1, None, None) == -1    # no ranks
+    assert ex(one, one, one, two, two, pkg.BF16, 17, 0, 0, 8, *f, 1, None, None) == -1   # more than 16
+    assert ex(one, one, one, two, two, pkg.BF16, 2, 2, 0, 8, *f, 1, None, None) == -1    # rank outside the set
+    assert ex(one, one, one, two, two, pkg.BF16, 2, 0, 4, 8, *f, 1, None, None) == -1    # bf16 shard not on 8 elements
+    assert ex(one, one, one, two, two, pkg.F32, 2, 0, 4, 6, *f, 1, None, None) == -1     # fp32 shard not on 4 elements
+    assert ex(one, one, one, two, two, 9, 2, 0, 0, 8, *f, 1, None, None) == -1           # unknown dtype
+    assert ex(one, one, one, two, two, pkg.BF16, 2, 0, 0, 8, *f, 0, None, None) == -1    # steps count from 1
+    assert ex(None, one, one, two, two, pkg.BF16, 2, 0, 0, 8, *f, 1, None, None) == -1
+    assert ex(one, one, one, (C.c_void_p * 2)(16, None), two, pkg.BF16, 2, 0, 0, 8, *f, 1, None, None) == -1
+    assert ex(one, one, one, (C.c_void_p * 2)(16, 36), two, pkg.BF16, 2, 0, 0, 8, *f, 1, None, None) == -6  # alignment
+    assert ex(None, None, None, two, two, pkg.BF16, 2, 1, 8, 0, *f, 1, None, None) == 0  # a rank that owns nothing
+    p = C.c_void_p()
+    assert lib.cxxattn_peer_alloc(0, C.byref(p)) == -1 and lib.cxxattn_peer_alloc(16, None) == -1
+    assert lib.cxxattn_peer_export(None, C.create_string_buffer(64)) == -1
+    assert lib.cxxattn_peer_open(None, C.byref(p)) == -1
+    assert lib.cxxattn_peer_free(None) == 0 and lib.cxxattn_peer_close(None) == 0
 
 
 def test_options_are_validated_and_readable(pkg):

@@ -156,6 +156,170 @@ def test_nccl_ranks_follow_the_single_rank_loss_curve(pkg, dev, tmp_path):
     assert rel_err(got["param"].numpy(), model.flat_param.cpu().numpy()) < 1e-4
 
 
+@pytest.mark.parametrize("world,dtype", [(1, torch.bfloat16), (2, torch.bfloat16), (4, torch.bfloat16),
+                                         (8, torch.bfloat16), (3, torch.float32), (16, torch.float32)])
+def test_exchange_step_on_emulated_ranks_is_mean_then_adamw(pkg, dev, world, dtype):
+    """cxxattn_adamw_step_exchange with every rank's buffers on ONE GPU and the ranks' calls made in turn (the
+    kernel waits for nothing, so that is a faithful run of the multi-GPU data flow): afterwards every rank's
+    parameter buffer holds the same bits, the masters follow the fp64 restatement of mean + AdamW, and the
+    ranks' norm shares add up."""
+    n = 8 * 12_347
+    mixed = dtype == torch.bfloat16
+    g = torch.Generator().manual_seed(world)
+    param0 = torch.randn(n, generator=g)
+    per = (n // 8 + world - 1) // world * 8
+    bounds = [(min(n, r * per), min(n, r * per + per)) for r in range(world)]
+    copies = [(param0.to(dtype)).to(dev) for _ in range(world)]
+    masters = [param0[lo:hi].clone().to(dev) if mixed else copies[r][lo:hi] for r, (lo, hi) in enumerate(bounds)]
+    m0, v0 = torch.randn(n, generator=g) * 0.1, torch.rand(n, generator=g) * 0.1
+    ms = [m0[lo:hi].clone().to(dev) for lo, hi in bounds]
+    vs = [v0[lo:hi].clone().to(dev) for lo, hi in bounds]
+    want = [param0.clone().double(), None, m0.double(), v0.double()]
+    nsq_want = torch.zeros(1, dtype=torch.float64)
+    for step in (1, 2, 3):
+        grads = [(torch.randn(n, generator=g) * (1 + r)).to(dtype) for r in range(world)]
+        dgrads = [x.to(dev) for x in grads]
+        want[1] = sum(x.double() for x in grads)
+        nsq_want.zero_()
+        reference_adamw(want[0], want[1], want[2], want[3], step, 1e-3, 0.9, 0.999, 0.01, 1e-8, 1.0 / world, nsq_want)
+        shares = []
+        for r, (lo, hi) in enumerate(bounds):
+            nsq = torch.zeros(1, device=dev)
+            pkg.adamw_step_exchange(masters[r], ms[r], vs[r], [x.data_ptr() for x in dgrads],
+                                    [x.data_ptr() for x in copies], dtype, r, lo, step, 1e-3,
+                                    grad_scale=1.0 / world, grad_norm_sq=nsq)
+            shares.append(nsq)
+        torch.cuda.synchronize()
+        for x, y in zip(dgrads, grads):
+            assert torch.equal(x.cpu(), y)  # gradients are read only
+        for r in range(1, world):
+            assert torch.equal(copies[0], copies[r]), (step, r)
+        master = torch.cat([x.float() for x in masters]).cpu()
+        assert rel_err(master.numpy(), want[0].numpy()) < 1e-5, step
+        if mixed:
+            assert torch.equal(copies[0].cpu(), master.bfloat16())
+        assert abs(sum(float(x) for x in shares) - float(nsq_want)) < 1e-5 * float(nsq_want)
+    assert rel_err(torch.cat(ms).cpu().numpy(), want[2].numpy()) < 1e-5
+    assert rel_err(torch.cat(vs).cpu().numpy(), want[3].numpy()) < 1e-5
+
+
+def test_peer_buffer_is_a_zeroed_torch_view_with_an_exportable_handle(pkg, dev):
+    buf = pkg.PeerBuffer(1000, torch.bfloat16, dev)
+    assert buf.tensor.dtype == torch.bfloat16 and buf.tensor.numel() == 1000 and buf.tensor.data_ptr() == buf.ptr.value
+    assert float(buf.tensor.float().abs().sum()) == 0.0
+    buf.tensor.fill_(1.5)
+    assert float(buf.tensor.float().sum()) == 1500.0
+    h = buf.handle()
+    assert len(h) == 64 and any(h)
+    del buf.tensor
+    buf.close()
+    buf.close()  # idempotent
+
+
+def _peer_rank(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    hy = load_hybrid()
+    result = {}
+    # (a) fp32 compute on the exact kernels, eager: against one rank on the whole batch
+    cfg = hy.HybridConfig(vocab_size=50, block_size=32, n_embd=64, n_head=2, n_layer=2, compute_dtype=torch.float32)
+    model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=13, peer=True)
+    step = hy.DataParallelStep(model, lr=1e-2, exchange="peer")
+    idx, tgt = make_batch(17, 2 * world, 24, 50)
+    lo, hi = 2 * rank, 2 * rank + 2
+    losses = []
+    for _ in range(5):
+        loss, _ = step.step(idx[lo:hi].to(dev), tgt[lo:hi].to(dev))
+        t = loss.clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / world)
+    result.update(losses=losses, param=step.gather_master().cpu(), work=model.flat_work.cpu())
+    step.close()
+    # (b) mixed precision with graph replay: the peer exchange against the NCCL all-reduce on the same batches
+    cfg = hy.HybridConfig(vocab_size=50, block_size=32, n_embd=128, n_head=2, n_layer=2)
+    curves, norms = {}, {}
+    for mode in ("nccl", "peer"):
+        model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=5, peer=mode == "peer")
+        step = hy.DataParallelStep(model, lr=1e-2, cuda_graph=True, exchange=mode)
+        curves[mode], norms[mode] = [], []
+        for i in range(7):
+            idx, tgt = make_batch(100 + i, 2 * world, 24, 50)
+            loss, nsq = step.step(idx[lo:hi].to(dev), tgt[lo:hi].to(dev))
+            t = loss.clone()
+            dist.all_reduce(t)
+            curves[mode].append(float(t) / world)
+            norms[mode].append(float(nsq))
+        assert step.graph is not None
+        if mode == "peer":
+            # every rank reads the same parameter bits
+            mine = model.flat_work.view(torch.int16).to(torch.int64)
+            both = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(both, mine)
+            result["same_bits"] = all(torch.equal(both[0], b) for b in both)
+            step.close()
+    pkg.sync_status()
+    result.update(curves=curves, norms=norms)
+    dist.barrier()
+    if rank == 0:
+        torch.save(result, out)
+    dist.destroy_process_group()
+
+
+def test_peer_exchange_ranks_follow_the_single_rank_loss_curve(pkg, dev, tmp_path):
+    """Two ranks, one process per GPU, with the exchange + optimiser kernel over peer memory in place of the
+    all-reduce: fp32 compute gives one rank's loss curve and parameters on the whole batch; in mixed precision
+    with graph replay it follows the NCCL variant, and all ranks hold the same parameter bits."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "peer.pt")
+    mp.spawn(_peer_rank, args=(2, 29533, out), nprocs=2, join=True)
+    got = torch.load(out)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        hy = load_hybrid()
+        cfg = hy.HybridConfig(vocab_size=50, block_size=32, n_embd=64, n_head=2, n_layer=2, compute_dtype=torch.float32)
+        model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=13)
+        step = hy.DataParallelStep(model, lr=1e-2)
+        idx, tgt = make_batch(17, 4, 24, 50)
+        losses = [float(step.step(idx.to(dev), tgt.to(dev))[0]) for _ in range(5)]
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    assert np.allclose(got["losses"], losses, rtol=1e-5), (got["losses"], losses)
+    assert rel_err(got["param"].numpy(), model.flat_param.cpu().numpy()) < 1e-4
+    assert torch.equal(got["work"], got["param"])  # fp32 compute: the buffer the passes read IS the master
+    assert got["same_bits"]
+    assert np.allclose(got["curves"]["peer"], got["curves"]["nccl"], rtol=2e-2), got["curves"]
+    assert np.allclose(got["norms"]["peer"], got["norms"]["nccl"], rtol=5e-2), got["norms"]
+
+
+def test_peer_exchange_on_one_rank_equals_the_plain_step(pkg, dev):
+    """world = 1: the exchange kernel reads and writes only this rank's buffers and must give the plain step."""
+    hy = load_hybrid()
+    cfg = hy.HybridConfig(vocab_size=50, block_size=32, n_embd=128, n_head=2, n_layer=2)
+    batches = [tuple(t.to(dev) for t in make_batch(60 + i, 2, 24, 50)) for i in range(5)]
+    curves, works = [], []
+    for mode in ("nccl", "peer"):
+        model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=8, peer=mode == "peer")
+        step = hy.DataParallelStep(model, lr=1e-2, exchange=mode)
+        curves.append([float(step.step(i, t)[0]) for i, t in batches])
+        works.append(model.flat_work.clone())
+        master = step.gather_master()
+        assert torch.equal(master.bfloat16(), model.flat_work)
+    torch.cuda.synchronize()
+    # the tensor-core backward sums dQ tiles in the order they arrive, so two runs agree to rounding, not in bits
+    assert np.allclose(curves[0], curves[1], rtol=1e-3), curves
+    assert rel_err(works[1].float().cpu().numpy(), works[0].float().cpu().numpy()) < 2e-2
+
+
 def test_cuda_graph_replay_follows_the_eager_steps(pkg, dev):
     """Forward + backward captured in a CUDA graph after three eager steps and replayed give the loss
     curve of launching every kernel (fp32 compute on the exact kernels, which are deterministic)."""
