@@ -647,7 +647,7 @@ def run_dp_step(args):
     e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
     # the optimiser kernel alone.  After an all-reduce it is HBM-bound, 28 bytes per parameter.  The exchange
     # kernel is timed between barriers on all ranks at once (its loads and stores cross NVLink while the
-    # other ranks' do): (world-1)/world of the gradient bytes come in and as many parameter bytes go out.
+    # other ranks' do).
     oe = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     opt_ms = 0.0
@@ -684,9 +684,11 @@ def run_dp_step(args):
                 "launch_ms": opt_ms, "achieved": gbs, "peak": hbm, "peak_source": how, "unit": "GB/s",
                 "frac": gbs / hbm, "traffic": None}
         if exchange == "peer" and world > 1:
-            # bytes that must cross NVLink per GPU and direction / the measured peer-copy bandwidth
+            # bytes that must cross NVLink per GPU and direction (the other ranks' gradients of the shard come
+            # in as load responses, the other shards' parameters as the peers' stores; as much goes out) / the
+            # measured peer-copy bandwidth
             item = model.flat_work.element_size()
-            link = (world - 1) / world * model.numel * item / (opt_ms * 1e-3) / 1e9
+            link = 2 * (world - 1) / world * model.numel * item / (opt_ms * 1e-3) / 1e9
             roof = {"bound": "nvlink", "kernel": "adamw_exchange_kernel (gradient exchange + AdamW over peer memory)",
                     "launch_ms": opt_ms, "achieved": link, "peak": 770.0,
                     "peak_source": "peer copy per direction measured on this pool", "unit": "GB/s",

@@ -9,12 +9,15 @@
 //     - writes the updated parameters, in the dtype the forward pass reads, into the parameter buffer of
 //       EVERY rank (its own included).
 //
-// So a step moves (world-1)/world of the gradient bytes into each GPU and the same amount of parameter
-// bytes out of it, once, where a ring all-reduce moves twice that and is followed by a full-size
-// optimiser pass on every rank.  The kernel does not wait for anything: the caller orders it after
-// "every rank's gradients are final" and before "every rank may read its parameters" with two
-// stream-ordered barriers (a one-element all-reduce each; the second one carries the partial squared
-// gradient norms).  Plain loads and stores only: no TMA, no multicast.
+// The link traffic is that of a reduce-scatter followed by an all-gather, i.e. of an all-reduce:
+// (world-1)/world of the gradient bytes come into each GPU as load responses and the same amount of
+// parameter bytes arrive as the peers' stores, and as much leaves it.  What the fusion removes is the
+// full-size optimiser pass on every rank (each rank updates 1/world of the parameters and keeps 1/world of
+// the master copy and moments), the gradient sum's round trip through memory, and all but one launch.
+// The kernel does not wait for anything: the caller orders it after "every rank's gradients are final"
+// and before "every rank may read its parameters" with two stream-ordered barriers (a one-element
+// all-reduce each; the second one carries the partial squared gradient norms).  Plain loads and stores
+// only: no TMA, no multicast.
 //
 // The buffers peers read and write are cudaMalloc allocations exported with CUDA IPC handles
 // (cxxattn_peer_*): one process per GPU opens the other ranks' handles once at start-up.
@@ -68,14 +71,23 @@ __global__ void __launch_bounds__(256) adamw_exchange_kernel(float* __restrict__
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
         const size_t e = lo + i * VEC;  // element index in the whole buffers
+        // every load of the pass is issued before the first use: the local master and moments, then the
+        // ranks' gradients in the order rank+1, rank+2, ..., rank (at any moment the ranks read from
+        // different peers), eight ranks to a batch
+        float p[VEC], mm[VEC], vv[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; k += 4) {
+            *reinterpret_cast<float4*>(&p[k]) = reinterpret_cast<const float4*>(param + i * VEC)[k / 4];
+            *reinterpret_cast<float4*>(&mm[k]) = reinterpret_cast<const float4*>(m + i * VEC)[k / 4];
+            *reinterpret_cast<float4*>(&vv[k]) = reinterpret_cast<const float4*>(v + i * VEC)[k / 4];
+        }
         float g[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; k++) g[k] = 0.f;
-        // the ranks in the order rank+1, rank+2, ..., rank: at any moment the ranks read from different peers
-        for (int q0 = 0; q0 < a.world; q0 += 4) {
-            uint4 raw[4];
+        for (int q0 = 0; q0 < a.world; q0 += 8) {
+            uint4 raw[8];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 8; j++) {
                 const int q = q0 + j;
                 if (q < a.world) {
                     int src = a.rank + 1 + q;
@@ -84,7 +96,7 @@ __global__ void __launch_bounds__(256) adamw_exchange_kernel(float* __restrict__
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 8; j++) {
                 if (q0 + j < a.world) {
                     if constexpr (BF16) {
                         add_bf16x8(g, raw[j]);
@@ -96,13 +108,6 @@ __global__ void __launch_bounds__(256) adamw_exchange_kernel(float* __restrict__
                     }
                 }
             }
-        }
-        float p[VEC], mm[VEC], vv[VEC];
-#pragma unroll
-        for (int k = 0; k < VEC; k += 4) {
-            *reinterpret_cast<float4*>(&p[k]) = reinterpret_cast<const float4*>(param + i * VEC)[k / 4];
-            *reinterpret_cast<float4*>(&mm[k]) = reinterpret_cast<const float4*>(m + i * VEC)[k / 4];
-            *reinterpret_cast<float4*>(&vv[k]) = reinterpret_cast<const float4*>(v + i * VEC)[k / 4];
         }
 #pragma unroll
         for (int k = 0; k < VEC; k++) accn += adam_one(p[k], g[k], mm[k], vv[k], a);
