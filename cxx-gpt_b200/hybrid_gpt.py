@@ -153,6 +153,31 @@ class _LinearStage(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+class _Linear(torch.autograd.Function):
+    """y = x W^T (+ b) whose backward pass writes dW and db straight into the parameters' views of the flat
+    gradient buffer.  Left to the autograd engine, each would be produced in a temporary and then added into
+    its view by one more launch per parameter (some 220 launches of a few microseconds per step)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, model, name):
+        ctx.save_for_backward(x, w)
+        ctx.model, ctx.name, ctx.has_bias = model, name, b is not None
+        return F.linear(x, w, b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        model, name = ctx.model, ctx.name
+        dy = dy.contiguous()
+        dx = dy @ w
+        torch.mm(dy.t(), x, out=model.p[name + ".w"].grad)
+        model.grad_ready(name + ".w")
+        if ctx.has_bias:
+            torch.sum(dy, 0, out=model.p[name + ".b"].grad)
+            model.grad_ready(name + ".b")
+        return dx, None, None, None, None
+
+
 def parameter_table(cfg):
     """(name, shape, init std or None for ones / 0.0 for zeros) in the order the forward pass uses them,
     which is the reverse of the order in which the backward pass finishes their gradients."""
@@ -224,16 +249,27 @@ class HybridGPT:
             view.grad = self.flat_grad[o:o + n].view(shape)  # autograd accumulates into the flat buffer in place
             self.p[name] = view
         self.order = [name for name, _, _ in table]
+        # parameters whose gradient the backward pass of `_Linear` writes in place
+        self.direct_grad = {name for name in self.order
+                            if name.startswith("h") and name.split(".")[1] in
+                            ("attn_q", "attn_k", "attn_v", "lq_proj", "lk_proj", "lv_proj", "attn_proj", "mlp_fc", "mlp_proj")}
+        self.on_grad_ready = None
 
     def _linear(self, x, name, bias=True):
-        dt = x.dtype
-        w = self.p[name + ".w"].to(dt)
-        return F.linear(x, w, self.p[name + ".b"].to(dt) if bias else None)
+        return _Linear.apply(x, self.p[name + ".w"], self.p[name + ".b"] if bias else None, self, name)
+
+    def grad_ready(self, name):
+        """Called by backward passes that write a parameter's gradient themselves (`direct_grad`): the autograd
+        engine's post-accumulate hooks do not fire for those."""
+        if self.on_grad_ready is not None:
+            self.on_grad_ready(name)
 
     def _ln(self, x, name):
         E = self.cfg.n_embd
-        return F.layer_norm(x.float(), (E,), self.p[name + ".g"].float(), self.p[name + ".b"].float(),
-                            self.cfg.ln_eps).to(x.dtype)
+        g, b = self.p[name + ".g"], self.p[name + ".b"]
+        if x.dtype == g.dtype:  # one kernel each way; statistics are accumulated in fp32 inside it
+            return F.layer_norm(x, (E,), g, b, self.cfg.ln_eps)
+        return F.layer_norm(x.float(), (E,), g.float(), b.float(), self.cfg.ln_eps).to(x.dtype)
 
     def loss(self, idx, targets):
         """Mean next-token cross-entropy of logits = model(idx); idx, targets [B, S] int64."""
@@ -241,7 +277,7 @@ class HybridGPT:
         B, S = idx.shape
         E, H, Dh, dt = cfg.n_embd, cfg.n_head, cfg.head_dim, cfg.compute_dtype
         pos = torch.arange(S, device=idx.device)
-        h = (F.embedding(idx, self.p["wte"]).float() + F.embedding(pos, self.p["wpe"]).float()[None]).reshape(B * S, E).to(dt)
+        h = (F.embedding(idx, self.p["wte"]) + F.embedding(pos, self.p["wpe"])[None]).reshape(B * S, E).to(dt)
         for i in range(cfg.n_layer):
             p = f"h{i}."
             a = self._ln(h, p + "ln_1")
@@ -320,8 +356,11 @@ class DataParallelStep:
         # replay, last bucket first, and the optimiser kernel follows.
         self.reduce_in_hooks = self.world > 1 and not cuda_graph and exchange == "nccl"
         if self.reduce_in_hooks:
+            hooks = {name: self._make_hook(name) for name in names}
             for name in names:
-                model.p[name].register_post_accumulate_grad_hook(self._make_hook(name))
+                if name not in model.direct_grad:
+                    model.p[name].register_post_accumulate_grad_hook(hooks[name])
+            model.on_grad_ready = lambda name: hooks[name](None)
 
     def _setup_peers(self):
         """Shard bounds, shard-sized moments, and the addresses of every rank's gradient and parameter
