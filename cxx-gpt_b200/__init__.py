@@ -31,7 +31,7 @@ SYMBOLS = [
     "cxxattn_lin_host_plan_create", "cxxattn_lin_host_plan_destroy", "cxxattn_linattn_fwd_bwd_host",
     "cxxattn_set_option", "cxxattn_get_option", "cxxattn_selftest_wait_limit", "cxxattn_adamw_step",
     "cxxattn_adamw_step_mixed", "cxxattn_adamw_step_exchange",
-    "cxxattn_peer_alloc", "cxxattn_peer_free", "cxxattn_peer_export", "cxxattn_peer_open", "cxxattn_peer_close",
+    "cxxattn_colsum_workspace_bytes", "cxxattn_colsum", "cxxattn_peer_alloc", "cxxattn_peer_free", "cxxattn_peer_export", "cxxattn_peer_open", "cxxattn_peer_close",
 ]
 
 # cxxattn_set_option keys (include/cxxattn.h)
@@ -116,6 +116,9 @@ def lib():
         L.cxxattn_adamw_step_mixed.argtypes = [vp, vp, vp, vp, vp, sz, f32, f32, f32, f32, f32, f32, i32, vp, vp]
         L.cxxattn_adamw_step_exchange.argtypes = [vp, vp, vp, C.POINTER(vp), C.POINTER(vp), i32, i32, i32, sz, sz,
                                                   f32, f32, f32, f32, f32, f32, i32, vp, vp]
+        L.cxxattn_colsum_workspace_bytes.argtypes = [sz]
+        L.cxxattn_colsum_workspace_bytes.restype = sz
+        L.cxxattn_colsum.argtypes = [vp, i32, vp, sz, sz, vp, sz, vp]
         L.cxxattn_peer_alloc.argtypes = [sz, C.POINTER(vp)]
         L.cxxattn_peer_free.argtypes = [vp]
         L.cxxattn_peer_export.argtypes = [vp, C.c_char_p]
@@ -366,6 +369,18 @@ def adamw_step_exchange(param_shard, m_shard, v_shard, grad_ptrs, param_ptrs, dt
                                             param_shard.numel(), float(grad_scale), float(lr), float(beta1),
                                             float(beta2), float(weight_decay), float(eps), int(step),
                                             _ptr(grad_norm_sq), _stream()), "cxxattn_adamw_step_exchange")
+
+
+def colsum_workspace_bytes(cols):
+    return int(lib().cxxattn_colsum_workspace_bytes(int(cols)))
+
+
+def colsum(X, out, workspace):
+    """out[c] = sum over the rows of the 2-D tensor X (cxxattn_colsum); `workspace`: a uint8 tensor of at least
+    colsum_workspace_bytes(cols) bytes that was zero before its first use."""
+    rows, cols = X.shape
+    check(lib().cxxattn_colsum(_ptr(X), _dtype_code(X), _ptr(out), rows, cols, _ptr(workspace), workspace.numel(),
+                               _stream()), "cxxattn_colsum")
 
 
 class PeerBuffer:

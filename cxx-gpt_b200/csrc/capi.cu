@@ -325,6 +325,14 @@ int cxxattn_adamw_step_exchange(float* param_shard, float* m_shard, float* v_sha
                           beta1, beta2, weight_decay, eps, step, grad_norm_sq, static_cast<cudaStream_t>(stream));
 }
 
+size_t cxxattn_colsum_workspace_bytes(size_t cols) { return cols ? colsum_workspace(cols) : 0; }
+
+int cxxattn_colsum(const void* X, int dtype, void* out, size_t rows, size_t cols, void* workspace, size_t workspace_bytes,
+                   cxxattn_stream_t stream) {
+    if (!X || !out || rows == 0 || cols == 0 || (dtype != CXXATTN_F32 && dtype != CXXATTN_BF16)) return CXXATTN_ERR_INVALID;
+    return colsum(X, dtype, out, rows, cols, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 int cxxattn_peer_alloc(size_t bytes, void** ptr) { return peer_alloc(bytes, ptr); }
 int cxxattn_peer_free(void* ptr) { return ptr ? peer_free(ptr) : CXXATTN_OK; }
 int cxxattn_peer_export(const void* ptr, unsigned char handle[CXXATTN_PEER_HANDLE_BYTES]) { return peer_export(ptr, handle); }

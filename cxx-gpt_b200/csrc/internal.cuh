@@ -135,6 +135,9 @@ int peer_free(void* ptr);
 int peer_export(const void* ptr, unsigned char* handle);
 int peer_open(const unsigned char* handle, void** ptr);
 int peer_close(void* ptr);
+// ---- column sums (colsum.cu) ----
+size_t colsum_workspace(size_t cols);
+int colsum(const void* X, int dtype, void* out, size_t rows, size_t cols, void* ws, size_t ws_bytes, cudaStream_t st);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
 

@@ -56,6 +56,20 @@ class CudaKernels:
         if not torch.cuda.is_available():
             raise RuntimeError("the training step needs a CUDA device: there is no CPU path in the product")
         self.pkg = pkg
+        self.colsum_ws = {}  # per device: the zeroed workspace of cxxattn_colsum (it leaves it zeroed)
+
+    COLSUM_MAX_COLS = 1 << 16
+
+    def colsum(self, x, out):
+        """out[c] = sum of column c of the 2-D bf16 tensor x; False if the shape is not covered."""
+        if x.dtype != torch.bfloat16 or x.shape[1] % 8 or x.shape[1] > self.COLSUM_MAX_COLS or not x.is_contiguous():
+            return False
+        ws = self.colsum_ws.get(x.device)
+        if ws is None:
+            ws = torch.zeros(self.pkg.colsum_workspace_bytes(self.COLSUM_MAX_COLS), dtype=torch.uint8, device=x.device)
+            self.colsum_ws[x.device] = ws
+        self.pkg.colsum(x, out, ws)
+        return True
 
     def rope_cast(self, x, B, S, D, head_dim, sign, out_dtype):
         out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
@@ -173,7 +187,11 @@ class _Linear(torch.autograd.Function):
         torch.mm(dy.t(), x, out=model.p[name + ".w"].grad)
         model.grad_ready(name + ".w")
         if ctx.has_bias:
-            torch.sum(dy, 0, out=model.p[name + ".b"].grad)
+            gb = model.p[name + ".b"].grad
+            colsum = getattr(model.kernels, "colsum", None)
+            # bf16: one pass of the library's column-sum kernel; fp32 stays on torch's deterministic reduction
+            if colsum is None or not colsum(dy, gb):
+                torch.sum(dy, 0, out=gb)
             model.grad_ready(name + ".b")
         return dx, None, None, None, None
 

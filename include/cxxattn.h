@@ -262,6 +262,16 @@ int cxxattn_adamw_step_exchange(float* param_shard, float* m_shard, float* v_sha
                                 float grad_scale, float lr, float beta1, float beta2, float weight_decay, float eps,
                                 int step, float* grad_norm_sq, cxxattn_stream_t stream);
 
+/* Column sums out[c] = sum_r X[r][c] of a dense row-major matrix (rows x cols, CXXATTN_F32 or CXXATTN_BF16,
+ * cols a multiple of 4 / 8, X 16-byte aligned), accumulated in fp32: the bias gradient of a linear layer
+ * (TensorN::cuda::sum_axis(dout, 0) in the reference's Linear::backward, gpt_gpt.hpp:111).  `workspace`
+ * (cxxattn_colsum_workspace_bytes(cols), 16-byte aligned) must be all zero before the first call; every
+ * call leaves it all zero, so one buffer cleared once serves all later calls on the same stream (calls
+ * sharing a workspace must not overlap).  The order of the fp32 additions is not fixed. */
+size_t cxxattn_colsum_workspace_bytes(size_t cols);
+int cxxattn_colsum(const void* X, int dtype, void* out, size_t rows, size_t cols, void* workspace, size_t workspace_bytes,
+                   cxxattn_stream_t stream);
+
 /* Device buffers that other processes' GPUs of the same machine can map (CUDA IPC): _alloc / _free own
  * the memory, _export fills the handle another process passes to _open, which returns the address the
  * buffer has in the opening process (peer access is enabled as needed); _close unmaps it.  A handle

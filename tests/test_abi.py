@@ -96,6 +96,14 @@ def test_bad_arguments_are_rejected_without_a_device(pkg):
     assert ex(one, one, one, (C.c_void_p * 2)(16, None), two, pkg.BF16, 2, 0, 0, 8, *f, 1, None, None) == -1
     assert ex(one, one, one, (C.c_void_p * 2)(16, 36), two, pkg.BF16, 2, 0, 0, 8, *f, 1, None, None) == -6  # alignment
     assert ex(None, None, None, two, two, pkg.BF16, 2, 1, 8, 0, *f, 1, None, None) == 0  # a rank that owns nothing
+    # column sums
+    assert lib.cxxattn_colsum_workspace_bytes(0) == 0 and lib.cxxattn_colsum_workspace_bytes(768) >= 768 * 4
+    assert lib.cxxattn_colsum(None, pkg.BF16, one, 4, 8, one, 1 << 20, None) == -1
+    assert lib.cxxattn_colsum(one, pkg.BF16, one, 0, 8, one, 1 << 20, None) == -1
+    assert lib.cxxattn_colsum(one, 5, one, 4, 8, one, 1 << 20, None) == -1
+    assert lib.cxxattn_colsum(one, pkg.BF16, one, 4, 12, one, 1 << 20, None) == -2     # bf16 rows in 16-byte vectors
+    assert lib.cxxattn_colsum(one, pkg.BF16, one, 4, 8, one, 8, None) == -3            # workspace too small
+    assert lib.cxxattn_colsum(one, pkg.BF16, one, 4, 8, None, 0, None) == -3
     p = C.c_void_p()
     assert lib.cxxattn_peer_alloc(0, C.byref(p)) == -1 and lib.cxxattn_peer_alloc(16, None) == -1
     assert lib.cxxattn_peer_export(None, C.create_string_buffer(64)) == -1

@@ -203,6 +203,25 @@ def test_exchange_step_on_emulated_ranks_is_mean_then_adamw(pkg, dev, world, dty
     assert rel_err(torch.cat(vs).cpu().numpy(), want[3].numpy()) < 1e-5
 
 
+@pytest.mark.parametrize("rows,cols,dtype", [(2048, 768, torch.bfloat16), (2048, 3072, torch.bfloat16),
+                                             (1, 8, torch.bfloat16), (333, 200, torch.bfloat16), (100, 4, torch.float32),
+                                             (5000, 1028, torch.float32), (129, 65544, torch.bfloat16)])
+def test_column_sums_match_fp64_and_leave_the_workspace_zero(pkg, dev, rows, cols, dtype):
+    g = torch.Generator().manual_seed(rows + cols)
+    X = torch.randn(rows, cols, generator=g).to(dtype)
+    want = X.double().sum(0)
+    ws = torch.zeros(pkg.colsum_workspace_bytes(cols), dtype=torch.uint8, device=dev)
+    dX = X.to(dev)
+    for _ in range(3):  # the same workspace, never cleared again
+        out = torch.full((cols,), 7.0, dtype=dtype, device=dev)
+        pkg.colsum(dX, out, ws)
+        torch.cuda.synchronize()
+        tol = 2 ** -8 if dtype == torch.bfloat16 else 1e-6  # the output rounding; sums are fp32
+        assert rel_err(out.double().cpu().numpy(), want.numpy()) < tol
+        assert int(ws.count_nonzero()) == 0
+    assert torch.equal(dX.cpu(), X)
+
+
 def test_peer_buffer_is_a_zeroed_torch_view_with_an_exportable_handle(pkg, dev):
     buf = pkg.PeerBuffer(1000, torch.bfloat16, dev)
     assert buf.tensor.dtype == torch.bfloat16 and buf.tensor.numel() == 1000 and buf.tensor.data_ptr() == buf.ptr.value
