@@ -320,23 +320,41 @@ def test_peer_exchange_ranks_follow_the_single_rank_loss_curve(pkg, dev, tmp_pat
     assert np.allclose(got["norms"]["peer"], got["norms"]["nccl"], rtol=5e-2), got["norms"]
 
 
-def test_peer_exchange_on_one_rank_equals_the_plain_step(pkg, dev):
-    """world = 1: the exchange kernel reads and writes only this rank's buffers and must give the plain step."""
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_peer_exchange_on_one_rank_equals_the_plain_step(pkg, dev, dtype):
+    """world = 1: the exchange kernel reads and writes only this rank's buffers and must give the plain step.
+    fp32 compute runs on the exact kernels, which are deterministic: the two variants agree to rounding of the
+    optimiser arithmetic.  In bf16 the tensor-core backward sums dQ tiles in the order they arrive and AdamW
+    turns a last-bit difference of a tiny gradient into a different step, so single parameters may differ by a
+    step; the curves and the bulk of the parameters agree."""
     hy = load_hybrid()
-    cfg = hy.HybridConfig(vocab_size=50, block_size=32, n_embd=128, n_head=2, n_layer=2)
-    batches = [tuple(t.to(dev) for t in make_batch(60 + i, 2, 24, 50)) for i in range(5)]
+    mixed = dtype == torch.bfloat16
+    cfg = hy.HybridConfig(vocab_size=50, block_size=32, n_embd=128 if mixed else 64, n_head=2, n_layer=2, compute_dtype=dtype)
+    batches = [tuple(t.to(dev) for t in make_batch(60 + i, 2, 24, 50)) for i in range(2 if mixed else 5)]
     curves, works = [], []
-    for mode in ("nccl", "peer"):
-        model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=8, peer=mode == "peer")
-        step = hy.DataParallelStep(model, lr=1e-2, exchange=mode)
-        curves.append([float(step.step(i, t)[0]) for i, t in batches])
-        works.append(model.flat_work.clone())
-        master = step.gather_master()
-        assert torch.equal(master.bfloat16(), model.flat_work)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for mode in ("nccl", "peer"):
+            model = hy.HybridGPT(cfg, hy.CudaKernels(pkg), dev, seed=8, peer=mode == "peer")
+            step = hy.DataParallelStep(model, lr=1e-2, exchange=mode)
+            curves.append([float(step.step(i, t)[0]) for i, t in batches])
+            works.append(model.flat_work.float().cpu())
+            master = step.gather_master()
+            assert torch.equal(master.to(dtype), model.flat_work)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
     torch.cuda.synchronize()
-    # the tensor-core backward sums dQ tiles in the order they arrive, so two runs agree to rounding, not in bits
-    assert np.allclose(curves[0], curves[1], rtol=1e-3), curves
-    assert rel_err(works[1].float().cpu().numpy(), works[0].float().cpu().numpy()) < 2e-2
+    if mixed:
+        # after two steps of at most lr each, a parameter whose tiny gradient changed sign between the runs is
+        # up to 4 lr apart; they must be few
+        assert np.allclose(curves[0][:2], curves[1][:2], rtol=1e-3), curves
+        delta = (works[0] - works[1]).abs()
+        assert float(delta.max()) <= 4.2e-2, float(delta.max())
+        assert float((delta > 2e-3).float().mean()) < 0.05, float((delta > 2e-3).float().mean())
+    else:
+        assert np.allclose(curves[0], curves[1], rtol=1e-6), curves
+        assert rel_err(works[1].numpy(), works[0].numpy()) < 1e-5
 
 
 def test_cuda_graph_replay_follows_the_eager_steps(pkg, dev):
