@@ -31,7 +31,7 @@ SYMBOLS = [
     "cxxattn_lin_host_plan_create", "cxxattn_lin_host_plan_destroy", "cxxattn_linattn_fwd_bwd_host",
     "cxxattn_set_option", "cxxattn_get_option", "cxxattn_selftest_wait_limit", "cxxattn_adamw_step",
     "cxxattn_adamw_step_mixed", "cxxattn_adamw_step_exchange",
-    "cxxattn_colsum_workspace_bytes", "cxxattn_colsum", "cxxattn_peer_alloc", "cxxattn_peer_free", "cxxattn_peer_export", "cxxattn_peer_open", "cxxattn_peer_close",
+    "cxxattn_colsum_workspace_bytes", "cxxattn_colsum", "cxxattn_layernorm_bwd_workspace_bytes", "cxxattn_layernorm_bwd", "cxxattn_peer_alloc", "cxxattn_peer_free", "cxxattn_peer_export", "cxxattn_peer_open", "cxxattn_peer_close",
 ]
 
 # cxxattn_set_option keys (include/cxxattn.h)
@@ -119,6 +119,9 @@ def lib():
         L.cxxattn_colsum_workspace_bytes.argtypes = [sz]
         L.cxxattn_colsum_workspace_bytes.restype = sz
         L.cxxattn_colsum.argtypes = [vp, i32, vp, sz, sz, vp, sz, vp]
+        L.cxxattn_layernorm_bwd_workspace_bytes.argtypes = [sz]
+        L.cxxattn_layernorm_bwd_workspace_bytes.restype = sz
+        L.cxxattn_layernorm_bwd.argtypes = [vp] * 8 + [sz, sz, i32, vp, sz, vp]
         L.cxxattn_peer_alloc.argtypes = [sz, C.POINTER(vp)]
         L.cxxattn_peer_free.argtypes = [vp]
         L.cxxattn_peer_export.argtypes = [vp, C.c_char_p]
@@ -381,6 +384,19 @@ def colsum(X, out, workspace):
     rows, cols = X.shape
     check(lib().cxxattn_colsum(_ptr(X), _dtype_code(X), _ptr(out), rows, cols, _ptr(workspace), workspace.numel(),
                                _stream()), "cxxattn_colsum")
+
+
+def layernorm_bwd_workspace_bytes(cols):
+    return int(lib().cxxattn_layernorm_bwd_workspace_bytes(int(cols)))
+
+
+def layernorm_bwd(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, workspace):
+    """LayerNorm backward (cxxattn_layernorm_bwd): dy, x, dx 2-D, gamma / dgamma / dbeta of the row width, all of one
+    dtype; mean, rstd fp32 per row; `workspace` a uint8 tensor that was zero before its first use."""
+    rows, cols = x.shape
+    check(lib().cxxattn_layernorm_bwd(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(dgamma),
+                                      _ptr(dbeta), rows, cols, _dtype_code(x), _ptr(workspace), workspace.numel(),
+                                      _stream()), "cxxattn_layernorm_bwd")
 
 
 class PeerBuffer:

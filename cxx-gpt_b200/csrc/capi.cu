@@ -333,6 +333,18 @@ int cxxattn_colsum(const void* X, int dtype, void* out, size_t rows, size_t cols
     return colsum(X, dtype, out, rows, cols, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+size_t cxxattn_layernorm_bwd_workspace_bytes(size_t cols) { return cols ? layernorm_bwd_workspace(cols) : 0; }
+
+int cxxattn_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                          void* dgamma, void* dbeta, size_t rows, size_t cols, int dtype, void* workspace,
+                          size_t workspace_bytes, cxxattn_stream_t stream) {
+    if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || rows == 0 || cols == 0 ||
+        (dtype != CXXATTN_F32 && dtype != CXXATTN_BF16))
+        return CXXATTN_ERR_INVALID;
+    return layernorm_bwd(dy, x, gamma, mean, rstd, dx, dgamma, dbeta, rows, cols, dtype, workspace, workspace_bytes,
+                         static_cast<cudaStream_t>(stream));
+}
+
 int cxxattn_peer_alloc(size_t bytes, void** ptr) { return peer_alloc(bytes, ptr); }
 int cxxattn_peer_free(void* ptr) { return ptr ? peer_free(ptr) : CXXATTN_OK; }
 int cxxattn_peer_export(const void* ptr, unsigned char handle[CXXATTN_PEER_HANDLE_BYTES]) { return peer_export(ptr, handle); }

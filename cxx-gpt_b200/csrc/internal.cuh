@@ -138,6 +138,10 @@ int peer_close(void* ptr);
 // ---- column sums (colsum.cu) ----
 size_t colsum_workspace(size_t cols);
 int colsum(const void* X, int dtype, void* out, size_t rows, size_t cols, void* ws, size_t ws_bytes, cudaStream_t st);
+// ---- LayerNorm backward (layernorm.cu) ----
+size_t layernorm_bwd_workspace(size_t cols);
+int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                  void* dgamma, void* dbeta, size_t rows, size_t cols, int dtype, void* ws, size_t ws_bytes, cudaStream_t st);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
 

@@ -57,6 +57,7 @@ class CudaKernels:
             raise RuntimeError("the training step needs a CUDA device: there is no CPU path in the product")
         self.pkg = pkg
         self.colsum_ws = {}  # per device: the zeroed workspace of cxxattn_colsum (it leaves it zeroed)
+        self.ln_ws = {}      # the same for cxxattn_layernorm_bwd
 
     COLSUM_MAX_COLS = 1 << 16
 
@@ -101,6 +102,19 @@ class CudaKernels:
     def adamw(self, param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq, param_copy=None):
         self.pkg.adamw_step(param, grad, m, v, step, lr, beta1, beta2, weight_decay, eps, grad_scale, norm_sq,
                             param_copy=param_copy)
+
+    def layernorm_bwd(self, dy, x, gamma, mean, rstd, dgamma, dbeta):
+        """dx of a LayerNorm over the rows of the 2-D bf16 tensor x; dgamma and dbeta are written in place.
+        None if the shape is not covered."""
+        if x.dtype != torch.bfloat16 or x.shape[1] % 8 or x.shape[1] > self.COLSUM_MAX_COLS:
+            return None
+        ws = self.ln_ws.get(x.device)
+        if ws is None:
+            ws = torch.zeros(self.pkg.layernorm_bwd_workspace_bytes(self.COLSUM_MAX_COLS), dtype=torch.uint8, device=x.device)
+            self.ln_ws[x.device] = ws
+        dx = torch.empty_like(x)
+        self.pkg.layernorm_bwd(dy.contiguous(), x, gamma, mean, rstd, dx, dgamma, dbeta, ws)
+        return dx
 
     def peer_buffer(self, numel, dtype, device):
         """A zeroed flat buffer that the other ranks' GPUs can map."""
@@ -196,6 +210,28 @@ class _Linear(torch.autograd.Function):
         return dx, None, None, None, None
 
 
+class _LayerNorm(torch.autograd.Function):
+    """LayerNorm over the rows of a 2-D bf16 tensor: torch's forward kernel (which returns the row statistics),
+    the library's backward (cxxattn_layernorm_bwd: two launches, dgamma and dbeta written straight into their views
+    of the flat gradient buffer)."""
+
+    @staticmethod
+    def forward(ctx, x, g, b, model, name):
+        y, mean, rstd = torch.native_layer_norm(x, (x.shape[1],), g, b, model.cfg.ln_eps)
+        ctx.save_for_backward(x, g, mean.reshape(-1).float(), rstd.reshape(-1).float())
+        ctx.model, ctx.name = model, name
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, g, mean, rstd = ctx.saved_tensors
+        model, name = ctx.model, ctx.name
+        dx = model.kernels.layernorm_bwd(dy, x, g, mean, rstd, model.p[name + ".g"].grad, model.p[name + ".b"].grad)
+        model.grad_ready(name + ".g")
+        model.grad_ready(name + ".b")
+        return dx, None, None, None, None
+
+
 def parameter_table(cfg):
     """(name, shape, init std or None for ones / 0.0 for zeros) in the order the forward pass uses them,
     which is the reverse of the order in which the backward pass finishes their gradients."""
@@ -271,6 +307,10 @@ class HybridGPT:
         self.direct_grad = {name for name in self.order
                             if name.startswith("h") and name.split(".")[1] in
                             ("attn_q", "attn_k", "attn_v", "lq_proj", "lk_proj", "lv_proj", "attn_proj", "mlp_fc", "mlp_proj")}
+        # bf16 compute on the library's kernels: LayerNorm backward is the library's too, and writes dgamma, dbeta itself
+        self.custom_ln = self.mixed and hasattr(kernels, "layernorm_bwd") and cfg.n_embd % 8 == 0
+        if self.custom_ln:
+            self.direct_grad |= {name for name in self.order if ".ln_" in "." + name}
         self.on_grad_ready = None
 
     def _linear(self, x, name, bias=True):
@@ -285,6 +325,8 @@ class HybridGPT:
     def _ln(self, x, name):
         E = self.cfg.n_embd
         g, b = self.p[name + ".g"], self.p[name + ".b"]
+        if self.custom_ln:
+            return _LayerNorm.apply(x, g, b, self, name)
         if x.dtype == g.dtype:  # one kernel each way; statistics are accumulated in fp32 inside it
             return F.layer_norm(x, (E,), g, b, self.cfg.ln_eps)
         return F.layer_norm(x.float(), (E,), g.float(), b.float(), self.cfg.ln_eps).to(x.dtype)

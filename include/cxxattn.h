@@ -272,6 +272,19 @@ size_t cxxattn_colsum_workspace_bytes(size_t cols);
 int cxxattn_colsum(const void* X, int dtype, void* out, size_t rows, size_t cols, void* workspace, size_t workspace_bytes,
                    cxxattn_stream_t stream);
 
+/* LayerNorm backward over rows of `cols` elements (gpt_cuda::layernorm_backward, gpt_cuda_kernels.cu:250-320):
+ * with xhat = (x - mean[r]) rstd[r] and g = dy gamma,
+ *   dx = rstd (g - (sum_c g + xhat sum_c g xhat) / cols),  dgamma[c] = sum_r dy xhat,  dbeta[c] = sum_r dy.
+ * dy, x, dx (rows x cols), gamma, dgamma, dbeta (cols) are `dtype` (CXXATTN_F32 / CXXATTN_BF16; cols a multiple
+ * of 4 / 8; dy, x, gamma, dx 16-byte aligned), mean and rstd are fp32 as the forward pass saved them; sums are
+ * formed in fp32.  dgamma and dbeta are OVERWRITTEN (the reference adds into them).  `workspace`
+ * (cxxattn_layernorm_bwd_workspace_bytes(cols), 16-byte aligned): all zero before the first call, left all
+ * zero by every call; calls sharing one must not overlap.  The order of the fp32 additions is not fixed. */
+size_t cxxattn_layernorm_bwd_workspace_bytes(size_t cols);
+int cxxattn_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                          void* dgamma, void* dbeta, size_t rows, size_t cols, int dtype, void* workspace,
+                          size_t workspace_bytes, cxxattn_stream_t stream);
+
 /* Device buffers that other processes' GPUs of the same machine can map (CUDA IPC): _alloc / _free own
  * the memory, _export fills the handle another process passes to _open, which returns the address the
  * buffer has in the opening process (peer access is enabled as needed); _close unmaps it.  A handle

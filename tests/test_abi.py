@@ -104,6 +104,14 @@ def test_bad_arguments_are_rejected_without_a_device(pkg):
     assert lib.cxxattn_colsum(one, pkg.BF16, one, 4, 12, one, 1 << 20, None) == -2     # bf16 rows in 16-byte vectors
     assert lib.cxxattn_colsum(one, pkg.BF16, one, 4, 8, one, 8, None) == -3            # workspace too small
     assert lib.cxxattn_colsum(one, pkg.BF16, one, 4, 8, None, 0, None) == -3
+    # LayerNorm backward
+    ln = lib.cxxattn_layernorm_bwd
+    assert lib.cxxattn_layernorm_bwd_workspace_bytes(768) >= 2 * 768 * 4
+    assert ln(None, one, one, one, one, one, one, one, 4, 8, pkg.BF16, one, 1 << 20, None) == -1
+    assert ln(one, one, one, one, one, one, one, one, 4, 0, pkg.BF16, one, 1 << 20, None) == -1
+    assert ln(one, one, one, one, one, one, one, one, 4, 12, pkg.BF16, one, 1 << 20, None) == -2
+    assert ln(one, one, one, one, one, one, one, one, 4, 8, pkg.BF16, one, 8, None) == -3
+    assert ln(one, one, one, one, one, C.c_void_p(20), one, one, 4, 8, pkg.BF16, one, 1 << 20, None) == -6
     p = C.c_void_p()
     assert lib.cxxattn_peer_alloc(0, C.byref(p)) == -1 and lib.cxxattn_peer_alloc(16, None) == -1
     assert lib.cxxattn_peer_export(None, C.create_string_buffer(64)) == -1

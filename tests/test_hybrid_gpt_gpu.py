@@ -222,6 +222,35 @@ def test_column_sums_match_fp64_and_leave_the_workspace_zero(pkg, dev, rows, col
     assert torch.equal(dX.cpu(), X)
 
 
+@pytest.mark.parametrize("rows,cols,dtype", [(2048, 768, torch.bfloat16), (7, 8, torch.bfloat16), (300, 1000, torch.bfloat16),
+                                             (129, 260, torch.float32), (2048, 3072, torch.float32)])
+def test_layernorm_backward_matches_autograd_in_fp64(pkg, dev, rows, cols, dtype):
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 2 + 0.5).to(dtype)
+    gamma = (torch.randn(cols, generator=g) * 0.5 + 1).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    xd = x.double().requires_grad_(True)
+    gd = gamma.double().requires_grad_(True)
+    bd = torch.zeros(cols, dtype=torch.float64, requires_grad=True)
+    y = torch.nn.functional.layer_norm(xd, (cols,), gd, bd, 1e-5)
+    y.backward(dy.double())
+    mean = x.double().mean(1)
+    rstd = 1.0 / torch.sqrt(x.double().var(1, unbiased=False) + 1e-5)
+    ws = torch.zeros(pkg.layernorm_bwd_workspace_bytes(cols), dtype=torch.uint8, device=dev)
+    args = [t.to(dev) for t in (dy, x, gamma, mean.float(), rstd.float())]
+    tol = 2 ** -7 if dtype == torch.bfloat16 else 2e-5  # output rounding of bf16; fp32 sums against fp64
+    for _ in range(2):  # the workspace is left clean for the second call
+        dx = torch.full((rows, cols), 3.0, dtype=dtype, device=dev)
+        dg = torch.full((cols,), 3.0, dtype=dtype, device=dev)
+        db = torch.full((cols,), 3.0, dtype=dtype, device=dev)
+        pkg.layernorm_bwd(*args, dx, dg, db, ws)
+        torch.cuda.synchronize()
+        assert rel_err(dx.double().cpu().numpy(), xd.grad.numpy()) < tol
+        assert rel_err(dg.double().cpu().numpy(), gd.grad.numpy()) < tol
+        assert rel_err(db.double().cpu().numpy(), bd.grad.numpy()) < tol
+        assert int(ws.count_nonzero()) == 0
+
+
 def test_peer_buffer_is_a_zeroed_torch_view_with_an_exportable_handle(pkg, dev):
     buf = pkg.PeerBuffer(1000, torch.bfloat16, dev)
     assert buf.tensor.dtype == torch.bfloat16 and buf.tensor.numel() == 1000 and buf.tensor.data_ptr() == buf.ptr.value
