@@ -169,6 +169,7 @@ __global__ void rope_cast_kernel(const TI* __restrict__ src, TO* __restrict__ ds
     float s0, c0, s1, c1;
     sincosf(sign * (float)pos * expf(-2.0f * (float)i0 / (float)hd * 9.210340371976184f), &s0, &c0);
     sincosf(sign * (float)pos * expf(-2.0f * (float)(i0 + 1) / (float)hd * 9.210340371976184f), &s1, &c1);
+#pragma unroll 4  // the batch items of a position are independent: their loads go out together
     for (size_t b = 0; b < B; b++) {
         const size_t off = (b * S + pos) * D + col;
         float x0, x1, x2, x3;
