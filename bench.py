@@ -296,39 +296,50 @@ def run_ours(args):
     pkg.sync_status()
 
     # ---- device-resident timing: K steps between two events on the launching stream ----
+    # The per-kernel split (forward call, backward call, backward main kernel of the first call of a step) is
+    # taken INSIDE the timed region, on up to 32 of its steps, with events of their own: the GPU's clock under
+    # a long run of these kernels is set by the power cap, and a split measured before or after the region
+    # would be taken at another clock than the value it explains.
+    nsamp = min(args.steps, 32)
+    stride = args.steps // nsamp
+    ef = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(nsamp)]
+    for row in ef:
+        for e in row:
+            e.record()  # creates the underlying CUDA events
+    c0 = work[0]
+
+    def sampled_step(row):
+        t = c0.sets[turn[0] % nset]
+        q_, k_, v_, g_, o_, dq_, dk_, dv_, l_ = t
+        pkg.set_timing_events(row[3], row[4])  # recorded by the library around the main backward kernel
+        row[0].record()
+        pkg.mha_fwd(q_, k_, v_, o_, c0.nb, S, c0.nh, DH, lse=l_, strides=c0.strides)
+        row[1].record()
+        pkg.mha_bwd(q_, k_, v_, o_, g_, dq_, dk_, dv_, c0.nb, S, c0.nh, DH, lse=l_, strides=c0.strides)
+        row[2].record()
+        pkg.set_timing_events(None, None)
+        for c in work[1:]:
+            run_call(c, c.sets[turn[0] % nset])
+        turn[0] += 1
+
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for i in range(args.steps):
+        if i % stride == 0 and i // stride < nsamp:
+            sampled_step(ef[i // stride])
+        else:
+            step()
     e1.record()
     barrier()
     sampler.stop_flag = True
     ms = e0.elapsed_time(e1) / args.steps
     pkg.sync_status()
-
-    # ---- per-kernel split (forward call, backward call, backward main kernel) on the first call ----
-    ef = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
-    for e in ef:
-        e.record()  # creates the underlying CUDA events
-    fwd_ms = bwd_ms = bwd_main_ms = 0.0
-    reps = max(3, min(args.steps, 10))
-    c0 = work[0]
-    pkg.set_timing_events(ef[3], ef[4])  # recorded by the library around the main backward kernel
-    for i in range(reps):
-        q_, k_, v_, g_, o_, dq_, dk_, dv_, l_ = c0.sets[i % nset]
-        ef[0].record()
-        pkg.mha_fwd(q_, k_, v_, o_, c0.nb, S, c0.nh, DH, lse=l_, strides=c0.strides)
-        ef[1].record()
-        pkg.mha_bwd(q_, k_, v_, o_, g_, dq_, dk_, dv_, c0.nb, S, c0.nh, DH, lse=l_, strides=c0.strides)
-        ef[2].record()
-        torch.cuda.synchronize()
-        fwd_ms += ef[0].elapsed_time(ef[1]) / reps
-        bwd_ms += ef[1].elapsed_time(ef[2]) / reps
-        bwd_main_ms += ef[3].elapsed_time(ef[4]) / reps
-    pkg.set_timing_events(None, None)
+    fwd_ms = sum(r[0].elapsed_time(r[1]) for r in ef) / nsamp
+    bwd_ms = sum(r[1].elapsed_time(r[2]) for r in ef) / nsamp
+    bwd_main_ms = sum(r[3].elapsed_time(r[4]) for r in ef) / nsamp
     units_c0 = c0.nb * c0.nh
 
     # ---- end to end: host buffers in, host buffers out, through the C-ABI host entry point ----
@@ -389,7 +400,12 @@ def run_ours(args):
         mult = world if args.weak else 1
         fl = flops_fwd_bwd(B, S) * mult          # whole job
         fl_c0 = 7.0 * units_c0 * S * S * DH      # rank 0's first call, the one the split timings cover
-        peak, peak_sustained, how = measured_peaks()
+        peak_burst, peak_sustained, how = measured_peaks()
+        clocks = sampler.result()
+        # The denominator follows the clock the region ran at: the burst figure of the measured GEMM peak for a region
+        # at full clock, the sustained one (same GEMM, seconds under the power cap) when the power cap was active in it.
+        capped = "sw_power_cap" in clocks["reasons"]
+        peak = peak_sustained if capped else peak_burst
         main_tf = fl_c0 * (2.5 / 3.5) / (bwd_main_ms * 1e-3) / 1e12
         nbytes = 4 * B * S * H * DH * 2 * mult // world  # per rank and direction
         per_unit = load_traffic("mha_tc_bwd_kernel")
@@ -404,11 +420,12 @@ def run_ours(args):
                 "bwd_tflops": fl_c0 * (2.5 / 3.5) / (bwd_ms * 1e-3) / 1e12,
                 "frac_of_peak_fwd_bwd": fl / (ms * 1e-3) / 1e12 / (peak * world),
                 "gpu_launches": args.steps * 4 * len(work) * world,
-                "clocks": sampler.result(),
+                "clocks": clocks,
                 "e2e": {"value": fl / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": nbytes * world},
                 "roofline": {"bound": "tensor", "kernel": "mha_tc_bwd_kernel", "launch_ms": bwd_main_ms,
-                             "achieved": main_tf, "peak": peak, "peak_sustained": peak_sustained,
+                             "achieved": main_tf, "peak": peak, "peak_kind": "sustained" if capped else "burst",
+                             "peak_burst": peak_burst, "peak_sustained": peak_sustained,
                              "peak_source": how, "unit": UNIT, "frac": main_tf / peak,
                              # DRAM bytes of one launch: the profiler's figure per (batch, head) unit of a
                              # captured smaller launch of the same sequence length, times this launch's units
