@@ -428,10 +428,8 @@ class DataParallelStep:
         model, world, rank = self.model, self.world, self.rank
         if model.peer is None:
             raise ValueError('exchange="peer" needs a model built with peer=True')
-        per = (model.numel // 8 + world - 1) // world * 8  # numel is a multiple of 8 by construction
-        self.lo = min(model.numel, rank * per)
-        self.hi = min(model.numel, self.lo + per)
-        self.shard_len = per
+        from .sharding import parameter_shard
+        self.lo, self.hi, self.shard_len = parameter_shard(model.numel, world, rank)  # numel is a multiple of 8
         n = self.hi - self.lo
         # the fp32 master of the shard: a view of the parameter buffer in fp32 compute (which the exchange
         # kernel then also fills for the other shards), a buffer of its own in mixed precision

@@ -46,6 +46,17 @@ def calls(B, H, world, rank):
     return out
 
 
+def parameter_shard(numel, world, rank, vector=8):
+    """The range [lo, hi) of a flat parameter buffer of `numel` elements (a multiple of `vector`) that rank
+    `rank` owns in the peer-memory exchange step: equal shards of whole 16-byte vectors, the last ones shorter
+    or empty when the ranks do not divide the vectors.  Returns (lo, hi, shard_length)."""
+    if world <= 0 or not 0 <= rank < world or numel % vector:
+        raise ValueError("bad world/rank/numel")
+    per = (numel // vector + world - 1) // world * vector
+    lo = min(numel, rank * per)
+    return lo, min(numel, lo + per), per
+
+
 def max_over_ranks(values, group=None):
     """Element-wise maximum of a list of floats over all ranks (the slowest rank counts)."""
     import torch

@@ -78,6 +78,20 @@ def _worker(rank, world, port, tmp):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("numel,world", [(8, 1), (8, 3), (111_401_472, 8), (111_401_472, 7), (4096, 16), (24, 5)])
+def test_parameter_shards_tile_the_buffer_in_whole_vectors(numel, world):
+    sharding = load_sharding()
+    edge = 0
+    for rank in range(world):
+        lo, hi, per = sharding.parameter_shard(numel, world, rank)
+        assert lo == edge and lo <= hi <= numel and lo % 8 == 0 and (hi - lo) % 8 == 0 and hi - lo <= per
+        assert per * world >= numel and per % 8 == 0
+        edge = hi
+    assert edge == numel
+    with pytest.raises(ValueError):
+        sharding.parameter_shard(12, 2, 0)
+
+
 def test_two_gloo_ranks_reproduce_single_rank_result(tmp_path):
     world = 2
     port = 29500 + os.getpid() % 2000
