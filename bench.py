@@ -716,10 +716,10 @@ def run_dp_step(args):
                 "config": dp_config(world),
                 "parameters": model.numel, "loss_first": first, "loss_last": last,
                 "cuda_graph": stepper.graph is not None,
-                # this library's kernels per step and rank: per block 8 RoPE/conversion passes, 4 of the softmax stage,
-                # 10 of the linear stage, 6 bias-gradient column sums, 4 of the two LayerNorm backward passes; the
-                # final LayerNorm's 2; the optimiser (or exchange) kernel
-                "gpu_launches": args.steps * world * (cfg.n_layer * (8 + 4 + 10 + 6 + 4) + 2 + 1),
+                # this library's kernels per step and rank: per block 4 RoPE/conversion passes (query and key
+                # together), 4 of the softmax stage, 10 of the linear stage, 6 bias-gradient column sums, 4 of the
+                # two LayerNorm backward passes; the final LayerNorm's 2; the optimiser (or exchange) kernel
+                "gpu_launches": args.steps * world * (cfg.n_layer * (4 + 4 + 10 + 6 + 4) + 2 + 1),
                 "clocks": sampler.result(),
                 "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": world * 2 * B * S * 8, "d2h_bytes_per_step": world * 4},

@@ -23,7 +23,7 @@ SYMBOLS = [
     "cxxattn_linattn_workspace_bytes", "cxxattn_linattn_fwd", "cxxattn_linattn_bwd_step1",
     "cxxattn_linattn_bwd_dq", "cxxattn_linattn_bwd_dkdv", "cxxattn_linattn_bwd",
     "cxxattn_phi_elu_fwd", "cxxattn_phi_elu_bwd", "cxxattn_rope", "cxxattn_gelu_exact",
-    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_cast", "cxxattn_rope_cast",
+    "cxxattn_sync_status", "cxxattn_last_timeout_site", "cxxattn_cast", "cxxattn_rope_cast", "cxxattn_rope_cast_pair",
     "cxxattn_linattn_decode_step", "cxxattn_mha_decode_workspace_bytes", "cxxattn_mha_decode_step",
     "cxxattn_selftest_umma",
     "cxxattn_host_plan_create", "cxxattn_host_plan_destroy", "cxxattn_mha_fwd_bwd_host",
@@ -89,6 +89,7 @@ def lib():
         L.cxxattn_gelu_exact.argtypes = [vp, vp, sz, i32, vp]
         L.cxxattn_cast.argtypes = [vp, i32, vp, i32, sz, vp]
         L.cxxattn_rope_cast.argtypes = [vp, i32, vp, i32, sz, sz, sz, sz, C.c_float, vp]
+        L.cxxattn_rope_cast_pair.argtypes = [vp, vp, i32, vp, vp, i32, sz, sz, sz, sz, C.c_float, vp]
         L.cxxattn_linattn_decode_step.argtypes = [C.POINTER(LinDesc)] + [vp] * 7 + [vp]
         L.cxxattn_mha_decode_workspace_bytes.restype = sz
         L.cxxattn_mha_decode_workspace_bytes.argtypes = [C.POINTER(MhaDesc)]
@@ -481,6 +482,12 @@ def rope_cast(src, dst, B, S, D, head_dim, sign=1.0):
     that the tensor-core kernels need)."""
     check(lib().cxxattn_rope_cast(_ptr(src), _dtype_code(src), _ptr(dst), _dtype_code(dst), B, S, D, head_dim,
                                   float(sign), _stream()), "cxxattn_rope_cast")
+
+
+def rope_cast_pair(src0, src1, dst0, dst1, B, S, D, head_dim, sign=1.0):
+    """rope_cast on two tensors of one shape and dtype pair in one launch (the reference's rope_fwd(Q, K, ...))."""
+    check(lib().cxxattn_rope_cast_pair(_ptr(src0), _ptr(src1), _dtype_code(src0), _ptr(dst0), _ptr(dst1), _dtype_code(dst0),
+                                       B, S, D, head_dim, float(sign), _stream()), "cxxattn_rope_cast_pair")
 
 
 def linattn_decode_step(q, k, v, state_S, state_z, o, den, B, D, E, feature_map=MAP_ELU1, eps_in_den=0):

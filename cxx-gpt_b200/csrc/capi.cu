@@ -293,6 +293,14 @@ int cxxattn_rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, 
     return rope_cast(src, src_dtype, dst, dst_dtype, B, S, D, head_dim, sign, static_cast<cudaStream_t>(stream));
 }
 
+int cxxattn_rope_cast_pair(const void* src0, const void* src1, int src_dtype, void* dst0, void* dst1, int dst_dtype,
+                           size_t B, size_t S, size_t D, size_t head_dim, float sign, cxxattn_stream_t stream) {
+    if (!src0 || !dst0 || !src1 || !dst1 || B == 0 || S == 0 || D == 0 || head_dim == 0 || head_dim % 4 || D % head_dim)
+        return CXXATTN_ERR_INVALID;
+    return rope_cast_pair(src0, src1, src_dtype, dst0, dst1, dst_dtype, B, S, D, head_dim, sign,
+                          static_cast<cudaStream_t>(stream));
+}
+
 int cxxattn_adamw_step(float* param, const float* grad, float* m, float* v, size_t n, float grad_scale, float lr,
                        float beta1, float beta2, float weight_decay, float eps, int step, float* grad_norm_sq,
                        cxxattn_stream_t stream) {

@@ -159,8 +159,11 @@ int cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t n, cud
 // position, forms its two sine/cosine pairs once and walks over the batch.  Same angle formula
 // as rope_kernel (ts.cu:1820-1857).
 template <typename TI, typename TO>
-__global__ void rope_cast_kernel(const TI* __restrict__ src, TO* __restrict__ dst, size_t B, size_t S, size_t D,
-                                 size_t hd, float sign) {
+__global__ void rope_cast_kernel(const TI* __restrict__ src0, TO* __restrict__ dst0, const TI* __restrict__ src1,
+                                 TO* __restrict__ dst1, size_t B, size_t S, size_t D, size_t hd, float sign) {
+    // blockIdx.y picks the tensor: the reference rotates Q and K in one call, and so can this
+    const TI* __restrict__ src = blockIdx.y ? src1 : src0;
+    TO* __restrict__ dst = blockIdx.y ? dst1 : dst0;
     const size_t qpr = D / 4;  // quads per row
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= S * qpr) return;
@@ -194,26 +197,36 @@ __global__ void rope_cast_kernel(const TI* __restrict__ src, TO* __restrict__ ds
     }
 }
 
-int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
-              float sign, cudaStream_t st) {
-    if (reinterpret_cast<uintptr_t>(src) % 16 || reinterpret_cast<uintptr_t>(dst) % 16) return CXXATTN_ERR_ALIGNMENT;
+int rope_cast_pair(const void* src0, const void* src1, int src_dtype, void* dst0, void* dst1, int dst_dtype, size_t B,
+                   size_t S, size_t D, size_t hd, float sign, cudaStream_t st) {
+    for (const void* q : {src0, src1, (const void*)dst0, (const void*)dst1})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
     const size_t threads = S * (D / 4);
-    const unsigned grid = (unsigned)((threads + 255) / 256);
+    const dim3 grid((unsigned)((threads + 255) / 256), src1 != nullptr ? 2u : 1u);
     const bool si = src_dtype == CXXATTN_F32, so = dst_dtype == CXXATTN_F32;
     if ((!si && src_dtype != CXXATTN_BF16) || (!so && dst_dtype != CXXATTN_BF16)) return CXXATTN_ERR_UNSUPPORTED;
     if (si && so)
-        rope_cast_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), static_cast<float*>(dst),
+        rope_cast_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(src0), static_cast<float*>(dst0),
+                                                            static_cast<const float*>(src1), static_cast<float*>(dst1),
                                                             B, S, D, hd, sign);
     else if (si)
         rope_cast_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>(
-            static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), B, S, D, hd, sign);
+            static_cast<const float*>(src0), static_cast<__nv_bfloat16*>(dst0), static_cast<const float*>(src1),
+            static_cast<__nv_bfloat16*>(dst1), B, S, D, hd, sign);
     else if (so)
         rope_cast_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(src), static_cast<float*>(dst), B, S, D, hd, sign);
+            static_cast<const __nv_bfloat16*>(src0), static_cast<float*>(dst0), static_cast<const __nv_bfloat16*>(src1),
+            static_cast<float*>(dst1), B, S, D, hd, sign);
     else
         rope_cast_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), B, S, D, hd, sign);
+            static_cast<const __nv_bfloat16*>(src0), static_cast<__nv_bfloat16*>(dst0),
+            static_cast<const __nv_bfloat16*>(src1), static_cast<__nv_bfloat16*>(dst1), B, S, D, hd, sign);
     return check_launch();
+}
+
+int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
+              float sign, cudaStream_t st) {
+    return rope_cast_pair(src, nullptr, src_dtype, dst, nullptr, dst_dtype, B, S, D, hd, sign, st);
 }
 
 int gelu_exact(const float* A, float* C, size_t n, int deriv, cudaStream_t st) {

@@ -144,5 +144,7 @@ int layernorm_bwd(const void* dy, const void* x, const void* gamma, const float*
                   void* dgamma, void* dbeta, size_t rows, size_t cols, int dtype, void* ws, size_t ws_bytes, cudaStream_t st);
 int rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D, size_t hd,
               float sign, cudaStream_t st);
+int rope_cast_pair(const void* src0, const void* src1, int src_dtype, void* dst0, void* dst1, int dst_dtype, size_t B,
+                   size_t S, size_t D, size_t hd, float sign, cudaStream_t st);
 
 }  // namespace cxxattn

@@ -77,6 +77,12 @@ class CudaKernels:
         self.pkg.rope_cast(x.contiguous(), out, B, S, D, head_dim, sign)
         return out
 
+    def rope_cast_pair(self, x0, x1, B, S, D, head_dim, sign, out_dtype):
+        y0 = torch.empty(x0.shape, dtype=out_dtype, device=x0.device)
+        y1 = torch.empty(x1.shape, dtype=out_dtype, device=x1.device)
+        self.pkg.rope_cast_pair(x0.contiguous(), x1.contiguous(), y0, y1, B, S, D, head_dim, sign)
+        return y0, y1
+
     def mha_fwd(self, q, k, v, B, S, H, Dh):
         o = torch.empty_like(q)
         lse = torch.empty(B * H * S, dtype=torch.float32, device=q.device)
@@ -142,6 +148,28 @@ class _RopeCast(torch.autograd.Function):
     def backward(ctx, g):
         B, S, D, hd = ctx.dims
         return ctx.kernels.rope_cast(g, B, S, D, hd, -1.0, ctx.in_dtype), None, None, None, None, None, None
+
+
+class _RopeCastPair(torch.autograd.Function):
+    """_RopeCast on the query and the key tensor in one launch each way (rope_fwd / rope_bwd take both)."""
+
+    @staticmethod
+    def forward(ctx, x0, x1, kernels, B, S, D, head_dim, out_dtype):
+        ctx.kernels, ctx.dims, ctx.in_dtype = kernels, (B, S, D, head_dim), x0.dtype
+        return kernels.rope_cast_pair(x0, x1, B, S, D, head_dim, 1.0, out_dtype)
+
+    @staticmethod
+    def backward(ctx, g0, g1):
+        B, S, D, hd = ctx.dims
+        d0, d1 = ctx.kernels.rope_cast_pair(g0, g1, B, S, D, hd, -1.0, ctx.in_dtype)
+        return d0, d1, None, None, None, None, None, None
+
+
+def _rope_pair(x0, x1, kernels, B, S, D, head_dim, out_dtype):
+    if hasattr(kernels, "rope_cast_pair") and x0.dtype == x1.dtype:
+        return _RopeCastPair.apply(x0, x1, kernels, B, S, D, head_dim, out_dtype)
+    return (_RopeCast.apply(x0, kernels, B, S, D, head_dim, out_dtype),
+            _RopeCast.apply(x1, kernels, B, S, D, head_dim, out_dtype))
 
 
 class _SoftmaxStage(torch.autograd.Function):
@@ -342,15 +370,13 @@ class HybridGPT:
             p = f"h{i}."
             a = self._ln(h, p + "ln_1")
             q, k, v = (self._linear(a, p + n) for n in ("attn_q", "attn_k", "attn_v"))
-            q = _RopeCast.apply(q, K, B, S, E, Dh, dt)
-            k = _RopeCast.apply(k, K, B, S, E, Dh, dt)
+            q, k = _rope_pair(q, k, K, B, S, E, Dh, dt)
             ra = _SoftmaxStage.apply(q, k, v, K, B, S, H, Dh)
             lq, lk, lv = (self._linear(ra, p + n, bias=False) for n in ("lq_proj", "lk_proj", "lv_proj"))
             # stage 2, one head of width n_embd: the tensor-core kernels in bf16 when the width is a multiple
             # of 64, the exact fp32 kernels otherwise
             dt2 = dt if (dt == torch.bfloat16 and E % 64 == 0) else torch.float32
-            lq = _RopeCast.apply(lq, K, B, S, E, E, dt2)
-            lk = _RopeCast.apply(lk, K, B, S, E, E, dt2)
+            lq, lk = _rope_pair(lq, lk, K, B, S, E, E, dt2)
             ac = _LinearStage.apply(lq, lk, lv.to(dt2), K, B, S, E, E).to(dt)
             h = h + self._linear(ac, p + "attn_proj")
             m = self._linear(F.gelu(self._linear(self._ln(h, p + "ln_2"), p + "mlp_fc")), p + "mlp_proj")

@@ -213,6 +213,10 @@ int cxxattn_rope(float* Q, float* K, size_t B, size_t S, size_t D, size_t head_d
  * and divide D; 16-byte aligned pointers; src and dst must not overlap. */
 int cxxattn_rope_cast(const void* src, int src_dtype, void* dst, int dst_dtype, size_t B, size_t S, size_t D,
                       size_t head_dim, float sign, cxxattn_stream_t stream);
+/* The same for two tensors of one shape in one launch, as the reference rotates Q and K together
+ * (two_stage_cuda::rope_fwd(Q, K, ...), ts.cuh:72-79): dst0 = rope(src0), dst1 = rope(src1). */
+int cxxattn_rope_cast_pair(const void* src0, const void* src1, int src_dtype, void* dst0, void* dst1, int dst_dtype,
+                           size_t B, size_t S, size_t D, size_t head_dim, float sign, cxxattn_stream_t stream);
 /* erf-GELU (deriv=0) and its derivative (deriv=1).  two_stage_cuda::gelu_exact /
  * gelu_exact_deriv (ts.cuh:84-85, ts.cu:1888-1924). */
 int cxxattn_gelu_exact(const float* A, float* C, size_t n, int deriv, cxxattn_stream_t stream);

@@ -77,6 +77,24 @@ def test_rope_cast_all_type_pairs(pkg, dev, orc, B, S, D, hd):
     assert torch.equal(bb, back.bfloat16())
 
 
+@pytest.mark.parametrize("src_dtype,dst_dtype", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16),
+                                                 (torch.bfloat16, torch.float32)])
+def test_rope_cast_pair_is_two_single_calls(pkg, dev, src_dtype, dst_dtype):
+    B, S, D, hd = 3, 130, 768, 64
+    X0, X1 = seeded_normal(71, [(B * S, D), (B * S, D)])
+    a, b = (torch.from_numpy(x).to(dev).to(src_dtype) for x in (X0, X1))
+    for sign in (1.0, -1.0):
+        want = [torch.empty(B * S, D, dtype=dst_dtype, device=dev) for _ in range(2)]
+        got = [torch.full((B * S, D), 9.0, dtype=dst_dtype, device=dev) for _ in range(2)]
+        pkg.rope_cast(a, want[0], B, S, D, hd, sign)
+        pkg.rope_cast(b, want[1], B, S, D, hd, sign)
+        pkg.rope_cast_pair(a, b, got[0], got[1], B, S, D, hd, sign)
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    lib = pkg.lib()
+    assert lib.cxxattn_rope_cast_pair(a.data_ptr(), None, 0, want[0].data_ptr(), want[1].data_ptr(), 1, B, S, D, hd, 1.0,
+                                      None) == -1
+
+
 def test_rope_cast_rejects_unaligned_and_unknown_types(pkg, dev):
     src = torch.zeros(64, 64, device=dev)
     dst = torch.zeros(64, 64, device=dev)
