@@ -265,7 +265,11 @@ __device__ __forceinline__ float phi(float a) { return a > 0.f ? a + 1.f : expf(
 __device__ __forceinline__ float dphi(float a) { return a > 0.f ? 1.f : expf(a); }
 
 // y = phi(x), bf16 -> bf16, n8 groups of eight elements
-__global__ void wide_phi_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, size_t n8) {
+// (blockIdx.y = 1: the second tensor of a pair, so that Q and K take one launch)
+__global__ void wide_phi_kernel(const uint4* __restrict__ x0, uint4* __restrict__ y0, const uint4* __restrict__ x1,
+                                uint4* __restrict__ y1, size_t n8) {
+    const uint4* __restrict__ x = blockIdx.y ? x1 : x0;
+    uint4* __restrict__ y = blockIdx.y ? y1 : y0;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
         const uint4 v = x[i];
         y[i] = make_uint4(pack_bf16(phi(bf_lo(v.x)), phi(bf_hi(v.x))), pack_bf16(phi(bf_lo(v.y)), phi(bf_hi(v.y))),
@@ -273,8 +277,12 @@ __global__ void wide_phi_kernel(const uint4* __restrict__ x, uint4* __restrict__
     }
 }
 // dx = dy o phi'(x), bf16
-__global__ void wide_dphi_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, uint4* __restrict__ dx,
+__global__ void wide_dphi_kernel(const uint4* __restrict__ dy0, const uint4* __restrict__ x0, uint4* __restrict__ dx0,
+                                 const uint4* __restrict__ dy1, const uint4* __restrict__ x1, uint4* __restrict__ dx1,
                                  size_t n8) {
+    const uint4* __restrict__ dy = blockIdx.y ? dy1 : dy0;
+    const uint4* __restrict__ x = blockIdx.y ? x1 : x0;
+    uint4* __restrict__ dx = blockIdx.y ? dx1 : dx0;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
         const uint4 v = x[i], d = dy[i];
         dx[i] = make_uint4(pack_bf16(bf_lo(d.x) * dphi(bf_lo(v.x)), bf_hi(d.x) * dphi(bf_hi(v.x))),
@@ -397,6 +405,25 @@ bool linattn_wide_supported(const cxxattn_lin_desc& d) {
 
 size_t linattn_wide_workspace(const cxxattn_lin_desc& d) { return linattn_wide_supported(d) ? carve(d, nullptr).bytes : 0; }
 
+namespace {
+// phi of one tensor, or of two of the same size in one launch (x1 == nullptr: one)
+int phi_pass(const void* x0, void* y0, const void* x1, void* y1, size_t n8, cudaStream_t st) {
+    const dim3 grid(flat_grid8(n8), x1 != nullptr ? 2u : 1u);
+    wide_phi_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(x0), static_cast<uint4*>(y0),
+                                         static_cast<const uint4*>(x1), static_cast<uint4*>(y1), n8);
+    return check_launch();
+}
+// dx = dy o phi'(x), likewise
+int dphi_pass(const void* dy0, const void* x0, void* dx0, const void* dy1, const void* x1, void* dx1, size_t n8,
+              cudaStream_t st) {
+    const dim3 grid(flat_grid8(n8), dy1 != nullptr ? 2u : 1u);
+    wide_dphi_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(dy0), static_cast<const uint4*>(x0), static_cast<uint4*>(dx0),
+                                          static_cast<const uint4*>(dy1), static_cast<const uint4*>(x1), static_cast<uint4*>(dx1),
+                                          n8);
+    return check_launch();
+}
+}  // namespace
+
 int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, void* O, float* den,
                      float* z_cache, void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!linattn_wide_supported(d)) return CXXATTN_ERR_UNSUPPORTED;
@@ -409,9 +436,7 @@ int linattn_wide_fwd(const cxxattn_lin_desc& d, const void* Q, const void* K, co
     const bool map = d.feature_map == CXXATTN_MAP_ELU1;
     if (map) {
         const size_t n8 = (size_t)d.B * d.S * d.D / 8;
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(Q), reinterpret_cast<uint4*>(w.pq), n8);
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
-        if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+        if (phi_pass(Q, w.pq, K, w.pk, n8, st) != CXXATTN_OK) return CXXATTN_ERR_CUDA;
         q = w.pq;
         k = w.pk;
     }
@@ -439,15 +464,12 @@ int linattn_wide_bwd_dq(const cxxattn_lin_desc& d, const void* K, const void* V,
     const size_t n8 = (size_t)d.B * d.S * d.D / 8;
     const void* k = K;
     if (map) {  // the mapped copies are rebuilt: the workspace need not survive from an earlier call
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
-        if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+        if (phi_pass(K, w.pk, nullptr, nullptr, n8, st) != CXXATTN_OK) return CXXATTN_ERR_CUDA;
         k = w.pk;
     }
     int rc = launch<DQ>(d, dnum, V, k, (int)d.E, (int)d.D, map ? (void*)w.dpq : dQ, nullptr, dden, ldw(d, map), st);
     if (rc != CXXATTN_OK || !map) return rc;
-    wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpq), static_cast<const uint4*>(Q),
-                                                    static_cast<uint4*>(dQ), n8);
-    return check_launch();
+    return dphi_pass(w.dpq, Q, dQ, nullptr, nullptr, nullptr, n8, st);
 }
 
 int linattn_wide_bwd_dkdv(const cxxattn_lin_desc& d, const void* Q, const void* K, const void* V, const void* dnum,
@@ -462,9 +484,7 @@ int linattn_wide_bwd_dkdv(const cxxattn_lin_desc& d, const void* Q, const void* 
     const size_t n8 = (size_t)d.B * d.S * d.D / 8;
     const void *q = Q, *k = K;
     if (map) {
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(Q), reinterpret_cast<uint4*>(w.pq), n8);
-        wide_phi_kernel<<<flat_grid8(n8), 256, 0, st>>>(static_cast<const uint4*>(K), reinterpret_cast<uint4*>(w.pk), n8);
-        if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+        if (phi_pass(Q, w.pq, K, w.pk, n8, st) != CXXATTN_OK) return CXXATTN_ERR_CUDA;
         q = w.pq;
         k = w.pk;
     }
@@ -472,9 +492,7 @@ int linattn_wide_bwd_dkdv(const cxxattn_lin_desc& d, const void* Q, const void* 
     if (rc != CXXATTN_OK) return rc;
     rc = launch<DK>(d, V, dnum, q, (int)d.E, (int)d.D, map ? (void*)w.dpk : dK, nullptr, dden, ldw(d, map), st);
     if (rc != CXXATTN_OK || !map) return rc;
-    wide_dphi_kernel<<<flat_grid8(n8), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.dpk), static_cast<const uint4*>(K),
-                                                    static_cast<uint4*>(dK), n8);
-    return check_launch();
+    return dphi_pass(w.dpk, K, dK, nullptr, nullptr, nullptr, n8, st);
 }
 
 // The whole backward: step 1, then the two halves.
@@ -490,9 +508,24 @@ int linattn_wide_bwd(const cxxattn_lin_desc& d, const void* Q, const void* K, co
     wide_step1_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO), den,
                                                               reinterpret_cast<uint4*>(w.dnum), w.dden, N, (int)(d.E / 8));
     if (check_launch() != CXXATTN_OK) return CXXATTN_ERR_CUDA;
-    int rc = linattn_wide_bwd_dq(d, K, V, w.dnum, w.dden, Q, dQ, ws, ws_bytes, st);
+    // the two halves in one go: phi(Q) and phi(K) are built once and together, and so are the two phi' passes
+    for (const void* q : {Q, K, V, (const void*)dQ, (const void*)dK, (const void*)dV})
+        if (reinterpret_cast<uintptr_t>(q) % 16) return CXXATTN_ERR_ALIGNMENT;
+    const bool map = d.feature_map == CXXATTN_MAP_ELU1;
+    const size_t n8 = (size_t)d.B * d.S * d.D / 8;
+    const void *q = Q, *k = K;
+    if (map) {
+        if (phi_pass(Q, w.pq, K, w.pk, n8, st) != CXXATTN_OK) return CXXATTN_ERR_CUDA;
+        q = w.pq;
+        k = w.pk;
+    }
+    int rc = launch<DQ>(d, w.dnum, V, k, (int)d.E, (int)d.D, map ? (void*)w.dpq : dQ, nullptr, w.dden, ldw(d, map), st);
     if (rc != CXXATTN_OK) return rc;
-    return linattn_wide_bwd_dkdv(d, Q, K, V, w.dnum, w.dden, dK, dV, ws, ws_bytes, st);
+    rc = launch<DV>(d, k, q, w.dnum, (int)d.D, (int)d.E, dV, nullptr, nullptr, ldw(d, map), st);
+    if (rc != CXXATTN_OK) return rc;
+    rc = launch<DK>(d, V, w.dnum, q, (int)d.E, (int)d.D, map ? (void*)w.dpk : dK, nullptr, w.dden, ldw(d, map), st);
+    if (rc != CXXATTN_OK || !map) return rc;
+    return dphi_pass(w.dpq, Q, dQ, w.dpk, K, dK, n8, st);
 }
 
 }  // namespace cxxattn
